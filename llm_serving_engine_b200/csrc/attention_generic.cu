@@ -1,0 +1,189 @@
+// Paged attention, general form: any head size that is a multiple of 16 (up to
+// 256), any number of heads and groups, any page size, float32 or bfloat16
+// storage, optional window.  One block computes one query row (one token of the
+// step) for up to GC query heads that share one key/value head.
+//
+// For row t of the step: the request's pages are block_tables[segment_of_token[t]],
+// its position is positions[t], and it attends to keys j with
+//     max(0, pos + 1 - window) <= j <= pos        (window <= 0: all keys j <= pos).
+// Keys are walked in tiles of KT in logical order with the online-softmax
+// recurrence of the reference (src/llmserve/model.py:143-176;
+// src/llmserve/triton_kernels/paged_attention.py:62-138):
+//     s_j = (q . k_j) * scale;  m' = max(m, max_j s_j);  c = exp(m - m')
+//     p_j = exp(s_j - m');  acc = acc * c + sum_j p_j v_j;  l = l * c + sum_j p_j
+//     out = acc / l
+// The walk depends on the row's own position only, so a row's result is the same
+// bit for bit whatever else is in the batch and however the prompt was cut.
+//
+// Cache layout: [page][kv head][offset in page][D].
+#include "common.cuh"
+
+namespace {
+constexpr int KT = 32;        // keys per tile (one warp lane per key)
+constexpr int GC = 8;         // query heads per block (chunk of a group)
+constexpr int THREADS = 128;  // 4 warps
+constexpr int MAX_D = 256;
+constexpr int DPT = MAX_D / THREADS;  // output values per thread and head
+
+template <typename T>
+__global__ void __launch_bounds__(THREADS)
+paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
+                               const T* __restrict__ v_cache, T* __restrict__ out,
+                               const int* __restrict__ block_tables, int bt_stride,
+                               const int* __restrict__ segment_of_token,
+                               const int* __restrict__ positions, int n_q, int n_kv, int head_dim,
+                               int page_size, float scale, int window) {
+  extern __shared__ float smem[];
+  const int t = blockIdx.x;
+  const int kv_head = blockIdx.y;
+  const int group = n_q / n_kv;
+  const int g0 = blockIdx.z * GC;
+  const int gcount = min(GC, group - g0);
+  const int seg = segment_of_token[t];
+  if (seg < 0) return;
+  const int pos = positions[t];
+  const int ctx = pos + 1;
+  const int kv_begin = window > 0 ? max(0, ctx - window) : 0;
+  const int* bt = block_tables + (size_t)seg * bt_stride;
+
+  const int D = head_dim;
+  float* q_s = smem;                       // [GC][D]
+  float* k_s = q_s + GC * D;               // [KT][D + 1]
+  float* v_s = k_s + KT * (D + 1);         // [KT][D]
+  float* p_s = v_s + KT * D;               // [GC][KT]
+  float* corr_s = p_s + GC * KT;           // [GC]
+  float* l_s = corr_s + GC;                // [GC]
+  long long* base_s = (long long*)(l_s + GC);  // [KT] element offset of key j in the cache, -1 = masked
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int first_head = kv_head * group + g0;
+  for (int e = tid; e < gcount * D; e += THREADS) {
+    const int g = e / D, d = e % D;
+    q_s[g * D + d] = to_f32<T>(q[((size_t)t * n_q + first_head + g) * D + d]);
+  }
+
+  float acc[GC][DPT];
+#pragma unroll
+  for (int g = 0; g < GC; ++g)
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) acc[g][i] = 0.f;
+  // running max and sum of the heads this warp owns (g = warp, warp + 4), same value in every lane
+  float m_run[GC / 4], l_run[GC / 4];
+#pragma unroll
+  for (int i = 0; i < GC / 4; ++i) { m_run[i] = -INFINITY; l_run[i] = 0.f; }
+
+  const int tile_begin = (kv_begin / KT) * KT;
+  for (int base = tile_begin; base < ctx; base += KT) {
+    __syncthreads();  // previous tile fully consumed (also orders the q_s fill)
+    if (tid < KT) {
+      const int j = base + tid;
+      long long off = -1;
+      if (j < ctx && j >= kv_begin) {
+        const int page = bt[j / page_size];
+        off = (((long long)page * n_kv + kv_head) * page_size + (j % page_size)) * D;
+      }
+      base_s[tid] = off;
+    }
+    __syncthreads();
+    for (int e = tid; e < KT * D; e += THREADS) {
+      const int j = e / D, d = e % D;
+      const long long off = base_s[j];
+      float kv = 0.f, vv = 0.f;
+      if (off >= 0) { kv = to_f32<T>(k_cache[off + d]); vv = to_f32<T>(v_cache[off + d]); }
+      k_s[j * (D + 1) + d] = kv;
+      v_s[j * D + d] = vv;
+    }
+    __syncthreads();
+    // scores and softmax statistics: warp w owns heads g = w, w + 4; lane = key
+#pragma unroll
+    for (int i = 0; i < GC / 4; ++i) {
+      const int g = warp + 4 * i;
+      if (g < gcount) {
+        const bool valid = base_s[lane] >= 0;
+        float s = 0.f;
+        const float* qr = q_s + g * D;
+        const float* kr = k_s + lane * (D + 1);
+        for (int d = 0; d < D; ++d) s = fmaf(qr[d], kr[d], s);
+        s = valid ? s * scale : -INFINITY;
+        const float m_new = fmaxf(m_run[i], warp_max(s));
+        const float c = expf(m_run[i] - m_new);  // exp(-inf) = 0 on the first tile
+        const float p = valid ? expf(s - m_new) : 0.f;
+        p_s[g * KT + lane] = p;
+        float tile_sum = 0.f;  // keys in order, the same in every lane
+        for (int j = 0; j < KT; ++j) tile_sum += __shfl_sync(0xffffffffu, p, j);
+        l_run[i] = l_run[i] * c + tile_sum;
+        m_run[i] = m_new;
+        if (lane == 0) { corr_s[g] = c; l_s[g] = l_run[i]; }
+      }
+    }
+    __syncthreads();
+    // acc = acc * c + P V: thread owns output columns d = tid, tid + 128
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) {
+      const int d = tid + i * THREADS;
+      if (d < D) {
+#pragma unroll
+        for (int g = 0; g < GC; ++g) {
+          if (g < gcount) {
+            float a = acc[g][i] * corr_s[g];
+            const float* pr = p_s + g * KT;
+            for (int j = 0; j < KT; ++j) a = fmaf(pr[j], v_s[j * D + d], a);
+            acc[g][i] = a;
+          }
+        }
+      }
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < DPT; ++i) {
+    const int d = tid + i * THREADS;
+    if (d < D) {
+#pragma unroll
+      for (int g = 0; g < GC; ++g) {
+        if (g < gcount)
+          out[((size_t)t * n_q + first_head + g) * D + d] = from_f32<T>(acc[g][i] / l_s[g]);
+      }
+    }
+  }
+}
+
+size_t generic_smem_bytes(int D) {
+  return sizeof(float) * ((size_t)GC * D + (size_t)KT * (D + 1) + (size_t)KT * D + GC * KT + 2 * GC) +
+         sizeof(long long) * KT + 16;
+}
+}  // namespace
+
+extern "C" int lse_paged_attention_generic(const void* q, const void* k_cache, const void* v_cache,
+                                           void* out, int dtype, const int* block_tables,
+                                           int bt_stride, const int* segment_of_token,
+                                           const int* positions, int tokens, int n_q, int n_kv,
+                                           int head_dim, int page_size, float scale, int window,
+                                           cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (head_dim <= 0 || head_dim > MAX_D || head_dim % 16 || n_kv <= 0 || n_q % n_kv || page_size <= 0)
+    return LSE_ERR_BAD_ARGUMENT;
+  const int group = n_q / n_kv;
+  dim3 grid(tokens, n_kv, (group + GC - 1) / GC);
+  const size_t smem = generic_smem_bytes(head_dim);
+  cudaError_t err;
+  if (dtype == LSE_DTYPE_F32) {
+    err = cudaFuncSetAttribute(paged_attention_generic_kernel<float>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (err != cudaSuccess) return (int)err;
+    paged_attention_generic_kernel<float><<<grid, THREADS, smem, stream>>>(
+        (const float*)q, (const float*)k_cache, (const float*)v_cache, (float*)out, block_tables,
+        bt_stride, segment_of_token, positions, n_q, n_kv, head_dim, page_size, scale, window);
+  } else if (dtype == LSE_DTYPE_BF16) {
+    err = cudaFuncSetAttribute(paged_attention_generic_kernel<__nv_bfloat16>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (err != cudaSuccess) return (int)err;
+    paged_attention_generic_kernel<__nv_bfloat16><<<grid, THREADS, smem, stream>>>(
+        (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
+        (__nv_bfloat16*)out, block_tables, bt_stride, segment_of_token, positions, n_q, n_kv,
+        head_dim, page_size, scale, window);
+  } else {
+    return LSE_ERR_BAD_ARGUMENT;
+  }
+  LSE_LAUNCH_CHECK();
+}

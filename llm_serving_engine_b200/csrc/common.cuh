@@ -1,0 +1,65 @@
+// Shared device helpers for the engine's kernels (sm_100a).
+//
+// Conventions used by every launcher in this directory:
+//   * dtype codes: 0 = float32, 1 = bfloat16.
+//   * every launcher is extern "C", takes raw device pointers and the CUDA
+//     stream to launch on, allocates nothing and returns a cudaError_t as int.
+//   * all arithmetic inside a kernel is float32; a value is rounded once, when
+//     it is stored in a bfloat16 tensor.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define LSE_DTYPE_F32 0
+#define LSE_DTYPE_BF16 1
+
+// Returned (as a negative number, so that it cannot be taken for a cudaError_t)
+// when a launcher refuses its arguments.
+#define LSE_ERR_BAD_ARGUMENT (-1)
+#define LSE_ERR_TOO_LARGE (-2)
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a whole block in a fixed order (lanes by butterfly, then warps in
+// index order), so the result depends on the block size only.  `scratch` holds
+// at least 32 floats.  Every thread gets the result.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float total = 0.f;
+  for (int w = 0; w < nwarps; ++w) total += scratch[w];
+  return total;
+}
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float total = scratch[0];
+  for (int w = 1; w < nwarps; ++w) total = fmaxf(total, scratch[w]);
+  return total;
+}
+
+#define LSE_LAUNCH_CHECK() return (int)cudaGetLastError()

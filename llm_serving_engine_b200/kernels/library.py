@@ -1,0 +1,78 @@
+"""Loads the compiled CUDA library and declares its C entry points.
+
+There is no fallback: if the library cannot be built or loaded, or a launch
+reports an error, an exception is raised.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+from ..csrc import build
+
+_lib = None
+
+_SIGNATURES = {
+    "lse_embedding": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "lse_add_rmsnorm": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
+                        c_float, c_int, c_void_p],
+    "lse_rope_kv_write": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                          c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_longlong, c_void_p],
+    "lse_silu_mul": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "lse_gemm_f32_nt": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong,
+                        c_longlong, c_longlong, c_void_p],
+    "lse_paged_attention_generic": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
+                                    c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
+                                    c_int, c_void_p],
+    "lse_argmax": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p],
+    "lse_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                   c_void_p, c_void_p, c_void_p],
+}
+
+
+class KernelError(RuntimeError):
+    """A kernel launcher refused its arguments or CUDA reported an error."""
+
+
+def load(verbose: bool = True):
+    """The ctypes handle of the kernel library (built at the first call)."""
+    global _lib
+    if _lib is None:
+        path = build.library_path(verbose=verbose)
+        lib = ctypes.CDLL(str(path))
+        for name, argtypes in _SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.argtypes = argtypes
+            fn.restype = c_int
+        _lib = lib
+    return _lib
+
+
+def register_signatures(signatures: dict) -> None:
+    """Declare further entry points (used by kernel files added later)."""
+    _SIGNATURES.update(signatures)
+    if _lib is not None:
+        for name, argtypes in signatures.items():
+            fn = getattr(_lib, name)
+            fn.argtypes = argtypes
+            fn.restype = c_int
+
+
+_launch_count = 0
+
+
+def launches() -> int:
+    """How many kernels of this library have been launched by this process."""
+    return _launch_count
+
+
+def check(code: int, name: str) -> None:
+    global _launch_count
+    _launch_count += 1
+    if code == 0:
+        return
+    if code == -1:
+        raise KernelError(f"{name}: unsupported or inconsistent arguments")
+    if code == -2:
+        raise KernelError(f"{name}: size beyond what this kernel was built for")
+    raise KernelError(f"{name}: CUDA error {code}")

@@ -1,0 +1,186 @@
+"""Python faces of the CUDA kernels: they check tensors and launch on the
+current CUDA stream.  Every function needs CUDA tensors; there is no CPU path."""
+from __future__ import annotations
+
+import torch
+
+from . import library
+from .library import KernelError, check
+
+F32, BF16 = 0, 1
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"unsupported dtype {dtype}: the kernels take float32 and bfloat16")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need_cuda(*tensors: torch.Tensor) -> None:
+    for tensor in tensors:
+        if tensor is not None and not tensor.is_cuda:
+            raise KernelError("the kernels run on CUDA tensors only; there is no CPU fallback")
+
+
+def _ptr(tensor: torch.Tensor | None) -> int | None:
+    return None if tensor is None else tensor.data_ptr()
+
+
+def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t] = float32(table[ids[t]]); ids int32 [T], out float32 [T, H]."""
+    _need_cuda(table, ids, out)
+    vocab, hidden = table.shape
+    assert ids.dtype == torch.int32 and out.dtype == torch.float32 and table.is_contiguous()
+    assert out.shape == (ids.shape[0], hidden) and out.is_contiguous()
+    lib = library.load()
+    check(lib.lse_embedding(table.data_ptr(), dtype_code(table.dtype), ids.data_ptr(), out.data_ptr(),
+                            ids.shape[0], hidden, vocab, _stream()), "embedding")
+    return out
+
+
+def add_rmsnorm(residual: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float,
+                out: torch.Tensor, rows: torch.Tensor | None = None, write_residual: bool = True) -> torch.Tensor:
+    """residual (+= delta); out = rmsnorm(residual) * weight.
+
+    residual float32 [T, H]; delta [T, H] float32/bfloat16 or None; weight
+    float32 [H]; out [R, H] float32/bfloat16 where R = len(rows) when ``rows``
+    (int32 row indices into residual) is given, else T.  With ``rows`` the
+    residual is left unchanged unless ``write_residual``.
+    """
+    _need_cuda(residual, delta, weight, out, rows)
+    hidden = residual.shape[-1]
+    assert residual.dtype == torch.float32 and weight.dtype == torch.float32 and weight.shape == (hidden,)
+    assert residual.is_contiguous() and out.is_contiguous() and out.shape[-1] == hidden
+    if delta is not None:
+        assert delta.shape == residual.shape and delta.is_contiguous()
+    n_rows = out.shape[0]
+    if rows is not None:
+        assert rows.dtype == torch.int32 and rows.shape[0] == n_rows
+    else:
+        assert n_rows == residual.shape[0]
+    lib = library.load()
+    delta_code = dtype_code(delta.dtype) if delta is not None else dtype_code(out.dtype)
+    check(lib.lse_add_rmsnorm(residual.data_ptr(), _ptr(delta), delta_code, weight.data_ptr(),
+                              out.data_ptr(), dtype_code(out.dtype), _ptr(rows), n_rows, hidden,
+                              float(eps), int(write_residual), _stream()), "add_rmsnorm")
+    return out
+
+
+def gemm_f32_nt(a: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, out: torch.Tensor) -> torch.Tensor:
+    """out[M, N] = a[M, K] @ weight[N, K]^T (+ bias[N]) in true float32."""
+    _need_cuda(a, weight, bias, out)
+    m, k = a.shape
+    n = weight.shape[0]
+    assert a.dtype == weight.dtype == out.dtype == torch.float32
+    assert weight.shape[1] == k and out.shape == (m, n)
+    assert a.stride(1) == 1 and weight.stride(1) == 1 and out.stride(1) == 1
+    if bias is not None:
+        assert bias.dtype == torch.float32 and bias.shape == (n,)
+    lib = library.load()
+    check(lib.lse_gemm_f32_nt(a.data_ptr(), weight.data_ptr(), _ptr(bias), out.data_ptr(), m, n, k,
+                              a.stride(0), weight.stride(0), out.stride(0), _stream()), "gemm_f32_nt")
+    return out
+
+
+def rope_kv_write(qkv: torch.Tensor, bias: torch.Tensor | None, positions: torch.Tensor,
+                  slot_mapping: torch.Tensor, inv_freq: torch.Tensor, q_out: torch.Tensor,
+                  k_cache: torch.Tensor, v_cache: torch.Tensor, n_q: int, n_kv: int, head_dim: int,
+                  pairing: int) -> None:
+    """Bias, rotary encoding of queries and keys, and the write of keys and values
+    into the paged cache (k_cache/v_cache: [pages, n_kv, page_size, head_dim])."""
+    _need_cuda(qkv, bias, positions, slot_mapping, inv_freq, q_out, k_cache, v_cache)
+    tokens = qkv.shape[0]
+    width = (n_q + 2 * n_kv) * head_dim
+    assert qkv.shape[1] == width and qkv.stride(1) == 1
+    assert positions.dtype == torch.int32 and slot_mapping.dtype == torch.int32
+    assert positions.shape[0] >= tokens and slot_mapping.shape[0] >= tokens
+    assert inv_freq.dtype == torch.float32 and inv_freq.shape == (head_dim // 2,)
+    assert q_out.dtype == qkv.dtype == k_cache.dtype == v_cache.dtype
+    assert q_out.is_contiguous() and q_out.shape == (tokens, n_q, head_dim)
+    assert k_cache.is_contiguous() and v_cache.is_contiguous()
+    assert k_cache.shape[1] == n_kv and k_cache.shape[3] == head_dim and v_cache.shape == k_cache.shape
+    if bias is not None:
+        assert bias.dtype == torch.float32 and bias.shape == (width,)
+    lib = library.load()
+    check(lib.lse_rope_kv_write(qkv.data_ptr(), dtype_code(qkv.dtype), _ptr(bias), positions.data_ptr(),
+                                slot_mapping.data_ptr(), inv_freq.data_ptr(), q_out.data_ptr(),
+                                k_cache.data_ptr(), v_cache.data_ptr(), tokens, n_q, n_kv, head_dim,
+                                k_cache.shape[2], pairing, qkv.stride(0), _stream()), "rope_kv_write")
+
+
+def paged_attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                            out: torch.Tensor, block_tables: torch.Tensor,
+                            segment_of_token: torch.Tensor, positions: torch.Tensor, scale: float,
+                            window: int = 0) -> torch.Tensor:
+    """Attention of every token of the step over its request's cached keys.
+
+    q, out [T, n_q, D]; k_cache, v_cache [pages, n_kv, page_size, D];
+    block_tables int32 [S, max_pages]; segment_of_token, positions int32 [T].
+    """
+    _need_cuda(q, k_cache, v_cache, out, block_tables, segment_of_token, positions)
+    tokens, n_q, head_dim = q.shape
+    n_kv, page_size = k_cache.shape[1], k_cache.shape[2]
+    if head_dim % 16 or head_dim > 256:
+        raise KernelError(f"attention: head size {head_dim} is not a multiple of 16 up to 256")
+    if n_q % n_kv:
+        raise KernelError(f"attention: {n_q} query heads do not divide into {n_kv} groups")
+    assert q.is_contiguous() and out.is_contiguous() and out.shape == q.shape
+    assert k_cache.is_contiguous() and v_cache.is_contiguous() and v_cache.shape == k_cache.shape
+    assert q.dtype == out.dtype == k_cache.dtype == v_cache.dtype
+    assert block_tables.dtype == torch.int32 and block_tables.dim() == 2 and block_tables.stride(1) == 1
+    assert segment_of_token.dtype == torch.int32 and positions.dtype == torch.int32
+    lib = library.load()
+    check(lib.lse_paged_attention_generic(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+                                          out.data_ptr(), dtype_code(q.dtype), block_tables.data_ptr(),
+                                          block_tables.stride(0), segment_of_token.data_ptr(),
+                                          positions.data_ptr(), tokens, n_q, n_kv, head_dim, page_size,
+                                          float(scale), int(window), _stream()), "paged_attention_generic")
+    return out
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
+    _need_cuda(gate_up, out)
+    tokens, two_i = gate_up.shape
+    assert two_i % 2 == 0 and out.shape == (tokens, two_i // 2)
+    assert gate_up.is_contiguous() and out.is_contiguous() and gate_up.dtype == out.dtype
+    lib = library.load()
+    check(lib.lse_silu_mul(gate_up.data_ptr(), out.data_ptr(), dtype_code(out.dtype), tokens, two_i // 2,
+                           _stream()), "silu_mul")
+    return out
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[r] = index of the first largest value of logits[r] (float32 [R, V])."""
+    _need_cuda(logits, out)
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and out.dtype == torch.int32
+    rows, vocab = logits.shape
+    lib = library.load()
+    check(lib.lse_argmax(logits.data_ptr(), logits.stride(0), rows, vocab, out.data_ptr(), _stream()), "argmax")
+    return out
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Tensor, seed: torch.Tensor,
+           counter: torch.Tensor, scratch: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """Temperature / top-p sampling of one token per row (rows with temperature <= 0 take the argmax).
+
+    temperature, top_p float32 [R]; seed, counter int64 [R]; scratch float32 with
+    at least R * V values; out int32 [R].
+    """
+    _need_cuda(logits, temperature, top_p, seed, counter, scratch, out)
+    rows, vocab = logits.shape
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and out.dtype == torch.int32
+    assert temperature.dtype == torch.float32 and top_p.dtype == torch.float32
+    assert seed.dtype == torch.int64 and counter.dtype == torch.int64
+    assert scratch.dtype == torch.float32 and scratch.numel() >= rows * vocab and scratch.is_contiguous()
+    lib = library.load()
+    check(lib.lse_sample(logits.data_ptr(), logits.stride(0), rows, vocab, temperature.data_ptr(),
+                         top_p.data_ptr(), seed.data_ptr(), counter.data_ptr(), scratch.data_ptr(),
+                         out.data_ptr(), _stream()), "sample")
+    return out

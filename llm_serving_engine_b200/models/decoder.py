@@ -1,0 +1,114 @@
+"""The generic decoder: embedding, blocks run in the order the description gives,
+final norm and LM head on the wanted rows only.  Built from a ``ModelSpec``; it
+does not know which architecture it serves."""
+from __future__ import annotations
+
+import torch
+
+from ..config.model_config import LayerSpec, ModelSpec, PartSpec
+from ..kernels import ops
+from ..parts.base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, BuildContext, ResidualStream)
+from ..parts.linear import linear
+from ..weights.tensor_spec import TensorSpec
+
+_MIXER_PREFIX = "self_attn."
+_FF_PREFIX = "mlp."
+
+
+def _layer_part_prefixes(layer: LayerSpec) -> dict[str, str]:
+    names = dict(layer.block.params.get("tensor_prefixes", {}))
+    return {
+        "mixer": layer.prefix + names.get("mixer", _MIXER_PREFIX),
+        "feed_forward": layer.prefix + names.get("feed_forward", _FF_PREFIX),
+        "mixer_norm": layer.prefix + names.get("mixer_norm", "input_layernorm."),
+        "feed_forward_norm": layer.prefix + names.get("feed_forward_norm", "post_attention_layernorm."),
+    }
+
+
+def _layer_parts(layer: LayerSpec) -> list[tuple[str, type, PartSpec]]:
+    prefixes = _layer_part_prefixes(layer)
+    return [
+        (prefixes["mixer_norm"], NORMS.get(layer.mixer_norm.kind), layer.mixer_norm),
+        (prefixes["mixer"], MIXERS.get(layer.mixer.kind), layer.mixer),
+        (prefixes["feed_forward_norm"], NORMS.get(layer.feed_forward_norm.kind), layer.feed_forward_norm),
+        (prefixes["feed_forward"], FEED_FORWARDS.get(layer.feed_forward.kind), layer.feed_forward),
+    ]
+
+
+def expected_tensors(spec: ModelSpec) -> dict[str, TensorSpec]:
+    """Every tensor the model reads from the checkpoint, by its full name."""
+    out: dict[str, TensorSpec] = {spec.embedding_name: TensorSpec((spec.vocab_size, spec.hidden_size))}
+    for layer in spec.layers:
+        for prefix, cls, part in _layer_parts(layer):
+            for local, tensor in cls.expected_tensors(part.params, spec.hidden_size).items():
+                out[prefix + local] = tensor
+    norm_cls = NORMS.get(spec.final_norm.kind)
+    for local, tensor in norm_cls.expected_tensors(spec.final_norm.params, spec.hidden_size).items():
+        out[spec.final_norm_prefix + local] = tensor
+    if not spec.tie_word_embeddings:
+        out[spec.lm_head_name] = TensorSpec((spec.vocab_size, spec.hidden_size))
+    return out
+
+
+def cache_requirements(spec: ModelSpec) -> list:
+    """Per layer: what its mixer keeps between steps (``PagedKV``, ``RequestState``
+    or ``None``), or the index of the layer whose cache it reads."""
+    out = []
+    for layer in spec.layers:
+        if layer.cache_from is not None:
+            out.append(layer.cache_from)
+        else:
+            out.append(MIXERS.get(layer.mixer.kind).cache_requirement(layer.mixer.params, spec.hidden_size))
+    return out
+
+
+class DecoderModel:
+    def __init__(self, spec: ModelSpec, weights: dict[str, torch.Tensor], dtype: torch.dtype, device) -> None:
+        self.spec = spec
+        self.dtype = dtype
+        self.device = torch.device(device)
+        self.embedding = weights[spec.embedding_name].contiguous()
+        self.lm_head = self.embedding if spec.tie_word_embeddings else weights[spec.lm_head_name].contiguous()
+        self.blocks = []
+        for index, layer in enumerate(spec.layers):
+            ctx = BuildContext(dtype, self.device, spec.hidden_size, index, spec.max_position_embeddings)
+            built = []
+            for prefix, cls, part in _layer_parts(layer):
+                local = {name[len(prefix):]: tensor for name, tensor in weights.items() if name.startswith(prefix)}
+                built.append(cls(part.params, local, ctx))
+            block_cls = BLOCKS.get(layer.block.kind)
+            self.blocks.append(block_cls(layer.block.params, *built))
+        ctx = BuildContext(dtype, self.device, spec.hidden_size, -1, spec.max_position_embeddings)
+        prefix = spec.final_norm_prefix
+        local = {name[len(prefix):]: tensor for name, tensor in weights.items() if name.startswith(prefix)}
+        self.final_norm = NORMS.get(spec.final_norm.kind)(spec.final_norm.params, local, ctx)
+
+    @property
+    def vocab_size(self) -> int:
+        return self.spec.vocab_size
+
+    def weight_bytes_per_step(self) -> int:
+        """Bytes of weights a step reads once: every matrix of every layer run, and
+        the LM head (the embedding rows that a step gathers are not counted)."""
+        total = self.lm_head.numel() * self.lm_head.element_size()
+        for index in self.spec.order:
+            block = self.blocks[index]
+            for part in (block.mixer, block.feed_forward, block.mixer_norm, block.feed_forward_norm):
+                for value in vars(part).values():
+                    if isinstance(value, torch.Tensor) and value.dim() >= 1 and value.is_floating_point():
+                        total += value.numel() * value.element_size()
+        return total
+
+    def forward(self, step, caches) -> torch.Tensor:
+        """Run the step's rows through the layers and return float32 logits
+        [number of wanted rows, vocab] (an empty tensor when nothing is wanted)."""
+        tokens = step.num_tokens
+        residual = torch.empty((tokens, self.spec.hidden_size), dtype=torch.float32, device=self.device)
+        ops.embedding(self.embedding, step.token_ids, residual)
+        stream = ResidualStream(residual)
+        for index in self.spec.order:
+            self.blocks[index].forward(stream, step, caches[index])
+        if step.num_wanted == 0:
+            return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
+        x = self.final_norm.forward(stream, rows=step.want_rows)
+        return linear(x, self.lm_head, out_dtype=torch.float32)

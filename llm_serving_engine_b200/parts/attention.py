@@ -1,0 +1,73 @@
+"""Grouped-query attention over the paged cache
+(reference ``src/llmserve/model.py:46-177``)."""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..kernels import ops
+from ..weights.tensor_spec import TensorSpec
+from .base import POSITION_ENCODINGS, Mixer, PagedKV, register_mixer
+from .linear import linear
+
+
+@register_mixer("gqa_attention")
+class GroupedQueryAttention(Mixer):
+    """params: ``num_heads``, ``num_kv_heads``, ``head_dim``, ``bias`` (on q/k/v),
+    ``window`` (0 = all keys), ``position`` (a PartSpec-like dict: kind, params).
+
+    Tensors: ``q_proj/k_proj/v_proj.weight`` (+ ``.bias``), ``o_proj.weight``; the
+    three projections are stacked into one matrix when the part is built.
+    Every row of the step writes its key and value first, then attends to the
+    keys of its own request up to its own position, scaled by 1/sqrt(head_dim).
+    """
+
+    def __init__(self, params, weights, ctx) -> None:
+        super().__init__(params, weights, ctx)
+        self.n_q = int(params["num_heads"])
+        self.n_kv = int(params["num_kv_heads"])
+        self.head_dim = int(params["head_dim"])
+        self.window = int(params.get("window", 0))
+        self.scale = 1.0 / math.sqrt(self.head_dim)
+        if self.head_dim % 16 or self.head_dim > 256:
+            raise ops.KernelError(
+                f"attention: head size {self.head_dim} is not supported (multiples of 16 up to 256)")
+        self.qkv_weight = torch.cat(
+            [weights["q_proj.weight"], weights["k_proj.weight"], weights["v_proj.weight"]], dim=0).contiguous()
+        self.qkv_bias = None
+        if params.get("bias", True):
+            self.qkv_bias = torch.cat(
+                [weights["q_proj.bias"], weights["k_proj.bias"], weights["v_proj.bias"]]).float().contiguous()
+        self.o_weight = weights["o_proj.weight"].contiguous()
+        position = params["position"]
+        self.position = POSITION_ENCODINGS.get(position["kind"])(position["params"], {}, ctx)
+
+    @classmethod
+    def expected_tensors(cls, params, hidden_size):
+        n_q, n_kv, d = int(params["num_heads"]), int(params["num_kv_heads"]), int(params["head_dim"])
+        out = {
+            "q_proj.weight": TensorSpec((n_q * d, hidden_size)),
+            "k_proj.weight": TensorSpec((n_kv * d, hidden_size)),
+            "v_proj.weight": TensorSpec((n_kv * d, hidden_size)),
+            "o_proj.weight": TensorSpec((hidden_size, n_q * d)),
+        }
+        if params.get("bias", True):
+            out["q_proj.bias"] = TensorSpec((n_q * d,), "bias")
+            out["k_proj.bias"] = TensorSpec((n_kv * d,), "bias")
+            out["v_proj.bias"] = TensorSpec((n_kv * d,), "bias")
+        return out
+
+    @classmethod
+    def cache_requirement(cls, params, hidden_size):
+        return PagedKV(int(params["num_kv_heads"]), int(params["head_dim"]), int(params.get("window", 0)))
+
+    def forward(self, x, step, cache):
+        tokens = x.shape[0]
+        qkv = linear(x, self.qkv_weight)  # bias is added with the rotation, in float32
+        q = torch.empty((tokens, self.n_q, self.head_dim), dtype=x.dtype, device=x.device)
+        self.position.encode_and_store(qkv, self.qkv_bias, step, cache, q, self.n_q, self.n_kv, self.head_dim)
+        attended = torch.empty_like(q)
+        ops.paged_attention_generic(q, cache.keys, cache.values, attended, cache.block_tables,
+                                    step.segment_of_token, step.positions, self.scale, self.window)
+        return linear(attended.view(tokens, self.n_q * self.head_dim), self.o_weight)

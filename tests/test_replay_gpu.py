@@ -1,0 +1,82 @@
+"""Trace replay on the GPU against the plain implementation: each request whole;
+most of it in one step and the last 32 tokens one by one; portions of changing
+size; and mixed batches with so few pages that they are used again.  In float32
+and in bfloat16, for tiny configurations that differ in every size and option."""
+import random
+
+import pytest
+
+import helpers
+from tiny_configs import ALL
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = ("float32", "bfloat16")
+LENGTHS = {"A": (5, 17, 33, 150), "B": (1, 9, 24, 40, 131), "C": (3, 66, 97)}
+
+
+def _requests(name: str, seed: int = 0) -> dict[str, list[int]]:
+    config, _, _ = ALL[name]
+    rng = random.Random(1000 + seed)
+    return {f"r{index}": helpers.random_tokens(rng, config["vocab_size"], length)
+            for index, length in enumerate(LENGTHS[name])}
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", sorted(ALL))
+def test_whole(name, dtype):
+    requests = _requests(name)
+    steps = helpers.trace_whole(requests)
+    got = helpers.run_trace(name, dtype, steps, helpers.max_tokens_for(requests), ALL[name][1])
+    helpers.assert_close(name, dtype, requests, got, "whole prompts")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", sorted(ALL))
+def test_tail_decoded_one_by_one(name, dtype):
+    requests = _requests(name)
+    steps = helpers.trace_tail_decode(requests, tail=32)
+    got = helpers.run_trace(name, dtype, steps, helpers.max_tokens_for(requests), ALL[name][1])
+    helpers.assert_close(name, dtype, requests, got, "last 32 tokens one by one")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", sorted(ALL))
+def test_portions_of_changing_size(name, dtype):
+    requests = _requests(name)
+    steps = helpers.trace_portions(requests)
+    got = helpers.run_trace(name, dtype, steps, helpers.max_tokens_for(requests), ALL[name][1])
+    helpers.assert_close(name, dtype, requests, got, "portions of changing size")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", sorted(ALL))
+def test_mixed_with_page_reuse(name, dtype):
+    config, page, _ = ALL[name]
+    rng = random.Random(77)
+    lengths = [rng.randrange(20, 140) for _ in range(9)]
+    requests = {f"m{index}": helpers.random_tokens(rng, config["vocab_size"], length)
+                for index, length in enumerate(lengths)}
+    steps, peak = helpers.trace_mixed(requests, seed=5)
+    total_rounded = sum(-(-length // 64) * 64 for length in lengths)
+    assert peak < total_rounded, "the pool must be smaller than all requests together, so pages are used again"
+    got = helpers.run_trace(name, dtype, steps, peak, page)
+    helpers.assert_close(name, dtype, requests, got, "mixed batches with page reuse")
+
+
+def test_float32_is_bitwise_the_same_however_it_is_cut():
+    """In float32 every kernel sums in an order that depends on the row alone, so the
+    logits of a position are the same bit for bit in every way of cutting and batching."""
+    import torch
+
+    name = "B"
+    config, page, _ = ALL[name]
+    requests = _requests(name, seed=3)
+    whole = helpers.run_trace(name, "float32", helpers.trace_whole(requests), helpers.max_tokens_for(requests), page)
+    portions = helpers.run_trace(name, "float32", helpers.trace_portions(requests),
+                                 helpers.max_tokens_for(requests), page)
+    steps, peak = helpers.trace_mixed(requests, seed=9)
+    mixed = helpers.run_trace(name, "float32", steps, peak, page)
+    for rid in requests:
+        assert torch.equal(whole[rid], portions[rid]), f"{rid}: portions differ from whole"
+        assert torch.equal(whole[rid], mixed[rid]), f"{rid}: mixed differs from whole"
