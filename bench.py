@@ -1,0 +1,306 @@
+"""Decode and prefill throughput of the engine on one B200, with roofline fractions.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+A "step" is one decode step.  The default run has the layer sizes of the
+Qwen2.5-1.5B shape with random weights, a batch of 8 requests that each hold a
+2,048-token prompt (context limit 4,096), bfloat16.  One JSON line is printed:
+``value`` is decoded tokens per second timed on the device, ``e2e`` the same
+through ``LLMEngine.generate_many`` (host token ids in, host token ids out),
+``prefill`` the 2,048-token prompt step, ``roofline`` the decode step's bytes
+(every weight once plus the cache of the live requests) over its time against
+the measured copy bandwidth, ``points`` decoding at batch 1 and 64.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+QWEN25_1P5B = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "vocab_size": 151936, "hidden_size": 1536, "intermediate_size": 8960, "num_hidden_layers": 28,
+    "num_attention_heads": 12, "num_key_value_heads": 2, "max_position_embeddings": 4096,
+    "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "attention_bias": True, "tie_word_embeddings": True,
+}
+FULL_LAYERS = QWEN25_1P5B["num_hidden_layers"]
+PROMPT = 2048
+BLOCK = 16
+
+
+def peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    out = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+    if os.path.exists(path):
+        try:
+            data = json.load(open(path))
+            out["hbm_gbs"] = float(data.get("hbm_gbs", out["hbm_gbs"]))
+            out["bf16_tflops"] = float(data.get("bf16_tflops", out["bf16_tflops"]))
+            out["source"] = "measured"
+        except Exception:
+            pass
+    return out
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self) -> None:
+        self.rows: list[list[str]] = []
+        self._stop = threading.Event()
+        self._thread = threading.Thread(target=self._loop, daemon=True)
+
+    def _loop(self) -> None:
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
+                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5)
+                if out.returncode == 0 and out.stdout.strip():
+                    self.rows.append([item.strip() for item in out.stdout.strip().splitlines()[0].split(",")])
+            except Exception:
+                pass
+            self._stop.wait(0.2)
+
+    def __enter__(self):
+        self._thread.start()
+        return self
+
+    def __exit__(self, *_):
+        self._stop.set()
+        self._thread.join(timeout=6)
+
+    def summary(self) -> dict:
+        clocks = sorted(int(row[0]) for row in self.rows if row and row[0].isdigit())
+        maxima = [int(row[1]) for row in self.rows if len(row) > 1 and row[1].isdigit()]
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        reasons = [name for index, name in enumerate(names, start=2)
+                   if any(len(row) > index and row[index].lower().startswith("active") for row in self.rows)]
+        return {"sm_mhz": clocks[len(clocks) // 2] if clocks else None,
+                "sm_max_mhz": max(maxima) if maxima else None, "reasons": reasons, "samples": len(self.rows)}
+
+
+def build_model(layers: int):
+    import torch
+
+    from llm_serving_engine_b200.config import load_config
+    from llm_serving_engine_b200.models import DecoderModel, expected_tensors
+    from llm_serving_engine_b200.weights.loader import held_dtype
+
+    config = dict(QWEN25_1P5B, num_hidden_layers=layers)
+    _, _, spec = load_config(config)
+    generator = torch.Generator(device="cuda").manual_seed(0)
+    weights = {}
+    for name, tensor_spec in expected_tensors(spec).items():
+        if tensor_spec.kind == "norm":
+            tensor = 1.0 + (torch.rand(tensor_spec.shape, generator=generator, device="cuda") * 0.2 - 0.1)
+        else:
+            tensor = torch.randn(tensor_spec.shape, generator=generator, device="cuda") * 0.02
+        weights[name] = tensor.to(held_dtype(tensor_spec, tensor.dtype, torch.bfloat16))
+    return DecoderModel(spec, weights, torch.bfloat16, "cuda"), config
+
+
+def time_decode(model, batch: int, steps: int, warmup: int):
+    """Device time of ``steps`` decode steps at ``batch`` requests that hold PROMPT tokens each."""
+    import torch
+
+    from llm_serving_engine_b200.cache.manager import CacheManager
+    from llm_serving_engine_b200.config.runtime_config import CacheConfig
+    from llm_serving_engine_b200.engine.step import StepEntry, StepRunner
+    from llm_serving_engine_b200.kernels import library, ops
+    from llm_serving_engine_b200.models import cache_requirements
+
+    context = model.spec.max_position_embeddings
+    pages = batch * (context // BLOCK)
+    cache = CacheManager(cache_requirements(model.spec), CacheConfig(BLOCK, pages), model.dtype, model.device,
+                         context, num_state_slots=batch)
+    runner = StepRunner(model, cache, max_tokens_per_step=max(PROMPT, batch), max_segments=batch)
+    generator = torch.Generator().manual_seed(1)
+    ids = [f"d{index}" for index in range(batch)]
+    with torch.inference_mode():
+        for rid in ids:
+            cache.create(rid)
+            prompt = torch.randint(0, model.vocab_size, (PROMPT,), generator=generator).tolist()
+            runner.run([StepEntry(rid, prompt, [])])
+        tokens = torch.randint(0, model.vocab_size, (batch,), generator=generator).tolist()
+        out = torch.empty(batch, dtype=torch.int32, device=model.device)
+
+        def one_step():
+            logits = runner.run([StepEntry(rid, [token], [0]) for rid, token in zip(ids, tokens)])
+            ops.argmax(logits, out)
+
+        for _ in range(warmup):
+            one_step()
+        torch.cuda.synchronize()
+        launches = library.launches()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(steps):
+            one_step()
+        end.record()
+        torch.cuda.synchronize()
+        launches = library.launches() - launches
+    ms = start.elapsed_time(end) / steps
+    kv_bytes = batch * (PROMPT + warmup + steps // 2) * cache.kv_bytes_per_token()
+    cache.free_all()
+    del runner, cache
+    torch.cuda.empty_cache()
+    return ms, kv_bytes, launches
+
+
+def time_prefill(model, repeats: int = 5):
+    import torch
+
+    from llm_serving_engine_b200.cache.manager import CacheManager
+    from llm_serving_engine_b200.config.runtime_config import CacheConfig
+    from llm_serving_engine_b200.engine.step import StepEntry, StepRunner
+    from llm_serving_engine_b200.models import cache_requirements
+
+    context = model.spec.max_position_embeddings
+    cache = CacheManager(cache_requirements(model.spec), CacheConfig(BLOCK, context // BLOCK), model.dtype,
+                         model.device, context, num_state_slots=1)
+    runner = StepRunner(model, cache, max_tokens_per_step=PROMPT, max_segments=1)
+    generator = torch.Generator().manual_seed(2)
+    prompt = torch.randint(0, model.vocab_size, (PROMPT,), generator=generator).tolist()
+    times = []
+    with torch.inference_mode():
+        for index in range(repeats + 2):
+            cache.create("p")
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            runner.run([StepEntry("p", prompt, [PROMPT - 1])])
+            end.record()
+            torch.cuda.synchronize()
+            cache.free("p")
+            if index >= 2:
+                times.append(start.elapsed_time(end))
+    times.sort()
+    return times[len(times) // 2]
+
+
+def prefill_flops(config: dict, layers: int, tokens: int) -> float:
+    h, inter = config["hidden_size"], config["intermediate_size"]
+    n_q, n_kv = config["num_attention_heads"], config["num_key_value_heads"]
+    d = h // n_q
+    linear = (n_q + 2 * n_kv) * d * h + n_q * d * h + 3 * inter * h
+    attention = 4 * n_q * d * tokens * (tokens + 1) / 2
+    return layers * (2.0 * tokens * linear + attention) + 2.0 * config["vocab_size"] * h
+
+
+def time_e2e(model, batch: int, new_tokens: int):
+    """Decode tokens per second through the Python entry point: host ids in, host ids out."""
+    import torch
+
+    from llm_serving_engine_b200 import CacheConfig, GenerationConfig, LLMEngine, SchedulerConfig
+
+    context = model.spec.max_position_embeddings
+    engine = LLMEngine(model, None, cache_config=CacheConfig(BLOCK, batch * (context // BLOCK)),
+                       scheduler_config=SchedulerConfig(max_batch_size=batch, max_tokens_per_step=max(PROMPT, batch)),
+                       prefill_chunk_size=PROMPT)
+    generator = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, model.vocab_size, (PROMPT,), generator=generator).tolist() for _ in range(batch)]
+    stamps: list[float] = []
+    counts = [0] * batch
+
+    def make_callback(index: int):
+        def callback(_token: int) -> None:
+            counts[index] += 1
+            stamps.append(time.perf_counter())
+        return callback
+
+    engine.generate_many(prompts, GenerationConfig(max_new_tokens=new_tokens),
+                         [make_callback(index) for index in range(batch)])
+    torch.cuda.synchronize()
+    # the decode phase starts when every request has its first token
+    first_all = stamps[batch - 1] if len(stamps) >= batch else stamps[0]
+    decoded = len(stamps) - batch
+    seconds = stamps[-1] - first_all
+    steps = max(new_tokens - 1, 1)
+    h2d = engine.runner.last_h2d_bytes
+    del engine
+    torch.cuda.empty_cache()
+    return decoded / max(seconds, 1e-9), h2d, 4 * batch, steps
+
+
+def run_ours(args) -> dict:
+    import torch
+
+    import __graft_entry__
+    __graft_entry__.build()
+    torch.cuda.set_device(0)
+    layers = args.layers or FULL_LAYERS
+    model, config = build_model(layers)
+    peak = peaks()
+    weight_bytes = model.weight_bytes_per_step()
+    batch = args.batch
+
+    with ClockSampler() as clocks:
+        ms, kv_bytes, launches = time_decode(model, batch, args.steps, args.warmup)
+    value = batch / (ms / 1e3)
+    achieved = (weight_bytes + kv_bytes) / (ms / 1e3) / 1e9
+
+    prefill_ms = time_prefill(model)
+    flops = prefill_flops(config, layers, PROMPT)
+    points = {}
+    for point_batch in (1, 64):
+        point_ms, _, _ = time_decode(model, point_batch, max(args.steps // 2, 8), args.warmup)
+        points[f"decode_b{point_batch}"] = round(point_batch / (point_ms / 1e3), 1)
+    e2e_value, h2d, d2h, _ = time_e2e(model, batch, max(args.steps, 16))
+
+    return {
+        "metric": "decode tok/s at batch 8 (Qwen2.5-1.5B shape, 2,048-token prompts)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic (random weights, uniform random token ids)", "impl": "ours",
+        "config": {
+            "model": "Qwen2.5-1.5B shape", "layers": layers, "layers_full": FULL_LAYERS, "hidden": config["hidden_size"],
+            "heads": config["num_attention_heads"], "kv_heads": config["num_key_value_heads"],
+            "head_dim": config["hidden_size"] // config["num_attention_heads"],
+            "intermediate": config["intermediate_size"], "vocab": config["vocab_size"], "tied": True,
+            "global_batch": batch, "seq_len": PROMPT, "context": config["max_position_embeddings"],
+            "kv_block": BLOCK, "parallelism": "single GPU", "l2": "inputs larger than L2 (weights 3 GB per step)",
+        },
+        "prefill": {"value": round(PROMPT / (prefill_ms / 1e3), 1), "tokens": PROMPT, "ms": round(prefill_ms, 3),
+                    "frac": round(flops / (prefill_ms / 1e3) / (peak["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / peak["hbm_gbs"], 4), "peaks": peak["source"]},
+        "points": points,
+        "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches,
+        "clocks": clocks.summary(),
+    }
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=64)
+    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--layers", type=int, default=0, help="fewer layers than the full model (0 = all)")
+    args = parser.parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "offline pip install of the reference fails: its build backend (hatchling) is not in the wheelhouse"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py measures a single-GPU engine; --gpus {args.gpus} is not supported")
+        return 2
+    args.warmup = max(args.warmup, 3)
+    print(json.dumps(run_ours(args)))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -86,6 +86,7 @@ class StepRunner:
         self._copied = torch.cuda.Event() if self.device.type == "cuda" else None
         self._copy_pending = False
         self.steps_run = 0
+        self.last_h2d_bytes = 0
 
     # -- the step ------------------------------------------------------------------
     def run(self, entries: list[StepEntry]) -> torch.Tensor:
@@ -179,6 +180,7 @@ class StepRunner:
         host[r_start[0] + n_seg] = row
 
         self._device[:cursor].copy_(self._host[:cursor], non_blocking=True)
+        self.last_h2d_bytes = cursor * 4
         if self._copied is not None:
             self._copied.record()
             self._copy_pending = True

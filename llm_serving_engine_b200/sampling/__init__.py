@@ -1,0 +1,3 @@
+from .sampler import GenerationConfig, Sampler, uniform01
+
+__all__ = ["GenerationConfig", "Sampler", "uniform01"]
