@@ -119,8 +119,9 @@ class LayerCache:
 class CacheManager:
     """Owns every layer's memory between steps.
 
-    ``requirements``: one entry per layer: ``PagedKV``, ``RequestState``, ``None``,
-    or an int (the layer whose cache this layer reads).
+    ``requirements``: one entry per layer run (a position in the model's order):
+    ``PagedKV``, ``RequestState``, ``None``, or an int (the position whose cache this
+    run reads).  "Layer" below means such a position.
     """
 
     def __init__(self, requirements: list, config: CacheConfig, dtype: torch.dtype, device,
@@ -129,7 +130,9 @@ class CacheManager:
         self.dtype = dtype
         self.device = torch.device(device)
         self.page_size = config.block_size
-        self.max_pages_per_request = min(config.num_blocks, math.ceil(max_position_embeddings / config.block_size))
+        # logical pages of one request: the position limit decides (a windowed group may walk
+        # through more logical pages than its pool holds, because it gives pages back on the way)
+        self.max_pages_per_request = math.ceil(max_position_embeddings / config.block_size)
         self.groups: list[CacheGroup] = []
         self.layer_group: dict[int, int] = {}
         self.layer_source: dict[int, int] = {}

@@ -191,11 +191,12 @@ class LLMEngine:
             events[0].record()
         planned = plan_iteration(list(self.scheduler.active), self.scheduler_config.max_tokens_per_step,
                                  self.prefill_chunk_size)
-        planned, victims, failed = resolve_page_pressure(
-            planned, lambda plan: self.cache.fits([(r.request_id, n) for r, n in plan]))
-        for victim in victims:
+        def preempt(victim: RequestState) -> None:
             self.cache.free(victim.request_id)
             self.scheduler.preempt(victim)
+
+        planned, _, failed = resolve_page_pressure(
+            planned, lambda plan: self.cache.fits([(r.request_id, n) for r, n in plan]), preempt)
         if failed is not None:
             self._finish(failed, CacheFullError("one sequence exceeds total KV cache capacity"))
         if planned:

@@ -126,12 +126,15 @@ def plan_iteration(active: list[RequestState], max_tokens_per_step: int,
 
 
 def resolve_page_pressure(planned: list[tuple[RequestState, int]],
-                          fits: Callable[[list[tuple[RequestState, int]]], bool]):
+                          fits: Callable[[list[tuple[RequestState, int]]], bool],
+                          preempt: Callable[[RequestState], None] = lambda request: None):
     """Drop requests from the plan until it fits the free pages.
 
-    Returns ``(planned, victims, failed)``: the plan that runs, the requests to
-    preempt (in the order chosen) and the single request that cannot fit even
-    alone (or ``None``).  ``fits(plan)`` answers whether the pages suffice.
+    ``fits(plan)`` answers whether the free pages suffice; ``preempt(victim)`` is
+    called at once for every request that is dropped, so that the pages it gives
+    back count for the next answer.  Returns ``(planned, victims, failed)``: the
+    plan that runs, the requests that were preempted (in the order chosen) and the
+    single request that cannot fit even alone (or ``None``).
     """
     planned = list(planned)
     victims: list[RequestState] = []
@@ -139,6 +142,7 @@ def resolve_page_pressure(planned: list[tuple[RequestState, int]],
         victim, _ = max(planned, key=lambda item: item[0].processed_tokens)
         victims.append(victim)
         planned = [item for item in planned if item[0] is not victim]
+        preempt(victim)
     failed = None
     if planned and not fits(planned):
         failed = planned[0][0]

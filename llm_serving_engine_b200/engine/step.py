@@ -82,7 +82,7 @@ class StepRunner:
         self._host = torch.empty(capacity, dtype=torch.int32, pin_memory=self.device.type == "cuda")
         self._host_np = self._host.numpy()
         self._device = torch.empty(capacity, dtype=torch.int32, device=self.device)
-        self._layer_views = [cache.layer_view(layer) for layer in range(len(model.spec.layers))]
+        self._layer_views = [cache.layer_view(position) for position in range(len(model.spec.order))]
         self._copied = torch.cuda.Event() if self.device.type == "cuda" else None
         self._copy_pending = False
         self.steps_run = 0

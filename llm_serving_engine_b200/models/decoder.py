@@ -51,14 +51,27 @@ def expected_tensors(spec: ModelSpec) -> dict[str, TensorSpec]:
 
 
 def cache_requirements(spec: ModelSpec) -> list:
-    """Per layer: what its mixer keeps between steps (``PagedKV``, ``RequestState``
-    or ``None``), or the index of the layer whose cache it reads."""
+    """What each entry of ``spec.order`` keeps between steps.
+
+    The list runs along ``order``, not along ``layers``: a layer that is named twice
+    runs twice with the same weights, and each run has a cache of its own.  An entry
+    is ``PagedKV``, ``RequestState`` or ``None`` (from the mixer), or an int: the
+    position in ``order`` whose cache this run reads (``LayerSpec.cache_from`` names a
+    layer; its first run is meant, and it must come earlier in the order).
+    """
+    from ..config.model_config import ConfigError
+
+    first_run: dict[int, int] = {}
     out = []
-    for layer in spec.layers:
+    for position, index in enumerate(spec.order):
+        layer = spec.layers[index]
         if layer.cache_from is not None:
-            out.append(layer.cache_from)
+            if layer.cache_from not in first_run:
+                raise ConfigError(f"layer {index} reads the cache of layer {layer.cache_from}, which has not run before it")
+            out.append(first_run[layer.cache_from])
         else:
             out.append(MIXERS.get(layer.mixer.kind).cache_requirement(layer.mixer.params, spec.hidden_size))
+        first_run.setdefault(index, position)
     return out
 
 
@@ -106,8 +119,8 @@ class DecoderModel:
         residual = torch.empty((tokens, self.spec.hidden_size), dtype=torch.float32, device=self.device)
         ops.embedding(self.embedding, step.token_ids, residual)
         stream = ResidualStream(residual)
-        for index in self.spec.order:
-            self.blocks[index].forward(stream, step, caches[index])
+        for position, index in enumerate(self.spec.order):   # caches run along the order
+            self.blocks[index].forward(stream, step, caches[position])
         if step.num_wanted == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
         x = self.final_norm.forward(stream, rows=step.want_rows)

@@ -1,0 +1,341 @@
+"""Each CUDA kernel alone against a plain PyTorch float32/float64 reference of the
+same operation, at sizes other than the tiny models': widths and vocabularies that
+are no power of two, head sizes in steps of 16, any number of heads and groups."""
+import math
+import random
+
+import pytest
+import torch
+
+from plain import qwen2_plain
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+def ops():
+    from llm_serving_engine_b200.kernels import ops as kernel_ops
+    return kernel_ops
+
+
+def rel_err(got: torch.Tensor, want: torch.Tensor) -> float:
+    return float((got.double() - want.double()).abs().max() / want.double().abs().max().clamp_min(1e-30))
+
+
+TOL = {torch.float32: 2e-6, torch.bfloat16: 2.0 ** -8}
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embedding(dtype):
+    table = torch.randn(1000, 96, device=DEV).to(dtype)
+    ids = torch.tensor([0, 999, 5, 5, 731], dtype=torch.int32, device=DEV)
+    out = torch.empty(5, 96, device=DEV)
+    ops().embedding(table, ids, out)
+    assert torch.equal(out, table[ids.long()].float())
+
+
+@pytest.mark.parametrize("hidden", [80, 1536, 3000])
+@pytest.mark.parametrize("delta_dtype, out_dtype", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16)])
+def test_add_rmsnorm(hidden, delta_dtype, out_dtype):
+    torch.manual_seed(hidden)
+    residual = torch.randn(7, hidden, device=DEV) * 3
+    delta = torch.randn(7, hidden, device=DEV).to(delta_dtype)
+    weight = 1 + 0.1 * torch.randn(hidden, device=DEV)
+    eps = 1e-5
+    want_residual = residual.double() + delta.double()
+    want = qwen2_plain.rms_norm(want_residual, weight.double(), eps)
+    got_residual = residual.clone()
+    out = torch.empty(7, hidden, device=DEV, dtype=out_dtype)
+    ops().add_rmsnorm(got_residual, delta, weight, eps, out)
+    assert rel_err(got_residual, want_residual) < 1e-6        # the residual sum is float32
+    assert rel_err(out, want) < TOL[out_dtype] * 2
+    # no pending branch output: the residual stays as it is
+    plain_out = torch.empty(7, hidden, device=DEV, dtype=out_dtype)
+    keep = residual.clone()
+    ops().add_rmsnorm(keep, None, weight, eps, plain_out)
+    assert torch.equal(keep, residual)
+    assert rel_err(plain_out, qwen2_plain.rms_norm(residual.double(), weight.double(), eps)) < TOL[out_dtype] * 2
+    # selected rows only (final norm): rows are gathered, the residual is not written
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32, device=DEV)
+    picked = torch.empty(3, hidden, device=DEV, dtype=out_dtype)
+    keep = residual.clone()
+    ops().add_rmsnorm(keep, delta, weight, eps, picked, rows=rows, write_residual=False)
+    assert torch.equal(keep, residual)
+    assert rel_err(picked, want[rows.long()]) < TOL[out_dtype] * 2
+
+
+@pytest.mark.parametrize("m, n, k", [(1, 33, 7), (5, 1000, 96), (17, 130, 1539), (70, 257, 300), (200, 64, 64)])
+def test_gemm_f32_is_true_float32_and_row_invariant(m, n, k):
+    torch.manual_seed(m * n)
+    a = torch.randn(m, k, device=DEV)
+    w = torch.randn(n, k, device=DEV)
+    bias = torch.randn(n, device=DEV)
+    out = torch.empty(m, n, device=DEV)
+    ops().gemm_f32_nt(a, w, bias, out)
+    want = a.double() @ w.double().t() + bias.double()
+    # float32 accumulation over k terms: error of a few units in the last place of the sum of magnitudes
+    bound = (a.abs().double() @ w.abs().double().t()) * (k * 2.0 ** -24) + 1e-6
+    assert bool(((out.double() - want).abs() <= bound).all())
+    # a reduced-precision product (TF32/bfloat16) would be off by about 2^-11 of the magnitudes
+    assert float((out.double() - want).abs().max()) < 2.0 ** -15 * float((a.abs().double() @ w.abs().double().t()).max())
+    # one row alone gives the same bits as that row inside the batch
+    row = m // 2
+    alone = torch.empty(1, n, device=DEV)
+    ops().gemm_f32_nt(a[row:row + 1].contiguous(), w, bias, alone)
+    assert torch.equal(alone[0], out[row])
+    no_bias = torch.empty(m, n, device=DEV)
+    ops().gemm_f32_nt(a, w, None, no_bias)
+    assert rel_err(no_bias, a.double() @ w.double().t()) < 1e-5
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("head_dim, n_q, n_kv, page, pairing", [(16, 4, 2, 16, "interleaved"), (48, 10, 2, 8, "half"),
+                                                             (128, 12, 2, 16, "interleaved"), (256, 3, 1, 4, "half")])
+def test_rope_bias_and_cache_write(dtype, head_dim, n_q, n_kv, page, pairing):
+    torch.manual_seed(head_dim)
+    tokens, pages = 9, 40
+    theta = 1e6
+    width = (n_q + 2 * n_kv) * head_dim
+    qkv = torch.randn(tokens, width, device=DEV).to(dtype)
+    bias = torch.randn(width, device=DEV) * 0.1
+    positions = torch.tensor([0, 1, 2, 15, 16, 17, 4095, 30000, 131071], dtype=torch.int32, device=DEV)
+    slots = torch.tensor([5, 17, 0, page * pages - 1, 33, 64, 7, -1, 100], dtype=torch.int32, device=DEV)
+    inv_freq = qwen2_plain.rope_inverse_frequencies(head_dim, theta).to(DEV)
+    q_out = torch.zeros(tokens, n_q, head_dim, device=DEV, dtype=dtype)
+    k_cache = torch.zeros(pages, n_kv, page, head_dim, device=DEV, dtype=dtype)
+    v_cache = torch.zeros_like(k_cache)
+    ops().rope_kv_write(qkv, bias, positions, slots, inv_freq, q_out, k_cache, v_cache, n_q, n_kv, head_dim,
+                        0 if pairing == "interleaved" else 1)
+    x = (qkv.float() + bias).cpu()
+    q, k, v = x.split([n_q * head_dim, n_kv * head_dim, n_kv * head_dim], dim=1)
+    want_q = qwen2_plain.rope(q.view(tokens, n_q, head_dim), positions.cpu(), theta, pairing)
+    want_k = qwen2_plain.rope(k.view(tokens, n_kv, head_dim), positions.cpu(), theta, pairing)
+    want_v = v.view(tokens, n_kv, head_dim)
+    tol = 3e-5 if dtype == torch.float32 else 2.0 ** -7   # float32: sin/cos of angles up to 1e5 rad
+    assert float((q_out.float().cpu() - want_q).abs().max()) < tol * float(want_q.abs().max())
+    written = torch.zeros_like(k_cache, dtype=torch.bool)
+    for t in range(tokens):
+        slot = int(slots[t])
+        if slot < 0:
+            continue
+        p, off = divmod(slot, page)
+        assert float((k_cache[p, :, off].float().cpu() - want_k[t]).abs().max()) < tol * float(want_k.abs().max())
+        assert float((v_cache[p, :, off].float().cpu() - want_v[t]).abs().max()) < tol * float(want_v.abs().max())
+        written[p, :, off] = True
+    assert float(k_cache[~written].abs().sum()) == 0 and float(v_cache[~written].abs().sum()) == 0  # nothing else touched
+    # no bias
+    q2 = torch.zeros_like(q_out)
+    ops().rope_kv_write(qkv, None, positions, slots, inv_freq, q2, k_cache, v_cache, n_q, n_kv, head_dim,
+                        0 if pairing == "interleaved" else 1)
+    want_q2 = qwen2_plain.rope(qkv.float().cpu()[:, :n_q * head_dim].reshape(tokens, n_q, head_dim), positions.cpu(), theta, pairing)
+    assert float((q2.float().cpu() - want_q2).abs().max()) < tol * float(want_q2.abs().max())
+
+
+def dense_attention(q, k, v, scale, window=0):
+    """q [Hq, D] at the last position of k, v [ctx, Hkv, D]; float64."""
+    n_q, n_kv = q.shape[0], k.shape[1]
+    ctx = k.shape[0]
+    out = torch.empty_like(q, dtype=torch.float64)
+    first = max(0, ctx - window) if window > 0 else 0
+    for head in range(n_q):
+        g = head // (n_q // n_kv)
+        scores = (k[first:, g].double() @ q[head].double()) * scale
+        out[head] = torch.softmax(scores, 0) @ v[first:, g].double()
+    return out
+
+
+def paged_setup(rng, contexts, n_kv, head_dim, page, dtype, extra_pages=5):
+    """Random keys/values of each request scattered over randomly permuted physical pages."""
+    need = sum(-(-c // page) for c in contexts)
+    pages = need + extra_pages
+    order = list(range(pages))
+    rng.shuffle(order)
+    k_cache = torch.randn(pages, n_kv, page, head_dim, device=DEV).to(dtype)   # unused pages hold noise
+    v_cache = torch.randn(pages, n_kv, page, head_dim, device=DEV).to(dtype)
+    width = max(-(-c // page) for c in contexts)
+    tables = torch.full((len(contexts), width), -1, dtype=torch.int32)
+    dense = []
+    for s, ctx in enumerate(contexts):
+        k = torch.randn(ctx, n_kv, head_dim, device=DEV).to(dtype)
+        v = torch.randn(ctx, n_kv, head_dim, device=DEV).to(dtype)
+        for logical in range(-(-ctx // page)):
+            physical = order.pop()
+            tables[s, logical] = physical
+            lo, hi = logical * page, min(ctx, (logical + 1) * page)
+            k_cache[physical, :, :hi - lo] = k[lo:hi].transpose(0, 1)
+            v_cache[physical, :, :hi - lo] = v[lo:hi].transpose(0, 1)
+        dense.append((k, v))
+    return k_cache, v_cache, tables.to(DEV), dense
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("head_dim, n_q, n_kv, page", [(16, 4, 2, 16), (32, 3, 1, 8), (64, 14, 2, 1), (128, 12, 2, 16),
+                                                       (128, 28, 4, 64), (256, 5, 5, 16), (80, 18, 2, 32)])
+def test_paged_attention_generic(dtype, head_dim, n_q, n_kv, page):
+    rng = random.Random(head_dim * n_q)
+    torch.manual_seed(head_dim + n_q)
+    contexts = [1, 15, 16, 17, 31, 32, 33, 65, 200, 513]
+    k_cache, v_cache, tables, dense = paged_setup(rng, contexts, n_kv, head_dim, page, dtype)
+    # rows: for each request its last position, and for the long ones also earlier positions (a prompt portion)
+    rows = []
+    for s, ctx in enumerate(contexts):
+        for pos in sorted({ctx - 1, max(0, ctx - 2), ctx // 2, 0}):
+            rows.append((s, pos))
+    q = torch.randn(len(rows), n_q, head_dim, device=DEV).to(dtype)
+    segs = torch.tensor([s for s, _ in rows], dtype=torch.int32, device=DEV)
+    positions = torch.tensor([p for _, p in rows], dtype=torch.int32, device=DEV)
+    out = torch.empty_like(q)
+    scale = 1.0 / math.sqrt(head_dim)
+    ops().paged_attention_generic(q, k_cache, v_cache, out, tables, segs, positions, scale)
+    for r, (s, pos) in enumerate(rows):
+        k, v = dense[s]
+        want = dense_attention(q[r], k[:pos + 1], v[:pos + 1], scale)
+        err = float((out[r].double() - want).abs().max())
+        assert err < (1e-5 if dtype == torch.float32 else 2.0 ** -7) * max(1.0, float(want.abs().max())), (r, s, pos, err)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("needle", [0, 15, 16, 17, 255, 256, 700, 1023, 1024, 1499])
+def test_one_far_key_among_hundreds_is_found(dtype, needle):
+    """Random keys would hide a key that is skipped or read from the wrong page: here one
+    key is made to match the query so that it takes nearly all the weight."""
+    rng = random.Random(needle)
+    torch.manual_seed(needle)
+    n_q, n_kv, head_dim, page, ctx = 6, 2, 64, 16, 1500
+    k_cache, v_cache, tables, dense = paged_setup(rng, [ctx], n_kv, head_dim, page, dtype)
+    q = torch.randn(1, n_q, head_dim, device=DEV).to(dtype)
+    k, v = dense[0]
+    for g in range(n_kv):   # key `needle` of group g points along that group's first query head
+        k[needle, g] = (q[0, g * 3].float() * 6).to(dtype)
+        physical, off = int(tables[0, needle // page]), needle % page
+        k_cache[physical, g, off] = k[needle, g]
+    out = torch.empty_like(q)
+    segs = torch.zeros(1, dtype=torch.int32, device=DEV)
+    positions = torch.tensor([ctx - 1], dtype=torch.int32, device=DEV)
+    ops().paged_attention_generic(q, k_cache, v_cache, out, tables, segs, positions, 1.0 / math.sqrt(head_dim))
+    want = dense_attention(q[0], k, v, 1.0 / math.sqrt(head_dim))
+    assert float((out[0].double() - want).abs().max()) < (1e-5 if dtype == torch.float32 else 2.0 ** -6)
+    for g in range(n_kv):   # and the answer is that key's value
+        assert float((out[0, g * 3].double() - v[needle, g].double()).abs().max()) < 0.05
+
+
+@pytest.mark.parametrize("window", [1, 5, 16, 33, 100])
+def test_window_edge(window):
+    rng = random.Random(window)
+    torch.manual_seed(window)
+    n_q, n_kv, head_dim, page, ctx = 4, 2, 32, 8, 120
+    k_cache, v_cache, tables, dense = paged_setup(rng, [ctx], n_kv, head_dim, page, torch.float32)
+    k, v = dense[0]
+    rows = [3, window - 1, window, window + 1, 64, ctx - 1]
+    rows = sorted({min(max(r, 0), ctx - 1) for r in rows})
+    q = torch.randn(len(rows), n_q, head_dim, device=DEV)
+    # the key just outside the window is made to match the query: it must NOT be read
+    for r, pos in enumerate(rows):
+        outside = pos - window
+        if outside >= 0 and all(outside != p - window for p in rows[:r]):
+            k[outside, :] = q[r, 0] * 8
+            k_cache[int(tables[0, outside // page]), :, outside % page] = k[outside]
+    out = torch.empty_like(q)
+    segs = torch.zeros(len(rows), dtype=torch.int32, device=DEV)
+    positions = torch.tensor(rows, dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(head_dim)
+    ops().paged_attention_generic(q, k_cache, v_cache, out, tables, segs, positions, scale, window=window)
+    for r, pos in enumerate(rows):
+        want = dense_attention(q[r], k[:pos + 1], v[:pos + 1], scale, window=window)
+        assert float((out[r].double() - want).abs().max()) < 1e-5, (window, pos)
+
+
+def test_attention_refuses_sizes_it_cannot_run():
+    from llm_serving_engine_b200.kernels.library import KernelError
+    q = torch.zeros(1, 2, 24, device=DEV)
+    cache = torch.zeros(2, 1, 16, 24, device=DEV)
+    with pytest.raises(KernelError, match="head size"):
+        ops().paged_attention_generic(q, cache, cache, torch.empty_like(q), torch.zeros(1, 1, dtype=torch.int32, device=DEV),
+                                      torch.zeros(1, dtype=torch.int32, device=DEV),
+                                      torch.zeros(1, dtype=torch.int32, device=DEV), 1.0)
+    with pytest.raises(KernelError, match="CUDA tensors only"):
+        ops().silu_mul(torch.zeros(2, 4), torch.zeros(2, 2))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_silu_mul(dtype):
+    gate_up = (torch.randn(13, 2 * 177, device=DEV) * 3).to(dtype)
+    out = torch.empty(13, 177, device=DEV, dtype=dtype)
+    ops().silu_mul(gate_up, out)
+    g, u = gate_up.double()[:, :177], gate_up.double()[:, 177:]
+    assert rel_err(out, torch.nn.functional.silu(g) * u) < TOL[dtype] * 2
+
+
+@pytest.mark.parametrize("vocab", [7, 1000, 151936])
+def test_argmax_takes_the_first_largest(vocab):
+    torch.manual_seed(vocab)
+    logits = torch.randn(5, vocab, device=DEV)
+    logits[1, vocab // 2] = 50.0
+    logits[2, vocab - 1] = 50.0
+    logits[3, 3] = 50.0
+    logits[3, vocab - 2] = 50.0     # a tie: the first wins
+    logits[4] = -3.0                # all equal
+    out = torch.empty(5, dtype=torch.int32, device=DEV)
+    ops().argmax(logits, out)
+    assert out.tolist() == [int(logits[0].argmax()), vocab // 2, vocab - 1, 3, 0]
+
+
+def plain_sample(logits, temperature, top_p, u):
+    """Float64 restatement of the sampler: returns (token, distance of u*mass to the nearest boundary)."""
+    z = logits.double() / temperature
+    e = torch.exp(z - z.max())
+    keep = torch.ones_like(e, dtype=torch.bool)
+    if top_p < 1.0:
+        order = torch.argsort(e, descending=True, stable=True)
+        before = torch.cumsum(e[order], 0) - e[order]
+        kept_sorted = before < top_p * e.sum()
+        threshold = e[order][kept_sorted].min()
+        keep = e >= threshold
+    kept = torch.where(keep, e, torch.zeros_like(e))
+    cdf = torch.cumsum(kept, 0)
+    target = u * cdf[-1]
+    token = int(torch.searchsorted(cdf, target, right=True).clamp_max(len(e) - 1))
+    gap = float((cdf - target).abs().min() / cdf[-1])
+    return token, gap
+
+
+@pytest.mark.parametrize("vocab", [50, 1000, 151936])
+def test_sampling_is_the_inverse_cdf_of_the_softmax(vocab):
+    from llm_serving_engine_b200.sampling import uniform01
+    torch.manual_seed(vocab)
+    rows = 24
+    logits = torch.randn(rows, vocab, device=DEV) * 2
+    temperature = torch.tensor([0.8, 1.0, 0.3, 1.7] * 6, device=DEV)
+    top_p = torch.tensor([1.0] * 12 + [0.9, 0.5, 0.8, 0.3] * 3, device=DEV)
+    seed = torch.arange(rows, dtype=torch.int64, device=DEV) * 7919 + 3
+    counter = torch.arange(rows, dtype=torch.int64, device=DEV) % 5
+    scratch = torch.empty(rows * vocab, device=DEV)
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    ops().sample(logits, temperature, top_p, seed, counter, scratch, out)
+    for r in range(rows):
+        u = uniform01(int(seed[r]), int(counter[r]))
+        token, gap = plain_sample(logits[r].cpu(), float(temperature[r]), float(top_p[r]), u)
+        assert int(out[r]) == token or gap < 1e-5, (r, int(out[r]), token, gap)
+    # greedy rows inside a sampled batch take the argmax
+    temperature[3] = 0.0
+    ops().sample(logits, temperature, top_p, seed, counter, scratch, out)
+    assert int(out[3]) == int(logits[3].argmax())
+
+
+def test_sampling_follows_the_distribution():
+    from llm_serving_engine_b200.sampling import uniform01
+    vocab, draws = 11, 4000
+    logits = torch.tensor([0.0, 1.0, 2.0, -1.0, 0.5, 3.0, -2.0, 1.5, 0.2, 2.5, -0.5], device=DEV).repeat(draws, 1)
+    temperature = torch.full((draws,), 1.3, device=DEV)
+    top_p = torch.ones(draws, device=DEV)
+    seed = torch.full((draws,), 12345, dtype=torch.int64, device=DEV)
+    counter = torch.arange(draws, dtype=torch.int64, device=DEV)
+    out = torch.empty(draws, dtype=torch.int32, device=DEV)
+    ops().sample(logits, temperature, top_p, seed, counter, torch.empty(draws * vocab, device=DEV), out)
+    counts = torch.bincount(out.long().cpu(), minlength=vocab).double()
+    probabilities = torch.softmax(logits[0].double().cpu() / 1.3, 0)
+    chi2 = float(((counts - draws * probabilities) ** 2 / (draws * probabilities)).sum())
+    assert chi2 < 40.0, chi2          # 10 degrees of freedom: 40 is far in the tail
+    numbers = [uniform01(12345, c) for c in range(2000)]
+    assert 0.47 < sum(numbers) / len(numbers) < 0.53 and min(numbers) >= 0.0 and max(numbers) < 1.0

@@ -80,3 +80,33 @@ def test_float32_is_bitwise_the_same_however_it_is_cut():
     for rid in requests:
         assert torch.equal(whole[rid], portions[rid]), f"{rid}: portions differ from whole"
         assert torch.equal(whole[rid], mixed[rid]), f"{rid}: mixed differs from whole"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_long_decoding(name, dtype):
+    """A short prompt, then hundreds of tokens one by one, across many pages."""
+    config, page, _ = ALL[name]
+    rng = random.Random(21)
+    tokens = helpers.random_tokens(rng, config["vocab_size"], 8 + 400)
+    requests = {"long": tokens}
+    steps = helpers.trace_tail_decode(requests, tail=400)
+    got = helpers.run_trace(name, dtype, steps, helpers.max_tokens_for(requests), page)
+    helpers.assert_close(name, dtype, requests, got, "long decoding")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", sorted(ALL))
+def test_first_tokens_of_a_sequence(name, dtype):
+    """Positions 0, 1, 2, ... each in a step of its own, and prompts of one and two tokens."""
+    config, page, _ = ALL[name]
+    rng = random.Random(22)
+    requests = {"one": helpers.random_tokens(rng, config["vocab_size"], 1),
+                "two": helpers.random_tokens(rng, config["vocab_size"], 2),
+                "steps": helpers.random_tokens(rng, config["vocab_size"], 6)}
+    steps = helpers.trace_whole({"one": requests["one"], "two": requests["two"]})
+    for index, token in enumerate(requests["steps"]):
+        steps.append({"step": len(steps), "entries": [{"id": "steps", "tokens": [token], "want": [0]}],
+                      "end": ["steps"] if index == 5 else []})
+    got = helpers.run_trace(name, dtype, steps, 64, page)
+    helpers.assert_close(name, dtype, requests, got, "first tokens")
