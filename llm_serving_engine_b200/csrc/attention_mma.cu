@@ -1,0 +1,541 @@
+// Paged attention on the tensor cores for bfloat16, head sizes 64 and 128.
+//
+// Two kernels share the fragment code:
+//   * attn_decode_kernel: every row of the step is a single decoded token.  One
+//     block = (row, kv head, split of the keys); its 4 warps walk different 16-key
+//     tiles (cp.async pipeline per warp), merge in shared memory and write either
+//     the result or an unnormalised partial (split-KV), which attn_combine_kernel
+//     reduces in a fixed order.
+//   * attn_prefill_kernel: portions of prompts (any mix of segment lengths).  One
+//     block = (tile of consecutive rows of one request, kv head); the 64 rows of its
+//     score matrix are (row, query head of the group) pairs, so the keys and values
+//     of a kv head are loaded once for all its query heads; keys are walked in tiles
+//     of 64 with a two-stage cp.async pipeline; causal inside the portion, all of
+//     the earlier context before it.
+// Scores, softmax and the output accumulation are float32 (mma.sync m16n8k16 with
+// float32 accumulators; probabilities are rounded to bfloat16 for the second
+// product).  Formulas as in attention_generic.cu (reference
+// src/llmserve/model.py:143-176).  Cache layout: [page][kv head][offset][D].
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool pred) {
+  const int bytes = pred ? 16 : 0;  // 0: nothing is read, the 16 bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+// Byte offset of 16-byte chunk `c` of row `r` in a [rows][D] bfloat16 tile whose
+// chunks are XOR-swizzled by the row, so that ldmatrix reads are conflict-free.
+template <int D> __device__ __forceinline__ uint32_t tile_off(int r, int c) {
+  return (uint32_t)(r * (D * 2) + ((c ^ (r & 7)) << 4));
+}
+
+constexpr float LOG2E = 1.4426950408889634f;
+
+// ---------------------------------------------------------------------------------------------
+// decode: one query row per request
+// ---------------------------------------------------------------------------------------------
+constexpr int DEC_STAGES = 3;
+constexpr int DEC_TILE = 16;
+
+template <int D>
+__global__ void __launch_bounds__(128)
+attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kc,
+                   const __nv_bfloat16* __restrict__ vc, __nv_bfloat16* __restrict__ out,
+                   float* __restrict__ part_o, float* __restrict__ part_ml,
+                   const int* __restrict__ block_tables, int bt_stride,
+                   const int* __restrict__ segment_of_token, const int* __restrict__ positions,
+                   int n_q, int n_kv, int page_size, float scale_log2e, int num_splits) {
+  constexpr int CH = D / 8;                 // 16-byte chunks per row
+  constexpr int TILE_BYTES = DEC_TILE * D * 2;
+  extern __shared__ __align__(128) unsigned char smem[];
+  unsigned char* q_s = smem;                                   // [16][D] bf16
+  unsigned char* kv_s = smem + TILE_BYTES;                     // [warp][stage][K|V][16][D]
+  const int t = blockIdx.x;
+  const int group = n_q / n_kv;
+  const int gchunks = (group + 15) / 16;
+  const int kvh = blockIdx.y / gchunks;
+  const int g0 = (blockIdx.y % gchunks) * 16;
+  const int gcount = min(16, group - g0);
+  const int split = blockIdx.z;
+  const int seg = segment_of_token[t];
+  if (seg < 0) return;
+  const int ctx = positions[t] + 1;
+  const int* bt = block_tables + (size_t)seg * bt_stride;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int first_head = kvh * group + g0;
+
+  const int total_tiles = (ctx + DEC_TILE - 1) / DEC_TILE;
+  const int per_split = (total_tiles + num_splits - 1) / num_splits;
+  const int tile_lo = split * per_split;
+  const int tile_hi = min(total_tiles, tile_lo + per_split);
+
+  // queries of the group -> shared memory (rows beyond the group are zero)
+  for (int e = tid; e < 16 * CH; e += 128) {
+    const int r = e / CH, c = e % CH;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < gcount) v = *reinterpret_cast<const uint4*>(q + ((size_t)t * n_q + first_head + r) * D + c * 8);
+    *reinterpret_cast<uint4*>(q_s + tile_off<D>(r, c)) = v;
+  }
+  __syncthreads();
+  uint32_t qf[D / 16][4];
+  {
+    const int mi = lane >> 3, r = (lane & 7) + (mi & 1) * 8;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) ldmatrix_x4(qf[ks], smem_u32(q_s + tile_off<D>(r, ks * 2 + (mi >> 1))));
+  }
+
+  float acc[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+
+  unsigned char* my_s = kv_s + (size_t)warp * DEC_STAGES * 2 * TILE_BYTES;
+  auto load_tile = [&](int tile, int stage) {
+    unsigned char* ks_ = my_s + (size_t)stage * 2 * TILE_BYTES;
+    unsigned char* vs_ = ks_ + TILE_BYTES;
+#pragma unroll
+    for (int i = 0; i < DEC_TILE * CH / 32; ++i) {
+      const int idx = i * 32 + lane;
+      const int key = idx / CH, c = idx % CH;
+      const int j = tile * DEC_TILE + key;
+      const bool valid = j < ctx;
+      size_t off = 0;
+      if (valid) {
+        const int page = bt[j / page_size];
+        off = (((size_t)page * n_kv + kvh) * page_size + (j % page_size)) * D + c * 8;
+      }
+      cp_async16(smem_u32(ks_ + tile_off<D>(key, c)), kc + off, valid);
+      cp_async16(smem_u32(vs_ + tile_off<D>(key, c)), vc + off, valid);
+    }
+  };
+
+  // this warp's tiles: tile_lo + warp, + 4, ...
+  const int first = tile_lo + warp;
+  const int n_mine = first < tile_hi ? (tile_hi - first + 3) / 4 : 0;
+#pragma unroll
+  for (int s = 0; s < DEC_STAGES - 1; ++s) {
+    if (s < n_mine) load_tile(first + 4 * s, s);
+    cp_async_commit();
+  }
+  for (int it = 0; it < n_mine; ++it) {
+    const int pre = it + DEC_STAGES - 1;
+    if (pre < n_mine) load_tile(first + 4 * pre, pre % DEC_STAGES);
+    cp_async_commit();
+    cp_async_wait<DEC_STAGES - 1>();
+    __syncwarp();
+    const int tile = first + 4 * it;
+    unsigned char* ks_ = my_s + (size_t)(it % DEC_STAGES) * 2 * TILE_BYTES;
+    unsigned char* vs_ = ks_ + TILE_BYTES;
+
+    float s[2][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+    {
+      const int mi = lane >> 3, key = (lane & 7) + (mi >> 1) * 8;
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+        uint32_t b[4];
+        ldmatrix_x4(b, smem_u32(ks_ + tile_off<D>(key, ks * 2 + (mi & 1))));
+        mma_bf16(s[0], qf[ks], b[0], b[1]);
+        mma_bf16(s[1], qf[ks], b[2], b[3]);
+      }
+    }
+#pragma unroll
+    for (int nb = 0; nb < 2; ++nb)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int j = tile * DEC_TILE + nb * 8 + (lane & 3) * 2 + (e & 1);
+        s[nb][e] = j < ctx ? s[nb][e] * scale_log2e : -INFINITY;
+      }
+    float mx0 = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+    float mx1 = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+    const float c0 = exp2f(m0 - mn0), c1 = exp2f(m1 - mn1);
+    m0 = mn0; m1 = mn1;
+    float p[2][4];
+#pragma unroll
+    for (int nb = 0; nb < 2; ++nb) {
+      p[nb][0] = exp2f(s[nb][0] - mn0); p[nb][1] = exp2f(s[nb][1] - mn0);
+      p[nb][2] = exp2f(s[nb][2] - mn1); p[nb][3] = exp2f(s[nb][3] - mn1);
+    }
+    l0 = l0 * c0 + (p[0][0] + p[0][1]) + (p[1][0] + p[1][1]);
+    l1 = l1 * c1 + (p[0][2] + p[0][3]) + (p[1][2] + p[1][3]);
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) { acc[i][0] *= c0; acc[i][1] *= c0; acc[i][2] *= c1; acc[i][3] *= c1; }
+    uint32_t pa[4] = {pack_bf16(p[0][0], p[0][1]), pack_bf16(p[0][2], p[0][3]),
+                      pack_bf16(p[1][0], p[1][1]), pack_bf16(p[1][2], p[1][3])};
+    {
+      const int mi = lane >> 3, key = (lane & 7) + (mi & 1) * 8;
+#pragma unroll
+      for (int nbp = 0; nbp < D / 16; ++nbp) {
+        uint32_t b[4];
+        ldmatrix_x4_trans(b, smem_u32(vs_ + tile_off<D>(key, nbp * 2 + (mi >> 1))));
+        mma_bf16(acc[2 * nbp], pa, b[0], b[1]);
+        mma_bf16(acc[2 * nbp + 1], pa, b[2], b[3]);
+      }
+    }
+    __syncwarp();
+  }
+  cp_async_wait<0>();
+  // row sums over the 4 lanes that share a row
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  __syncthreads();  // every warp is done with its pipeline buffers: reuse them for the merge
+
+  float* mg_acc = reinterpret_cast<float*>(kv_s);                // [4][16][D]
+  float* mg_m = mg_acc + 4 * 16 * D;                             // [4][16]
+  float* mg_l = mg_m + 4 * 16;                                   // [4][16]
+  {
+    const int r0 = lane >> 2, r1 = r0 + 8;
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      const int d = i * 8 + (lane & 3) * 2;
+      float* a0 = mg_acc + ((size_t)warp * 16 + r0) * D + d;
+      float* a1 = mg_acc + ((size_t)warp * 16 + r1) * D + d;
+      a0[0] = acc[i][0]; a0[1] = acc[i][1]; a1[0] = acc[i][2]; a1[1] = acc[i][3];
+    }
+    if ((lane & 3) == 0) {
+      mg_m[warp * 16 + r0] = m0; mg_m[warp * 16 + r1] = m1;
+      mg_l[warp * 16 + r0] = l0; mg_l[warp * 16 + r1] = l1;
+    }
+  }
+  __syncthreads();
+  for (int e = tid; e < gcount * D; e += 128) {
+    const int g = e / D, d = e % D;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, mg_m[w * 16 + g]);
+    float L = 0.f, O = 0.f;
+    if (M > -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float wgt = exp2f(mg_m[w * 16 + g] - M);
+        L += mg_l[w * 16 + g] * wgt;
+        O += mg_acc[((size_t)w * 16 + g) * D + d] * wgt;
+      }
+    }
+    const int head = first_head + g;
+    if (num_splits == 1) {
+      out[((size_t)t * n_q + head) * D + d] = __float2bfloat16_rn(O / L);
+    } else {
+      const size_t pidx = ((size_t)t * n_q + head) * num_splits + split;
+      part_o[pidx * D + d] = O;
+      if (d == 0) { part_ml[pidx * 2] = M; part_ml[pidx * 2 + 1] = L; }
+    }
+  }
+}
+
+// out = sum_s part_o[s] 2^(m_s - M) / sum_s l_s 2^(m_s - M), splits in index order
+template <int D>
+__global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                    __nv_bfloat16* __restrict__ out, const int* __restrict__ segment_of_token,
+                                    int n_q, int num_splits) {
+  const int t = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
+  if (segment_of_token[t] < 0) return;
+  const size_t base = ((size_t)t * n_q + head) * num_splits;
+  float M = -INFINITY;
+  for (int s = 0; s < num_splits; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
+  float L = 0.f, O = 0.f;
+  for (int s = 0; s < num_splits; ++s) {
+    const float m = part_ml[(base + s) * 2];
+    if (m == -INFINITY) continue;
+    const float w = exp2f(m - M);
+    L += part_ml[(base + s) * 2 + 1] * w;
+    O += part_o[(base + s) * D + d] * w;
+  }
+  out[((size_t)t * n_q + head) * D + d] = __float2bfloat16_rn(O / L);
+}
+
+// ---------------------------------------------------------------------------------------------
+// prefill: tiles of consecutive rows of one request
+// ---------------------------------------------------------------------------------------------
+constexpr int PF_BM = 64;   // (row, head-of-group) pairs per block
+constexpr int PF_BN = 64;   // keys per tile
+
+template <int D>
+__global__ void __launch_bounds__(128)
+attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kc,
+                    const __nv_bfloat16* __restrict__ vc, __nv_bfloat16* __restrict__ out,
+                    const int* __restrict__ block_tables, int bt_stride,
+                    const int* __restrict__ segment_start, const int* __restrict__ segment_first_pos,
+                    int num_segments, int n_q, int n_kv, int page_size, float scale_log2e,
+                    int rows_per_tile) {
+  constexpr int CH = D / 8;
+  constexpr int TILE_BYTES = PF_BN * D * 2;
+  extern __shared__ __align__(128) unsigned char smem[];
+  unsigned char* q_s = smem;                       // [64][D]
+  unsigned char* kv_s = smem + PF_BM * D * 2;      // [2 stages][K|V][64][D]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int kvh = blockIdx.y;
+  const int group = n_q / n_kv;
+
+  // which tile of which request is this block's (blocks beyond the last tile leave)
+  int seg = -1, r0 = 0, cnt = 0;
+  {
+    int before = 0;
+    const int tile = gridDim.x - 1 - blockIdx.x;   // late tiles (longest walks) are launched first
+    for (int s = 0; s < num_segments; ++s) {
+      const int c = segment_start[s + 1] - segment_start[s];
+      const int nt = (c + rows_per_tile - 1) / rows_per_tile;
+      if (tile < before + nt) { seg = s; r0 = (tile - before) * rows_per_tile; cnt = c; break; }
+      before += nt;
+    }
+  }
+  if (seg < 0) return;
+  const int nrows = min(rows_per_tile, cnt - r0);
+  const int row_base = segment_start[seg] + r0;
+  const int pos0 = segment_first_pos[seg] + r0;
+  const int last_pos = pos0 + nrows - 1;
+  const int n_tiles = (last_pos + PF_BN) / PF_BN;
+  const int* bt = block_tables + (size_t)seg * bt_stride;
+
+  for (int e = tid; e < PF_BM * CH; e += 128) {
+    const int m = e / CH, c = e % CH;
+    const int rl = m / group, g = m % group;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (rl < nrows) v = *reinterpret_cast<const uint4*>(q + ((size_t)(row_base + rl) * n_q + kvh * group + g) * D + c * 8);
+    *reinterpret_cast<uint4*>(q_s + tile_off<D>(m, c)) = v;
+  }
+
+  auto load_tile = [&](int kt, int stage) {
+    unsigned char* ks_ = kv_s + (size_t)stage * 2 * TILE_BYTES;
+    unsigned char* vs_ = ks_ + TILE_BYTES;
+#pragma unroll
+    for (int i = 0; i < PF_BN * CH / 128; ++i) {
+      const int idx = i * 128 + tid;
+      const int key = idx / CH, c = idx % CH;
+      const int j = kt * PF_BN + key;
+      const bool valid = j <= last_pos;
+      size_t off = 0;
+      if (valid) {
+        const int page = bt[j / page_size];
+        off = (((size_t)page * n_kv + kvh) * page_size + (j % page_size)) * D + c * 8;
+      }
+      cp_async16(smem_u32(ks_ + tile_off<D>(key, c)), kc + off, valid);
+      cp_async16(smem_u32(vs_ + tile_off<D>(key, c)), vc + off, valid);
+    }
+  };
+  load_tile(0, 0);
+  cp_async_commit();
+  __syncthreads();   // q_s is filled
+
+  uint32_t qf[D / 16][4];
+  {
+    const int mi = lane >> 3, r = warp * 16 + (lane & 7) + (mi & 1) * 8;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) ldmatrix_x4(qf[ks], smem_u32(q_s + tile_off<D>(r, ks * 2 + (mi >> 1))));
+  }
+  // key limit of this thread's two rows
+  const int ma = warp * 16 + (lane >> 2), mb = ma + 8;
+  const int pos_a = pos0 + min(ma / group, nrows - 1), pos_b = pos0 + min(mb / group, nrows - 1);
+
+  float acc[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+
+  for (int kt = 0; kt < n_tiles; ++kt) {
+    if (kt + 1 < n_tiles) load_tile(kt + 1, (kt + 1) & 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    unsigned char* ks_ = kv_s + (size_t)(kt & 1) * 2 * TILE_BYTES;
+    unsigned char* vs_ = ks_ + TILE_BYTES;
+
+    float s[PF_BN / 8][4];
+#pragma unroll
+    for (int i = 0; i < PF_BN / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+    {
+      const int mi = lane >> 3, key = (lane & 7) + (mi >> 1) * 8;
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+#pragma unroll
+        for (int nbp = 0; nbp < PF_BN / 16; ++nbp) {
+          uint32_t b[4];
+          ldmatrix_x4(b, smem_u32(ks_ + tile_off<D>(nbp * 16 + key, ks * 2 + (mi & 1))));
+          mma_bf16(s[2 * nbp], qf[ks], b[0], b[1]);
+          mma_bf16(s[2 * nbp + 1], qf[ks], b[2], b[3]);
+        }
+      }
+    }
+    const bool diagonal = (kt + 1) * PF_BN - 1 > pos0;   // some row of the tile ends inside these keys
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int nb = 0; nb < PF_BN / 8; ++nb) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float v = s[nb][e] * scale_log2e;
+        if (diagonal) {
+          const int j = kt * PF_BN + nb * 8 + (lane & 3) * 2 + (e & 1);
+          if (j > ((e >> 1) ? pos_b : pos_a)) v = -INFINITY;
+        }
+        s[nb][e] = v;
+      }
+      mx0 = fmaxf(mx0, fmaxf(s[nb][0], s[nb][1]));
+      mx1 = fmaxf(mx1, fmaxf(s[nb][2], s[nb][3]));
+    }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);   // finite from the first tile on: key 0 is read by every row
+    const float c0 = exp2f(m0 - mn0), c1 = exp2f(m1 - mn1);
+    m0 = mn0; m1 = mn1;
+    float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+    for (int nb = 0; nb < PF_BN / 8; ++nb) {
+      s[nb][0] = exp2f(s[nb][0] - mn0); s[nb][1] = exp2f(s[nb][1] - mn0);
+      s[nb][2] = exp2f(s[nb][2] - mn1); s[nb][3] = exp2f(s[nb][3] - mn1);
+      sum0 += s[nb][0] + s[nb][1];
+      sum1 += s[nb][2] + s[nb][3];
+    }
+    l0 = l0 * c0 + sum0;
+    l1 = l1 * c1 + sum1;
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) { acc[i][0] *= c0; acc[i][1] *= c0; acc[i][2] *= c1; acc[i][3] *= c1; }
+    {
+      const int mi = lane >> 3, key = (lane & 7) + (mi & 1) * 8;
+#pragma unroll
+      for (int kk = 0; kk < PF_BN / 16; ++kk) {
+        uint32_t pa[4] = {pack_bf16(s[2 * kk][0], s[2 * kk][1]), pack_bf16(s[2 * kk][2], s[2 * kk][3]),
+                          pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]), pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3])};
+#pragma unroll
+        for (int nbp = 0; nbp < D / 16; ++nbp) {
+          uint32_t b[4];
+          ldmatrix_x4_trans(b, smem_u32(vs_ + tile_off<D>(kk * 16 + key, nbp * 2 + (mi >> 1))));
+          mma_bf16(acc[2 * nbp], pa, b[0], b[1]);
+          mma_bf16(acc[2 * nbp + 1], pa, b[2], b[3]);
+        }
+      }
+    }
+    __syncthreads();   // the stage is free for the load after next
+  }
+  cp_async_wait<0>();
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  const float inv0 = 1.0f / l0, inv1 = 1.0f / l1;
+  const int rla = ma / group, ga = ma % group, rlb = mb / group, gb = mb % group;
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) {
+    const int d = i * 8 + (lane & 3) * 2;
+    if (rla < nrows)
+      *reinterpret_cast<__nv_bfloat162*>(out + ((size_t)(row_base + rla) * n_q + kvh * group + ga) * D + d) =
+          __floats2bfloat162_rn(acc[i][0] * inv0, acc[i][1] * inv0);
+    if (rlb < nrows)
+      *reinterpret_cast<__nv_bfloat162*>(out + ((size_t)(row_base + rlb) * n_q + kvh * group + gb) * D + d) =
+          __floats2bfloat162_rn(acc[i][2] * inv1, acc[i][3] * inv1);
+  }
+}
+
+template <int D> size_t decode_smem() { return (size_t)DEC_TILE * D * 2 * (1 + 4 * DEC_STAGES * 2); }
+template <int D> size_t prefill_smem() { return (size_t)PF_BM * D * 2 + (size_t)2 * 2 * PF_BN * D * 2; }
+
+template <int D>
+int launch_decode(const void* q, const void* kc, const void* vc, void* out, float* part_o, float* part_ml,
+                  const int* block_tables, int bt_stride, const int* seg, const int* positions, int tokens,
+                  int n_q, int n_kv, int page_size, float scale, int num_splits, cudaStream_t stream) {
+  const size_t smem = decode_smem<D>();
+  cudaError_t err = cudaFuncSetAttribute(attn_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (err != cudaSuccess) return (int)err;
+  const int group = n_q / n_kv;
+  dim3 grid(tokens, n_kv * ((group + 15) / 16), num_splits);
+  attn_decode_kernel<D><<<grid, 128, smem, stream>>>(
+      (const __nv_bfloat16*)q, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, (__nv_bfloat16*)out, part_o,
+      part_ml, block_tables, bt_stride, seg, positions, n_q, n_kv, page_size, scale * LOG2E, num_splits);
+  if (num_splits > 1) {
+    dim3 cgrid(tokens, n_q);
+    attn_combine_kernel<D><<<cgrid, D, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, seg, n_q, num_splits);
+  }
+  return (int)cudaGetLastError();
+}
+
+template <int D>
+int launch_prefill(const void* q, const void* kc, const void* vc, void* out, const int* block_tables,
+                   int bt_stride, const int* segment_start, const int* segment_first_pos, int num_segments,
+                   int tokens, int n_q, int n_kv, int page_size, float scale, cudaStream_t stream) {
+  const size_t smem = prefill_smem<D>();
+  cudaError_t err = cudaFuncSetAttribute(attn_prefill_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (err != cudaSuccess) return (int)err;
+  const int group = n_q / n_kv;
+  const int rows_per_tile = PF_BM / group;
+  const int tiles = (tokens + rows_per_tile - 1) / rows_per_tile + num_segments;   // upper bound
+  dim3 grid(tiles, n_kv);
+  attn_prefill_kernel<D><<<grid, 128, smem, stream>>>(
+      (const __nv_bfloat16*)q, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, (__nv_bfloat16*)out,
+      block_tables, bt_stride, segment_start, segment_first_pos, num_segments, n_q, n_kv, page_size,
+      scale * LOG2E, rows_per_tile);
+  return (int)cudaGetLastError();
+}
+}  // namespace
+
+// Whether the tensor-core kernels take this shape (else the caller uses the general kernel).
+extern "C" int lse_attention_mma_supported(int head_dim, int n_q, int n_kv) {
+  if (head_dim != 64 && head_dim != 128) return 0;
+  if (n_kv <= 0 || n_q % n_kv) return 0;
+  return (n_q / n_kv) <= PF_BM ? 1 : 0;
+}
+
+// Scratch floats that a decode launch with `num_splits` > 1 needs (outputs, then max/sum pairs).
+extern "C" long long lse_attention_decode_scratch_floats(int tokens, int n_q, int head_dim, int num_splits) {
+  return (long long)tokens * n_q * num_splits * (head_dim + 2);
+}
+
+extern "C" int lse_paged_attention_decode(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                          float* scratch, const int* block_tables, int bt_stride,
+                                          const int* segment_of_token, const int* positions, int tokens,
+                                          int n_q, int n_kv, int head_dim, int page_size, float scale,
+                                          int num_splits, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (!lse_attention_mma_supported(head_dim, n_q, n_kv) || page_size <= 0 || num_splits < 1) return LSE_ERR_BAD_ARGUMENT;
+  if (num_splits > 1 && scratch == nullptr) return LSE_ERR_BAD_ARGUMENT;
+  float* part_o = scratch;
+  float* part_ml = scratch ? scratch + (size_t)tokens * n_q * num_splits * head_dim : nullptr;
+  if (head_dim == 128)
+    return launch_decode<128>(q, k_cache, v_cache, out, part_o, part_ml, block_tables, bt_stride, segment_of_token,
+                              positions, tokens, n_q, n_kv, page_size, scale, num_splits, stream);
+  return launch_decode<64>(q, k_cache, v_cache, out, part_o, part_ml, block_tables, bt_stride, segment_of_token,
+                           positions, tokens, n_q, n_kv, page_size, scale, num_splits, stream);
+}
+
+extern "C" int lse_paged_attention_prefill(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                           const int* block_tables, int bt_stride, const int* segment_start,
+                                           const int* segment_first_pos, int num_segments, int tokens, int n_q,
+                                           int n_kv, int head_dim, int page_size, float scale,
+                                           cudaStream_t stream) {
+  if (tokens <= 0 || num_segments <= 0) return 0;
+  if (!lse_attention_mma_supported(head_dim, n_q, n_kv) || page_size <= 0) return LSE_ERR_BAD_ARGUMENT;
+  if (head_dim == 128)
+    return launch_prefill<128>(q, k_cache, v_cache, out, block_tables, bt_stride, segment_start, segment_first_pos,
+                               num_segments, tokens, n_q, n_kv, page_size, scale, stream);
+  return launch_prefill<64>(q, k_cache, v_cache, out, block_tables, bt_stride, segment_start, segment_first_pos,
+                            num_segments, tokens, n_q, n_kv, page_size, scale, stream);
+}

@@ -58,7 +58,8 @@ class StepContext:
         self.segment_state_slot: torch.Tensor = None  # [S]
         self.want_rows: torch.Tensor = None          # [W]
         self.max_segment_tokens = 0
-        self.max_context = 0
+        self.max_context = 0                         # None: not known on the host (a replayed graph)
+        self.decode_only = False                     # every segment brings exactly one token
 
 
 def _round4(n: int) -> int:
@@ -178,6 +179,7 @@ class StepRunner:
             step.max_context = max(step.max_context, first + count)
             row += count
         host[r_start[0] + n_seg] = row
+        step.decode_only = step.max_segment_tokens == 1
 
         self._device[:cursor].copy_(self._host[:cursor], non_blocking=True)
         self.last_h2d_bytes = cursor * 4

@@ -24,6 +24,11 @@ _SIGNATURES = {
     "lse_paged_attention_generic": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
                                     c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
                                     c_int, c_void_p],
+    "lse_paged_attention_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                   c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+    "lse_paged_attention_prefill": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                    c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
+    "lse_attention_mma_supported": [c_int, c_int, c_int],
     "lse_argmax": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p],
     "lse_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                    c_void_p, c_void_p, c_void_p],

@@ -144,6 +144,70 @@ def paged_attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
     return out
 
 
+def attention_mma_supported(head_dim: int, n_q: int, n_kv: int, dtype: torch.dtype, window: int = 0) -> bool:
+    """Whether the tensor-core attention kernels take this shape (bfloat16, head size 64 or 128,
+    no window); other shapes run the general kernel."""
+    if dtype != torch.bfloat16 or window > 0:
+        return False
+    return bool(library.load().lse_attention_mma_supported(head_dim, n_q, n_kv))
+
+
+def decode_splits(tokens: int, n_q: int, n_kv: int, max_context: int | None) -> int:
+    """How many splits of the keys a decode launch uses: enough blocks to fill the GPU,
+    at least one 16-key tile per warp and split."""
+    base = tokens * n_kv * ((n_q // n_kv + 15) // 16)
+    splits = max(1, min(32, -(-592 // base)))
+    if max_context is not None:
+        splits = min(splits, max(1, -(-max_context // 64)))
+    return splits
+
+
+def paged_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
+                           block_tables: torch.Tensor, segment_of_token: torch.Tensor, positions: torch.Tensor,
+                           scale: float, num_splits: int) -> torch.Tensor:
+    """Attention of single decoded tokens (one row per request) with the keys split over
+    ``num_splits`` blocks; bfloat16, head size 64 or 128."""
+    _need_cuda(q, k_cache, v_cache, out, block_tables, segment_of_token, positions)
+    tokens, n_q, head_dim = q.shape
+    n_kv, page_size = k_cache.shape[1], k_cache.shape[2]
+    assert q.dtype == out.dtype == k_cache.dtype == v_cache.dtype == torch.bfloat16
+    assert q.is_contiguous() and out.is_contiguous() and k_cache.is_contiguous() and v_cache.is_contiguous()
+    assert block_tables.dtype == torch.int32 and block_tables.stride(1) == 1
+    scratch = None
+    if num_splits > 1:
+        scratch = torch.empty(tokens * n_q * num_splits * (head_dim + 2), dtype=torch.float32, device=q.device)
+    lib = library.load()
+    check(lib.lse_paged_attention_decode(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
+                                         _ptr(scratch), block_tables.data_ptr(), block_tables.stride(0),
+                                         segment_of_token.data_ptr(), positions.data_ptr(), tokens, n_q, n_kv,
+                                         head_dim, page_size, float(scale), int(num_splits), _stream()),
+          "paged_attention_decode")
+    return out
+
+
+def paged_attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
+                            block_tables: torch.Tensor, segment_start: torch.Tensor,
+                            segment_first_position: torch.Tensor, scale: float) -> torch.Tensor:
+    """Attention of prompt portions (any mix of segment lengths): causal inside the portion,
+    all earlier keys of the request before it; bfloat16, head size 64 or 128.
+
+    segment_start int32 [S + 1]: first row of each segment; segment_first_position int32 [S].
+    """
+    _need_cuda(q, k_cache, v_cache, out, block_tables, segment_start, segment_first_position)
+    tokens, n_q, head_dim = q.shape
+    n_kv, page_size = k_cache.shape[1], k_cache.shape[2]
+    segments = segment_first_position.shape[0]
+    assert q.dtype == out.dtype == k_cache.dtype == v_cache.dtype == torch.bfloat16
+    assert q.is_contiguous() and out.is_contiguous() and k_cache.is_contiguous() and v_cache.is_contiguous()
+    assert block_tables.dtype == torch.int32 and block_tables.stride(1) == 1 and segment_start.shape[0] == segments + 1
+    lib = library.load()
+    check(lib.lse_paged_attention_prefill(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
+                                          block_tables.data_ptr(), block_tables.stride(0), segment_start.data_ptr(),
+                                          segment_first_position.data_ptr(), segments, tokens, n_q, n_kv, head_dim,
+                                          page_size, float(scale), _stream()), "paged_attention_prefill")
+    return out
+
+
 def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
     _need_cuda(gate_up, out)

@@ -68,6 +68,15 @@ class GroupedQueryAttention(Mixer):
         q = torch.empty((tokens, self.n_q, self.head_dim), dtype=x.dtype, device=x.device)
         self.position.encode_and_store(qkv, self.qkv_bias, step, cache, q, self.n_q, self.n_kv, self.head_dim)
         attended = torch.empty_like(q)
-        ops.paged_attention_generic(q, cache.keys, cache.values, attended, cache.block_tables,
-                                    step.segment_of_token, step.positions, self.scale, self.window)
+        if ops.attention_mma_supported(self.head_dim, self.n_q, self.n_kv, x.dtype, self.window):
+            if step.decode_only:
+                splits = ops.decode_splits(tokens, self.n_q, self.n_kv, step.max_context)
+                ops.paged_attention_decode(q, cache.keys, cache.values, attended, cache.block_tables,
+                                           step.segment_of_token, step.positions, self.scale, splits)
+            else:
+                ops.paged_attention_prefill(q, cache.keys, cache.values, attended, cache.block_tables,
+                                            step.segment_start, step.segment_first_position, self.scale)
+        else:   # float32, other head sizes, windows: the general kernel
+            ops.paged_attention_generic(q, cache.keys, cache.values, attended, cache.block_tables,
+                                        step.segment_of_token, step.positions, self.scale, self.window)
         return linear(attended.view(tokens, self.n_q * self.head_dim), self.o_weight)

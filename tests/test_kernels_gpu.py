@@ -339,3 +339,106 @@ def test_sampling_follows_the_distribution():
     assert chi2 < 40.0, chi2          # 10 degrees of freedom: 40 is far in the tail
     numbers = [uniform01(12345, c) for c in range(2000)]
     assert 0.47 < sum(numbers) / len(numbers) < 0.53 and min(numbers) >= 0.0 and max(numbers) < 1.0
+
+
+# ------------------------------------------------------------------ tensor-core attention (bfloat16)
+MMA_SHAPES = [(64, 6, 2, 16), (128, 12, 2, 16), (128, 7, 1, 8), (64, 4, 4, 1), (128, 40, 2, 64), (64, 3, 1, 32)]
+
+
+@pytest.mark.parametrize("splits", [1, 3, 32])
+@pytest.mark.parametrize("head_dim, n_q, n_kv, page", MMA_SHAPES)
+def test_decode_attention_split_keys(head_dim, n_q, n_kv, page, splits):
+    rng = random.Random(head_dim + n_q + splits)
+    torch.manual_seed(n_q * splits)
+    contexts = [1, 15, 16, 17, 63, 64, 65, 130, 1000, 2049]
+    k_cache, v_cache, tables, dense = paged_setup(rng, contexts, n_kv, head_dim, page, torch.bfloat16)
+    q = torch.randn(len(contexts), n_q, head_dim, device=DEV).bfloat16()
+    segs = torch.arange(len(contexts), dtype=torch.int32, device=DEV)
+    positions = torch.tensor([c - 1 for c in contexts], dtype=torch.int32, device=DEV)
+    out = torch.empty_like(q)
+    scale = 1.0 / math.sqrt(head_dim)
+    assert ops().attention_mma_supported(head_dim, n_q, n_kv, torch.bfloat16)
+    ops().paged_attention_decode(q, k_cache, v_cache, out, tables, segs, positions, scale, splits)
+    for r, ctx in enumerate(contexts):
+        k, v = dense[r]
+        want = dense_attention(q[r], k, v, scale)
+        err = float((out[r].double() - want).abs().max())
+        assert err < 2.0 ** -7 * max(1.0, float(want.abs().max())), (r, ctx, err)
+    # a padding row (segment -1) is left alone
+    segs[2] = -1
+    out.fill_(7.0)
+    ops().paged_attention_decode(q, k_cache, v_cache, out, tables, segs, positions, scale, splits)
+    assert float((out[2].float() - 7.0).abs().max()) == 0.0 and float((out[3].float() - 7.0).abs().max()) > 0.0
+
+
+@pytest.mark.parametrize("needle", [0, 15, 16, 255, 256, 1023, 1024, 1499])
+@pytest.mark.parametrize("splits", [1, 5])
+def test_decode_attention_finds_one_far_key(needle, splits):
+    rng = random.Random(needle)
+    torch.manual_seed(needle)
+    n_q, n_kv, head_dim, page, ctx = 12, 2, 128, 16, 1500
+    k_cache, v_cache, tables, dense = paged_setup(rng, [ctx], n_kv, head_dim, page, torch.bfloat16)
+    q = torch.randn(1, n_q, head_dim, device=DEV).bfloat16()
+    k, v = dense[0]
+    for g in range(n_kv):
+        k[needle, g] = (q[0, g * 6 + 5].float() * 4).bfloat16()        # matches the last head of the group
+        k_cache[int(tables[0, needle // page]), g, needle % page] = k[needle, g]
+    out = torch.empty_like(q)
+    ops().paged_attention_decode(q, k_cache, v_cache, out, tables, torch.zeros(1, dtype=torch.int32, device=DEV),
+                                 torch.tensor([ctx - 1], dtype=torch.int32, device=DEV), 1.0 / math.sqrt(head_dim), splits)
+    want = dense_attention(q[0], k, v, 1.0 / math.sqrt(head_dim))
+    assert float((out[0].double() - want).abs().max()) < 2.0 ** -6
+    for g in range(n_kv):
+        assert float((out[0, g * 6 + 5].double() - v[needle, g].double()).abs().max()) < 0.05
+
+
+@pytest.mark.parametrize("head_dim, n_q, n_kv, page", MMA_SHAPES)
+def test_prefill_attention_portions_with_earlier_context(head_dim, n_q, n_kv, page):
+    rng = random.Random(head_dim * n_kv + page)
+    torch.manual_seed(head_dim + page)
+    # (keys already cached before the portion, rows of the portion)
+    portions = [(0, 1), (0, 70), (5, 2), (63, 3), (64, 64), (100, 129), (1000, 1), (300, 11), (0, 200)]
+    contexts = [before + rows for before, rows in portions]
+    k_cache, v_cache, tables, dense = paged_setup(rng, contexts, n_kv, head_dim, page, torch.bfloat16)
+    total = sum(rows for _, rows in portions)
+    q = torch.randn(total, n_q, head_dim, device=DEV).bfloat16()
+    starts, firsts, cursor = [], [], 0
+    for before, rows in portions:
+        starts.append(cursor)
+        firsts.append(before)
+        cursor += rows
+    starts.append(cursor)
+    out = torch.empty_like(q)
+    scale = 1.0 / math.sqrt(head_dim)
+    ops().paged_attention_prefill(q, k_cache, v_cache, out, tables, torch.tensor(starts, dtype=torch.int32, device=DEV),
+                                  torch.tensor(firsts, dtype=torch.int32, device=DEV), scale)
+    for s, (before, rows) in enumerate(portions):
+        k, v = dense[s]
+        for local in sorted({0, 1, rows // 2, rows - 2, rows - 1} & set(range(rows))):
+            pos = before + local
+            want = dense_attention(q[starts[s] + local], k[:pos + 1], v[:pos + 1], scale)
+            err = float((out[starts[s] + local].double() - want).abs().max())
+            assert err < 2.0 ** -7 * max(1.0, float(want.abs().max())), (s, before, rows, local, err)
+
+
+def test_prefill_attention_keeps_the_causal_edge():
+    """The key right after a row's own position is made to match the query: it must not be read."""
+    rng = random.Random(5)
+    torch.manual_seed(5)
+    n_q, n_kv, head_dim, page = 6, 2, 64, 16
+    before, rows = 37, 150
+    k_cache, v_cache, tables, dense = paged_setup(rng, [before + rows], n_kv, head_dim, page, torch.bfloat16)
+    q = torch.randn(rows, n_q, head_dim, device=DEV).bfloat16()
+    k, v = dense[0]
+    for local in range(rows - 1):          # key pos+1 looks like the query of row `local`
+        pos = before + local
+        k[pos + 1, :] = (q[local, 0].float() * 4).bfloat16()
+        k_cache[int(tables[0, (pos + 1) // page]), :, (pos + 1) % page] = k[pos + 1]
+    out = torch.empty_like(q)
+    scale = 1.0 / math.sqrt(head_dim)
+    ops().paged_attention_prefill(q, k_cache, v_cache, out, tables, torch.tensor([0, rows], dtype=torch.int32, device=DEV),
+                                  torch.tensor([before], dtype=torch.int32, device=DEV), scale)
+    for local in (0, 1, 26, 27, 63, 64, 100, rows - 1):
+        pos = before + local
+        want = dense_attention(q[local], k[:pos + 1], v[:pos + 1], scale)
+        assert float((out[local].double() - want).abs().max()) < 2.0 ** -6, local

@@ -12,7 +12,8 @@ from tiny_configs import ALL
 pytestmark = pytest.mark.gpu
 
 DTYPES = ("float32", "bfloat16")
-LENGTHS = {"A": (5, 17, 33, 150), "B": (1, 9, 24, 40, 131), "C": (3, 66, 97)}
+LENGTHS = {"A": (5, 17, 33, 150), "B": (1, 9, 24, 40, 131), "C": (3, 66, 97), "D": (7, 64, 65, 200),
+           "E": (2, 129, 90)}
 
 
 def _requests(name: str, seed: int = 0) -> dict[str, list[int]]:
@@ -83,7 +84,7 @@ def test_float32_is_bitwise_the_same_however_it_is_cut():
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "D"])
 def test_long_decoding(name, dtype):
     """A short prompt, then hundreds of tokens one by one, across many pages."""
     config, page, _ = ALL[name]

@@ -32,4 +32,22 @@ TINY_C = {
 }
 TINY_C_PAGE = 32
 
-ALL = {"A": (TINY_A, TINY_A_PAGE, 0), "B": (TINY_B, TINY_B_PAGE, 1), "C": (TINY_C, TINY_C_PAGE, 2)}
+# head sizes 64 and 128: the tensor-core attention kernels run in bfloat16
+TINY_D = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "vocab_size": 320, "hidden_size": 112, "intermediate_size": 96, "num_hidden_layers": 2,
+    "num_attention_heads": 6, "num_key_value_heads": 2, "head_dim": 64, "max_position_embeddings": 512,
+    "rope_theta": 10000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": True,
+}
+TINY_D_PAGE = 16
+
+TINY_E = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "vocab_size": 411, "hidden_size": 72, "intermediate_size": 200, "num_hidden_layers": 1,
+    "num_attention_heads": 7, "num_key_value_heads": 1, "head_dim": 128, "max_position_embeddings": 512,
+    "rope_theta": 500000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "rope_pairing": "half",
+}
+TINY_E_PAGE = 8
+
+ALL = {"A": (TINY_A, TINY_A_PAGE, 0), "B": (TINY_B, TINY_B_PAGE, 1), "C": (TINY_C, TINY_C_PAGE, 2),
+       "D": (TINY_D, TINY_D_PAGE, 3), "E": (TINY_E, TINY_E_PAGE, 4)}
