@@ -142,14 +142,14 @@ def time_decode(model, batch: int, steps: int, warmup: int):
         for _ in range(warmup):
             one_step()
         torch.cuda.synchronize()
-        launches = library.launches()
+        launches = library.launches() + runner.graph_kernel_launches
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
         for _ in range(steps):
             one_step()
         end.record()
         torch.cuda.synchronize()
-        launches = library.launches() - launches
+        launches = library.launches() + runner.graph_kernel_launches - launches
     ms = start.elapsed_time(end) / steps
     kv_bytes = batch * (PROMPT + warmup + steps // 2) * cache.kv_bytes_per_token()
     cache.free_all()

@@ -166,18 +166,23 @@ extern "C" int lse_paged_attention_generic(const void* q, const void* k_cache, c
   const int group = n_q / n_kv;
   dim3 grid(tokens, n_kv, (group + GC - 1) / GC);
   const size_t smem = generic_smem_bytes(head_dim);
-  cudaError_t err;
-  if (dtype == LSE_DTYPE_F32) {
-    err = cudaFuncSetAttribute(paged_attention_generic_kernel<float>,
-                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  // the largest head size once per process (not repeated while a stream is captured)
+  static bool configured = false;
+  if (!configured) {
+    const int most = (int)generic_smem_bytes(MAX_D);
+    cudaError_t err = cudaFuncSetAttribute(paged_attention_generic_kernel<float>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+    if (err == cudaSuccess)
+      err = cudaFuncSetAttribute(paged_attention_generic_kernel<__nv_bfloat16>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, most);
     if (err != cudaSuccess) return (int)err;
+    configured = true;
+  }
+  if (dtype == LSE_DTYPE_F32) {
     paged_attention_generic_kernel<float><<<grid, THREADS, smem, stream>>>(
         (const float*)q, (const float*)k_cache, (const float*)v_cache, (float*)out, block_tables,
         bt_stride, segment_of_token, positions, n_q, n_kv, head_dim, page_size, scale, window);
   } else if (dtype == LSE_DTYPE_BF16) {
-    err = cudaFuncSetAttribute(paged_attention_generic_kernel<__nv_bfloat16>,
-                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (err != cudaSuccess) return (int)err;
     paged_attention_generic_kernel<__nv_bfloat16><<<grid, THREADS, smem, stream>>>(
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
         (__nv_bfloat16*)out, block_tables, bt_stride, segment_of_token, positions, n_q, n_kv,

@@ -464,8 +464,12 @@ int launch_decode(const void* q, const void* kc, const void* vc, void* out, floa
                   const int* block_tables, int bt_stride, const int* seg, const int* positions, int tokens,
                   int n_q, int n_kv, int page_size, float scale, int num_splits, cudaStream_t stream) {
   const size_t smem = decode_smem<D>();
-  cudaError_t err = cudaFuncSetAttribute(attn_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  if (err != cudaSuccess) return (int)err;
+  static bool configured = false;   // once per process: not repeated while a stream is captured
+  if (!configured) {
+    cudaError_t err = cudaFuncSetAttribute(attn_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (err != cudaSuccess) return (int)err;
+    configured = true;
+  }
   const int group = n_q / n_kv;
   dim3 grid(tokens, n_kv * ((group + 15) / 16), num_splits);
   attn_decode_kernel<D><<<grid, 128, smem, stream>>>(
@@ -483,8 +487,12 @@ int launch_prefill(const void* q, const void* kc, const void* vc, void* out, con
                    int bt_stride, const int* segment_start, const int* segment_first_pos, int num_segments,
                    int tokens, int n_q, int n_kv, int page_size, float scale, cudaStream_t stream) {
   const size_t smem = prefill_smem<D>();
-  cudaError_t err = cudaFuncSetAttribute(attn_prefill_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  if (err != cudaSuccess) return (int)err;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t err = cudaFuncSetAttribute(attn_prefill_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (err != cudaSuccess) return (int)err;
+    configured = true;
+  }
   const int group = n_q / n_kv;
   const int rows_per_tile = PF_BM / group;
   const int tiles = (tokens + rows_per_tile - 1) / rows_per_tile + num_segments;   // upper bound

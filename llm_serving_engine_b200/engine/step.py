@@ -11,6 +11,12 @@ All rows write their key and value before any row attends (``model.py:114``).
 
 The step's metadata is packed into ONE pinned int32 buffer and copied to the
 device with one transfer; ``StepContext`` holds views into the device copy.
+
+Steps in which every request brings exactly one token (decoding) are replayed
+from CUDA graphs: the model's launches are captured once per (batch bucket,
+block-table width) with the metadata at fixed addresses, rows beyond the batch
+being padding (segment -1, cache slot -1) that every kernel skips.  Only models
+whose mixers all say ``graph_safe`` are captured; others run launch by launch.
 """
 from __future__ import annotations
 
@@ -19,7 +25,7 @@ from dataclasses import dataclass, field
 import numpy as np
 import torch
 
-from ..cache.manager import CacheManager, LayerCache
+from ..cache.manager import CacheFullError, CacheManager, LayerCache
 
 
 @dataclass
@@ -51,7 +57,7 @@ class StepContext:
         self.segments: list[Segment] = []
         self.token_ids: torch.Tensor = None          # [T]
         self.positions: torch.Tensor = None          # [T]
-        self.segment_of_token: torch.Tensor = None   # [T]
+        self.segment_of_token: torch.Tensor = None   # [T], -1 for padding rows
         self.segment_start: torch.Tensor = None      # [S + 1] first row of each segment
         self.segment_first_position: torch.Tensor = None  # [S]
         self.segment_context: torch.Tensor = None    # [S] keys of the request after this step
@@ -66,40 +72,85 @@ def _round4(n: int) -> int:
     return (n + 3) & ~3
 
 
+class _Layout:
+    """Where each array of a step lies in the packed int32 buffer, for given capacities."""
+
+    def __init__(self, tokens: int, segments: int, wanted: int, table_width: int, groups: int) -> None:
+        self.tokens, self.segments, self.wanted, self.table_width = tokens, segments, wanted, table_width
+        cursor = 0
+
+        def take(n: int) -> tuple[int, int]:
+            nonlocal cursor
+            view = (cursor, cursor + n)
+            cursor += _round4(n)
+            return view
+
+        self.tok, self.pos, self.seg = take(tokens), take(tokens), take(tokens)
+        self.start, self.first, self.ctx, self.slot = take(segments + 1), take(segments), take(segments), take(segments)
+        self.want = take(wanted)
+        self.maps = [take(tokens) for _ in range(groups)]
+        self.tables = [take(segments * table_width) for _ in range(groups)]
+        self.size = cursor
+
+
+class _Graph:
+    """A captured decode step: fixed buffers, the graph and its output."""
+
+    def __init__(self, layout: _Layout, device, pinned: bool) -> None:
+        self.layout = layout
+        self.host = torch.empty(layout.size, dtype=torch.int32, pin_memory=pinned)
+        self.host_np = self.host.numpy()
+        self.device = torch.empty(layout.size, dtype=torch.int32, device=device)
+        self.graph: torch.cuda.CUDAGraph | None = None
+        self.logits: torch.Tensor | None = None
+        self.launches = 0        # launches of the engine's own kernels inside the graph
+
+
 class StepRunner:
     """Packs a step, runs the model on it and keeps the cache manager in step."""
 
-    def __init__(self, model, cache: CacheManager, max_tokens_per_step: int, max_segments: int) -> None:
+    GRAPH_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256)
+
+    def __init__(self, model, cache: CacheManager, max_tokens_per_step: int, max_segments: int,
+                 use_graphs: bool = True) -> None:
         self.model = model
         self.cache = cache
         self.device = model.device
         self.max_tokens = int(max_tokens_per_step)
         self.max_segments = int(max_segments)
-        n_groups = len(cache.groups)
-        table_width = _round4(cache.max_pages_per_request)
-        capacity = (4 * _round4(self.max_tokens) + _round4(self.max_segments + 1) + 3 * _round4(self.max_segments)
-                    + n_groups * (_round4(self.max_tokens) + self.max_segments * table_width))
-        self._capacity = capacity
-        self._host = torch.empty(capacity, dtype=torch.int32, pin_memory=self.device.type == "cuda")
+        self._groups = len(cache.groups)
+        full = _Layout(self.max_tokens, self.max_segments, self.max_tokens,
+                       _round4(cache.max_pages_per_request), self._groups)
+        self._capacity = full.size
+        pinned = self.device.type == "cuda"
+        self._host = torch.empty(self._capacity, dtype=torch.int32, pin_memory=pinned)
         self._host_np = self._host.numpy()
-        self._device = torch.empty(capacity, dtype=torch.int32, device=self.device)
+        self._device = torch.empty(self._capacity, dtype=torch.int32, device=self.device)
         self._layer_views = [cache.layer_view(position) for position in range(len(model.spec.order))]
-        self._copied = torch.cuda.Event() if self.device.type == "cuda" else None
+        self._copied = torch.cuda.Event() if pinned else None
         self._copy_pending = False
+        self.use_graphs = bool(use_graphs) and pinned and getattr(model, "graph_safe", False)
+        self._graphs: dict[tuple[int, int], _Graph] = {}
         self.steps_run = 0
+        self.graph_replays = 0
+        self.graph_kernel_launches = 0
         self.last_h2d_bytes = 0
 
     # -- the step ------------------------------------------------------------------
     def run(self, entries: list[StepEntry]) -> torch.Tensor:
         """Run one step.  Returns float32 logits [total wanted, vocab] on the device, in the
-        order of the entries and of each entry's ``want``."""
-        step, caches = self.prepare(entries)
-        logits = self.model.forward(step, caches)
+        order of the entries and of each entry's ``want``.  The tensor may be a view of a
+        buffer that the next step overwrites: use or copy it before the next ``run``."""
+        self._validate(entries)
+        if self.use_graphs and all(len(entry.tokens) == 1 for entry in entries):
+            logits = self._run_graph(entries)
+        else:
+            step, caches = self.prepare(entries, validated=True)
+            logits = self.model.forward(step, caches)
         self.finish(entries)
         return logits
 
-    def prepare(self, entries: list[StepEntry]):
-        cache = self.cache
+    def _validate(self, entries: list[StepEntry]) -> None:
         if not entries:
             raise ValueError("a step needs at least one entry")
         if len(entries) > self.max_segments:
@@ -120,85 +171,73 @@ class StepRunner:
             for index in entry.want:
                 if not 0 <= index < len(entry.tokens):
                     raise ValueError(f"request {entry.request_id!r}: wanted place {index} outside its tokens")
-        planned = [(entry.request_id, len(entry.tokens)) for entry in entries]
-        if not cache.fits(planned):
-            from ..cache.manager import CacheFullError
+        if not self.cache.fits([(entry.request_id, len(entry.tokens)) for entry in entries]):
             raise CacheFullError("paged KV cache has no free blocks for this step")
 
-        if self._copy_pending:   # the pinned buffer is reused: the last copy must have left it
-            self._copied.synchronize()
-            self._copy_pending = False
+    def _pages_after(self, entries: list[StepEntry]) -> int:
+        cache = self.cache
+        return max(1, max((cache.requests[e.request_id].length + len(e.tokens) + cache.page_size - 1)
+                          // cache.page_size for e in entries))
+
+    def _pack(self, entries: list[StepEntry], host: np.ndarray, lay: _Layout, wanted_all_rows: bool) -> StepContext:
+        """Reserve cache room for every entry and write the step's arrays into ``host``.
+        Capacities of ``lay`` beyond the entries are filled as padding."""
+        cache = self.cache
         step = StepContext()
-        n_seg = len(entries)
-        wanted = sum(len(entry.want) for entry in entries)
-        table_width = _round4(max(1, max(
-            (cache.requests[e.request_id].length + len(e.tokens) + cache.page_size - 1) // cache.page_size
-            for e in entries)))
-        host = self._host_np
-        cursor = 0
-
-        def take(n: int):
-            nonlocal cursor
-            view = (cursor, cursor + n)
-            cursor += _round4(n)
-            return view
-
-        r_tok, r_pos, r_seg = take(total), take(total), take(total)
-        r_start, r_first, r_ctx, r_slot = take(n_seg + 1), take(n_seg), take(n_seg), take(n_seg)
-        r_want = take(wanted)
-        r_maps = [take(total) for _ in cache.groups]
-        r_tables = [take(n_seg * table_width) for _ in cache.groups]
-        if cursor > self._capacity:
-            raise ValueError("step metadata exceeds its buffer")
-        for lo, hi in r_tables:
+        host[lay.tok[0]:lay.tok[1]] = 0
+        host[lay.pos[0]:lay.pos[1]] = 0
+        host[lay.seg[0]:lay.seg[1]] = -1
+        host[lay.first[0]:lay.first[1]] = 0
+        host[lay.ctx[0]:lay.ctx[1]] = 0
+        host[lay.slot[0]:lay.slot[1]] = 0
+        for lo, hi in lay.maps:
             host[lo:hi] = -1
-
+        for lo, hi in lay.tables:
+            host[lo:hi] = -1
         row = 0
-        want_cursor = r_want[0]
+        want_cursor = lay.want[0]
         for index, entry in enumerate(entries):
             count = len(entry.tokens)
             first = cache.reserve(entry.request_id, count)
             request = cache.requests[entry.request_id]
             step.segments.append(Segment(entry.request_id, request.state_slot, first, count, row))
-            host[r_tok[0] + row: r_tok[0] + row + count] = entry.tokens
-            host[r_pos[0] + row: r_pos[0] + row + count] = np.arange(first, first + count, dtype=np.int32)
-            host[r_seg[0] + row: r_seg[0] + row + count] = index
-            host[r_start[0] + index] = row
-            host[r_first[0] + index] = first
-            host[r_ctx[0] + index] = first + count
-            host[r_slot[0] + index] = request.state_slot
-            for offset in entry.want:
-                host[want_cursor] = row + offset
-                want_cursor += 1
-            for g in range(len(cache.groups)):
-                host[r_maps[g][0] + row: r_maps[g][0] + row + count] = cache.slot_mapping(g, entry.request_id, first, count)
+            host[lay.tok[0] + row: lay.tok[0] + row + count] = entry.tokens
+            host[lay.pos[0] + row: lay.pos[0] + row + count] = np.arange(first, first + count, dtype=np.int32)
+            host[lay.seg[0] + row: lay.seg[0] + row + count] = index
+            host[lay.start[0] + index] = row
+            host[lay.first[0] + index] = first
+            host[lay.ctx[0] + index] = first + count
+            host[lay.slot[0] + index] = request.state_slot
+            if not wanted_all_rows:
+                for offset in entry.want:
+                    host[want_cursor] = row + offset
+                    want_cursor += 1
+            for g in range(self._groups):
+                host[lay.maps[g][0] + row: lay.maps[g][0] + row + count] = cache.slot_mapping(g, entry.request_id, first, count)
                 table = cache.block_table(g, entry.request_id)
-                base = r_tables[g][0] + index * table_width
+                base = lay.tables[g][0] + index * lay.table_width
                 host[base: base + len(table)] = table
             step.max_segment_tokens = max(step.max_segment_tokens, count)
             step.max_context = max(step.max_context, first + count)
             row += count
-        host[r_start[0] + n_seg] = row
+        host[lay.start[0] + len(entries): lay.start[1]] = row      # padding segments are empty
+        if wanted_all_rows:
+            host[lay.want[0]:lay.want[1]] = np.arange(lay.wanted, dtype=np.int32)
         step.decode_only = step.max_segment_tokens == 1
+        return step
 
-        self._device[:cursor].copy_(self._host[:cursor], non_blocking=True)
-        self.last_h2d_bytes = cursor * 4
-        if self._copied is not None:
-            self._copied.record()
-            self._copy_pending = True
-        dev = self._device
-        step.num_tokens, step.num_segments, step.num_wanted = total, n_seg, wanted
-        step.token_ids = dev[r_tok[0]:r_tok[1]]
-        step.positions = dev[r_pos[0]:r_pos[1]]
-        step.segment_of_token = dev[r_seg[0]:r_seg[1]]
-        step.segment_start = dev[r_start[0]:r_start[1]]
-        step.segment_first_position = dev[r_first[0]:r_first[1]]
-        step.segment_context = dev[r_ctx[0]:r_ctx[1]]
-        step.segment_state_slot = dev[r_slot[0]:r_slot[1]]
-        step.want_rows = dev[r_want[0]:r_want[1]]
-
-        group_maps = [dev[lo:hi] for lo, hi in r_maps]
-        group_tables = [dev[lo:hi].view(n_seg, table_width) for lo, hi in r_tables]
+    def _views(self, step: StepContext, dev: torch.Tensor, lay: _Layout):
+        step.num_tokens, step.num_segments, step.num_wanted = lay.tokens, lay.segments, lay.wanted
+        step.token_ids = dev[lay.tok[0]:lay.tok[1]]
+        step.positions = dev[lay.pos[0]:lay.pos[1]]
+        step.segment_of_token = dev[lay.seg[0]:lay.seg[1]]
+        step.segment_start = dev[lay.start[0]:lay.start[1]]
+        step.segment_first_position = dev[lay.first[0]:lay.first[1]]
+        step.segment_context = dev[lay.ctx[0]:lay.ctx[1]]
+        step.segment_state_slot = dev[lay.slot[0]:lay.slot[1]]
+        step.want_rows = dev[lay.want[0]:lay.want[1]]
+        group_maps = [dev[lo:hi] for lo, hi in lay.maps]
+        group_tables = [dev[lo:hi].view(lay.segments, lay.table_width) for lo, hi in lay.tables]
         caches = []
         for view in self._layer_views:
             layer_cache = LayerCache(keys=view.keys, values=view.values, state=view.state, group=view.group)
@@ -207,6 +246,72 @@ class StepRunner:
                 layer_cache.block_tables = group_tables[view.group]
             caches.append(layer_cache)
         return step, caches
+
+    def prepare(self, entries: list[StepEntry], validated: bool = False):
+        """Reserve, pack and upload a step; returns ``(StepContext, [LayerCache per layer run])``."""
+        if not validated:
+            self._validate(entries)
+        if self._copy_pending:   # the pinned buffer is reused: the last copy must have left it
+            self._copied.synchronize()
+            self._copy_pending = False
+        total = sum(len(entry.tokens) for entry in entries)
+        wanted = sum(len(entry.want) for entry in entries)
+        lay = _Layout(total, len(entries), wanted, _round4(self._pages_after(entries)), self._groups)
+        if lay.size > self._capacity:
+            raise ValueError("step metadata exceeds its buffer")
+        step = self._pack(entries, self._host_np, lay, wanted_all_rows=False)
+        self._device[:lay.size].copy_(self._host[:lay.size], non_blocking=True)
+        self.last_h2d_bytes = lay.size * 4
+        if self._copied is not None:
+            self._copied.record()
+            self._copy_pending = True
+        return self._views(step, self._device, lay)
+
+    # -- decode steps from CUDA graphs ---------------------------------------------
+    def _run_graph(self, entries: list[StepEntry]) -> torch.Tensor:
+        count = len(entries)
+        bucket = next((b for b in self.GRAPH_BUCKETS if b >= count), None)
+        if bucket is None:
+            step, caches = self.prepare(entries, validated=True)
+            return self.model.forward(step, caches)
+        need = self._pages_after(entries)
+        width = 16
+        while width < need:
+            width *= 2
+        key = (bucket, width)
+        slot = self._graphs.get(key)
+        if slot is None:
+            slot = _Graph(_Layout(bucket, bucket, bucket, width, self._groups), self.device, True)
+            self._graphs[key] = slot
+        if self._copy_pending:
+            self._copied.synchronize()
+            self._copy_pending = False
+        step = self._pack(entries, slot.host_np, slot.layout, wanted_all_rows=True)
+        step.max_context = None
+        slot.device.copy_(slot.host, non_blocking=True)
+        self.last_h2d_bytes = slot.layout.size * 4
+        self._copied.record()
+        self._copy_pending = True
+        if slot.graph is None:
+            step, caches = self._views(step, slot.device, slot.layout)
+            self.model.forward(step, caches)           # once launch by launch: first-use set-up happens here
+            torch.cuda.current_stream().synchronize()
+            from ..kernels import library
+            before = library.launches()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                slot.logits = self.model.forward(step, caches)
+            slot.launches = library.launches() - before
+            slot.graph = graph
+        slot.graph.replay()
+        self.graph_replays += 1
+        self.graph_kernel_launches += slot.launches
+        rows = [index for index, entry in enumerate(entries) for _ in entry.want]
+        if rows == list(range(count)):
+            return slot.logits[:count]
+        if not rows:
+            return slot.logits[:0]
+        return slot.logits[torch.tensor(rows, device=self.device)]
 
     def finish(self, entries: list[StepEntry]) -> None:
         """After the step: give back pages that a window has passed."""

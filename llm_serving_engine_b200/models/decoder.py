@@ -97,6 +97,11 @@ class DecoderModel:
         self.final_norm = NORMS.get(spec.final_norm.kind)(spec.final_norm.params, local, ctx)
 
     @property
+    def graph_safe(self) -> bool:
+        """Whether a decode step of this model can be captured in a CUDA graph."""
+        return all(getattr(block.mixer, "graph_safe", False) for block in self.blocks)
+
+    @property
     def vocab_size(self) -> int:
         return self.spec.vocab_size
 

@@ -23,6 +23,8 @@ class GroupedQueryAttention(Mixer):
     keys of its own request up to its own position, scaled by 1/sqrt(head_dim).
     """
 
+    graph_safe = True
+
     def __init__(self, params, weights, ctx) -> None:
         super().__init__(params, weights, ctx)
         self.n_q = int(params["num_heads"])

@@ -89,6 +89,11 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    # True when ``forward`` only launches work whose shape depends on the number of rows and
+    # reads everything else (positions, segments, tables) from device memory: such a step
+    # can be captured in a CUDA graph and replayed with other contents.
+    graph_safe = False
+
     @classmethod
     def cache_requirement(cls, params: dict[str, Any], hidden_size: int):
         """``PagedKV``, ``RequestState`` or ``None``."""
