@@ -177,3 +177,50 @@ extern "C" int lse_sample(const float* logits, long long row_stride, int rows, i
                                               counter, scratch, out);
   LSE_LAUNCH_CHECK();
 }
+
+// ------------------------------------------------------------------------------------------
+// lse_sample_noalloc: the same sampling kernel with scratch that lives in the library image,
+// for callers that cannot allocate device memory.  See sampling_noalloc.h for the contract.
+// ------------------------------------------------------------------------------------------
+#include <stdio.h>
+
+#include "sampling_noalloc.h"
+
+// The scratch itself.  In device code this name is the array; in host code it is only a
+// handle for cudaGetSymbolAddress and must never be passed to a kernel as if it were a pointer.
+static __device__ __align__(256) float lse_noalloc_scratch[LSE_SAMPLE_NOALLOC_MAX_FLOATS];
+
+namespace {
+constexpr int NOALLOC_MAX_DEVICES = 64;
+float* noalloc_scratch_of_device[NOALLOC_MAX_DEVICES];   // device address of the array, per device; null = not looked up yet
+}  // namespace
+
+extern "C" int lse_sample_noalloc(const float* logits, long long row_stride, int rows, int vocab,
+                                  const float* temperature, const float* top_p, const long long* seed,
+                                  const long long* counter, int* out, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (vocab <= 0 || !logits || !temperature || !top_p || !seed || !counter || !out)
+    return LSE_SAMPLE_NOALLOC_BAD_ARGUMENT;
+  if ((long long)rows * (long long)vocab > (long long)LSE_SAMPLE_NOALLOC_MAX_FLOATS) {
+    fprintf(stderr,
+            "lse_sample_noalloc: %d rows x %d vocabulary = %lld floats of scratch, but the built-in scratch "
+            "holds %d; sample fewer rows per call or use lse_sample with your own buffer\n",
+            rows, vocab, (long long)rows * vocab, (int)LSE_SAMPLE_NOALLOC_MAX_FLOATS);
+    return LSE_SAMPLE_NOALLOC_TOO_LARGE;
+  }
+  int device = -1;
+  cudaError_t err = cudaGetDevice(&device);
+  if (err != cudaSuccess) return (int)err;
+  if (device < 0 || device >= NOALLOC_MAX_DEVICES) return LSE_SAMPLE_NOALLOC_BAD_ARGUMENT;
+  float* scratch = noalloc_scratch_of_device[device];
+  if (scratch == nullptr) {
+    // first call on this device (which is current): ask the runtime where the array lives here
+    err = cudaGetSymbolAddress((void**)&scratch, lse_noalloc_scratch);
+    if (err != cudaSuccess) return (int)err;
+    if (scratch == nullptr) return LSE_SAMPLE_NOALLOC_BAD_ARGUMENT;
+    noalloc_scratch_of_device[device] = scratch;
+  }
+  sample_kernel<<<rows, THREADS, 0, stream>>>(logits, row_stride, vocab, temperature, top_p, seed, counter,
+                                              scratch, out);
+  return (int)cudaGetLastError();
+}
