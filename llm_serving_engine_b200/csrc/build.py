@@ -109,7 +109,7 @@ def library_path(verbose: bool = True, force: bool = False) -> Path:
         with ThreadPoolExecutor(max_workers=min(8, len(srcs), os.cpu_count() or 1)) as pool:
             objects = list(pool.map(compile_one, srcs))
         tmp_lib = build_dir / f"{LIB_NAME}.{os.getpid()}.tmp"
-        cmd = [nvcc, "-shared", "-o", str(tmp_lib), *map(str, objects), "-lcuda"]
+        cmd = [nvcc, "-shared", "-o", str(tmp_lib), *map(str, objects)]
         result = subprocess.run(cmd, capture_output=True, text=True)
         if result.returncode != 0:
             raise BuildError(f"link failed:\n{result.stdout}\n{result.stderr}")

@@ -2,6 +2,11 @@
 // residual sum, rotary position encoding fused with the bias and the write into
 // the paged cache, and the SiLU gate.  Formulas follow the reference project's
 // src/llmserve/model.py (RMSNorm :20-23, rotary :29-43, MLP :188).
+//
+// An input that comes from a matrix product may be given as a stack of
+// `n_partials` float32 partial sums (split-K), `partial_stride` elements apart;
+// the kernels add them in index order before anything else, so the sum is the
+// same whatever else runs.
 #include "common.cuh"
 
 // ------------------------------------------------------------------ embedding
@@ -35,13 +40,89 @@ extern "C" int lse_embedding(const void* table, int table_dtype, const int* ids,
 
 // ------------------------------------------------------------------ add + RMSNorm
 // For output row r (source row s = rows ? rows[r] : r):
-//   x = residual[s] + float(delta[s])          (delta may be null)
-//   if write_residual: residual[s] = x         (float32 residual stream)
+//   x = residual[s] + sum_p float(delta[p][s])   (delta may be null)
+//   if write_residual: residual[s] = x           (float32 residual stream)
 //   out[r] = (x * rsqrt(mean(x^2) + eps)) * weight
+template <typename TD> __device__ __forceinline__ void load4(const TD* p, float (&v)[4]);
+template <> __device__ __forceinline__ void load4<float>(const float* p, float (&v)[4]) {
+  const float4 t = *reinterpret_cast<const float4*>(p);
+  v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+template <> __device__ __forceinline__ void load4<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[4]) {
+  const uint2 t = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&t.x);
+  const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&t.y);
+  v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(b); v[3] = __high2float(b);
+}
+template <typename TO> __device__ __forceinline__ void store4(TO* p, const float (&v)[4]);
+template <> __device__ __forceinline__ void store4<float>(float* p, const float (&v)[4]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, const float (&v)[4]) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+  uint2 t;
+  t.x = *reinterpret_cast<uint32_t*>(&a);
+  t.y = *reinterpret_cast<uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = t;
+}
+
+constexpr int NORM_THREADS = 256;
+constexpr int NORM_CHUNKS = 8;   // float4 chunks a thread keeps: hidden <= 256 * 8 * 4 = 8192
+
+// One pass: the row stays in registers between the sum of squares and the scaling.
+// hidden % 4 == 0 and hidden <= NORM_THREADS * NORM_CHUNKS * 4.
 template <typename TD, typename TO>
-__global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __restrict__ delta,
-                                   const float* __restrict__ weight, TO* __restrict__ out,
-                                   const int* __restrict__ rows, int hidden, float eps,
+__global__ void __launch_bounds__(NORM_THREADS)
+add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* __restrict__ delta, int n_partials,
+                       long long partial_stride, const float* __restrict__ weight, TO* __restrict__ out,
+                       const int* __restrict__ rows, int hidden, float eps, int write_residual) {
+  __shared__ float scratch[32];
+  const int r = blockIdx.x;
+  const int s = rows ? rows[r] : r;
+  if (s < 0) return;
+  float* res = residual + (size_t)s * hidden;
+  const TD* del = delta ? delta + (size_t)s * hidden : nullptr;
+  const int chunks = hidden >> 2;
+  float x[NORM_CHUNKS][4];
+  float sq = 0.f;
+#pragma unroll
+  for (int c = 0; c < NORM_CHUNKS; ++c) {
+    const int i = (c * NORM_THREADS + threadIdx.x);
+    if (i < chunks) {
+      load4<float>(res + 4 * i, x[c]);
+      if (del) {
+        for (int p = 0; p < n_partials; ++p) {
+          float d[4];
+          load4<TD>(del + (size_t)p * partial_stride + 4 * i, d);
+          x[c][0] += d[0]; x[c][1] += d[1]; x[c][2] += d[2]; x[c][3] += d[3];
+        }
+        if (write_residual) store4<float>(res + 4 * i, x[c]);
+      }
+      sq = fmaf(x[c][0], x[c][0], sq); sq = fmaf(x[c][1], x[c][1], sq);
+      sq = fmaf(x[c][2], x[c][2], sq); sq = fmaf(x[c][3], x[c][3], sq);
+    }
+  }
+  const float total = block_sum(sq, scratch);
+  const float inv = 1.0f / sqrtf(total / (float)hidden + eps);
+  TO* dst = out + (size_t)r * hidden;
+#pragma unroll
+  for (int c = 0; c < NORM_CHUNKS; ++c) {
+    const int i = (c * NORM_THREADS + threadIdx.x);
+    if (i < chunks) {
+      float w[4], y[4];
+      load4<float>(weight + 4 * i, w);
+      y[0] = (x[c][0] * inv) * w[0]; y[1] = (x[c][1] * inv) * w[1];
+      y[2] = (x[c][2] * inv) * w[2]; y[3] = (x[c][3] * inv) * w[3];
+      store4<TO>(dst + 4 * i, y);
+    }
+  }
+}
+
+// Any width: two passes over the row.
+template <typename TD, typename TO>
+__global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __restrict__ delta, int n_partials,
+                                   long long partial_stride, const float* __restrict__ weight,
+                                   TO* __restrict__ out, const int* __restrict__ rows, int hidden, float eps,
                                    int write_residual) {
   __shared__ float scratch[32];
   const int r = blockIdx.x;
@@ -53,28 +134,46 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __res
   float sq = 0.f;
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
     float x = res[i];
-    if (del) x += to_f32<TD>(del[i]);
+    if (del)
+      for (int p = 0; p < n_partials; ++p) x += to_f32<TD>(del[(size_t)p * partial_stride + i]);
     if (del && write_residual) res[i] = x;
     sq = fmaf(x, x, sq);
   }
   const float total = block_sum(sq, scratch);
   const float inv = 1.0f / sqrtf(total / (float)hidden + eps);
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-    float x;
-    if (del && !write_residual) x = res[i] + to_f32<TD>(del[i]);
-    else x = res[i];
+    float x = res[i];
+    if (del && !write_residual)
+      for (int p = 0; p < n_partials; ++p) x += to_f32<TD>(del[(size_t)p * partial_stride + i]);
     dst[i] = from_f32<TO>((x * inv) * weight[i]);
   }
 }
 
-extern "C" int lse_add_rmsnorm(float* residual, const void* delta, int delta_dtype, const float* weight,
-                               void* out, int out_dtype, const int* rows, int n_rows, int hidden,
-                               float eps, int write_residual, cudaStream_t stream) {
+template <typename TD, typename TO>
+static void launch_add_rmsnorm(float* residual, const void* delta, int n_partials, long long partial_stride,
+                               const float* weight, void* out, const int* rows, int n_rows, int hidden, float eps,
+                               int write_residual, cudaStream_t stream) {
+  const bool aligned = (((uintptr_t)residual | (uintptr_t)delta | (uintptr_t)weight | (uintptr_t)out) & 15) == 0 &&
+                       (partial_stride % 4) == 0;
+  if (hidden % 4 == 0 && hidden <= NORM_THREADS * NORM_CHUNKS * 4 && aligned) {
+    add_rmsnorm_vec_kernel<TD, TO><<<n_rows, NORM_THREADS, 0, stream>>>(
+        residual, (const TD*)delta, n_partials, partial_stride, weight, (TO*)out, rows, hidden, eps, write_residual);
+  } else {
+    const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+    add_rmsnorm_kernel<TD, TO><<<n_rows, threads, 0, stream>>>(
+        residual, (const TD*)delta, n_partials, partial_stride, weight, (TO*)out, rows, hidden, eps, write_residual);
+  }
+}
+
+extern "C" int lse_add_rmsnorm(float* residual, const void* delta, int delta_dtype, int n_partials,
+                               long long partial_stride, const float* weight, void* out, int out_dtype,
+                               const int* rows, int n_rows, int hidden, float eps, int write_residual,
+                               cudaStream_t stream) {
   if (n_rows <= 0) return 0;
-  const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
-#define LSE_NORM_CASE(TD, TO)                                                                     \
-  add_rmsnorm_kernel<TD, TO><<<n_rows, threads, 0, stream>>>(residual, (const TD*)delta, weight,  \
-                                                             (TO*)out, rows, hidden, eps, write_residual)
+  if (delta && n_partials < 1) return LSE_ERR_BAD_ARGUMENT;
+#define LSE_NORM_CASE(TD, TO)                                                                               \
+  launch_add_rmsnorm<TD, TO>(residual, delta, n_partials, partial_stride, weight, out, rows, n_rows, hidden, \
+                             eps, write_residual, stream)
   if (delta_dtype == LSE_DTYPE_F32 && out_dtype == LSE_DTYPE_F32) LSE_NORM_CASE(float, float);
   else if (delta_dtype == LSE_DTYPE_BF16 && out_dtype == LSE_DTYPE_BF16) LSE_NORM_CASE(__nv_bfloat16, __nv_bfloat16);
   else if (delta_dtype == LSE_DTYPE_BF16 && out_dtype == LSE_DTYPE_F32) LSE_NORM_CASE(__nv_bfloat16, float);
@@ -86,109 +185,147 @@ extern "C" int lse_add_rmsnorm(float* residual, const void* delta, int delta_dty
 
 // ------------------------------------------------------------------ rotary + bias + cache write
 // qkv[t] holds the projections of token t: Hq query heads, then Hkv key heads,
-// then Hkv value heads, each of D values (row stride qkv_stride).  For every
-// head: add the bias, rotate query and key heads by angle = pos * inv_freq[i]
-// (float32), write queries to q_out[t, h, :] and keys/values into the paged
-// cache at slot = slot_mapping[t] (page = slot / page_size, offset = slot %
-// page_size; cache layout [page][kv head][offset][D]).  slot < 0: nothing is
-// cached for this token (padding row).  pairing 0: pairs (2i, 2i+1); 1: (i, i+D/2).
-template <typename T>
-__global__ void rope_kv_write_kernel(const T* __restrict__ qkv, const float* __restrict__ bias,
-                                     const int* __restrict__ positions,
-                                     const int* __restrict__ slot_mapping,
-                                     const float* __restrict__ inv_freq, T* __restrict__ q_out,
-                                     T* __restrict__ k_cache, T* __restrict__ v_cache, int n_q,
-                                     int n_kv, int head_dim, int page_size, int pairing,
+// then Hkv value heads, each of D values (row stride qkv_stride; optionally a
+// stack of float32 partial sums).  For every head: add the bias, rotate query
+// and key heads by angle = pos * inv_freq[i] (float32), write queries to
+// q_out[t, h, :] and keys/values into the paged cache at slot = slot_mapping[t]
+// (page = slot / page_size, offset = slot % page_size; cache layout
+// [page][kv head][offset][D]).  slot < 0: nothing is cached for this token
+// (padding row).  pairing 0: pairs (2i, 2i+1); 1: (i, i+D/2).
+//
+// One block per token.  A thread owns pair index i for the heads hg, hg + HG, ...
+// so the sine and cosine of an angle are computed once for all heads.
+template <typename TI, typename TO>
+__global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, int n_partials, long long partial_stride,
+                                     const float* __restrict__ bias, const int* __restrict__ positions,
+                                     const int* __restrict__ slot_mapping, const float* __restrict__ inv_freq,
+                                     TO* __restrict__ q_out, TO* __restrict__ k_cache, TO* __restrict__ v_cache,
+                                     int n_q, int n_kv, int head_dim, int page_size, int pairing,
                                      long long qkv_stride) {
   const int t = blockIdx.x;
-  const int head = blockIdx.y;  // 0..n_q-1 queries, then keys, then values
+  const int half = head_dim >> 1;
+  const int i = threadIdx.x % half;
+  const int hg = threadIdx.x / half;
+  const int head_groups = blockDim.x / half;
+  if (hg >= head_groups) return;
   const int pos = positions[t];
   const int slot = slot_mapping[t];
-  const T* src = qkv + (size_t)t * qkv_stride + (size_t)head * head_dim;
-  const float* b = bias ? bias + (size_t)head * head_dim : nullptr;
-  const bool is_q = head < n_q;
-  const bool is_k = !is_q && head < n_q + n_kv;
-  T* dst;
-  if (is_q) {
-    dst = q_out + ((size_t)t * n_q + head) * head_dim;
-  } else {
-    if (slot < 0) return;
-    const int kv_head = is_k ? head - n_q : head - n_q - n_kv;
-    const size_t page = slot / page_size, off = slot % page_size;
-    T* base = is_k ? k_cache : v_cache;
-    dst = base + ((page * n_kv + kv_head) * page_size + off) * head_dim;
-  }
-  if (is_q || is_k) {
-    const int half = head_dim >> 1;
-    for (int i = threadIdx.x; i < half; i += blockDim.x) {
-      const int ia = pairing == 0 ? 2 * i : i;
-      const int ib = pairing == 0 ? 2 * i + 1 : i + half;
-      float xa = to_f32<T>(src[ia]), xb = to_f32<T>(src[ib]);
-      if (b) { xa += b[ia]; xb += b[ib]; }
-      const float angle = (float)pos * inv_freq[i];
-      float sn, cs;
-      sincosf(angle, &sn, &cs);
-      dst[ia] = from_f32<T>(xa * cs - xb * sn);
-      dst[ib] = from_f32<T>(xb * cs + xa * sn);
+  const TI* row = qkv + (size_t)t * qkv_stride;
+  const size_t page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot % page_size : 0;
+  float sn, cs;
+  sincosf((float)pos * inv_freq[i], &sn, &cs);
+  const int ia = pairing == 0 ? 2 * i : i;
+  const int ib = pairing == 0 ? 2 * i + 1 : i + half;
+  // queries and keys: rotate
+  for (int head = hg; head < n_q + n_kv; head += head_groups) {
+    const size_t col = (size_t)head * head_dim;
+    float xa = 0.f, xb = 0.f;
+    for (int p = 0; p < n_partials; ++p) {
+      xa += to_f32<TI>(row[(size_t)p * partial_stride + col + ia]);
+      xb += to_f32<TI>(row[(size_t)p * partial_stride + col + ib]);
     }
-  } else {
-    for (int i = threadIdx.x; i < head_dim; i += blockDim.x) {
-      float x = to_f32<T>(src[i]);
-      if (b) x += b[i];
-      dst[i] = from_f32<T>(x);
+    if (bias) { xa += bias[col + ia]; xb += bias[col + ib]; }
+    const float ya = xa * cs - xb * sn, yb = xb * cs + xa * sn;
+    TO* dst;
+    if (head < n_q) {
+      dst = q_out + ((size_t)t * n_q + head) * head_dim;
+    } else {
+      if (slot < 0) continue;
+      dst = k_cache + ((page * n_kv + (head - n_q)) * page_size + off) * head_dim;
+    }
+    dst[ia] = from_f32<TO>(ya);
+    dst[ib] = from_f32<TO>(yb);
+  }
+  // values: bias only
+  if (slot >= 0) {
+    for (int head = hg; head < n_kv; head += head_groups) {
+      const size_t col = (size_t)(n_q + n_kv + head) * head_dim;
+      float xa = 0.f, xb = 0.f;
+      for (int p = 0; p < n_partials; ++p) {
+        xa += to_f32<TI>(row[(size_t)p * partial_stride + col + ia]);
+        xb += to_f32<TI>(row[(size_t)p * partial_stride + col + ib]);
+      }
+      if (bias) { xa += bias[col + ia]; xb += bias[col + ib]; }
+      TO* dst = v_cache + ((page * n_kv + head) * page_size + off) * head_dim;
+      dst[ia] = from_f32<TO>(xa);
+      dst[ib] = from_f32<TO>(xb);
     }
   }
 }
 
-extern "C" int lse_rope_kv_write(const void* qkv, int dtype, const float* bias, const int* positions,
-                                 const int* slot_mapping, const float* inv_freq, void* q_out,
-                                 void* k_cache, void* v_cache, int tokens, int n_q, int n_kv,
-                                 int head_dim, int page_size, int pairing, long long qkv_stride,
-                                 cudaStream_t stream) {
+extern "C" int lse_rope_kv_write(const void* qkv, int in_dtype, int n_partials, long long partial_stride,
+                                 const float* bias, const int* positions, const int* slot_mapping,
+                                 const float* inv_freq, void* q_out, void* k_cache, void* v_cache, int out_dtype,
+                                 int tokens, int n_q, int n_kv, int head_dim, int page_size, int pairing,
+                                 long long qkv_stride, cudaStream_t stream) {
   if (tokens <= 0) return 0;
-  if (head_dim % 2 || page_size <= 0 || (pairing != 0 && pairing != 1)) return LSE_ERR_BAD_ARGUMENT;
-  dim3 grid(tokens, n_q + 2 * n_kv);
-  const int threads = head_dim >= 128 ? 64 : 32;
-  if (dtype == LSE_DTYPE_F32)
-    rope_kv_write_kernel<float><<<grid, threads, 0, stream>>>(
-        (const float*)qkv, bias, positions, slot_mapping, inv_freq, (float*)q_out, (float*)k_cache,
-        (float*)v_cache, n_q, n_kv, head_dim, page_size, pairing, qkv_stride);
-  else if (dtype == LSE_DTYPE_BF16)
-    rope_kv_write_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
-        (const __nv_bfloat16*)qkv, bias, positions, slot_mapping, inv_freq, (__nv_bfloat16*)q_out,
-        (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, n_q, n_kv, head_dim, page_size, pairing,
-        qkv_stride);
-  else
+  if (head_dim % 2 || head_dim > 1024 || page_size <= 0 || (pairing != 0 && pairing != 1) || n_partials < 1)
     return LSE_ERR_BAD_ARGUMENT;
+  const int half = head_dim / 2;
+  int head_groups = 256 / half;
+  if (head_groups < 1) head_groups = 1;
+  if (head_groups > n_q + n_kv) head_groups = n_q + n_kv;
+  const int threads = half * head_groups;
+#define LSE_ROPE_CASE(TI, TO)                                                                                   \
+  rope_kv_write_kernel<TI, TO><<<tokens, threads, 0, stream>>>(                                                 \
+      (const TI*)qkv, n_partials, partial_stride, bias, positions, slot_mapping, inv_freq, (TO*)q_out,          \
+      (TO*)k_cache, (TO*)v_cache, n_q, n_kv, head_dim, page_size, pairing, qkv_stride)
+  if (in_dtype == LSE_DTYPE_F32 && out_dtype == LSE_DTYPE_F32) LSE_ROPE_CASE(float, float);
+  else if (in_dtype == LSE_DTYPE_BF16 && out_dtype == LSE_DTYPE_BF16) LSE_ROPE_CASE(__nv_bfloat16, __nv_bfloat16);
+  else if (in_dtype == LSE_DTYPE_F32 && out_dtype == LSE_DTYPE_BF16) LSE_ROPE_CASE(float, __nv_bfloat16);
+  else return LSE_ERR_BAD_ARGUMENT;
+#undef LSE_ROPE_CASE
   LSE_LAUNCH_CHECK();
 }
 
 // ------------------------------------------------------------------ SiLU gate
 // gate_up[t] = [gate (I values) | up (I values)];  out[t, i] = silu(gate_i) * up_i
-template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter,
-                                long long total) {
-  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= total) return;
-  const long long t = idx / inter;
-  const int i = (int)(idx - t * inter);
-  const float g = to_f32<T>(gate_up[t * 2 * inter + i]);
-  const float u = to_f32<T>(gate_up[t * 2 * inter + inter + i]);
-  const float s = g / (1.0f + expf(-g));
-  out[idx] = from_f32<T>(s * u);
+// grid: (chunks of the row, tokens); a thread handles 4 consecutive i when I % 4 == 0.
+template <typename TI, typename TO, int VEC>
+__global__ void silu_mul_kernel(const TI* __restrict__ gate_up, int n_partials, long long partial_stride,
+                                TO* __restrict__ out, int inter) {
+  const int t = blockIdx.y;
+  const int i = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
+  if (i >= inter) return;
+  const TI* row = gate_up + (size_t)t * 2 * inter;
+  float g[4] = {0.f, 0.f, 0.f, 0.f}, u[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int p = 0; p < n_partials; ++p) {
+    if (VEC == 4) {
+      float a[4], b[4];
+      load4<TI>(row + (size_t)p * partial_stride + i, a);
+      load4<TI>(row + (size_t)p * partial_stride + inter + i, b);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) { g[e] += a[e]; u[e] += b[e]; }
+    } else {
+      g[0] += to_f32<TI>(row[(size_t)p * partial_stride + i]);
+      u[0] += to_f32<TI>(row[(size_t)p * partial_stride + inter + i]);
+    }
+  }
+  float y[4];
+#pragma unroll
+  for (int e = 0; e < VEC; ++e) y[e] = (g[e] / (1.0f + expf(-g[e]))) * u[e];
+  TO* dst = out + (size_t)t * inter + i;
+  if (VEC == 4) store4<TO>(dst, y);
+  else dst[0] = from_f32<TO>(y[0]);
 }
 
-extern "C" int lse_silu_mul(const void* gate_up, void* out, int dtype, int tokens, int inter,
-                            cudaStream_t stream) {
-  const long long total = (long long)tokens * inter;
-  if (total <= 0) return 0;
+extern "C" int lse_silu_mul(const void* gate_up, int in_dtype, int n_partials, long long partial_stride, void* out,
+                            int out_dtype, int tokens, int inter, cudaStream_t stream) {
+  if (tokens <= 0 || inter <= 0) return 0;
+  if (n_partials < 1) return LSE_ERR_BAD_ARGUMENT;
+  const bool vec = inter % 4 == 0 && partial_stride % 4 == 0 && (((uintptr_t)gate_up | (uintptr_t)out) & 15) == 0;
   const int threads = 256;
-  const unsigned blocks = (unsigned)((total + threads - 1) / threads);
-  if (dtype == LSE_DTYPE_F32)
-    silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, inter, total);
-  else if (dtype == LSE_DTYPE_BF16)
-    silu_mul_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total);
-  else
-    return LSE_ERR_BAD_ARGUMENT;
+  const int per_row = vec ? inter / 4 : inter;
+  dim3 grid((per_row + threads - 1) / threads, tokens);
+#define LSE_SILU_CASE(TI, TO)                                                                                      \
+  if (vec) silu_mul_kernel<TI, TO, 4><<<grid, threads, 0, stream>>>((const TI*)gate_up, n_partials, partial_stride, \
+                                                                    (TO*)out, inter);                              \
+  else silu_mul_kernel<TI, TO, 1><<<grid, threads, 0, stream>>>((const TI*)gate_up, n_partials, partial_stride,     \
+                                                                (TO*)out, inter)
+  if (in_dtype == LSE_DTYPE_F32 && out_dtype == LSE_DTYPE_F32) { LSE_SILU_CASE(float, float); }
+  else if (in_dtype == LSE_DTYPE_BF16 && out_dtype == LSE_DTYPE_BF16) { LSE_SILU_CASE(__nv_bfloat16, __nv_bfloat16); }
+  else if (in_dtype == LSE_DTYPE_F32 && out_dtype == LSE_DTYPE_BF16) { LSE_SILU_CASE(float, __nv_bfloat16); }
+  else return LSE_ERR_BAD_ARGUMENT;
+#undef LSE_SILU_CASE
   LSE_LAUNCH_CHECK();
 }

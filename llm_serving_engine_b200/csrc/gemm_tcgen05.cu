@@ -1,0 +1,274 @@
+// bfloat16 matrix product for few rows (decoding): out[m, n] = sum_k x[m, k] * w[n, k]
+// on the 5th-generation tensor cores, written to stream the weights at HBM speed.
+//
+// The product is turned around so that the weights ride the wide side of the
+// instruction: one block owns 128 rows of w (the M side of tcgen05.mma, 128 TMEM
+// lanes) and all rows of x (the N side, padded to 16/32/.../256 columns).  Tiles
+// of 64 k-values are brought in by TMA (128-byte swizzle) through a ring of
+// mbarrier-guarded stages; one thread issues the MMAs, the accumulator lives in
+// tensor memory, and the four warps read it back with tcgen05.ld.  The k range may
+// be split over blockIdx.y; every split writes its own float32 partial sums
+// out[split][m][n], and the consumer (norm, rotary, SiLU kernels) adds the partials
+// in index order, so results do not depend on timing.
+//
+// Every wait on an mbarrier is bounded: when it gives up, the block sets
+// lse_gemm_error (readable with lse_gemm_bf16_skinny_status), skips its output,
+// frees its tensor memory and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+constexpr int BLOCK_N = 128;  // rows of w per block (UMMA M)
+constexpr int BLOCK_K = 64;   // k-values per stage: 128-byte rows
+constexpr int UMMA_K = 16;
+constexpr uint32_t A_BYTES = BLOCK_N * BLOCK_K * 2;
+constexpr uint32_t SPIN_LIMIT = 1u << 22;
+
+__device__ int lse_gemm_error;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Bounded wait for the phase with the given parity.  false: gave up (or another thread did).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}\n"
+        : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    if (done) return true;
+    if (*abort_flag) return false;
+  }
+  *abort_flag = 1;
+  atomicExch(&lse_gemm_error, 1);
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+// Shared-memory matrix descriptor: K-major tile, rows of 128 bytes, SWIZZLE_128B,
+// groups of 8 rows 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFFu) >> 4);   // start address, 16-byte units           bits [0,14)
+  d |= (uint64_t)1 << 16;                    // leading byte offset (not used here)    bits [16,30)
+  d |= (uint64_t)(1024 >> 4) << 32;          // stride byte offset between row groups  bits [32,46)
+  d |= (uint64_t)1 << 46;                    // descriptor version of sm_100           bits [46,48)
+  d |= (uint64_t)2 << 61;                    // SWIZZLE_128B                           bits [61,64)
+  return d;
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}\n"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+
+// grid: (ceil(N / 128), splits); block: 128 threads; dynamic shared memory:
+// stages * (16 KiB + m_pad * 128 B) + alignment slack + barriers.
+__global__ void __launch_bounds__(128)
+gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                        float* __restrict__ out, int M, int N, int k_tiles, int tiles_per_split, int m_pad,
+                        int stages) {
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t b_bytes = (uint32_t)m_pad * BLOCK_K * 2;
+  const uint32_t stage_bytes = A_BYTES + b_bytes;
+  const uint32_t bars = base + (uint32_t)stages * stage_bytes;   // full[stages], empty[stages], accum
+  const uint32_t accum_bar = bars + 16u * stages;
+  unsigned char* tail = smem_raw + (bars - smem_u32(smem_raw)) + 16 * stages + 8;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * BLOCK_N;
+  const int tile_lo = blockIdx.y * tiles_per_split;
+  const int n_tiles = min(k_tiles, tile_lo + tiles_per_split) - tile_lo;   // >= 1 by the launcher's choice of splits
+  const uint32_t tmem_cols = m_pad < 32 ? 32u : (uint32_t)m_pad;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(bars + 8u * s, 1);
+      mbar_init(bars + 8u * (stages + s), 1);
+    }
+    mbar_init(accum_bar, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+  }
+  if (warp == 0) {   // one warp allocates the accumulator columns
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
+                 ::"r"(smem_u32(tmem_slot)), "r"(tmem_cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {   // producer: TMA loads into the ring
+      for (int it = 0; it < n_tiles; ++it) {
+        const int s = it % stages;
+        const uint32_t parity = (uint32_t)(it / stages) & 1u;
+        if (!mbar_wait(bars + 8u * (stages + s), parity ^ 1u, abort_flag)) break;
+        const uint32_t full = bars + 8u * s;
+        mbar_expect_tx(full, stage_bytes);
+        const uint32_t a_dst = base + (uint32_t)s * stage_bytes;
+        const int k = (tile_lo + it) * BLOCK_K;
+        tma_load_2d(a_dst, &map_w, full, k, n0);
+        tma_load_2d(a_dst + A_BYTES, &map_x, full, k, 0);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {   // MMA issuer
+      // instruction descriptor: D float32, A and B bfloat16, both K-major, N = m_pad, M = 128
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(m_pad >> 3) << 17) |
+                             ((uint32_t)(BLOCK_N >> 4) << 24);
+      bool ok = true;
+      for (int it = 0; it < n_tiles && ok; ++it) {
+        const int s = it % stages;
+        const uint32_t parity = (uint32_t)(it / stages) & 1u;
+        ok = mbar_wait(bars + 8u * s, parity, abort_flag);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        const uint32_t a_src = base + (uint32_t)s * stage_bytes;
+#pragma unroll
+        for (int kk = 0; kk < BLOCK_K / UMMA_K; ++kk) {
+          const uint64_t da = smem_desc(a_src + kk * UMMA_K * 2);
+          const uint64_t db = smem_desc(a_src + A_BYTES + kk * UMMA_K * 2);
+          umma_bf16(tmem_base, da, db, idesc, (it | kk) != 0 ? 1u : 0u);
+        }
+        umma_commit(bars + 8u * (stages + s));   // the stage is free once these MMAs have read it
+      }
+      if (ok) umma_commit(accum_bar);            // the accumulator is complete
+    }
+    __syncwarp();
+  }
+
+  // epilogue: warp w reads TMEM lanes 32w .. 32w+31 (rows n0 + 32w + lane of w), all m_pad columns
+  const bool ready = mbar_wait(accum_bar, 0, abort_flag);
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+  if (ready) {
+    const int n = n0 + warp * 32 + lane;
+    float* dst = out + (size_t)blockIdx.y * M * N + n;
+    for (int c0 = 0; c0 < m_pad; c0 += 8) {
+      uint32_t r[8];
+      const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0;
+      asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];\n"
+                   : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                   : "r"(taddr));
+      asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+      if (n < N) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          if (c0 + i < M) dst[(size_t)(c0 + i) * N] = __uint_as_float(r[i]);
+      }
+    }
+  } else if (threadIdx.x == 0) {
+    // a wait gave up: give copies that may still be in flight time to land before the block leaves
+    for (int i = 0; i < 2000; ++i) __nanosleep(100);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  if (warp == 0)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult status;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &status) == cudaSuccess &&
+        status == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// Tensor map of a row-major bfloat16 matrix [rows, cols]; box = [box_rows, 64 columns], 128-byte swizzle.
+bool make_map(CUtensorMap* map, const void* ptr, int rows, int cols, int box_rows) {
+  EncodeTiledFn fn = encode_tiled();
+  if (fn == nullptr) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)BLOCK_K, (cuuint32_t)box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+}  // namespace
+
+// Rows of x are padded to this many columns of the instruction (0: more rows than the kernel takes).
+extern "C" int lse_gemm_bf16_skinny_pad(int M) {
+  for (int pad = 16; pad <= 256; pad *= 2)
+    if (M <= pad) return pad;
+  return 0;
+}
+
+// How many k-splits the launcher will really use for a wish of `splits` (every split gets work).
+extern "C" int lse_gemm_bf16_skinny_splits(int K, int splits) {
+  const int k_tiles = (K + BLOCK_K - 1) / BLOCK_K;
+  if (splits < 1) splits = 1;
+  if (splits > k_tiles) splits = k_tiles;
+  const int per = (k_tiles + splits - 1) / splits;
+  return (k_tiles + per - 1) / per;
+}
+
+// 0: no bounded wait has given up since the library was loaded (synchronises the device).
+extern "C" int lse_gemm_bf16_skinny_status(void) {
+  int value = 0;
+  if (cudaMemcpyFromSymbol(&value, lse_gemm_error, sizeof(int)) != cudaSuccess) return -1;
+  return value;
+}
+
+// out[split][m][n] (float32, splits * M * N values) = partial sums of x[M, K] * w[N, K]^T.
+// x, w bfloat16 row-major, 16-byte aligned, K a multiple of 8, M <= 256.
+extern "C" int lse_gemm_bf16_skinny(const void* x, const void* w, float* out, int M, int N, int K, int splits,
+                                    int stages, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  const int m_pad = lse_gemm_bf16_skinny_pad(M);
+  if (m_pad == 0 || K <= 0 || K % 8 || (((uintptr_t)x | (uintptr_t)w) & 15)) return LSE_ERR_BAD_ARGUMENT;
+  const int k_tiles = (K + BLOCK_K - 1) / BLOCK_K;
+  splits = lse_gemm_bf16_skinny_splits(K, splits);
+  const int per = (k_tiles + splits - 1) / splits;
+  const uint32_t stage_bytes = A_BYTES + (uint32_t)m_pad * BLOCK_K * 2;
+  if (stages < 2) stages = 2;
+  while (stages > 2 && (size_t)stages * stage_bytes + 2048 > 200 * 1024) --stages;
+  if (stages > per + 1) stages = per + 1 < 2 ? 2 : per + 1;
+  const size_t smem = (size_t)stages * stage_bytes + 1024 + 16 * (size_t)stages + 64;
+  CUtensorMap map_w, map_x;
+  if (!make_map(&map_w, w, N, K, BLOCK_N) || !make_map(&map_x, x, M, K, m_pad)) return LSE_ERR_BAD_ARGUMENT;
+  static size_t configured = 0;   // largest dynamic shared memory asked for so far
+  if (smem > configured) {
+    cudaError_t err = cudaFuncSetAttribute(gemm_bf16_skinny_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (err != cudaSuccess) return (int)err;
+    configured = smem;
+  }
+  dim3 grid((N + BLOCK_N - 1) / BLOCK_N, splits);
+  gemm_bf16_skinny_kernel<<<grid, 128, smem, stream>>>(map_w, map_x, out, M, N, k_tiles, per, m_pad, stages);
+  return (int)cudaGetLastError();
+}

@@ -44,29 +44,40 @@ def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> torc
     return out
 
 
+def _partials(tensor: torch.Tensor | None, rows: int, width: int):
+    """(tensor, number of partial sums, elements between them) of a [rows, width] tensor or a
+    float32 stack of partial sums [P, rows, width]."""
+    if tensor is None:
+        return None, 1, 0
+    if tensor.dim() == 3:
+        assert tensor.dtype == torch.float32 and tensor.shape[1:] == (rows, width) and tensor.is_contiguous()
+        return tensor, tensor.shape[0], rows * width
+    assert tensor.shape == (rows, width) and tensor.is_contiguous()
+    return tensor, 1, 0
+
+
 def add_rmsnorm(residual: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float,
                 out: torch.Tensor, rows: torch.Tensor | None = None, write_residual: bool = True) -> torch.Tensor:
     """residual (+= delta); out = rmsnorm(residual) * weight.
 
-    residual float32 [T, H]; delta [T, H] float32/bfloat16 or None; weight
-    float32 [H]; out [R, H] float32/bfloat16 where R = len(rows) when ``rows``
-    (int32 row indices into residual) is given, else T.  With ``rows`` the
-    residual is left unchanged unless ``write_residual``.
+    residual float32 [T, H]; delta [T, H] float32/bfloat16, a float32 stack of partial sums
+    [P, T, H] (added in index order), or None; weight float32 [H]; out [R, H]
+    float32/bfloat16 where R = len(rows) when ``rows`` (int32 row indices into residual) is
+    given, else T.  With ``rows`` the residual is left unchanged unless ``write_residual``.
     """
     _need_cuda(residual, delta, weight, out, rows)
-    hidden = residual.shape[-1]
+    tokens, hidden = residual.shape
     assert residual.dtype == torch.float32 and weight.dtype == torch.float32 and weight.shape == (hidden,)
     assert residual.is_contiguous() and out.is_contiguous() and out.shape[-1] == hidden
-    if delta is not None:
-        assert delta.shape == residual.shape and delta.is_contiguous()
+    delta, n_partials, stride = _partials(delta, tokens, hidden)
     n_rows = out.shape[0]
     if rows is not None:
         assert rows.dtype == torch.int32 and rows.shape[0] == n_rows
     else:
-        assert n_rows == residual.shape[0]
+        assert n_rows == tokens
     lib = library.load()
     delta_code = dtype_code(delta.dtype) if delta is not None else dtype_code(out.dtype)
-    check(lib.lse_add_rmsnorm(residual.data_ptr(), _ptr(delta), delta_code, weight.data_ptr(),
+    check(lib.lse_add_rmsnorm(residual.data_ptr(), _ptr(delta), delta_code, n_partials, stride, weight.data_ptr(),
                               out.data_ptr(), dtype_code(out.dtype), _ptr(rows), n_rows, hidden,
                               float(eps), int(write_residual), _stream()), "add_rmsnorm")
     return out
@@ -93,25 +104,33 @@ def rope_kv_write(qkv: torch.Tensor, bias: torch.Tensor | None, positions: torch
                   k_cache: torch.Tensor, v_cache: torch.Tensor, n_q: int, n_kv: int, head_dim: int,
                   pairing: int) -> None:
     """Bias, rotary encoding of queries and keys, and the write of keys and values
-    into the paged cache (k_cache/v_cache: [pages, n_kv, page_size, head_dim])."""
+    into the paged cache (k_cache/v_cache: [pages, n_kv, page_size, head_dim]).
+    ``qkv`` is [T, width] in the cache's dtype or in float32, or a float32 stack of
+    partial sums [P, T, width]."""
     _need_cuda(qkv, bias, positions, slot_mapping, inv_freq, q_out, k_cache, v_cache)
-    tokens = qkv.shape[0]
     width = (n_q + 2 * n_kv) * head_dim
-    assert qkv.shape[1] == width and qkv.stride(1) == 1
+    tokens = qkv.shape[-2]
+    if qkv.dim() == 3:
+        qkv, n_partials, stride = _partials(qkv, tokens, width)
+        row_stride = width
+    else:
+        assert qkv.shape[1] == width and qkv.stride(1) == 1
+        n_partials, stride, row_stride = 1, 0, qkv.stride(0)
     assert positions.dtype == torch.int32 and slot_mapping.dtype == torch.int32
     assert positions.shape[0] >= tokens and slot_mapping.shape[0] >= tokens
     assert inv_freq.dtype == torch.float32 and inv_freq.shape == (head_dim // 2,)
-    assert q_out.dtype == qkv.dtype == k_cache.dtype == v_cache.dtype
+    assert q_out.dtype == k_cache.dtype == v_cache.dtype
     assert q_out.is_contiguous() and q_out.shape == (tokens, n_q, head_dim)
     assert k_cache.is_contiguous() and v_cache.is_contiguous()
     assert k_cache.shape[1] == n_kv and k_cache.shape[3] == head_dim and v_cache.shape == k_cache.shape
     if bias is not None:
         assert bias.dtype == torch.float32 and bias.shape == (width,)
     lib = library.load()
-    check(lib.lse_rope_kv_write(qkv.data_ptr(), dtype_code(qkv.dtype), _ptr(bias), positions.data_ptr(),
-                                slot_mapping.data_ptr(), inv_freq.data_ptr(), q_out.data_ptr(),
-                                k_cache.data_ptr(), v_cache.data_ptr(), tokens, n_q, n_kv, head_dim,
-                                k_cache.shape[2], pairing, qkv.stride(0), _stream()), "rope_kv_write")
+    check(lib.lse_rope_kv_write(qkv.data_ptr(), dtype_code(qkv.dtype), n_partials, stride, _ptr(bias),
+                                positions.data_ptr(), slot_mapping.data_ptr(), inv_freq.data_ptr(),
+                                q_out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), dtype_code(q_out.dtype),
+                                tokens, n_q, n_kv, head_dim, k_cache.shape[2], pairing, row_stride, _stream()),
+          "rope_kv_write")
 
 
 def paged_attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
@@ -209,15 +228,50 @@ def paged_attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
 
 
 def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
+    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]; ``gate_up`` is [T, 2I] or a float32
+    stack of partial sums [P, T, 2I]."""
     _need_cuda(gate_up, out)
-    tokens, two_i = gate_up.shape
-    assert two_i % 2 == 0 and out.shape == (tokens, two_i // 2)
-    assert gate_up.is_contiguous() and out.is_contiguous() and gate_up.dtype == out.dtype
+    tokens, two_i = gate_up.shape[-2], gate_up.shape[-1]
+    assert two_i % 2 == 0 and out.shape == (tokens, two_i // 2) and out.is_contiguous()
+    gate_up, n_partials, stride = _partials(gate_up, tokens, two_i)
     lib = library.load()
-    check(lib.lse_silu_mul(gate_up.data_ptr(), out.data_ptr(), dtype_code(out.dtype), tokens, two_i // 2,
-                           _stream()), "silu_mul")
+    check(lib.lse_silu_mul(gate_up.data_ptr(), dtype_code(gate_up.dtype), n_partials, stride, out.data_ptr(),
+                           dtype_code(out.dtype), tokens, two_i // 2, _stream()), "silu_mul")
     return out
+
+
+GEMM_SKINNY_MAX_ROWS = 256
+
+
+def gemm_bf16_skinny_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    """Whether the few-rows tensor-core product takes these operands."""
+    return (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.shape[0] <= GEMM_SKINNY_MAX_ROWS
+            and x.shape[1] % 8 == 0 and x.is_contiguous() and weight.is_contiguous()
+            and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
+
+
+def gemm_bf16_skinny(x: torch.Tensor, weight: torch.Tensor, splits: int | None = None, stages: int = 6) -> torch.Tensor:
+    """Partial sums [P, M, N] (float32) of x[M, K] @ weight[N, K]^T for M <= 256, bfloat16 operands;
+    the k range is cut into P splits so that enough blocks stream the weights."""
+    _need_cuda(x, weight)
+    m, k = x.shape
+    n = weight.shape[0]
+    if not gemm_bf16_skinny_ok(x, weight) or weight.shape[1] != k:
+        raise KernelError("gemm_bf16_skinny: operands must be contiguous bfloat16, K a multiple of 8, at most 256 rows")
+    lib = library.load()
+    if splits is None:
+        n_tiles = -(-n // 128)
+        splits = max(1, min(-(-k // 128), round(296 / n_tiles))) if n_tiles < 148 else 1
+    splits = lib.lse_gemm_bf16_skinny_splits(k, int(splits))
+    out = torch.empty((splits, m, n), dtype=torch.float32, device=x.device)
+    check(lib.lse_gemm_bf16_skinny(x.data_ptr(), weight.data_ptr(), out.data_ptr(), m, n, k, splits, int(stages),
+                                   _stream()), "gemm_bf16_skinny")
+    return out
+
+
+def gemm_bf16_skinny_status() -> int:
+    """0 unless a bounded wait inside the kernel has given up (synchronises the device)."""
+    return int(library.load().lse_gemm_bf16_skinny_status())
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> torch.Tensor:

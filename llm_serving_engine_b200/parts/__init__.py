@@ -3,11 +3,11 @@ from .base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, Blo
                    FeedForward, Mixer, Norm, PagedKV, Part, PositionEncoding, RequestState,
                    ResidualStream, register_block, register_feed_forward, register_mixer,
                    register_norm, register_position_encoding)
-from .linear import linear
+from .linear import linear, linear_partials, reduce_partials
 
 __all__ = [
     "BLOCKS", "FEED_FORWARDS", "MIXERS", "NORMS", "POSITION_ENCODINGS", "Block", "BuildContext",
     "FeedForward", "Mixer", "Norm", "PagedKV", "Part", "PositionEncoding", "RequestState",
-    "ResidualStream", "linear", "register_block", "register_feed_forward", "register_mixer",
+    "ResidualStream", "linear", "linear_partials", "reduce_partials", "register_block", "register_feed_forward", "register_mixer",
     "register_norm", "register_position_encoding",
 ]

@@ -9,7 +9,7 @@ import torch
 from ..kernels import ops
 from ..weights.tensor_spec import TensorSpec
 from .base import POSITION_ENCODINGS, Mixer, PagedKV, register_mixer
-from .linear import linear
+from .linear import linear_partials
 
 
 @register_mixer("gqa_attention")
@@ -66,7 +66,7 @@ class GroupedQueryAttention(Mixer):
 
     def forward(self, x, step, cache):
         tokens = x.shape[0]
-        qkv = linear(x, self.qkv_weight)  # bias is added with the rotation, in float32
+        qkv = linear_partials(x, self.qkv_weight)  # bias is added with the rotation, in float32
         q = torch.empty((tokens, self.n_q, self.head_dim), dtype=x.dtype, device=x.device)
         self.position.encode_and_store(qkv, self.qkv_bias, step, cache, q, self.n_q, self.n_kv, self.head_dim)
         attended = torch.empty_like(q)
@@ -81,4 +81,4 @@ class GroupedQueryAttention(Mixer):
         else:   # float32, other head sizes, windows: the general kernel
             ops.paged_attention_generic(q, cache.keys, cache.values, attended, cache.block_tables,
                                         step.segment_of_token, step.positions, self.scale, self.window)
-        return linear(attended.view(tokens, self.n_q * self.head_dim), self.o_weight)
+        return linear_partials(attended.view(tokens, self.n_q * self.head_dim), self.o_weight)

@@ -8,7 +8,9 @@ configuration), ``weights`` (its own tensors, by their local names) and a
                        output to the float32 residual, returns the normalised rows)
 * ``PositionEncoding``: ``encode_and_store(...)`` (rotates queries and keys and
                        writes keys and values into the layer's cache pages)
-* ``Mixer``:           ``forward(x, step, cache) -> y`` over the step's flat rows,
+* ``Mixer``:           ``forward(x, step, cache) -> y`` over the step's flat rows
+                       (y is [T, H], or a float32 stack of partial sums [P, T, H]
+                       that the next norm adds up; ``reduce_partials`` gives [T, H]),
                        reading and writing its layer's cache; ``cache_requirement``
                        says what it needs (pages of keys and values, or a
                        fixed-size state per request, or nothing)

@@ -1,14 +1,35 @@
 """Matrix products of the layers: y = x W^T (+ b), W kept [out, in].
 
 float32: the engine's own FMA kernel (true 32-bit, fixed summation order).
-bfloat16: the library product with float32 accumulation, where the reference
-uses ``nn.Linear`` (``src/llmserve/model.py:51-66,183-185,248``).
+bfloat16, few rows (decoding): the engine's tcgen05 kernel, which streams the
+weights with TMA and may cut the k range into splits; it returns a float32 stack
+of partial sums [P, rows, out] that the next kernel (norm, rotary, SiLU) adds up.
+bfloat16, many rows: the library product with float32 accumulation, where the
+reference uses ``nn.Linear`` (``src/llmserve/model.py:51-66,183-185,248``).
 """
 from __future__ import annotations
 
 import torch
 
 from ..kernels import ops
+
+SKINNY_MAX_ROWS = 32   # above this the split-k partial sums cost more than they save
+
+
+def reduce_partials(y: torch.Tensor) -> torch.Tensor:
+    """[rows, out] from a branch output that may be a stack of partial sums [P, rows, out]."""
+    if y.dim() == 3:
+        return y[0] if y.shape[0] == 1 else y.sum(0)
+    return y
+
+
+def linear_partials(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """x W^T as [rows, out] or, for few bfloat16 rows, as a float32 stack of partial sums
+    [P, rows, out].  For callers whose consumer kernel adds the partials itself."""
+    if (x.is_cuda and weight.dtype == torch.bfloat16 and x.shape[0] <= SKINNY_MAX_ROWS
+            and ops.gemm_bf16_skinny_ok(x, weight)):
+        return ops.gemm_bf16_skinny(x, weight)
+    return linear(x, weight)
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
@@ -22,7 +43,10 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
     if weight.dtype != torch.bfloat16 or x.dtype != torch.bfloat16:
         raise ops.KernelError(f"linear: unsupported dtypes {x.dtype} x {weight.dtype}")
     if out_dtype == torch.float32:
-        y = torch.mm(x, weight.t(), out_dtype=torch.float32)
+        if rows <= SKINNY_MAX_ROWS and ops.gemm_bf16_skinny_ok(x, weight):
+            y = reduce_partials(ops.gemm_bf16_skinny(x, weight))
+        else:
+            y = torch.mm(x, weight.t(), out_dtype=torch.float32)
         return y if bias is None else y + bias
     y = torch.mm(x, weight.t())
     return y if bias is None else y + bias.to(y.dtype)

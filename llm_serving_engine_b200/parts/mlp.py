@@ -6,7 +6,7 @@ import torch
 from ..kernels import ops
 from ..weights.tensor_spec import TensorSpec
 from .base import FeedForward, register_feed_forward
-from .linear import linear
+from .linear import linear_partials
 
 
 @register_feed_forward("swiglu")
@@ -30,7 +30,7 @@ class SwiGLU(FeedForward):
         }
 
     def forward(self, x):
-        gate_up = linear(x, self.gate_up_weight)
+        gate_up = linear_partials(x, self.gate_up_weight)
         act = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
         ops.silu_mul(gate_up, act)
-        return linear(act, self.down_weight)
+        return linear_partials(act, self.down_weight)

@@ -442,3 +442,82 @@ def test_prefill_attention_keeps_the_causal_edge():
         pos = before + local
         want = dense_attention(q[local], k[:pos + 1], v[:pos + 1], scale)
         assert float((out[local].double() - want).abs().max()) < 2.0 ** -6, local
+
+
+# ------------------------------------------------------------------ tcgen05 product and partial-sum inputs
+@pytest.mark.parametrize("m, n, k, splits", [(1, 128, 64, 1), (8, 2048, 1536, 12), (3, 1536, 8960, 24), (16, 1000, 776, 3),
+                                             (32, 17920, 1536, None), (7, 151936, 1536, None), (200, 384, 520, 2),
+                                             (256, 130, 72, 5), (17, 96, 8, 4)])
+def test_few_rows_product_on_tensor_cores(m, n, k, splits):
+    torch.manual_seed(m + n + k)
+    x = torch.randn(m, k, device=DEV).bfloat16()
+    w = (torch.randn(n, k, device=DEV) * 0.05).bfloat16()
+    parts = ops().gemm_bf16_skinny(x, w, splits)
+    assert parts.dtype == torch.float32 and parts.shape[1:] == (m, n)
+    got = parts.double().sum(0)
+    want = x.double() @ w.double().t()
+    # float32 accumulation of exact bfloat16 products
+    bound = (x.abs().double() @ w.abs().double().t()) * (k * 2.0 ** -24) + 1e-6
+    assert bool(((got - want).abs() <= bound).all()), float((got - want).abs().max())
+    assert ops().gemm_bf16_skinny_status() == 0
+
+
+def test_few_rows_product_refuses_what_it_cannot_run():
+    from llm_serving_engine_b200.kernels.library import KernelError
+    x = torch.randn(4, 100, device=DEV).bfloat16()      # k not a multiple of 8
+    w = torch.randn(64, 100, device=DEV).bfloat16()
+    assert not ops().gemm_bf16_skinny_ok(x, w)
+    with pytest.raises(KernelError):
+        ops().gemm_bf16_skinny(x, w)
+    assert not ops().gemm_bf16_skinny_ok(torch.randn(300, 64, device=DEV).bfloat16(), torch.randn(64, 64, device=DEV).bfloat16())
+
+
+@pytest.mark.parametrize("hidden", [77, 80, 1536, 9000])
+def test_add_rmsnorm_of_partial_sums(hidden):
+    torch.manual_seed(hidden)
+    residual = torch.randn(5, hidden, device=DEV)
+    partials = torch.randn(7, 5, hidden, device=DEV)
+    weight = 1 + 0.1 * torch.randn(hidden, device=DEV)
+    want_residual = residual.double() + partials.double().sum(0)
+    want = qwen2_plain.rms_norm(want_residual, weight.double(), 1e-6)
+    for out_dtype in (torch.float32, torch.bfloat16):
+        got_residual = residual.clone()
+        out = torch.empty(5, hidden, device=DEV, dtype=out_dtype)
+        ops().add_rmsnorm(got_residual, partials, weight, 1e-6, out)
+        assert rel_err(got_residual, want_residual) < 1e-6
+        assert rel_err(out, want) < TOL[out_dtype] * 2
+    rows = torch.tensor([4, 1], dtype=torch.int32, device=DEV)
+    picked = torch.empty(2, hidden, device=DEV)
+    keep = residual.clone()
+    ops().add_rmsnorm(keep, partials, weight, 1e-6, picked, rows=rows, write_residual=False)
+    assert torch.equal(keep, residual) and rel_err(picked, want[rows.long()]) < 4e-6
+
+
+def test_rope_and_silu_of_partial_sums():
+    torch.manual_seed(3)
+    n_q, n_kv, head_dim, page, tokens = 12, 2, 128, 16, 6
+    width = (n_q + 2 * n_kv) * head_dim
+    partials = torch.randn(5, tokens, width, device=DEV)
+    bias = torch.randn(width, device=DEV) * 0.1
+    positions = torch.tensor([0, 3, 100, 2047, 17, 18], dtype=torch.int32, device=DEV)
+    slots = torch.tensor([0, 19, 33, 5, -1, 64], dtype=torch.int32, device=DEV)
+    inv_freq = qwen2_plain.rope_inverse_frequencies(head_dim, 1e6).to(DEV)
+    q_out = torch.zeros(tokens, n_q, head_dim, device=DEV, dtype=torch.bfloat16)
+    k_cache = torch.zeros(8, n_kv, page, head_dim, device=DEV, dtype=torch.bfloat16)
+    v_cache = torch.zeros_like(k_cache)
+    ops().rope_kv_write(partials, bias, positions, slots, inv_freq, q_out, k_cache, v_cache, n_q, n_kv, head_dim, 0)
+    x = (partials.sum(0) + bias).cpu()
+    q, k, v = x.split([n_q * head_dim, n_kv * head_dim, n_kv * head_dim], dim=1)
+    want_q = qwen2_plain.rope(q.view(tokens, n_q, head_dim), positions.cpu(), 1e6)
+    want_k = qwen2_plain.rope(k.view(tokens, n_kv, head_dim), positions.cpu(), 1e6)
+    assert float((q_out.float().cpu() - want_q).abs().max()) < 2.0 ** -7 * float(want_q.abs().max())
+    for t in (0, 1, 2, 3, 5):
+        p, off = divmod(int(slots[t]), page)
+        assert float((k_cache[p, :, off].float().cpu() - want_k[t]).abs().max()) < 2.0 ** -7 * float(want_k.abs().max())
+        assert float((v_cache[p, :, off].float().cpu() - v.view(tokens, n_kv, head_dim)[t]).abs().max()) < 2.0 ** -7 * float(v.abs().max())
+    for inter in (177, 8960):
+        gate_up = torch.randn(3, 4, 2 * inter, device=DEV)
+        out = torch.empty(4, inter, device=DEV, dtype=torch.bfloat16)
+        ops().silu_mul(gate_up, out)
+        total = gate_up.double().sum(0)
+        assert rel_err(out, torch.nn.functional.silu(total[:, :inter]) * total[:, inter:]) < TOL[torch.bfloat16] * 2

@@ -10,6 +10,11 @@ from tiny_configs import ALL
 pytestmark = pytest.mark.gpu
 
 
+def reduce_partials(y):
+    from llm_serving_engine_b200.parts import reduce_partials as reduce
+    return reduce(y)
+
+
 def build(name, dtype="float32", pages=64):
     from llm_serving_engine_b200.cache import CacheManager
     from llm_serving_engine_b200.config import CacheConfig
@@ -55,7 +60,7 @@ def test_attention_mixer_with_its_position_encoding(name, dtype):
     for lo, hi in ((0, 20), (20, 21), (21, 45)):           # a portion, one token, another portion
         step, caches = runner.prepare([StepEntry("r", [0] * (hi - lo), [])])
         part = model.blocks[0].mixer.forward(x[lo:hi].to("cuda", model.dtype).contiguous(), step, caches[0])
-        got.append(part.float().cpu())
+        got.append(reduce_partials(part).float().cpu())
     got = torch.cat(got)
     limit = 2e-5 if dtype == "float32" else 2.0 ** -6
     assert float((got - want).abs().max()) < limit * max(1.0, float(want.abs().max()))
@@ -69,7 +74,7 @@ def test_feed_forward_part(name, dtype):
     if dtype == "bfloat16":
         x = x.bfloat16().float()
     want = qwen2_plain.swiglu(x, weights, "model.layers.0.mlp.")
-    got = model.blocks[0].feed_forward.forward(x.to("cuda", model.dtype)).float().cpu()
+    got = reduce_partials(model.blocks[0].feed_forward.forward(x.to("cuda", model.dtype))).float().cpu()
     limit = 2e-5 if dtype == "float32" else 2.0 ** -6
     assert float((got - want).abs().max()) < limit * max(1.0, float(want.abs().max()))
 
@@ -86,5 +91,5 @@ def test_block_arrangement(name):
     step, caches = runner.prepare([StepEntry("r", [0] * length, [])])
     stream = ResidualStream(h.cuda())
     model.blocks[0].forward(stream, step, caches[0])
-    got = (stream.residual + stream.delta.float()).cpu()      # the last branch output is still pending
+    got = (stream.residual + reduce_partials(stream.delta).float()).cpu()      # the last branch output is still pending
     assert float((got - want).abs().max()) < 2e-5 * max(1.0, float(want.abs().max()))
