@@ -34,6 +34,8 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
                                const int* __restrict__ positions, int n_q, int n_kv, int head_dim,
                                int page_size, float scale, int window) {
   extern __shared__ float smem[];
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const int kv_head = blockIdx.y;
   const int group = n_q / n_kv;
@@ -179,11 +181,11 @@ extern "C" int lse_paged_attention_generic(const void* q, const void* k_cache, c
     configured = true;
   }
   if (dtype == LSE_DTYPE_F32) {
-    paged_attention_generic_kernel<float><<<grid, THREADS, smem, stream>>>(
+    lse_launch(paged_attention_generic_kernel<float>, grid, THREADS, smem, stream,
         (const float*)q, (const float*)k_cache, (const float*)v_cache, (float*)out, block_tables,
         bt_stride, segment_of_token, positions, n_q, n_kv, head_dim, page_size, scale, window);
   } else if (dtype == LSE_DTYPE_BF16) {
-    paged_attention_generic_kernel<__nv_bfloat16><<<grid, THREADS, smem, stream>>>(
+    lse_launch(paged_attention_generic_kernel<__nv_bfloat16>, grid, THREADS, smem, stream,
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
         (__nv_bfloat16*)out, block_tables, bt_stride, segment_of_token, positions, n_q, n_kv,
         head_dim, page_size, scale, window);

@@ -4,8 +4,8 @@
 //   * attn_decode_kernel: every row of the step is a single decoded token.  One
 //     block = (row, kv head, split of the keys); its 4 warps walk different 16-key
 //     tiles (cp.async pipeline per warp), merge in shared memory and write either
-//     the result or an unnormalised partial (split-KV), which attn_combine_kernel
-//     reduces in a fixed order.
+//     the result or an unnormalised partial (split-KV); the split that finishes last
+//     (an arrival counter, no waiting) adds the partials up in split order.
 //   * attn_prefill_kernel: portions of prompts (any mix of segment lengths).  One
 //     block = (tile of consecutive rows of one request, kv head); the 64 rows of its
 //     score matrix are (row, query head of the group) pairs, so the keys and values
@@ -66,7 +66,7 @@ template <int D>
 __global__ void __launch_bounds__(128)
 attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kc,
                    const __nv_bfloat16* __restrict__ vc, __nv_bfloat16* __restrict__ out,
-                   float* __restrict__ part_o, float* __restrict__ part_ml,
+                   float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ arrivals,
                    const int* __restrict__ block_tables, int bt_stride,
                    const int* __restrict__ segment_of_token, const int* __restrict__ positions,
                    int n_q, int n_kv, int page_size, float scale_log2e, int num_splits) {
@@ -75,6 +75,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* q_s = smem;                                   // [16][D] bf16
   unsigned char* kv_s = smem + TILE_BYTES;                     // [warp][stage][K|V][16][D]
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const int group = n_q / n_kv;
   const int gchunks = (group + 15) / 16;
@@ -252,27 +254,49 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
       if (d == 0) { part_ml[pidx * 2] = M; part_ml[pidx * 2 + 1] = L; }
     }
   }
-}
+  if (num_splits == 1) return;
 
-// out = sum_s part_o[s] 2^(m_s - M) / sum_s l_s 2^(m_s - M), splits in index order
-template <int D>
-__global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                    __nv_bfloat16* __restrict__ out, const int* __restrict__ segment_of_token,
-                                    int n_q, int num_splits) {
-  const int t = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
-  if (segment_of_token[t] < 0) return;
-  const size_t base = ((size_t)t * n_q + head) * num_splits;
-  float M = -INFINITY;
-  for (int s = 0; s < num_splits; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
-  float L = 0.f, O = 0.f;
-  for (int s = 0; s < num_splits; ++s) {
-    const float m = part_ml[(base + s) * 2];
-    if (m == -INFINITY) continue;
-    const float w = exp2f(m - M);
-    L += part_ml[(base + s) * 2 + 1] * w;
-    O += part_o[(base + s) * D + d] * w;
+  // The split that finishes last adds up all of them (in split order, so the sum does not depend
+  // on which one that is).  `arrivals` counts finished splits per (row, block column) and is put
+  // back to zero by the last one, ready for the next launch.
+  __shared__ int last_flag;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const int seen = atomicAdd(&arrivals[t * gridDim.y + blockIdx.y], 1);
+    last_flag = seen == num_splits - 1;
   }
-  out[((size_t)t * n_q + head) * D + d] = __float2bfloat16_rn(O / L);
+  __syncthreads();
+  if (!last_flag) return;
+  __threadfence();
+  // weights of the splits: w[g][sp] = 2^(m_sp - M_g) / L_g, worked out once into shared memory
+  float* w_s = mg_acc;                 // [16][32]; the merge buffers are free again
+  __syncthreads();
+  for (int e = tid; e < gcount * 32; e += 128) {
+    const int g = e >> 5, sp = e & 31;
+    const size_t pbase = ((size_t)t * n_q + first_head + g) * num_splits;
+    const float m = sp < num_splits ? __ldcg(part_ml + (pbase + sp) * 2) : -INFINITY;
+    const float l = sp < num_splits ? __ldcg(part_ml + (pbase + sp) * 2 + 1) : 0.f;
+    // the 32 lanes of a warp hold the 32 splits of one head
+    float M = m;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+    const float wgt = m == -INFINITY ? 0.f : exp2f(m - M);
+    float L = l * wgt;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
+    w_s[e] = wgt / L;
+  }
+  __syncthreads();
+  for (int e = tid; e < gcount * D; e += 128) {
+    const int g = e / D, d = e % D;
+    const float* src = part_o + ((size_t)t * n_q + first_head + g) * num_splits * D + d;
+    float O = 0.f;
+#pragma unroll 8
+    for (int sp = 0; sp < num_splits; ++sp) O += __ldcg(src + (size_t)sp * D) * w_s[g * 32 + sp];
+    out[((size_t)t * n_q + first_head + g) * D + d] = __float2bfloat16_rn(O);
+  }
+  if (tid == 0) arrivals[t * gridDim.y + blockIdx.y] = 0;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -294,6 +318,8 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* q_s = smem;                       // [64][D]
   unsigned char* kv_s = smem + PF_BM * D * 2;      // [2 stages][K|V][64][D]
+  pdl_launch_dependents();
+  pdl_wait();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int kvh = blockIdx.y;
   const int group = n_q / n_kv;
@@ -461,8 +487,8 @@ template <int D> size_t prefill_smem() { return (size_t)PF_BM * D * 2 + (size_t)
 
 template <int D>
 int launch_decode(const void* q, const void* kc, const void* vc, void* out, float* part_o, float* part_ml,
-                  const int* block_tables, int bt_stride, const int* seg, const int* positions, int tokens,
-                  int n_q, int n_kv, int page_size, float scale, int num_splits, cudaStream_t stream) {
+                  int* arrivals, const int* block_tables, int bt_stride, const int* seg, const int* positions,
+                  int tokens, int n_q, int n_kv, int page_size, float scale, int num_splits, cudaStream_t stream) {
   const size_t smem = decode_smem<D>();
   static bool configured = false;   // once per process: not repeated while a stream is captured
   if (!configured) {
@@ -472,13 +498,10 @@ int launch_decode(const void* q, const void* kc, const void* vc, void* out, floa
   }
   const int group = n_q / n_kv;
   dim3 grid(tokens, n_kv * ((group + 15) / 16), num_splits);
-  attn_decode_kernel<D><<<grid, 128, smem, stream>>>(
+  cudaError_t err = lse_launch(attn_decode_kernel<D>, grid, 128, smem, stream,
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, (__nv_bfloat16*)out, part_o,
-      part_ml, block_tables, bt_stride, seg, positions, n_q, n_kv, page_size, scale * LOG2E, num_splits);
-  if (num_splits > 1) {
-    dim3 cgrid(tokens, n_q);
-    attn_combine_kernel<D><<<cgrid, D, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, seg, n_q, num_splits);
-  }
+      part_ml, arrivals, block_tables, bt_stride, seg, positions, n_q, n_kv, page_size, scale * LOG2E, num_splits);
+  if (err != cudaSuccess) return (int)err;
   return (int)cudaGetLastError();
 }
 
@@ -497,7 +520,7 @@ int launch_prefill(const void* q, const void* kc, const void* vc, void* out, con
   const int rows_per_tile = PF_BM / group;
   const int tiles = (tokens + rows_per_tile - 1) / rows_per_tile + num_segments;   // upper bound
   dim3 grid(tiles, n_kv);
-  attn_prefill_kernel<D><<<grid, 128, smem, stream>>>(
+  lse_launch(attn_prefill_kernel<D>, grid, 128, smem, stream,
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, (__nv_bfloat16*)out,
       block_tables, bt_stride, segment_start, segment_first_pos, num_segments, n_q, n_kv, page_size,
       scale * LOG2E, rows_per_tile);
@@ -517,21 +540,24 @@ extern "C" long long lse_attention_decode_scratch_floats(int tokens, int n_q, in
   return (long long)tokens * n_q * num_splits * (head_dim + 2);
 }
 
+// `arrivals`: tokens * n_kv * ceil(group / 16) ints that are zero before the first launch (the kernel
+// leaves them zero); needed when num_splits > 1.
 extern "C" int lse_paged_attention_decode(const void* q, const void* k_cache, const void* v_cache, void* out,
-                                          float* scratch, const int* block_tables, int bt_stride,
+                                          float* scratch, int* arrivals, const int* block_tables, int bt_stride,
                                           const int* segment_of_token, const int* positions, int tokens,
                                           int n_q, int n_kv, int head_dim, int page_size, float scale,
                                           int num_splits, cudaStream_t stream) {
   if (tokens <= 0) return 0;
-  if (!lse_attention_mma_supported(head_dim, n_q, n_kv) || page_size <= 0 || num_splits < 1) return LSE_ERR_BAD_ARGUMENT;
-  if (num_splits > 1 && scratch == nullptr) return LSE_ERR_BAD_ARGUMENT;
+  if (!lse_attention_mma_supported(head_dim, n_q, n_kv) || page_size <= 0 || num_splits < 1 || num_splits > 32)
+    return LSE_ERR_BAD_ARGUMENT;
+  if (num_splits > 1 && (scratch == nullptr || arrivals == nullptr)) return LSE_ERR_BAD_ARGUMENT;
   float* part_o = scratch;
   float* part_ml = scratch ? scratch + (size_t)tokens * n_q * num_splits * head_dim : nullptr;
   if (head_dim == 128)
-    return launch_decode<128>(q, k_cache, v_cache, out, part_o, part_ml, block_tables, bt_stride, segment_of_token,
-                              positions, tokens, n_q, n_kv, page_size, scale, num_splits, stream);
-  return launch_decode<64>(q, k_cache, v_cache, out, part_o, part_ml, block_tables, bt_stride, segment_of_token,
-                           positions, tokens, n_q, n_kv, page_size, scale, num_splits, stream);
+    return launch_decode<128>(q, k_cache, v_cache, out, part_o, part_ml, arrivals, block_tables, bt_stride,
+                              segment_of_token, positions, tokens, n_q, n_kv, page_size, scale, num_splits, stream);
+  return launch_decode<64>(q, k_cache, v_cache, out, part_o, part_ml, arrivals, block_tables, bt_stride,
+                           segment_of_token, positions, tokens, n_q, n_kv, page_size, scale, num_splits, stream);
 }
 
 extern "C" int lse_paged_attention_prefill(const void* q, const void* k_cache, const void* v_cache, void* out,

@@ -63,3 +63,32 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 }
 
 #define LSE_LAUNCH_CHECK() return (int)cudaGetLastError()
+
+// ------------------------------------------------------------------ launches
+// Every kernel of the library is launched with programmatic dependent launch allowed:
+// the next kernel of the stream may be scheduled while this one still runs.  A kernel
+// calls pdl_launch_dependents() when it starts and pdl_wait() before it first touches
+// anything an earlier kernel of the stream wrote (and before it writes global memory at
+// all); what lies before pdl_wait() (setting up barriers, fetching weights) overlaps the
+// tail of the kernel before.  pdl_wait() returns when the earlier kernels have finished
+// and their writes are visible; it is a no-op when the launch carried no such permission.
+inline int lse_pdl_enabled = 1;
+
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t lse_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args&&... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = lse_pdl_enabled ? 1 : 0;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  return cudaLaunchKernelEx(&config, kernel, static_cast<Args&&>(args)...);
+}

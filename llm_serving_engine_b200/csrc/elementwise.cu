@@ -14,6 +14,8 @@
 template <typename T>
 __global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                                  float* __restrict__ out, int hidden, int vocab) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const int id = ids[t];
   float* dst = out + (size_t)t * hidden;
@@ -30,9 +32,9 @@ extern "C" int lse_embedding(const void* table, int table_dtype, const int* ids,
   if (tokens <= 0) return 0;
   const int threads = hidden >= 1024 ? 256 : 128;
   if (table_dtype == LSE_DTYPE_F32)
-    embedding_kernel<float><<<tokens, threads, 0, stream>>>((const float*)table, ids, out, hidden, vocab);
+    lse_launch(embedding_kernel<float>, tokens, threads, 0, stream, (const float*)table, ids, out, hidden, vocab);
   else if (table_dtype == LSE_DTYPE_BF16)
-    embedding_kernel<__nv_bfloat16><<<tokens, threads, 0, stream>>>((const __nv_bfloat16*)table, ids, out, hidden, vocab);
+    lse_launch(embedding_kernel<__nv_bfloat16>, tokens, threads, 0, stream, (const __nv_bfloat16*)table, ids, out, hidden, vocab);
   else
     return LSE_ERR_BAD_ARGUMENT;
   LSE_LAUNCH_CHECK();
@@ -76,6 +78,8 @@ __global__ void __launch_bounds__(NORM_THREADS)
 add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* __restrict__ delta, int n_partials,
                        long long partial_stride, const float* __restrict__ weight, TO* __restrict__ out,
                        const int* __restrict__ rows, int hidden, float eps, int write_residual) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float scratch[32];
   const int r = blockIdx.x;
   const int s = rows ? rows[r] : r;
@@ -91,6 +95,7 @@ add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* __restrict__ delt
     if (i < chunks) {
       load4<float>(res + 4 * i, x[c]);
       if (del) {
+#pragma unroll 4
         for (int p = 0; p < n_partials; ++p) {
           float d[4];
           load4<TD>(del + (size_t)p * partial_stride + 4 * i, d);
@@ -124,6 +129,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __res
                                    long long partial_stride, const float* __restrict__ weight,
                                    TO* __restrict__ out, const int* __restrict__ rows, int hidden, float eps,
                                    int write_residual) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float scratch[32];
   const int r = blockIdx.x;
   const int s = rows ? rows[r] : r;
@@ -156,11 +163,11 @@ static void launch_add_rmsnorm(float* residual, const void* delta, int n_partial
   const bool aligned = (((uintptr_t)residual | (uintptr_t)delta | (uintptr_t)weight | (uintptr_t)out) & 15) == 0 &&
                        (partial_stride % 4) == 0;
   if (hidden % 4 == 0 && hidden <= NORM_THREADS * NORM_CHUNKS * 4 && aligned) {
-    add_rmsnorm_vec_kernel<TD, TO><<<n_rows, NORM_THREADS, 0, stream>>>(
+    lse_launch(add_rmsnorm_vec_kernel<TD, TO>, n_rows, NORM_THREADS, 0, stream,
         residual, (const TD*)delta, n_partials, partial_stride, weight, (TO*)out, rows, hidden, eps, write_residual);
   } else {
     const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
-    add_rmsnorm_kernel<TD, TO><<<n_rows, threads, 0, stream>>>(
+    lse_launch(add_rmsnorm_kernel<TD, TO>, n_rows, threads, 0, stream,
         residual, (const TD*)delta, n_partials, partial_stride, weight, (TO*)out, rows, hidden, eps, write_residual);
   }
 }
@@ -193,8 +200,7 @@ extern "C" int lse_add_rmsnorm(float* residual, const void* delta, int delta_dty
 // [page][kv head][offset][D]).  slot < 0: nothing is cached for this token
 // (padding row).  pairing 0: pairs (2i, 2i+1); 1: (i, i+D/2).
 //
-// One block per token.  A thread owns pair index i for the heads hg, hg + HG, ...
-// so the sine and cosine of an angle are computed once for all heads.
+// grid: (tokens, groups of heads); a thread owns one pair (or, for values, two elements) of one head.
 template <typename TI, typename TO>
 __global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, int n_partials, long long partial_stride,
                                      const float* __restrict__ bias, const int* __restrict__ positions,
@@ -202,54 +208,43 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, int n_partials,
                                      TO* __restrict__ q_out, TO* __restrict__ k_cache, TO* __restrict__ v_cache,
                                      int n_q, int n_kv, int head_dim, int page_size, int pairing,
                                      long long qkv_stride) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const int half = head_dim >> 1;
   const int i = threadIdx.x % half;
-  const int hg = threadIdx.x / half;
-  const int head_groups = blockDim.x / half;
-  if (hg >= head_groups) return;
-  const int pos = positions[t];
+  const int head = blockIdx.y * (blockDim.x / half) + threadIdx.x / half;   // queries, then keys, then values
+  if (head >= n_q + 2 * n_kv) return;
   const int slot = slot_mapping[t];
-  const TI* row = qkv + (size_t)t * qkv_stride;
-  const size_t page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot % page_size : 0;
-  float sn, cs;
-  sincosf((float)pos * inv_freq[i], &sn, &cs);
+  const bool is_q = head < n_q, is_k = !is_q && head < n_q + n_kv;
+  if (!is_q && slot < 0) return;   // padding row: nothing is cached
   const int ia = pairing == 0 ? 2 * i : i;
   const int ib = pairing == 0 ? 2 * i + 1 : i + half;
-  // queries and keys: rotate
-  for (int head = hg; head < n_q + n_kv; head += head_groups) {
-    const size_t col = (size_t)head * head_dim;
-    float xa = 0.f, xb = 0.f;
-    for (int p = 0; p < n_partials; ++p) {
-      xa += to_f32<TI>(row[(size_t)p * partial_stride + col + ia]);
-      xb += to_f32<TI>(row[(size_t)p * partial_stride + col + ib]);
-    }
-    if (bias) { xa += bias[col + ia]; xb += bias[col + ib]; }
-    const float ya = xa * cs - xb * sn, yb = xb * cs + xa * sn;
-    TO* dst;
-    if (head < n_q) {
-      dst = q_out + ((size_t)t * n_q + head) * head_dim;
-    } else {
-      if (slot < 0) continue;
-      dst = k_cache + ((page * n_kv + (head - n_q)) * page_size + off) * head_dim;
-    }
-    dst[ia] = from_f32<TO>(ya);
-    dst[ib] = from_f32<TO>(yb);
+  const size_t col = (size_t)head * head_dim;
+  const TI* row = qkv + (size_t)t * qkv_stride + col;
+  float xa = 0.f, xb = 0.f;
+#pragma unroll 4
+  for (int p = 0; p < n_partials; ++p) {
+    xa += to_f32<TI>(row[(size_t)p * partial_stride + ia]);
+    xb += to_f32<TI>(row[(size_t)p * partial_stride + ib]);
   }
-  // values: bias only
-  if (slot >= 0) {
-    for (int head = hg; head < n_kv; head += head_groups) {
-      const size_t col = (size_t)(n_q + n_kv + head) * head_dim;
-      float xa = 0.f, xb = 0.f;
-      for (int p = 0; p < n_partials; ++p) {
-        xa += to_f32<TI>(row[(size_t)p * partial_stride + col + ia]);
-        xb += to_f32<TI>(row[(size_t)p * partial_stride + col + ib]);
-      }
-      if (bias) { xa += bias[col + ia]; xb += bias[col + ib]; }
-      TO* dst = v_cache + ((page * n_kv + head) * page_size + off) * head_dim;
-      dst[ia] = from_f32<TO>(xa);
-      dst[ib] = from_f32<TO>(xb);
-    }
+  if (bias) { xa += bias[col + ia]; xb += bias[col + ib]; }
+  TO* dst;
+  if (is_q) {
+    dst = q_out + ((size_t)t * n_q + head) * head_dim;
+  } else {
+    const size_t page = slot / page_size, off = slot % page_size;
+    const int kv_head = is_k ? head - n_q : head - n_q - n_kv;
+    dst = (is_k ? k_cache : v_cache) + ((page * n_kv + kv_head) * page_size + off) * head_dim;
+  }
+  if (is_q || is_k) {
+    float sn, cs;
+    sincosf((float)positions[t] * inv_freq[i], &sn, &cs);
+    dst[ia] = from_f32<TO>(xa * cs - xb * sn);
+    dst[ib] = from_f32<TO>(xb * cs + xa * sn);
+  } else {
+    dst[ia] = from_f32<TO>(xa);
+    dst[ib] = from_f32<TO>(xb);
   }
 }
 
@@ -262,12 +257,14 @@ extern "C" int lse_rope_kv_write(const void* qkv, int in_dtype, int n_partials, 
   if (head_dim % 2 || head_dim > 1024 || page_size <= 0 || (pairing != 0 && pairing != 1) || n_partials < 1)
     return LSE_ERR_BAD_ARGUMENT;
   const int half = head_dim / 2;
-  int head_groups = 256 / half;
-  if (head_groups < 1) head_groups = 1;
-  if (head_groups > n_q + n_kv) head_groups = n_q + n_kv;
-  const int threads = half * head_groups;
+  const int heads = n_q + 2 * n_kv;
+  int per_block = 128 / half;   // heads per block
+  if (per_block < 1) per_block = 1;
+  if (per_block > heads) per_block = heads;
+  const int threads = half * per_block;
+  dim3 grid(tokens, (heads + per_block - 1) / per_block);
 #define LSE_ROPE_CASE(TI, TO)                                                                                   \
-  rope_kv_write_kernel<TI, TO><<<tokens, threads, 0, stream>>>(                                                 \
+  lse_launch(rope_kv_write_kernel<TI, TO>, grid, threads, 0, stream,                                            \
       (const TI*)qkv, n_partials, partial_stride, bias, positions, slot_mapping, inv_freq, (TO*)q_out,          \
       (TO*)k_cache, (TO*)v_cache, n_q, n_kv, head_dim, page_size, pairing, qkv_stride)
   if (in_dtype == LSE_DTYPE_F32 && out_dtype == LSE_DTYPE_F32) LSE_ROPE_CASE(float, float);
@@ -284,6 +281,8 @@ extern "C" int lse_rope_kv_write(const void* qkv, int in_dtype, int n_partials, 
 template <typename TI, typename TO, int VEC>
 __global__ void silu_mul_kernel(const TI* __restrict__ gate_up, int n_partials, long long partial_stride,
                                 TO* __restrict__ out, int inter) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.y;
   const int i = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
   if (i >= inter) return;
@@ -318,14 +317,20 @@ extern "C" int lse_silu_mul(const void* gate_up, int in_dtype, int n_partials, l
   const int per_row = vec ? inter / 4 : inter;
   dim3 grid((per_row + threads - 1) / threads, tokens);
 #define LSE_SILU_CASE(TI, TO)                                                                                      \
-  if (vec) silu_mul_kernel<TI, TO, 4><<<grid, threads, 0, stream>>>((const TI*)gate_up, n_partials, partial_stride, \
-                                                                    (TO*)out, inter);                              \
-  else silu_mul_kernel<TI, TO, 1><<<grid, threads, 0, stream>>>((const TI*)gate_up, n_partials, partial_stride,     \
-                                                                (TO*)out, inter)
+  if (vec) lse_launch(silu_mul_kernel<TI, TO, 4>, grid, threads, 0, stream, (const TI*)gate_up, n_partials,         \
+                      partial_stride, (TO*)out, inter);                                                            \
+  else lse_launch(silu_mul_kernel<TI, TO, 1>, grid, threads, 0, stream, (const TI*)gate_up, n_partials,             \
+                  partial_stride, (TO*)out, inter)
   if (in_dtype == LSE_DTYPE_F32 && out_dtype == LSE_DTYPE_F32) { LSE_SILU_CASE(float, float); }
   else if (in_dtype == LSE_DTYPE_BF16 && out_dtype == LSE_DTYPE_BF16) { LSE_SILU_CASE(__nv_bfloat16, __nv_bfloat16); }
   else if (in_dtype == LSE_DTYPE_F32 && out_dtype == LSE_DTYPE_BF16) { LSE_SILU_CASE(float, __nv_bfloat16); }
   else return LSE_ERR_BAD_ARGUMENT;
 #undef LSE_SILU_CASE
   LSE_LAUNCH_CHECK();
+}
+
+// Switch programmatic dependent launch on (1, the default) or off (0) for every later launch.
+extern "C" int lse_set_pdl(int enabled) {
+  lse_pdl_enabled = enabled ? 1 : 0;
+  return 0;
 }

@@ -13,6 +13,8 @@ gemm_f32_nt_kernel(const float* __restrict__ A, const float* __restrict__ B,
                    const float* __restrict__ bias, float* __restrict__ C, int M, int N, int K,
                    long long lda, long long ldb, long long ldc) {
   constexpr int THREADS = (BM / TM) * (BN / TN);
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float As[BK][BM + 1];
   __shared__ float Bs[BK][BN + 1];
   const int tid = threadIdx.x;
@@ -77,13 +79,13 @@ extern "C" int lse_gemm_f32_nt(const float* A, const float* B, const float* bias
     // few rows (decoding): narrow tiles in M so that more blocks stream the weights
     constexpr int BM = 16, BN = 64, BK = 16, TM = 2, TN = 4;
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-    gemm_f32_nt_kernel<BM, BN, BK, TM, TN><<<grid, (BM / TM) * (BN / TN), 0, stream>>>(
-        A, B, bias, C, M, N, K, lda, ldb, ldc);
+    lse_launch(gemm_f32_nt_kernel<BM, BN, BK, TM, TN>, grid, (BM / TM) * (BN / TN), 0, stream,
+               A, B, bias, C, M, N, K, lda, ldb, ldc);
   } else {
     constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-    gemm_f32_nt_kernel<BM, BN, BK, TM, TN><<<grid, (BM / TM) * (BN / TN), 0, stream>>>(
-        A, B, bias, C, M, N, K, lda, ldb, ldc);
+    lse_launch(gemm_f32_nt_kernel<BM, BN, BK, TM, TN>, grid, (BM / TM) * (BN / TN), 0, stream,
+               A, B, bias, C, M, N, K, lda, ldb, ldc);
   }
   LSE_LAUNCH_CHECK();
 }

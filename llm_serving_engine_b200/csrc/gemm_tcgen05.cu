@@ -102,6 +102,7 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
   const int n_tiles = min(k_tiles, tile_lo + tiles_per_split) - tile_lo;   // >= 1 by the launcher's choice of splits
   const uint32_t tmem_cols = m_pad < 32 ? 32u : (uint32_t)m_pad;
 
+  pdl_launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
       mbar_init(bars + 8u * s, 1);
@@ -124,7 +125,19 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
 
   if (warp == 0) {
     if (lane == 0) {   // producer: TMA loads into the ring
-      for (int it = 0; it < n_tiles; ++it) {
+      // The weights do not depend on the kernels before this one: their first tiles are
+      // fetched at once, while the kernel before may still run.  The rows of x are its
+      // output and are fetched after pdl_wait().
+      const int early = n_tiles < stages ? n_tiles : stages;
+      for (int it = 0; it < early; ++it) {
+        const uint32_t full = bars + 8u * it;
+        mbar_expect_tx(full, stage_bytes);
+        tma_load_2d(base + (uint32_t)it * stage_bytes, &map_w, full, (tile_lo + it) * BLOCK_K, n0);
+      }
+      pdl_wait();
+      for (int it = 0; it < early; ++it)
+        tma_load_2d(base + (uint32_t)it * stage_bytes + A_BYTES, &map_x, bars + 8u * it, (tile_lo + it) * BLOCK_K, 0);
+      for (int it = early; it < n_tiles; ++it) {
         const int s = it % stages;
         const uint32_t parity = (uint32_t)(it / stages) & 1u;
         if (!mbar_wait(bars + 8u * (stages + s), parity ^ 1u, abort_flag)) break;
@@ -139,6 +152,7 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
     __syncwarp();
   } else if (warp == 1) {
     if (lane == 0) {   // MMA issuer
+      pdl_wait();      // sleep here, not in a bounded spin, while the kernel before still runs
       // instruction descriptor: D float32, A and B bfloat16, both K-major, N = m_pad, M = 128
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(m_pad >> 3) << 17) |
                              ((uint32_t)(BLOCK_N >> 4) << 24);
@@ -164,6 +178,7 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
   }
 
   // epilogue: warp w reads TMEM lanes 32w .. 32w+31 (rows n0 + 32w + lane of w), all m_pad columns
+  pdl_wait();   // nothing is written, and no bounded wait starts, before the earlier kernels are done
   const bool ready = mbar_wait(accum_bar, 0, abort_flag);
   asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
   if (ready) {
@@ -269,6 +284,8 @@ extern "C" int lse_gemm_bf16_skinny(const void* x, const void* w, float* out, in
     configured = smem;
   }
   dim3 grid((N + BLOCK_N - 1) / BLOCK_N, splits);
-  gemm_bf16_skinny_kernel<<<grid, 128, smem, stream>>>(map_w, map_x, out, M, N, k_tiles, per, m_pad, stages);
+  cudaError_t err = lse_launch(gemm_bf16_skinny_kernel, grid, 128, smem, stream, map_w, map_x, out, M, N, k_tiles, per,
+                               m_pad, stages);
+  if (err != cudaSuccess) return (int)err;
   return (int)cudaGetLastError();
 }

@@ -35,6 +35,8 @@ argmax_kernel(const float* __restrict__ logits, long long row_stride, int vocab,
               int* __restrict__ out) {
   __shared__ float best_v[32];
   __shared__ int best_i[32];
+  pdl_launch_dependents();
+  pdl_wait();
   const float* row = logits + (size_t)blockIdx.x * row_stride;
   float bv = -INFINITY;
   int bi = vocab;  // "none yet"
@@ -76,6 +78,8 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int vocab,
   __shared__ float red[32];
   __shared__ float chunk_sum[THREADS];
   __shared__ int chosen;
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x;
   const float* row = logits + (size_t)r * row_stride;
   float* e = scratch + (size_t)r * vocab;
@@ -164,7 +168,7 @@ extern "C" int lse_argmax(const float* logits, long long row_stride, int rows, i
                           cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (vocab <= 0) return LSE_ERR_BAD_ARGUMENT;
-  argmax_kernel<<<rows, THREADS, 0, stream>>>(logits, row_stride, vocab, out);
+  lse_launch(argmax_kernel, rows, THREADS, 0, stream, logits, row_stride, vocab, out);
   LSE_LAUNCH_CHECK();
 }
 
@@ -173,8 +177,8 @@ extern "C" int lse_sample(const float* logits, long long row_stride, int rows, i
                           const long long* counter, float* scratch, int* out, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (vocab <= 0) return LSE_ERR_BAD_ARGUMENT;
-  sample_kernel<<<rows, THREADS, 0, stream>>>(logits, row_stride, vocab, temperature, top_p, seed,
-                                              counter, scratch, out);
+  lse_launch(sample_kernel, rows, THREADS, 0, stream, logits, row_stride, vocab, temperature, top_p, seed,
+             counter, scratch, out);
   LSE_LAUNCH_CHECK();
 }
 

@@ -28,11 +28,12 @@ _SIGNATURES = {
     "lse_paged_attention_generic": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
                                     c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
                                     c_int, c_void_p],
-    "lse_paged_attention_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
-                                   c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+    "lse_paged_attention_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                   c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "lse_paged_attention_prefill": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                     c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
     "lse_attention_mma_supported": [c_int, c_int, c_int],
+    "lse_set_pdl": [c_int],
     "lse_argmax": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p],
     "lse_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                    c_void_p, c_void_p, c_void_p],
@@ -53,6 +54,9 @@ def load(verbose: bool = True):
             fn = getattr(lib, name)
             fn.argtypes = argtypes
             fn.restype = c_int
+        import os
+        if os.environ.get("LSE_PDL", "1") == "0":   # programmatic dependent launch off (for comparisons)
+            lib.lse_set_pdl(0)
         _lib = lib
     return _lib
 

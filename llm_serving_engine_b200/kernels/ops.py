@@ -175,10 +175,25 @@ def decode_splits(tokens: int, n_q: int, n_kv: int, max_context: int | None) -> 
     """How many splits of the keys a decode launch uses: enough blocks to fill the GPU,
     at least one 16-key tile per warp and split."""
     base = tokens * n_kv * ((n_q // n_kv + 15) // 16)
-    splits = max(1, min(32, -(-592 // base)))
+    splits = max(1, min(32, 296 // base))       # one wave of two blocks per SM
     if max_context is not None:
         splits = min(splits, max(1, -(-max_context // 64)))
     return splits
+
+
+_ARRIVALS: dict = {}
+
+
+def _arrival_counters(device, count: int) -> torch.Tensor:
+    """Zeroed int32 counters that the split-KV kernel uses and leaves zero; kept per device
+    so that a captured graph finds them at the same address."""
+    held = _ARRIVALS.get(device)
+    if held is None or held.numel() < count:
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError("arrival counters must exist before a stream is captured")
+        held = torch.zeros(max(count, 4096), dtype=torch.int32, device=device)
+        _ARRIVALS[device] = held
+    return held
 
 
 def paged_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
@@ -192,12 +207,13 @@ def paged_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
     assert q.dtype == out.dtype == k_cache.dtype == v_cache.dtype == torch.bfloat16
     assert q.is_contiguous() and out.is_contiguous() and k_cache.is_contiguous() and v_cache.is_contiguous()
     assert block_tables.dtype == torch.int32 and block_tables.stride(1) == 1
-    scratch = None
+    scratch = arrivals = None
     if num_splits > 1:
         scratch = torch.empty(tokens * n_q * num_splits * (head_dim + 2), dtype=torch.float32, device=q.device)
+        arrivals = _arrival_counters(q.device, tokens * n_kv * ((n_q // n_kv + 15) // 16))
     lib = library.load()
     check(lib.lse_paged_attention_decode(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
-                                         _ptr(scratch), block_tables.data_ptr(), block_tables.stride(0),
+                                         _ptr(scratch), _ptr(arrivals), block_tables.data_ptr(), block_tables.stride(0),
                                          segment_of_token.data_ptr(), positions.data_ptr(), tokens, n_q, n_kv,
                                          head_dim, page_size, float(scale), int(num_splits), _stream()),
           "paged_attention_decode")
