@@ -18,6 +18,8 @@
 // src/llmserve/model.py:143-176).  Cache layout: [page][kv head][offset][D].
 #include "common.cuh"
 
+LSE_TL_DEFINE(lse_timeline_attention)
+
 namespace {
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -56,11 +58,63 @@ template <int D> __device__ __forceinline__ uint32_t tile_off(int r, int c) {
 
 constexpr float LOG2E = 1.4426950408889634f;
 
+__device__ __forceinline__ float fast_exp2(float x) {   // 2^x, float32, 2^-inf = 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Copies 16 consecutive keys (rows of D bfloat16, contiguous in one cache page) of K and of V
+// into two swizzled [16][D] tiles with cp.async, by NT threads (this thread is `ti`).
+// Keys at or beyond `limit` (counted from the first key of the sub-tile) are zero-filled.
+template <int D, int NT>
+struct SubTileCopy {
+  static constexpr int CH = D / 8;           // 16-byte chunks per row
+  static constexpr int RPP = NT / CH;        // rows per pass
+  static constexpr int PASSES = 16 / RPP;
+  static_assert(NT % CH == 0 && 16 % RPP == 0, "thread count does not tile a 16-key sub-tile");
+  int row0;                                  // first row this thread copies
+  uint32_t lane_goff;                        // element offset of (row0, chunk) inside the 16 x D block
+  uint32_t soff[PASSES];                     // byte offsets inside a swizzled tile
+  __device__ __forceinline__ explicit SubTileCopy(int ti) {
+    const int c = ti % CH;
+    row0 = ti / CH;
+    lane_goff = (uint32_t)(row0 * D + c * 8);
+#pragma unroll
+    for (int i = 0; i < PASSES; ++i) soff[i] = tile_off<D>(row0 + i * RPP, c);
+  }
+  __device__ __forceinline__ void copy(uint32_t k_dst, uint32_t v_dst, const __nv_bfloat16* k_src,
+                                       const __nv_bfloat16* v_src, int limit) const {
+    k_src += lane_goff;
+    v_src += lane_goff;
+#pragma unroll
+    for (int i = 0; i < PASSES; ++i) {
+      const bool valid = row0 + i * RPP < limit;
+      cp_async16(k_dst + soff[i], valid ? k_src + i * RPP * D : k_src, valid);
+      cp_async16(v_dst + soff[i], valid ? v_src + i * RPP * D : v_src, valid);
+    }
+  }
+};
+
 // ---------------------------------------------------------------------------------------------
 // decode: one query row per request
 // ---------------------------------------------------------------------------------------------
 constexpr int DEC_STAGES = 3;
 constexpr int DEC_TILE = 16;
+constexpr int BT_STAGE = 1024;   // block-table entries a block keeps in shared memory
+
+// page and offset of key j: by shift and mask when the page size is a power of two
+struct PageMath {
+  int size, shift;
+  __device__ __forceinline__ explicit PageMath(int page_size) : size(page_size), shift(-1) {
+    if ((page_size & (page_size - 1)) == 0) {
+      shift = 0;
+      while ((1 << shift) < page_size) ++shift;
+    }
+  }
+  __device__ __forceinline__ int page(int j) const { return shift >= 0 ? j >> shift : j / size; }
+  __device__ __forceinline__ int offset(int j) const { return shift >= 0 ? j & (size - 1) : j % size; }
+};
 
 template <int D>
 __global__ void __launch_bounds__(128)
@@ -75,8 +129,11 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* q_s = smem;                                   // [16][D] bf16
   unsigned char* kv_s = smem + TILE_BYTES;                     // [warp][stage][K|V][16][D]
+  __shared__ int bt_s[BT_STAGE];
+  LSE_TL_BEGIN(6)
   pdl_launch_dependents();
   pdl_wait();
+  LSE_TL_MARK(2)
   const int t = blockIdx.x;
   const int group = n_q / n_kv;
   const int gchunks = (group + 15) / 16;
@@ -96,6 +153,13 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   const int tile_lo = split * per_split;
   const int tile_hi = min(total_tiles, tile_lo + per_split);
 
+  // this split's slice of the block table -> shared memory (one round trip instead of one per tile)
+  const PageMath pm(page_size);
+  const int first_page = pm.page(tile_lo * DEC_TILE);
+  const int n_pages = tile_lo < tile_hi ? pm.page(min(ctx, tile_hi * DEC_TILE) - 1) - first_page + 1 : 0;
+  const bool staged = n_pages <= BT_STAGE;
+  if (staged)
+    for (int i = tid; i < n_pages; i += 128) bt_s[i] = bt[first_page + i];
   // queries of the group -> shared memory (rows beyond the group are zero)
   for (int e = tid; e < 16 * CH; e += 128) {
     const int r = e / CH, c = e % CH;
@@ -117,7 +181,18 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
   unsigned char* my_s = kv_s + (size_t)warp * DEC_STAGES * 2 * TILE_BYTES;
+  const uint32_t my_u32 = smem_u32(my_s);
+  const bool page_tiles = (page_size % DEC_TILE) == 0 && staged;   // a 16-key tile never straddles pages
+  const SubTileCopy<D, 32> copier(lane);
   auto load_tile = [&](int tile, int stage) {
+    if (page_tiles) {
+      const int j0 = tile * DEC_TILE;
+      const int page = bt_s[pm.page(j0) - first_page];
+      const size_t base = (((size_t)page * n_kv + kvh) * page_size + pm.offset(j0)) * D;
+      const uint32_t k_dst = my_u32 + (uint32_t)stage * 2 * TILE_BYTES;
+      copier.copy(k_dst, k_dst + TILE_BYTES, kc + base, vc + base, ctx - j0);
+      return;
+    }
     unsigned char* ks_ = my_s + (size_t)stage * 2 * TILE_BYTES;
     unsigned char* vs_ = ks_ + TILE_BYTES;
 #pragma unroll
@@ -128,8 +203,9 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
       const bool valid = j < ctx;
       size_t off = 0;
       if (valid) {
-        const int page = bt[j / page_size];
-        off = (((size_t)page * n_kv + kvh) * page_size + (j % page_size)) * D + c * 8;
+        const int logical = pm.page(j);
+        const int page = staged ? bt_s[logical - first_page] : bt[logical];
+        off = (((size_t)page * n_kv + kvh) * page_size + pm.offset(j)) * D + c * 8;
       }
       cp_async16(smem_u32(ks_ + tile_off<D>(key, c)), kc + off, valid);
       cp_async16(smem_u32(vs_ + tile_off<D>(key, c)), vc + off, valid);
@@ -151,8 +227,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     cp_async_wait<DEC_STAGES - 1>();
     __syncwarp();
     const int tile = first + 4 * it;
-    unsigned char* ks_ = my_s + (size_t)(it % DEC_STAGES) * 2 * TILE_BYTES;
-    unsigned char* vs_ = ks_ + TILE_BYTES;
+    const uint32_t ks_ = my_u32 + (uint32_t)(it % DEC_STAGES) * 2 * TILE_BYTES;
+    const uint32_t vs_ = ks_ + TILE_BYTES;
 
     float s[2][4];
 #pragma unroll
@@ -162,7 +238,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
 #pragma unroll
       for (int ks = 0; ks < D / 16; ++ks) {
         uint32_t b[4];
-        ldmatrix_x4(b, smem_u32(ks_ + tile_off<D>(key, ks * 2 + (mi & 1))));
+        ldmatrix_x4(b, ks_ + tile_off<D>(key, ks * 2 + (mi & 1)));
         mma_bf16(s[0], qf[ks], b[0], b[1]);
         mma_bf16(s[1], qf[ks], b[2], b[3]);
       }
@@ -181,13 +257,13 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
     const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
-    const float c0 = exp2f(m0 - mn0), c1 = exp2f(m1 - mn1);
+    const float c0 = fast_exp2(m0 - mn0), c1 = fast_exp2(m1 - mn1);
     m0 = mn0; m1 = mn1;
     float p[2][4];
 #pragma unroll
     for (int nb = 0; nb < 2; ++nb) {
-      p[nb][0] = exp2f(s[nb][0] - mn0); p[nb][1] = exp2f(s[nb][1] - mn0);
-      p[nb][2] = exp2f(s[nb][2] - mn1); p[nb][3] = exp2f(s[nb][3] - mn1);
+      p[nb][0] = fast_exp2(s[nb][0] - mn0); p[nb][1] = fast_exp2(s[nb][1] - mn0);
+      p[nb][2] = fast_exp2(s[nb][2] - mn1); p[nb][3] = fast_exp2(s[nb][3] - mn1);
     }
     l0 = l0 * c0 + (p[0][0] + p[0][1]) + (p[1][0] + p[1][1]);
     l1 = l1 * c1 + (p[0][2] + p[0][3]) + (p[1][2] + p[1][3]);
@@ -200,7 +276,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
 #pragma unroll
       for (int nbp = 0; nbp < D / 16; ++nbp) {
         uint32_t b[4];
-        ldmatrix_x4_trans(b, smem_u32(vs_ + tile_off<D>(key, nbp * 2 + (mi >> 1))));
+        ldmatrix_x4_trans(b, vs_ + tile_off<D>(key, nbp * 2 + (mi >> 1)));
         mma_bf16(acc[2 * nbp], pa, b[0], b[1]);
         mma_bf16(acc[2 * nbp + 1], pa, b[2], b[3]);
       }
@@ -254,6 +330,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
       if (d == 0) { part_ml[pidx * 2] = M; part_ml[pidx * 2 + 1] = L; }
     }
   }
+  LSE_TL_MARK(3)
   if (num_splits == 1) return;
 
   // The split that finishes last adds up all of them (in split order, so the sum does not depend
@@ -267,6 +344,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     last_flag = seen == num_splits - 1;
   }
   __syncthreads();
+  LSE_TL_MARK_ANY(4, last_flag && tid == 0 && blockIdx.x == 0 && blockIdx.y == 0)
   if (!last_flag) return;
   __threadfence();
   // weights of the splits: w[g][sp] = 2^(m_sp - M_g) / L_g, worked out once into shared memory
@@ -288,15 +366,32 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     w_s[e] = wgt / L;
   }
   __syncthreads();
-  for (int e = tid; e < gcount * D; e += 128) {
-    const int g = e / D, d = e % D;
+  // out[g][d] = sum_sp part_o[g][sp][d] * w[g][sp]: four d-values per thread, the loads of up to
+  // eight splits issued together (splits are added in index order)
+  for (int item = tid; item < gcount * (D / 4); item += 128) {
+    const int g = item / (D / 4), d = (item % (D / 4)) * 4;
     const float* src = part_o + ((size_t)t * n_q + first_head + g) * num_splits * D + d;
-    float O = 0.f;
-#pragma unroll 8
-    for (int sp = 0; sp < num_splits; ++sp) O += __ldcg(src + (size_t)sp * D) * w_s[g * 32 + sp];
-    out[((size_t)t * n_q + first_head + g) * D + d] = __float2bfloat16_rn(O);
+    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int sp0 = 0; sp0 < num_splits; sp0 += 8) {
+      float4 v[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        v[i] = sp0 + i < num_splits ? __ldcg(reinterpret_cast<const float4*>(src + (size_t)(sp0 + i) * D))
+                                    : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float w = sp0 + i < num_splits ? w_s[g * 32 + sp0 + i] : 0.f;
+        o.x += v[i].x * w; o.y += v[i].y * w; o.z += v[i].z * w; o.w += v[i].w * w;
+      }
+    }
+    __nv_bfloat162 lo = __floats2bfloat162_rn(o.x, o.y), hi = __floats2bfloat162_rn(o.z, o.w);
+    uint2 packed;
+    packed.x = *reinterpret_cast<uint32_t*>(&lo);
+    packed.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(out + ((size_t)t * n_q + first_head + g) * D + d) = packed;
   }
   if (tid == 0) arrivals[t * gridDim.y + blockIdx.y] = 0;
+  LSE_TL_MARK_ANY(5, tid == 0 && blockIdx.x == 0 && blockIdx.y == 0)
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -318,6 +413,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* q_s = smem;                       // [64][D]
   unsigned char* kv_s = smem + PF_BM * D * 2;      // [2 stages][K|V][64][D]
+  __shared__ int bt_s[BT_STAGE];
   pdl_launch_dependents();
   pdl_wait();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -343,6 +439,11 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   const int last_pos = pos0 + nrows - 1;
   const int n_tiles = (last_pos + PF_BN) / PF_BN;
   const int* bt = block_tables + (size_t)seg * bt_stride;
+  const PageMath pm(page_size);
+  const int n_pages = pm.page(last_pos) + 1;
+  const bool staged = n_pages <= BT_STAGE;
+  if (staged)
+    for (int i = tid; i < n_pages; i += 128) bt_s[i] = bt[i];
 
   for (int e = tid; e < PF_BM * CH; e += 128) {
     const int m = e / CH, c = e % CH;
@@ -352,7 +453,23 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     *reinterpret_cast<uint4*>(q_s + tile_off<D>(m, c)) = v;
   }
 
+  const uint32_t kv_u32 = smem_u32(kv_s);
+  const bool page_tiles = (page_size % 16) == 0 && staged;   // a 16-key sub-tile never straddles pages
+  const SubTileCopy<D, 32> copier(lane);                      // warp w copies sub-tile w of the 64 keys
   auto load_tile = [&](int kt, int stage) {
+    if (page_tiles) {
+      const int j0 = kt * PF_BN + warp * 16;
+      if (j0 <= last_pos) {
+        const int page = bt_s[pm.page(j0)];
+        const size_t base = (((size_t)page * n_kv + kvh) * page_size + pm.offset(j0)) * D;
+        const uint32_t k_dst = kv_u32 + (uint32_t)stage * 2 * TILE_BYTES + (uint32_t)warp * 16 * D * 2;
+        copier.copy(k_dst, k_dst + TILE_BYTES, kc + base, vc + base, last_pos + 1 - j0);
+      } else {   // the whole sub-tile lies beyond the last key: zero-fill
+        const uint32_t k_dst = kv_u32 + (uint32_t)stage * 2 * TILE_BYTES + (uint32_t)warp * 16 * D * 2;
+        copier.copy(k_dst, k_dst + TILE_BYTES, kc, vc, 0);
+      }
+      return;
+    }
     unsigned char* ks_ = kv_s + (size_t)stage * 2 * TILE_BYTES;
     unsigned char* vs_ = ks_ + TILE_BYTES;
 #pragma unroll
@@ -363,16 +480,17 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
       const bool valid = j <= last_pos;
       size_t off = 0;
       if (valid) {
-        const int page = bt[j / page_size];
-        off = (((size_t)page * n_kv + kvh) * page_size + (j % page_size)) * D + c * 8;
+        const int logical = pm.page(j);
+        const int page = staged ? bt_s[logical] : bt[logical];
+        off = (((size_t)page * n_kv + kvh) * page_size + pm.offset(j)) * D + c * 8;
       }
       cp_async16(smem_u32(ks_ + tile_off<D>(key, c)), kc + off, valid);
       cp_async16(smem_u32(vs_ + tile_off<D>(key, c)), vc + off, valid);
     }
   };
+  __syncthreads();   // q_s and bt_s are filled
   load_tile(0, 0);
   cp_async_commit();
-  __syncthreads();   // q_s is filled
 
   uint32_t qf[D / 16][4];
   {
@@ -394,8 +512,8 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     cp_async_commit();
     cp_async_wait<1>();
     __syncthreads();
-    unsigned char* ks_ = kv_s + (size_t)(kt & 1) * 2 * TILE_BYTES;
-    unsigned char* vs_ = ks_ + TILE_BYTES;
+    const uint32_t ks_ = kv_u32 + (uint32_t)(kt & 1) * 2 * TILE_BYTES;
+    const uint32_t vs_ = ks_ + TILE_BYTES;
 
     float s[PF_BN / 8][4];
 #pragma unroll
@@ -407,7 +525,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
 #pragma unroll
         for (int nbp = 0; nbp < PF_BN / 16; ++nbp) {
           uint32_t b[4];
-          ldmatrix_x4(b, smem_u32(ks_ + tile_off<D>(nbp * 16 + key, ks * 2 + (mi & 1))));
+          ldmatrix_x4(b, ks_ + tile_off<D>(nbp * 16 + key, ks * 2 + (mi & 1)));
           mma_bf16(s[2 * nbp], qf[ks], b[0], b[1]);
           mma_bf16(s[2 * nbp + 1], qf[ks], b[2], b[3]);
         }
@@ -434,13 +552,13 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
     const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);   // finite from the first tile on: key 0 is read by every row
-    const float c0 = exp2f(m0 - mn0), c1 = exp2f(m1 - mn1);
+    const float c0 = fast_exp2(m0 - mn0), c1 = fast_exp2(m1 - mn1);
     m0 = mn0; m1 = mn1;
     float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
     for (int nb = 0; nb < PF_BN / 8; ++nb) {
-      s[nb][0] = exp2f(s[nb][0] - mn0); s[nb][1] = exp2f(s[nb][1] - mn0);
-      s[nb][2] = exp2f(s[nb][2] - mn1); s[nb][3] = exp2f(s[nb][3] - mn1);
+      s[nb][0] = fast_exp2(s[nb][0] - mn0); s[nb][1] = fast_exp2(s[nb][1] - mn0);
+      s[nb][2] = fast_exp2(s[nb][2] - mn1); s[nb][3] = fast_exp2(s[nb][3] - mn1);
       sum0 += s[nb][0] + s[nb][1];
       sum1 += s[nb][2] + s[nb][3];
     }
@@ -457,7 +575,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
 #pragma unroll
         for (int nbp = 0; nbp < D / 16; ++nbp) {
           uint32_t b[4];
-          ldmatrix_x4_trans(b, smem_u32(vs_ + tile_off<D>(kk * 16 + key, nbp * 2 + (mi >> 1))));
+          ldmatrix_x4_trans(b, vs_ + tile_off<D>(kk * 16 + key, nbp * 2 + (mi >> 1)));
           mma_bf16(acc[2 * nbp], pa, b[0], b[1]);
           mma_bf16(acc[2 * nbp + 1], pa, b[2], b[3]);
         }

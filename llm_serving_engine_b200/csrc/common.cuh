@@ -92,3 +92,44 @@ inline cudaError_t lse_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
   config.numAttrs = 1;
   return cudaLaunchKernelEx(&config, kernel, static_cast<Args&&>(args)...);
 }
+
+
+// ------------------------------------------------------------------ timeline (tuning builds only)
+// With -DLSE_TRACE every kernel's block 0 records when it started, when pdl_wait() returned and
+// when it ended (nanoseconds of %globaltimer) into a per-source-file buffer that a tuning script
+// reads back with the exported reader.  Without the flag the macros vanish.
+#ifdef LSE_TRACE
+#define LSE_TL_CAPACITY 4096
+#define LSE_TL_DEFINE(reader)                                                                              \
+  __device__ unsigned long long lse_tl_data[LSE_TL_CAPACITY * 8];                                          \
+  __device__ unsigned int lse_tl_count;                                                                    \
+  __device__ volatile int lse_tl_last = -1;                                                                \
+  extern "C" int reader(unsigned long long* host_out, int reset) {                                         \
+    unsigned int n = 0;                                                                                    \
+    cudaMemcpyFromSymbol(&n, lse_tl_count, sizeof(n));                                                     \
+    if (n > LSE_TL_CAPACITY) n = LSE_TL_CAPACITY;                                                          \
+    if (n) cudaMemcpyFromSymbol(host_out, lse_tl_data, sizeof(unsigned long long) * 8 * n);                \
+    if (reset) { unsigned int zero = 0; cudaMemcpyToSymbol(lse_tl_count, &zero, sizeof(zero)); }           \
+    return (int)n;                                                                                         \
+  }
+__device__ __forceinline__ unsigned long long lse_now() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define LSE_TL_BEGIN(id)                                                                                   \
+  int tl_slot_ = -1;                                                                                       \
+  if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {                         \
+    tl_slot_ = (int)atomicAdd(&lse_tl_count, 1u);                                                          \
+    if (tl_slot_ < LSE_TL_CAPACITY) { lse_tl_data[tl_slot_ * 8] = (id); lse_tl_data[tl_slot_ * 8 + 1] = lse_now(); lse_tl_last = tl_slot_; } \
+    else tl_slot_ = -1;                                                                                    \
+  }
+#define LSE_TL_MARK(k) if (tl_slot_ >= 0) lse_tl_data[tl_slot_ * 8 + (k)] = lse_now();
+// a mark by some other block of the same launch (the slot of the launch's block 0 is read back)
+#define LSE_TL_MARK_ANY(k, cond) if (cond) { const int sl_ = lse_tl_last; if (sl_ >= 0 && sl_ < LSE_TL_CAPACITY) lse_tl_data[sl_ * 8 + (k)] = lse_now(); }
+#else
+#define LSE_TL_DEFINE(reader)
+#define LSE_TL_BEGIN(id)
+#define LSE_TL_MARK(k)
+#define LSE_TL_MARK_ANY(k, cond)
+#endif

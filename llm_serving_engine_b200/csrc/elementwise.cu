@@ -9,13 +9,17 @@
 // same whatever else runs.
 #include "common.cuh"
 
+LSE_TL_DEFINE(lse_timeline_elementwise)
+
 // ------------------------------------------------------------------ embedding
 // residual[t, :] = float(table[ids[t], :])
 template <typename T>
 __global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                                  float* __restrict__ out, int hidden, int vocab) {
+  LSE_TL_BEGIN(1)
   pdl_launch_dependents();
   pdl_wait();
+  LSE_TL_MARK(2)
   const int t = blockIdx.x;
   const int id = ids[t];
   float* dst = out + (size_t)t * hidden;
@@ -25,6 +29,7 @@ __global__ void embedding_kernel(const T* __restrict__ table, const int* __restr
   }
   const T* src = table + (size_t)id * hidden;
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_f32<T>(src[i]);
+  LSE_TL_MARK(3)
 }
 
 extern "C" int lse_embedding(const void* table, int table_dtype, const int* ids, float* out,
@@ -68,8 +73,8 @@ template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16*
   *reinterpret_cast<uint2*>(p) = t;
 }
 
-constexpr int NORM_THREADS = 256;
-constexpr int NORM_CHUNKS = 8;   // float4 chunks a thread keeps: hidden <= 256 * 8 * 4 = 8192
+constexpr int NORM_THREADS = 512;
+constexpr int NORM_CHUNKS = 4;   // float4 chunks a thread keeps: hidden <= 512 * 4 * 4 = 8192
 
 // One pass: the row stays in registers between the sum of squares and the scaling.
 // hidden % 4 == 0 and hidden <= NORM_THREADS * NORM_CHUNKS * 4.
@@ -78,8 +83,10 @@ __global__ void __launch_bounds__(NORM_THREADS)
 add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* __restrict__ delta, int n_partials,
                        long long partial_stride, const float* __restrict__ weight, TO* __restrict__ out,
                        const int* __restrict__ rows, int hidden, float eps, int write_residual) {
+  LSE_TL_BEGIN(2)
   pdl_launch_dependents();
   pdl_wait();
+  LSE_TL_MARK(2)
   __shared__ float scratch[32];
   const int r = blockIdx.x;
   const int s = rows ? rows[r] : r;
@@ -95,11 +102,18 @@ add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* __restrict__ delt
     if (i < chunks) {
       load4<float>(res + 4 * i, x[c]);
       if (del) {
-#pragma unroll 4
-        for (int p = 0; p < n_partials; ++p) {
-          float d[4];
-          load4<TD>(del + (size_t)p * partial_stride + 4 * i, d);
-          x[c][0] += d[0]; x[c][1] += d[1]; x[c][2] += d[2]; x[c][3] += d[3];
+        // eight partial sums are fetched together (one round trip), then added in index order
+        for (int p0 = 0; p0 < n_partials; p0 += 8) {
+          float d[8][4];
+#pragma unroll
+          for (int p = 0; p < 8; ++p) {
+            if (p0 + p < n_partials) load4<TD>(del + (size_t)(p0 + p) * partial_stride + 4 * i, d[p]);
+            else d[p][0] = d[p][1] = d[p][2] = d[p][3] = 0.f;
+          }
+#pragma unroll
+          for (int p = 0; p < 8; ++p) {
+            if (p0 + p < n_partials) { x[c][0] += d[p][0]; x[c][1] += d[p][1]; x[c][2] += d[p][2]; x[c][3] += d[p][3]; }
+          }
         }
         if (write_residual) store4<float>(res + 4 * i, x[c]);
       }
@@ -121,6 +135,7 @@ add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* __restrict__ delt
       store4<TO>(dst + 4 * i, y);
     }
   }
+  LSE_TL_MARK(3)
 }
 
 // Any width: two passes over the row.
@@ -208,8 +223,10 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, int n_partials,
                                      TO* __restrict__ q_out, TO* __restrict__ k_cache, TO* __restrict__ v_cache,
                                      int n_q, int n_kv, int head_dim, int page_size, int pairing,
                                      long long qkv_stride) {
+  LSE_TL_BEGIN(3)
   pdl_launch_dependents();
   pdl_wait();
+  LSE_TL_MARK(2)
   const int t = blockIdx.x;
   const int half = head_dim >> 1;
   const int i = threadIdx.x % half;
@@ -223,10 +240,17 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, int n_partials,
   const size_t col = (size_t)head * head_dim;
   const TI* row = qkv + (size_t)t * qkv_stride + col;
   float xa = 0.f, xb = 0.f;
-#pragma unroll 4
-  for (int p = 0; p < n_partials; ++p) {
-    xa += to_f32<TI>(row[(size_t)p * partial_stride + ia]);
-    xb += to_f32<TI>(row[(size_t)p * partial_stride + ib]);
+  for (int p0 = 0; p0 < n_partials; p0 += 8) {   // eight partial sums per round trip, added in index order
+    float a[8], b[8];
+#pragma unroll
+    for (int p = 0; p < 8; ++p) {
+      const bool in = p0 + p < n_partials;
+      a[p] = in ? to_f32<TI>(row[(size_t)(p0 + p) * partial_stride + ia]) : 0.f;
+      b[p] = in ? to_f32<TI>(row[(size_t)(p0 + p) * partial_stride + ib]) : 0.f;
+    }
+#pragma unroll
+    for (int p = 0; p < 8; ++p)
+      if (p0 + p < n_partials) { xa += a[p]; xb += b[p]; }
   }
   if (bias) { xa += bias[col + ia]; xb += bias[col + ib]; }
   TO* dst;
@@ -246,6 +270,7 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, int n_partials,
     dst[ia] = from_f32<TO>(xa);
     dst[ib] = from_f32<TO>(xb);
   }
+  LSE_TL_MARK(3)
 }
 
 extern "C" int lse_rope_kv_write(const void* qkv, int in_dtype, int n_partials, long long partial_stride,
@@ -281,8 +306,10 @@ extern "C" int lse_rope_kv_write(const void* qkv, int in_dtype, int n_partials, 
 template <typename TI, typename TO, int VEC>
 __global__ void silu_mul_kernel(const TI* __restrict__ gate_up, int n_partials, long long partial_stride,
                                 TO* __restrict__ out, int inter) {
+  LSE_TL_BEGIN(4)
   pdl_launch_dependents();
   pdl_wait();
+  LSE_TL_MARK(2)
   const int t = blockIdx.y;
   const int i = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
   if (i >= inter) return;
@@ -306,6 +333,7 @@ __global__ void silu_mul_kernel(const TI* __restrict__ gate_up, int n_partials, 
   TO* dst = out + (size_t)t * inter + i;
   if (VEC == 4) store4<TO>(dst, y);
   else dst[0] = from_f32<TO>(y[0]);
+  LSE_TL_MARK(3)
 }
 
 extern "C" int lse_silu_mul(const void* gate_up, int in_dtype, int n_partials, long long partial_stride, void* out,

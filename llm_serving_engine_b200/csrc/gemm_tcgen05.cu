@@ -18,6 +18,8 @@
 
 #include "common.cuh"
 
+LSE_TL_DEFINE(lse_timeline_gemm)
+
 namespace {
 constexpr int BLOCK_N = 128;  // rows of w per block (UMMA M)
 constexpr int BLOCK_K = 64;   // k-values per stage: 128-byte rows
@@ -102,6 +104,7 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
   const int n_tiles = min(k_tiles, tile_lo + tiles_per_split) - tile_lo;   // >= 1 by the launcher's choice of splits
   const uint32_t tmem_cols = m_pad < 32 ? 32u : (uint32_t)m_pad;
 
+  LSE_TL_BEGIN(5)
   pdl_launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
@@ -135,6 +138,7 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
         tma_load_2d(base + (uint32_t)it * stage_bytes, &map_w, full, (tile_lo + it) * BLOCK_K, n0);
       }
       pdl_wait();
+      LSE_TL_MARK(2)
       for (int it = 0; it < early; ++it)
         tma_load_2d(base + (uint32_t)it * stage_bytes + A_BYTES, &map_x, bars + 8u * it, (tile_lo + it) * BLOCK_K, 0);
       for (int it = early; it < n_tiles; ++it) {
@@ -203,6 +207,7 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
   }
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
   __syncthreads();
+  LSE_TL_MARK(3)
   if (warp == 0)
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
 }

@@ -175,7 +175,7 @@ def decode_splits(tokens: int, n_q: int, n_kv: int, max_context: int | None) -> 
     """How many splits of the keys a decode launch uses: enough blocks to fill the GPU,
     at least one 16-key tile per warp and split."""
     base = tokens * n_kv * ((n_q // n_kv + 15) // 16)
-    splits = max(1, min(32, 296 // base))       # one wave of two blocks per SM
+    splits = max(1, min(8, 148 // base))        # about one block per SM; at most 8, which the last block adds up in one go
     if max_context is not None:
         splits = min(splits, max(1, -(-max_context // 64)))
     return splits
@@ -277,7 +277,7 @@ def gemm_bf16_skinny(x: torch.Tensor, weight: torch.Tensor, splits: int | None =
     lib = library.load()
     if splits is None:
         n_tiles = -(-n // 128)
-        splits = max(1, min(-(-k // 128), round(296 / n_tiles))) if n_tiles < 148 else 1
+        splits = max(1, min(-(-k // 128), 148 // n_tiles)) if n_tiles < 148 else 1   # about one block per SM
     splits = lib.lse_gemm_bf16_skinny_splits(k, int(splits))
     out = torch.empty((splits, m, n), dtype=torch.float32, device=x.device)
     check(lib.lse_gemm_bf16_skinny(x.data_ptr(), weight.data_ptr(), out.data_ptr(), m, n, k, splits, int(stages),
