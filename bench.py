@@ -198,7 +198,10 @@ def prefill_flops(config: dict, layers: int, tokens: int) -> float:
 
 
 def time_e2e(model, batch: int, new_tokens: int):
-    """Decode tokens per second through the Python entry point: host ids in, host ids out."""
+    """Decode tokens per second through the Python entry point: host token ids in, host token ids
+    out (``LLMEngine.generate_many`` with per-token callbacks).  The clock runs over the steps in
+    which all ``batch`` requests decode together: from the moment the last of them has its first
+    token to the moment the first of them ends."""
     import torch
 
     from llm_serving_engine_b200 import CacheConfig, GenerationConfig, LLMEngine, SchedulerConfig
@@ -207,29 +210,33 @@ def time_e2e(model, batch: int, new_tokens: int):
     engine = LLMEngine(model, None, cache_config=CacheConfig(BLOCK, batch * (context // BLOCK)),
                        scheduler_config=SchedulerConfig(max_batch_size=batch, max_tokens_per_step=max(PROMPT, batch)),
                        prefill_chunk_size=PROMPT)
+    engine.warmup()
     generator = torch.Generator().manual_seed(3)
     prompts = [torch.randint(0, model.vocab_size, (PROMPT,), generator=generator).tolist() for _ in range(batch)]
-    stamps: list[float] = []
-    counts = [0] * batch
+    stamps: list[tuple[float, int]] = []
 
     def make_callback(index: int):
         def callback(_token: int) -> None:
-            counts[index] += 1
-            stamps.append(time.perf_counter())
+            stamps.append((time.perf_counter(), index))
         return callback
 
-    engine.generate_many(prompts, GenerationConfig(max_new_tokens=new_tokens),
+    engine.generate_many(prompts, GenerationConfig(max_new_tokens=new_tokens + 2 * batch),
                          [make_callback(index) for index in range(batch)])
     torch.cuda.synchronize()
-    # the decode phase starts when every request has its first token
-    first_all = stamps[batch - 1] if len(stamps) >= batch else stamps[0]
-    decoded = len(stamps) - batch
-    seconds = stamps[-1] - first_all
-    steps = max(new_tokens - 1, 1)
+    counts = [0] * batch
+    window_start = window_end = None
+    for stamp, index in stamps:
+        counts[index] += 1
+        if window_start is None and min(counts) >= 1:
+            window_start = stamp           # the last request got its first token
+        if window_end is None and max(counts) >= new_tokens + 2 * batch:
+            window_end = stamp             # the first request got its last token
+    decoded = sum(1 for stamp, _ in stamps if window_start < stamp <= window_end)
+    seconds = window_end - window_start
     h2d = engine.runner.last_h2d_bytes
     del engine
     torch.cuda.empty_cache()
-    return decoded / max(seconds, 1e-9), h2d, 4 * batch, steps
+    return decoded / max(seconds, 1e-9), h2d, 4 * batch, decoded // batch
 
 
 def run_ours(args) -> dict:

@@ -102,6 +102,7 @@ class RequestCache:
     # per group: logical page -> physical page (-1 once a window has passed it)
     tables: list[list[int]] = field(default_factory=list)
     released: list[int] = field(default_factory=list)  # per group: logical pages given back so far
+    tables_np: list = field(default_factory=list)      # per group: the same table as an int32 array (grown as needed)
 
 
 @dataclass
@@ -177,7 +178,8 @@ class CacheManager:
         slot = self._free_slots.popleft()
         for tensor in self.states.tensors.values():
             tensor[slot].zero_()
-        request = RequestCache(request_id, slot, 0, [[] for _ in self.groups], [0 for _ in self.groups])
+        request = RequestCache(request_id, slot, 0, [[] for _ in self.groups], [0 for _ in self.groups],
+                               [np.full(16, -1, dtype=np.int32) for _ in self.groups])
         self.requests[request_id] = request
         return request
 
@@ -210,9 +212,16 @@ class CacheManager:
         for group, table in zip(self.groups, request.tables):
             if after - len(table) > group.pool.free_pages:
                 raise CacheFullError("paged KV cache has no free blocks")
-        for group, table in zip(self.groups, request.tables):
+        for index, (group, table) in enumerate(zip(self.groups, request.tables)):
             while len(table) < after:
-                table.append(group.pool.allocate(request_id))
+                page = group.pool.allocate(request_id)
+                mirror = request.tables_np[index]
+                if len(table) >= mirror.shape[0]:
+                    grown = np.full(max(2 * mirror.shape[0], after), -1, dtype=np.int32)
+                    grown[:mirror.shape[0]] = mirror
+                    request.tables_np[index] = mirror = grown
+                mirror[len(table)] = page
+                table.append(page)
         first = request.length
         request.length += count
         used = sum(group.pool.used_pages for group in self.groups)
@@ -237,6 +246,7 @@ class CacheManager:
             while page < len(table) and (page + 1) * self.page_size <= first_needed:
                 group.pool.free(table[page], request_id)
                 table[page] = -1
+                request.tables_np[index][page] = -1
                 page += 1
                 given += 1
             request.released[index] = page
@@ -264,6 +274,11 @@ class CacheManager:
 
     def block_table(self, group_index: int, request_id: str) -> list[int]:
         return self.requests[request_id].tables[group_index]
+
+    def block_table_array(self, group_index: int, request_id: str) -> np.ndarray:
+        """The request's block table as an int32 array (a view; its first len(block_table) entries count)."""
+        request = self.requests[request_id]
+        return request.tables_np[group_index][:len(request.tables[group_index])]
 
     def layer_view(self, layer: int) -> LayerCache:
         """The storage of ``layer`` (or of the layer whose cache it reads)."""

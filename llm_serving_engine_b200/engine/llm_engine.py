@@ -203,7 +203,7 @@ class LLMEngine:
             entries, sampled = [], []
             for request, count in planned:
                 first = request.processed_tokens
-                tokens = request.all_tokens[first:first + count]
+                tokens = request.tokens_from(first, count)
                 done = first + count == request.total_tokens
                 entries.append(StepEntry(request.request_id, tokens, [count - 1] if done else []))
                 if done:
@@ -258,6 +258,11 @@ class LLMEngine:
         self._configs.clear()
         self._pending_callbacks.clear()
         self._just_finished.clear()
+
+    def warmup(self, batch_sizes=None) -> None:
+        """Capture the CUDA graphs of decode steps ahead of time (one per batch bucket up to
+        ``max_batch_size``), so that no request pays for a capture.  Uses temporary requests."""
+        self.runner.warmup(batch_sizes)
 
     async def close(self) -> None:
         self._closed = True

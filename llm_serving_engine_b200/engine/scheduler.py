@@ -45,6 +45,16 @@ class RequestState:
     def all_tokens(self) -> list[int]:
         return self.prompt_token_ids + self.generated_token_ids
 
+    def tokens_from(self, first: int, count: int) -> list[int]:
+        """Tokens first .. first+count-1 of prompt + generated, without joining the two lists."""
+        prompt = self.prompt_token_ids
+        n_prompt = len(prompt)
+        if first >= n_prompt:
+            return self.generated_token_ids[first - n_prompt:first - n_prompt + count]
+        if first + count <= n_prompt:
+            return prompt[first:first + count]
+        return prompt[first:] + self.generated_token_ids[:first + count - n_prompt]
+
     @property
     def total_tokens(self) -> int:
         return len(self.prompt_token_ids) + len(self.generated_token_ids)

@@ -131,6 +131,9 @@ class StepRunner:
         self._copy_pending = False
         self.use_graphs = bool(use_graphs) and pinned and getattr(model, "graph_safe", False)
         self._graphs: dict[tuple[int, int], _Graph] = {}
+        self._graph_pool = None          # one memory pool for all graphs: only one of them runs at a time
+        self._capture_stream = None
+        self._arange = np.arange(max(self.GRAPH_BUCKETS), dtype=np.int32)
         self.steps_run = 0
         self.graph_replays = 0
         self.graph_kernel_launches = 0
@@ -214,9 +217,9 @@ class StepRunner:
                     want_cursor += 1
             for g in range(self._groups):
                 host[lay.maps[g][0] + row: lay.maps[g][0] + row + count] = cache.slot_mapping(g, entry.request_id, first, count)
-                table = cache.block_table(g, entry.request_id)
+                table = cache.block_table_array(g, entry.request_id)
                 base = lay.tables[g][0] + index * lay.table_width
-                host[base: base + len(table)] = table
+                host[base: base + table.shape[0]] = table
             step.max_segment_tokens = max(step.max_segment_tokens, count)
             step.max_context = max(step.max_context, first + count)
             row += count
@@ -224,6 +227,47 @@ class StepRunner:
         if wanted_all_rows:
             host[lay.want[0]:lay.want[1]] = np.arange(lay.wanted, dtype=np.int32)
         step.decode_only = step.max_segment_tokens == 1
+        return step
+
+    def _pack_decode(self, entries: list[StepEntry], host: np.ndarray, lay: _Layout) -> StepContext:
+        """``_pack`` for steps in which every entry brings one token and every row is wanted:
+        the arrays are built as lists and written with one assignment each."""
+        cache = self.cache
+        page_size = cache.page_size
+        count = len(entries)
+        step = StepContext()
+        tokens, firsts, slots_of = [], [], []
+        for lo, hi in lay.tables:
+            host[lo:hi] = -1
+        group_slots = [[] for _ in range(self._groups)]
+        for index, entry in enumerate(entries):
+            first = cache.reserve(entry.request_id, 1)
+            request = cache.requests[entry.request_id]
+            tokens.append(entry.tokens[0])
+            firsts.append(first)
+            slots_of.append(request.state_slot)
+            step.segments.append(Segment(entry.request_id, request.state_slot, first, 1, index))
+            for g in range(self._groups):
+                table = request.tables[g]
+                group_slots[g].append(table[first // page_size] * page_size + first % page_size)
+                mirror = request.tables_np[g]
+                base = lay.tables[g][0] + index * lay.table_width
+                host[base: base + len(table)] = mirror[:len(table)]
+        pad = lay.tokens - count
+        rows = list(range(count))
+        host[lay.tok[0]:lay.tok[1]] = tokens + [0] * pad
+        host[lay.pos[0]:lay.pos[1]] = firsts + [0] * pad
+        host[lay.seg[0]:lay.seg[1]] = rows + [-1] * pad
+        host[lay.start[0]:lay.start[1]] = rows + [count] * (lay.segments + 1 - count)
+        host[lay.first[0]:lay.first[1]] = firsts + [0] * pad
+        host[lay.ctx[0]:lay.ctx[1]] = [first + 1 for first in firsts] + [0] * pad
+        host[lay.slot[0]:lay.slot[1]] = slots_of + [0] * pad
+        host[lay.want[0]:lay.want[1]] = self._arange[:lay.wanted]
+        for g in range(self._groups):
+            host[lay.maps[g][0]:lay.maps[g][1]] = group_slots[g] + [-1] * pad
+        step.max_segment_tokens = 1
+        step.max_context = max(firsts) + 1
+        step.decode_only = True
         return step
 
     def _views(self, step: StepContext, dev: torch.Tensor, lay: _Layout):
@@ -274,35 +318,22 @@ class StepRunner:
         if bucket is None:
             step, caches = self.prepare(entries, validated=True)
             return self.model.forward(step, caches)
-        need = self._pages_after(entries)
-        width = 16
-        while width < need:
-            width *= 2
-        key = (bucket, width)
+        key = (bucket, self._graph_width(self._pages_after(entries)))
         slot = self._graphs.get(key)
         if slot is None:
-            slot = _Graph(_Layout(bucket, bucket, bucket, width, self._groups), self.device, True)
+            slot = _Graph(_Layout(bucket, bucket, bucket, key[1], self._groups), self.device, True)
             self._graphs[key] = slot
         if self._copy_pending:
             self._copied.synchronize()
             self._copy_pending = False
-        step = self._pack(entries, slot.host_np, slot.layout, wanted_all_rows=True)
+        step = self._pack_decode(entries, slot.host_np, slot.layout)
         step.max_context = None
         slot.device.copy_(slot.host, non_blocking=True)
         self.last_h2d_bytes = slot.layout.size * 4
         self._copied.record()
         self._copy_pending = True
         if slot.graph is None:
-            step, caches = self._views(step, slot.device, slot.layout)
-            self.model.forward(step, caches)           # once launch by launch: first-use set-up happens here
-            torch.cuda.current_stream().synchronize()
-            from ..kernels import library
-            before = library.launches()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                slot.logits = self.model.forward(step, caches)
-            slot.launches = library.launches() - before
-            slot.graph = graph
+            self._capture(slot, step)
         slot.graph.replay()
         self.graph_replays += 1
         self.graph_kernel_launches += slot.launches
@@ -312,6 +343,62 @@ class StepRunner:
         if not rows:
             return slot.logits[:0]
         return slot.logits[torch.tensor(rows, device=self.device)]
+
+    def _graph_width(self, pages_needed: int) -> int:
+        """Block-table width of a captured step: the whole table of a request when that is at most
+        2,048 entries (one graph per batch bucket), else the next power of two."""
+        full = _round4(self.cache.max_pages_per_request)
+        if full <= 2048:
+            return full
+        width = 2048
+        while width < pages_needed:
+            width *= 2
+        return width
+
+    def _capture(self, slot: _Graph, step: StepContext) -> None:
+        """Run the step once launch by launch (first-use set-up happens here), then capture the same
+        launches into a graph.  The captured step is this very step, so replaying it is harmless."""
+        from ..kernels import library
+
+        step, caches = self._views(step, slot.device, slot.layout)
+        self.model.forward(step, caches)
+        current = torch.cuda.current_stream()
+        current.synchronize()
+        if self._capture_stream is None:
+            self._capture_stream = torch.cuda.Stream()
+            self._graph_pool = torch.cuda.graph_pool_handle()
+        before = library.launches()
+        graph = torch.cuda.CUDAGraph()
+        self._capture_stream.wait_stream(current)
+        with torch.cuda.stream(self._capture_stream):
+            graph.capture_begin(pool=self._graph_pool)
+            try:
+                slot.logits = self.model.forward(step, caches)
+            finally:
+                graph.capture_end()
+        current.wait_stream(self._capture_stream)
+        slot.launches = library.launches() - before
+        slot.graph = graph
+
+    def warmup(self, batch_sizes=None) -> None:
+        """Capture the decode graphs of the given batch sizes (default: every bucket up to
+        ``max_segments``) with temporary one-token requests, then give their pages back."""
+        if not self.use_graphs:
+            return
+        sizes = batch_sizes or [b for b in self.GRAPH_BUCKETS if b <= self.max_segments]
+        if not batch_sizes and self.max_segments not in sizes:
+            sizes.append(next((b for b in self.GRAPH_BUCKETS if b >= self.max_segments), self.max_segments))
+        for size in sorted({min(int(n), self.max_segments) for n in sizes}):
+            names = [f"__warmup_{index}" for index in range(size)]
+            try:
+                for name in names:
+                    self.cache.create(name)
+                self.run([StepEntry(name, [0], [0]) for name in names])
+                torch.cuda.current_stream().synchronize()
+            finally:
+                for name in names:
+                    if name in self.cache.requests:
+                        self.cache.free(name)
 
     def finish(self, entries: list[StepEntry]) -> None:
         """After the step: give back pages that a window has passed."""
