@@ -32,6 +32,7 @@ QWEN25_1P5B = {
     "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "attention_bias": True, "tie_word_embeddings": True,
 }
 FULL_LAYERS = QWEN25_1P5B["num_hidden_layers"]
+USE_GRAPHS = True     # --no-graphs: launch by launch (for profilers)
 PROMPT = 2048
 BLOCK = 16
 
@@ -124,7 +125,8 @@ def time_decode(model, batch: int, steps: int, warmup: int):
     pages = batch * (context // BLOCK)
     cache = CacheManager(cache_requirements(model.spec), CacheConfig(BLOCK, pages), model.dtype, model.device,
                          context, num_state_slots=batch)
-    runner = StepRunner(model, cache, max_tokens_per_step=max(PROMPT, batch), max_segments=batch)
+    runner = StepRunner(model, cache, max_tokens_per_step=max(PROMPT, batch), max_segments=batch,
+                        use_graphs=USE_GRAPHS)
     generator = torch.Generator().manual_seed(1)
     ids = [f"d{index}" for index in range(batch)]
     with torch.inference_mode():
@@ -251,6 +253,11 @@ def run_ours(args) -> dict:
     weight_bytes = model.weight_bytes_per_step()
     batch = args.batch
 
+    if args.only == "decode":     # a short run of one part, for profilers; prints no bench line
+        ms, _, _ = time_decode(model, batch, args.steps, args.warmup)
+        return {"only": "decode", "batch": batch, "layers": layers, "ms_per_step": round(ms, 4)}
+    if args.only == "prefill":
+        return {"only": "prefill", "layers": layers, "ms": round(time_prefill(model, repeats=max(1, args.steps)), 4)}
     with ClockSampler() as clocks:
         ms, kv_bytes, launches = time_decode(model, batch, args.steps, args.warmup)
     value = batch / (ms / 1e3)
@@ -296,7 +303,12 @@ def main() -> int:
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the full model (0 = all)")
+    parser.add_argument("--only", choices=("all", "decode", "prefill"), default="all",
+                        help="run one part only (a small case for ncu; no bench line)")
+    parser.add_argument("--no-graphs", action="store_true", help="decode launch by launch instead of from CUDA graphs")
     args = parser.parse_args()
+    global USE_GRAPHS
+    USE_GRAPHS = not args.no_graphs
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
                           "offline pip install of the reference fails: its build backend (hatchling) is not in the wheelhouse"}))
@@ -304,7 +316,8 @@ def main() -> int:
     if args.gpus != 1:
         print(f"bench.py measures a single-GPU engine; --gpus {args.gpus} is not supported")
         return 2
-    args.warmup = max(args.warmup, 3)
+    if args.only == "all":
+        args.warmup = max(args.warmup, 3)
     print(json.dumps(run_ours(args)))
     return 0
 

@@ -98,7 +98,7 @@ add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* __restrict__ delt
   float sq = 0.f;
 #pragma unroll
   for (int c = 0; c < NORM_CHUNKS; ++c) {
-    const int i = (c * NORM_THREADS + threadIdx.x);
+    const int i = (c * (int)blockDim.x + threadIdx.x);
     if (i < chunks) {
       load4<float>(res + 4 * i, x[c]);
       if (del) {
@@ -126,7 +126,7 @@ add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* __restrict__ delt
   TO* dst = out + (size_t)r * hidden;
 #pragma unroll
   for (int c = 0; c < NORM_CHUNKS; ++c) {
-    const int i = (c * NORM_THREADS + threadIdx.x);
+    const int i = (c * (int)blockDim.x + threadIdx.x);
     if (i < chunks) {
       float w[4], y[4];
       load4<float>(weight + 4 * i, w);
@@ -178,7 +178,12 @@ static void launch_add_rmsnorm(float* residual, const void* delta, int n_partial
   const bool aligned = (((uintptr_t)residual | (uintptr_t)delta | (uintptr_t)weight | (uintptr_t)out) & 15) == 0 &&
                        (partial_stride % 4) == 0;
   if (hidden % 4 == 0 && hidden <= NORM_THREADS * NORM_CHUNKS * 4 && aligned) {
-    lse_launch(add_rmsnorm_vec_kernel<TD, TO>, n_rows, NORM_THREADS, 0, stream,
+    // few rows (decoding): one float4 chunk per thread, the shortest chain; many rows (prompts): up to
+    // four chunks per thread, so that more rows are in flight on an SM
+    const int per_thread = n_rows >= 256 ? NORM_CHUNKS : 1;
+    int threads = (((hidden / 4 + per_thread - 1) / per_thread + 31) / 32) * 32;
+    if (threads > NORM_THREADS) threads = NORM_THREADS;
+    lse_launch(add_rmsnorm_vec_kernel<TD, TO>, n_rows, threads, 0, stream,
         residual, (const TD*)delta, n_partials, partial_stride, weight, (TO*)out, rows, hidden, eps, write_residual);
   } else {
     const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
@@ -215,7 +220,11 @@ extern "C" int lse_add_rmsnorm(float* residual, const void* delta, int delta_dty
 // [page][kv head][offset][D]).  slot < 0: nothing is cached for this token
 // (padding row).  pairing 0: pairs (2i, 2i+1); 1: (i, i+D/2).
 //
-// grid: (tokens, groups of heads); a thread owns one pair (or, for values, two elements) of one head.
+// grid: (tokens, groups of heads); a thread owns four pairs of one head: eight consecutive
+// elements (pairs (2i, 2i+1)) or four elements of each half (pairs (i, i + D/2)); either way the
+// pairs have the frequency indices 4c .. 4c+3, c being the thread's index inside the head.
+template <typename T> __device__ __forceinline__ void rope_load4(const T* p, float (&v)[4]) { load4<T>(p, v); }
+
 template <typename TI, typename TO>
 __global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, int n_partials, long long partial_stride,
                                      const float* __restrict__ bias, const int* __restrict__ positions,
@@ -228,31 +237,44 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, int n_partials,
   pdl_wait();
   LSE_TL_MARK(2)
   const int t = blockIdx.x;
-  const int half = head_dim >> 1;
-  const int i = threadIdx.x % half;
-  const int head = blockIdx.y * (blockDim.x / half) + threadIdx.x / half;   // queries, then keys, then values
+  const int per_head = head_dim >> 3;   // threads per head
+  const int c = threadIdx.x % per_head;
+  const int head = blockIdx.y * (blockDim.x / per_head) + threadIdx.x / per_head;   // queries, then keys, then values
   if (head >= n_q + 2 * n_kv) return;
   const int slot = slot_mapping[t];
   const bool is_q = head < n_q, is_k = !is_q && head < n_q + n_kv;
   if (!is_q && slot < 0) return;   // padding row: nothing is cached
-  const int ia = pairing == 0 ? 2 * i : i;
-  const int ib = pairing == 0 ? 2 * i + 1 : i + half;
+  const int half = head_dim >> 1;
+  // the two groups of four elements this thread owns
+  const int e0 = pairing == 0 ? 8 * c : 4 * c;
+  const int e1 = pairing == 0 ? 8 * c + 4 : half + 4 * c;
   const size_t col = (size_t)head * head_dim;
   const TI* row = qkv + (size_t)t * qkv_stride + col;
-  float xa = 0.f, xb = 0.f;
+  float g0[4] = {0.f, 0.f, 0.f, 0.f}, g1[4] = {0.f, 0.f, 0.f, 0.f};
   for (int p0 = 0; p0 < n_partials; p0 += 8) {   // eight partial sums per round trip, added in index order
-    float a[8], b[8];
+    float a[8][4], b[8][4];
 #pragma unroll
     for (int p = 0; p < 8; ++p) {
-      const bool in = p0 + p < n_partials;
-      a[p] = in ? to_f32<TI>(row[(size_t)(p0 + p) * partial_stride + ia]) : 0.f;
-      b[p] = in ? to_f32<TI>(row[(size_t)(p0 + p) * partial_stride + ib]) : 0.f;
+      if (p0 + p < n_partials) {
+        load4<TI>(row + (size_t)(p0 + p) * partial_stride + e0, a[p]);
+        load4<TI>(row + (size_t)(p0 + p) * partial_stride + e1, b[p]);
+      }
     }
 #pragma unroll
-    for (int p = 0; p < 8; ++p)
-      if (p0 + p < n_partials) { xa += a[p]; xb += b[p]; }
+    for (int p = 0; p < 8; ++p) {
+      if (p0 + p < n_partials) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { g0[j] += a[p][j]; g1[j] += b[p][j]; }
+      }
+    }
   }
-  if (bias) { xa += bias[col + ia]; xb += bias[col + ib]; }
+  if (bias) {
+    float ba[4], bb[4];
+    load4<float>(bias + col + e0, ba);
+    load4<float>(bias + col + e1, bb);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { g0[j] += ba[j]; g1[j] += bb[j]; }
+  }
   TO* dst;
   if (is_q) {
     dst = q_out + ((size_t)t * n_q + head) * head_dim;
@@ -262,14 +284,30 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, int n_partials,
     dst = (is_k ? k_cache : v_cache) + ((page * n_kv + kv_head) * page_size + off) * head_dim;
   }
   if (is_q || is_k) {
-    float sn, cs;
-    sincosf((float)positions[t] * inv_freq[i], &sn, &cs);
-    dst[ia] = from_f32<TO>(xa * cs - xb * sn);
-    dst[ib] = from_f32<TO>(xb * cs + xa * sn);
-  } else {
-    dst[ia] = from_f32<TO>(xa);
-    dst[ib] = from_f32<TO>(xb);
+    const float pos = (float)positions[t];
+    float xa[4], xb[4];
+    if (pairing == 0) { xa[0] = g0[0]; xb[0] = g0[1]; xa[1] = g0[2]; xb[1] = g0[3]; xa[2] = g1[0]; xb[2] = g1[1]; xa[3] = g1[2]; xb[3] = g1[3]; }
+    else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { xa[j] = g0[j]; xb[j] = g1[j]; }
+    }
+    float freq[4];
+    load4<float>(inv_freq + 4 * c, freq);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float sn, cs;
+      sincosf(pos * freq[j], &sn, &cs);
+      const float ya = xa[j] * cs - xb[j] * sn, yb = xb[j] * cs + xa[j] * sn;
+      xa[j] = ya; xb[j] = yb;
+    }
+    if (pairing == 0) { g0[0] = xa[0]; g0[1] = xb[0]; g0[2] = xa[1]; g0[3] = xb[1]; g1[0] = xa[2]; g1[1] = xb[2]; g1[2] = xa[3]; g1[3] = xb[3]; }
+    else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { g0[j] = xa[j]; g1[j] = xb[j]; }
+    }
   }
+  store4<TO>(dst + e0, g0);
+  store4<TO>(dst + e1, g1);
   LSE_TL_MARK(3)
 }
 
@@ -279,14 +317,17 @@ extern "C" int lse_rope_kv_write(const void* qkv, int in_dtype, int n_partials, 
                                  int tokens, int n_q, int n_kv, int head_dim, int page_size, int pairing,
                                  long long qkv_stride, cudaStream_t stream) {
   if (tokens <= 0) return 0;
-  if (head_dim % 2 || head_dim > 1024 || page_size <= 0 || (pairing != 0 && pairing != 1) || n_partials < 1)
+  // eight elements per thread: the head size is a multiple of 8 (16 for the half-split pairing)
+  if (head_dim % 8 || (pairing == 1 && head_dim % 16) || head_dim > 2048 || page_size <= 0 ||
+      (pairing != 0 && pairing != 1) || n_partials < 1 || qkv_stride % 4 || partial_stride % 4 ||
+      (((uintptr_t)qkv | (uintptr_t)bias | (uintptr_t)inv_freq | (uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15))
     return LSE_ERR_BAD_ARGUMENT;
-  const int half = head_dim / 2;
+  const int per_head = head_dim / 8;
   const int heads = n_q + 2 * n_kv;
-  int per_block = 128 / half;   // heads per block
+  int per_block = (tokens >= 64 ? 256 : 64) / per_head;   // heads per block: few tokens -> more, smaller blocks
   if (per_block < 1) per_block = 1;
   if (per_block > heads) per_block = heads;
-  const int threads = half * per_block;
+  const int threads = per_head * per_block;
   dim3 grid(tokens, (heads + per_block - 1) / per_block);
 #define LSE_ROPE_CASE(TI, TO)                                                                                   \
   lse_launch(rope_kv_write_kernel<TI, TO>, grid, threads, 0, stream,                                            \
@@ -336,12 +377,66 @@ __global__ void silu_mul_kernel(const TI* __restrict__ gate_up, int n_partials, 
   LSE_TL_MARK(3)
 }
 
+// bfloat16 in and out, one split, I % 8 == 0: sixteen bytes per load, one load of gate and of up in
+// flight per thread (more did not help: the exponentials bound it); the chunks of all rows are
+// numbered flat so that no block is half empty
+constexpr int SILU_UNROLL = 1;
+__global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out,
+                                       int inter, long long total_chunks) {
+  LSE_TL_BEGIN(4)
+  pdl_launch_dependents();
+  pdl_wait();
+  LSE_TL_MARK(2)
+  const int per_row = inter >> 3;
+  const long long first = (long long)blockIdx.x * blockDim.x * SILU_UNROLL + threadIdx.x;
+  uint4 g[SILU_UNROLL], u[SILU_UNROLL];
+  long long where[SILU_UNROLL];
+#pragma unroll
+  for (int k = 0; k < SILU_UNROLL; ++k) {
+    const long long id = first + (long long)k * blockDim.x;
+    where[k] = -1;
+    if (id < total_chunks) {
+      const long long t = id / per_row;
+      const int i = (int)(id - t * per_row) * 8;
+      const __nv_bfloat16* row = gate_up + t * 2 * inter;
+      g[k] = *reinterpret_cast<const uint4*>(row + i);
+      u[k] = *reinterpret_cast<const uint4*>(row + inter + i);
+      where[k] = t * inter + i;
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < SILU_UNROLL; ++k) {
+    if (where[k] < 0) continue;
+    const uint32_t gw[4] = {g[k].x, g[k].y, g[k].z, g[k].w}, uw[4] = {u[k].x, u[k].y, u[k].z, u[k].w};
+    uint32_t yw[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const __nv_bfloat162 g2 = *reinterpret_cast<const __nv_bfloat162*>(&gw[e]);
+      const __nv_bfloat162 u2 = *reinterpret_cast<const __nv_bfloat162*>(&uw[e]);
+      const float ga = __low2float(g2), gb = __high2float(g2);
+      // the result is rounded to bfloat16: the fast exponential and division are far below that
+      __nv_bfloat162 y = __floats2bfloat162_rn(__fdividef(ga, 1.0f + __expf(-ga)) * __low2float(u2),
+                                               __fdividef(gb, 1.0f + __expf(-gb)) * __high2float(u2));
+      yw[e] = *reinterpret_cast<uint32_t*>(&y);
+    }
+    *reinterpret_cast<uint4*>(out + where[k]) = make_uint4(yw[0], yw[1], yw[2], yw[3]);
+  }
+  LSE_TL_MARK(3)
+}
+
 extern "C" int lse_silu_mul(const void* gate_up, int in_dtype, int n_partials, long long partial_stride, void* out,
                             int out_dtype, int tokens, int inter, cudaStream_t stream) {
   if (tokens <= 0 || inter <= 0) return 0;
   if (n_partials < 1) return LSE_ERR_BAD_ARGUMENT;
   const bool vec = inter % 4 == 0 && partial_stride % 4 == 0 && (((uintptr_t)gate_up | (uintptr_t)out) & 15) == 0;
   const int threads = 256;
+  if (vec && inter % 8 == 0 && n_partials == 1 && in_dtype == LSE_DTYPE_BF16 && out_dtype == LSE_DTYPE_BF16) {
+    const long long total_chunks = (long long)tokens * (inter / 8);
+    const unsigned blocks = (unsigned)((total_chunks + threads * SILU_UNROLL - 1) / (threads * SILU_UNROLL));
+    lse_launch(silu_mul_bf16x8_kernel, blocks, threads, 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out,
+               inter, total_chunks);
+    LSE_LAUNCH_CHECK();
+  }
   const int per_row = vec ? inter / 4 : inter;
   dim3 grid((per_row + threads - 1) / threads, tokens);
 #define LSE_SILU_CASE(TI, TO)                                                                                      \

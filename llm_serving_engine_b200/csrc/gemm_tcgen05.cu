@@ -87,11 +87,14 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
 __global__ void __launch_bounds__(128)
 gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                         float* __restrict__ out, int M, int N, int k_tiles, int tiles_per_split, int m_pad,
-                        int stages) {
+                        int stages, int kboxes) {
   extern __shared__ unsigned char smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  // a stage holds `kboxes` adjacent 64-wide k-boxes of w, then the same boxes of x: one row of w is
+  // then read in pieces of kboxes * 128 contiguous bytes, which DRAM serves better than 128
   const uint32_t b_bytes = (uint32_t)m_pad * BLOCK_K * 2;
-  const uint32_t stage_bytes = A_BYTES + b_bytes;
+  const uint32_t stage_bytes = (uint32_t)kboxes * (A_BYTES + b_bytes);
+  const uint32_t b_base = (uint32_t)kboxes * A_BYTES;   // offset of the x boxes inside a stage
   const uint32_t bars = base + (uint32_t)stages * stage_bytes;   // full[stages], empty[stages], accum
   const uint32_t accum_bar = bars + 16u * stages;
   unsigned char* tail = smem_raw + (bars - smem_u32(smem_raw)) + 16 * stages + 8;
@@ -135,12 +138,16 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
       for (int it = 0; it < early; ++it) {
         const uint32_t full = bars + 8u * it;
         mbar_expect_tx(full, stage_bytes);
-        tma_load_2d(base + (uint32_t)it * stage_bytes, &map_w, full, (tile_lo + it) * BLOCK_K, n0);
+        for (int b = 0; b < kboxes; ++b)
+          tma_load_2d(base + (uint32_t)it * stage_bytes + (uint32_t)b * A_BYTES, &map_w, full,
+                      ((tile_lo + it) * kboxes + b) * BLOCK_K, n0);
       }
       pdl_wait();
       LSE_TL_MARK(2)
       for (int it = 0; it < early; ++it)
-        tma_load_2d(base + (uint32_t)it * stage_bytes + A_BYTES, &map_x, bars + 8u * it, (tile_lo + it) * BLOCK_K, 0);
+        for (int b = 0; b < kboxes; ++b)
+          tma_load_2d(base + (uint32_t)it * stage_bytes + b_base + (uint32_t)b * b_bytes, &map_x, bars + 8u * it,
+                      ((tile_lo + it) * kboxes + b) * BLOCK_K, 0);
       for (int it = early; it < n_tiles; ++it) {
         const int s = it % stages;
         const uint32_t parity = (uint32_t)(it / stages) & 1u;
@@ -148,9 +155,11 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
         const uint32_t full = bars + 8u * s;
         mbar_expect_tx(full, stage_bytes);
         const uint32_t a_dst = base + (uint32_t)s * stage_bytes;
-        const int k = (tile_lo + it) * BLOCK_K;
-        tma_load_2d(a_dst, &map_w, full, k, n0);
-        tma_load_2d(a_dst + A_BYTES, &map_x, full, k, 0);
+        for (int b = 0; b < kboxes; ++b) {
+          const int k = ((tile_lo + it) * kboxes + b) * BLOCK_K;
+          tma_load_2d(a_dst + (uint32_t)b * A_BYTES, &map_w, full, k, n0);
+          tma_load_2d(a_dst + b_base + (uint32_t)b * b_bytes, &map_x, full, k, 0);
+        }
       }
     }
     __syncwarp();
@@ -168,11 +177,13 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         const uint32_t a_src = base + (uint32_t)s * stage_bytes;
+        for (int b = 0; b < kboxes; ++b) {
 #pragma unroll
-        for (int kk = 0; kk < BLOCK_K / UMMA_K; ++kk) {
-          const uint64_t da = smem_desc(a_src + kk * UMMA_K * 2);
-          const uint64_t db = smem_desc(a_src + A_BYTES + kk * UMMA_K * 2);
-          umma_bf16(tmem_base, da, db, idesc, (it | kk) != 0 ? 1u : 0u);
+          for (int kk = 0; kk < BLOCK_K / UMMA_K; ++kk) {
+            const uint64_t da = smem_desc(a_src + (uint32_t)b * A_BYTES + kk * UMMA_K * 2);
+            const uint64_t db = smem_desc(a_src + b_base + (uint32_t)b * b_bytes + kk * UMMA_K * 2);
+            umma_bf16(tmem_base, da, db, idesc, (it | b | kk) != 0 ? 1u : 0u);
+          }
         }
         umma_commit(bars + 8u * (stages + s));   // the stage is free once these MMAs have read it
       }
@@ -250,8 +261,9 @@ extern "C" int lse_gemm_bf16_skinny_pad(int M) {
 }
 
 // How many k-splits the launcher will really use for a wish of `splits` (every split gets work).
-extern "C" int lse_gemm_bf16_skinny_splits(int K, int splits) {
-  const int k_tiles = (K + BLOCK_K - 1) / BLOCK_K;
+extern "C" int lse_gemm_bf16_skinny_splits(int K, int splits, int kboxes) {
+  if (kboxes != 1 && kboxes != 2 && kboxes != 4) kboxes = 1;
+  const int k_tiles = (K + BLOCK_K * kboxes - 1) / (BLOCK_K * kboxes);
   if (splits < 1) splits = 1;
   if (splits > k_tiles) splits = k_tiles;
   const int per = (k_tiles + splits - 1) / splits;
@@ -268,14 +280,15 @@ extern "C" int lse_gemm_bf16_skinny_status(void) {
 // out[split][m][n] (float32, splits * M * N values) = partial sums of x[M, K] * w[N, K]^T.
 // x, w bfloat16 row-major, 16-byte aligned, K a multiple of 8, M <= 256.
 extern "C" int lse_gemm_bf16_skinny(const void* x, const void* w, float* out, int M, int N, int K, int splits,
-                                    int stages, cudaStream_t stream) {
+                                    int stages, int kboxes, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   const int m_pad = lse_gemm_bf16_skinny_pad(M);
   if (m_pad == 0 || K <= 0 || K % 8 || (((uintptr_t)x | (uintptr_t)w) & 15)) return LSE_ERR_BAD_ARGUMENT;
-  const int k_tiles = (K + BLOCK_K - 1) / BLOCK_K;
-  splits = lse_gemm_bf16_skinny_splits(K, splits);
+  if (kboxes != 1 && kboxes != 2 && kboxes != 4) return LSE_ERR_BAD_ARGUMENT;
+  const int k_tiles = (K + BLOCK_K * kboxes - 1) / (BLOCK_K * kboxes);
+  splits = lse_gemm_bf16_skinny_splits(K, splits, kboxes);
   const int per = (k_tiles + splits - 1) / splits;
-  const uint32_t stage_bytes = A_BYTES + (uint32_t)m_pad * BLOCK_K * 2;
+  const uint32_t stage_bytes = (uint32_t)kboxes * (A_BYTES + (uint32_t)m_pad * BLOCK_K * 2);
   if (stages < 2) stages = 2;
   while (stages > 2 && (size_t)stages * stage_bytes + 2048 > 200 * 1024) --stages;
   if (stages > per + 1) stages = per + 1 < 2 ? 2 : per + 1;
@@ -290,7 +303,7 @@ extern "C" int lse_gemm_bf16_skinny(const void* x, const void* w, float* out, in
   }
   dim3 grid((N + BLOCK_N - 1) / BLOCK_N, splits);
   cudaError_t err = lse_launch(gemm_bf16_skinny_kernel, grid, 128, smem, stream, map_w, map_x, out, M, N, k_tiles, per,
-                               m_pad, stages);
+                               m_pad, stages, kboxes);
   if (err != cudaSuccess) return (int)err;
   return (int)cudaGetLastError();
 }

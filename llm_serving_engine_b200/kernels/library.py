@@ -19,9 +19,9 @@ _SIGNATURES = {
     "lse_rope_kv_write": [c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                           c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_longlong, c_void_p],
     "lse_silu_mul": [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p],
-    "lse_gemm_bf16_skinny": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "lse_gemm_bf16_skinny": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "lse_gemm_bf16_skinny_pad": [c_int],
-    "lse_gemm_bf16_skinny_splits": [c_int, c_int],
+    "lse_gemm_bf16_skinny_splits": [c_int, c_int, c_int],
     "lse_gemm_bf16_skinny_status": [],
     "lse_gemm_f32_nt": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong,
                         c_longlong, c_longlong, c_void_p],

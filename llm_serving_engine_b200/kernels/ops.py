@@ -266,7 +266,8 @@ def gemm_bf16_skinny_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
             and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
 
 
-def gemm_bf16_skinny(x: torch.Tensor, weight: torch.Tensor, splits: int | None = None, stages: int = 6) -> torch.Tensor:
+def gemm_bf16_skinny(x: torch.Tensor, weight: torch.Tensor, splits: int | None = None, stages: int = 6,
+                     kboxes: int = 1) -> torch.Tensor:
     """Partial sums [P, M, N] (float32) of x[M, K] @ weight[N, K]^T for M <= 256, bfloat16 operands;
     the k range is cut into P splits so that enough blocks stream the weights."""
     _need_cuda(x, weight)
@@ -278,10 +279,10 @@ def gemm_bf16_skinny(x: torch.Tensor, weight: torch.Tensor, splits: int | None =
     if splits is None:
         n_tiles = -(-n // 128)
         splits = max(1, min(-(-k // 128), 148 // n_tiles)) if n_tiles < 148 else 1   # about one block per SM
-    splits = lib.lse_gemm_bf16_skinny_splits(k, int(splits))
+    splits = lib.lse_gemm_bf16_skinny_splits(k, int(splits), int(kboxes))
     out = torch.empty((splits, m, n), dtype=torch.float32, device=x.device)
     check(lib.lse_gemm_bf16_skinny(x.data_ptr(), weight.data_ptr(), out.data_ptr(), m, n, k, splits, int(stages),
-                                   _stream()), "gemm_bf16_skinny")
+                                   int(kboxes), _stream()), "gemm_bf16_skinny")
     return out
 
 
