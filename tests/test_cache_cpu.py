@@ -27,6 +27,7 @@ def check_invariants(cache: CacheManager) -> None:
             for page in request.tables[index]:
                 if page >= 0:
                     assert group.pool.owner_of(page) == request.request_id
+            assert cache.block_table_array(index, request.request_id).tolist() == request.tables[index]
             live = [p for p in request.tables[index] if p >= 0]
             needed = -(-request.length // cache.page_size) - request.released[index]
             assert len(live) == needed

@@ -182,3 +182,38 @@ def test_trace_run_program(tmp_path):
         limit = helpers.tolerance(dtype, reference)
         assert float((got["a"] - reference[[0, 39, 69]]).abs().max()) <= limit
         assert float((got["b"][0] - helpers.plain_logits(name, dtype, tokens[:3])[2]).abs().max()) <= limit
+
+
+def test_warmup_captures_decode_graphs_and_leaves_the_cache_empty():
+    from llm_serving_engine_b200 import GenerationConfig
+    engine = engine_for("D", dtype="bfloat16", batch=4, pages=128)
+    engine.warmup()
+    assert engine.runner.use_graphs and len(engine.runner._graphs) == 3           # batch buckets 1, 2, 4
+    assert all(slot.graph is not None for slot in engine.runner._graphs.values())
+    assert not engine.cache.requests and engine.cache.groups[0].pool.used_pages == 0
+    prompts = prompts_for("D", (9, 30, 4), seed=5)
+    replays = engine.runner.graph_replays
+    warm = engine.generate_many(prompts, GenerationConfig(max_new_tokens=12))
+    assert engine.runner.graph_replays > replays and len(engine.runner._graphs) == 3   # no new capture
+    cold = engine_for("D", dtype="bfloat16", batch=4, pages=128)
+    cold.runner.use_graphs = False
+    assert cold.generate_many(prompts, GenerationConfig(max_new_tokens=12)) == warm       # graphs change nothing
+
+
+def test_dependent_launch_off_gives_the_same_logits(tmp_path):
+    """LSE_PDL=0 launches every kernel fully serialised; the logits must not change."""
+    name = "D"
+    rng = random.Random(9)
+    tokens = helpers.random_tokens(rng, ALL[name][0]["vocab_size"], 40)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": tokens[:30], "want": [29]}], "end": []}]
+    steps += [{"step": 1 + i, "entries": [{"id": "a", "tokens": [tokens[30 + i]], "want": [0]}], "end": []} for i in range(10)]
+    outs = {}
+    for flag in ("1", "0"):
+        out_dir = tmp_path / flag
+        run = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model",
+                              str(helpers.model_folder(name)), "--dtype", "bfloat16", "--out", str(out_dir),
+                              "--max-tokens", "64"], input="\n".join(json.dumps(s) for s in steps) + "\n",
+                             capture_output=True, text=True, timeout=900, env=dict(os.environ, LSE_PDL=flag))
+        assert run.returncode == 0, run.stderr
+        outs[flag] = helpers.collect(steps, out_dir)["a"]
+    assert torch.equal(outs["0"], outs["1"])
