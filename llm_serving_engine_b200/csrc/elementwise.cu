@@ -85,15 +85,22 @@ add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* __restrict__ delt
                        const int* __restrict__ rows, int hidden, float eps, int write_residual) {
   LSE_TL_BEGIN(2)
   pdl_launch_dependents();
+  __shared__ float scratch[32];
+  const int chunks = hidden >> 2;
+  // the norm weights do not depend on earlier kernels: fetch them before waiting for those
+  float w[NORM_CHUNKS][4];
+#pragma unroll
+  for (int c = 0; c < NORM_CHUNKS; ++c) {
+    const int i = (c * (int)blockDim.x + threadIdx.x);
+    if (i < chunks) load4<float>(weight + 4 * i, w[c]);
+  }
   pdl_wait();
   LSE_TL_MARK(2)
-  __shared__ float scratch[32];
   const int r = blockIdx.x;
   const int s = rows ? rows[r] : r;
   if (s < 0) return;
   float* res = residual + (size_t)s * hidden;
   const TD* del = delta ? delta + (size_t)s * hidden : nullptr;
-  const int chunks = hidden >> 2;
   float x[NORM_CHUNKS][4];
   float sq = 0.f;
 #pragma unroll
@@ -128,10 +135,9 @@ add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* __restrict__ delt
   for (int c = 0; c < NORM_CHUNKS; ++c) {
     const int i = (c * (int)blockDim.x + threadIdx.x);
     if (i < chunks) {
-      float w[4], y[4];
-      load4<float>(weight + 4 * i, w);
-      y[0] = (x[c][0] * inv) * w[0]; y[1] = (x[c][1] * inv) * w[1];
-      y[2] = (x[c][2] * inv) * w[2]; y[3] = (x[c][3] * inv) * w[3];
+      float y[4];
+      y[0] = (x[c][0] * inv) * w[c][0]; y[1] = (x[c][1] * inv) * w[c][1];
+      y[2] = (x[c][2] * inv) * w[c][2]; y[3] = (x[c][3] * inv) * w[c][3];
       store4<TO>(dst + 4 * i, y);
     }
   }
@@ -234,21 +240,28 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, int n_partials,
                                      long long qkv_stride) {
   LSE_TL_BEGIN(3)
   pdl_launch_dependents();
-  pdl_wait();
-  LSE_TL_MARK(2)
   const int t = blockIdx.x;
   const int per_head = head_dim >> 3;   // threads per head
   const int c = threadIdx.x % per_head;
   const int head = blockIdx.y * (blockDim.x / per_head) + threadIdx.x / per_head;   // queries, then keys, then values
-  if (head >= n_q + 2 * n_kv) return;
-  const int slot = slot_mapping[t];
-  const bool is_q = head < n_q, is_k = !is_q && head < n_q + n_kv;
-  if (!is_q && slot < 0) return;   // padding row: nothing is cached
+  const bool in_range = head < n_q + 2 * n_kv;
   const int half = head_dim >> 1;
   // the two groups of four elements this thread owns
   const int e0 = pairing == 0 ? 8 * c : 4 * c;
   const int e1 = pairing == 0 ? 8 * c + 4 : half + 4 * c;
   const size_t col = (size_t)head * head_dim;
+  // frequencies and bias do not depend on earlier kernels: fetch them before waiting for those
+  float freq[4] = {0.f, 0.f, 0.f, 0.f}, ba[4] = {0.f, 0.f, 0.f, 0.f}, bb[4] = {0.f, 0.f, 0.f, 0.f};
+  if (in_range) {
+    load4<float>(inv_freq + 4 * c, freq);
+    if (bias) { load4<float>(bias + col + e0, ba); load4<float>(bias + col + e1, bb); }
+  }
+  pdl_wait();
+  LSE_TL_MARK(2)
+  if (!in_range) return;
+  const int slot = slot_mapping[t];
+  const bool is_q = head < n_q, is_k = !is_q && head < n_q + n_kv;
+  if (!is_q && slot < 0) return;   // padding row: nothing is cached
   const TI* row = qkv + (size_t)t * qkv_stride + col;
   float g0[4] = {0.f, 0.f, 0.f, 0.f}, g1[4] = {0.f, 0.f, 0.f, 0.f};
   for (int p0 = 0; p0 < n_partials; p0 += 8) {   // eight partial sums per round trip, added in index order
@@ -268,13 +281,8 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, int n_partials,
       }
     }
   }
-  if (bias) {
-    float ba[4], bb[4];
-    load4<float>(bias + col + e0, ba);
-    load4<float>(bias + col + e1, bb);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) { g0[j] += ba[j]; g1[j] += bb[j]; }
-  }
+  for (int j = 0; j < 4; ++j) { g0[j] += ba[j]; g1[j] += bb[j]; }
   TO* dst;
   if (is_q) {
     dst = q_out + ((size_t)t * n_q + head) * head_dim;
@@ -291,8 +299,6 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, int n_partials,
 #pragma unroll
       for (int j = 0; j < 4; ++j) { xa[j] = g0[j]; xb[j] = g1[j]; }
     }
-    float freq[4];
-    load4<float>(inv_freq + 4 * c, freq);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       float sn, cs;

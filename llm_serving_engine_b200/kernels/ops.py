@@ -257,6 +257,8 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
 
 
 GEMM_SKINNY_MAX_ROWS = 256
+_GEMM_TARGET_BLOCKS = int(__import__("os").environ.get("LSE_GEMM_BLOCKS", "296"))
+_GEMM_MAX_SPLITS = int(__import__("os").environ.get("LSE_GEMM_MAX_SPLITS", "16"))
 
 
 def gemm_bf16_skinny_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
@@ -277,8 +279,10 @@ def gemm_bf16_skinny(x: torch.Tensor, weight: torch.Tensor, splits: int | None =
         raise KernelError("gemm_bf16_skinny: operands must be contiguous bfloat16, K a multiple of 8, at most 256 rows")
     lib = library.load()
     if splits is None:
+        # about two blocks per SM (more of the weights are fetched ahead while earlier kernels run), but no
+        # more splits than keep the partial sums (4 bytes per row, column and split) well below the weight bytes
         n_tiles = -(-n // 128)
-        splits = max(1, min(-(-k // 128), 148 // n_tiles)) if n_tiles < 148 else 1   # about one block per SM
+        splits = max(1, min(-(-k // 128), _GEMM_TARGET_BLOCKS // n_tiles, max(1, k // (4 * m)), _GEMM_MAX_SPLITS)) if n_tiles < 148 else 1
     splits = lib.lse_gemm_bf16_skinny_splits(k, int(splits), int(kboxes))
     out = torch.empty((splits, m, n), dtype=torch.float32, device=x.device)
     check(lib.lse_gemm_bf16_skinny(x.data_ptr(), weight.data_ptr(), out.data_ptr(), m, n, k, splits, int(stages),

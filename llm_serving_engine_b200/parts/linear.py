@@ -13,7 +13,10 @@ import torch
 
 from ..kernels import ops
 
-SKINNY_MAX_ROWS = 32   # above this the split-k partial sums cost more than they save
+import os
+
+# above this many rows the library product is faster (LSE_SKINNY_MAX_ROWS overrides, for comparisons)
+SKINNY_MAX_ROWS = int(os.environ.get("LSE_SKINNY_MAX_ROWS", "8"))
 
 
 def reduce_partials(y: torch.Tensor) -> torch.Tensor:
