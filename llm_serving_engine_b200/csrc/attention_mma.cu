@@ -16,7 +16,11 @@
 // float32 accumulators; probabilities are rounded to bfloat16 for the second
 // product).  Formulas as in attention_generic.cu (reference
 // src/llmserve/model.py:143-176).  Cache layout: [page][kv head][offset][D].
+#include <cooperative_groups.h>
+
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 LSE_TL_DEFINE(lse_timeline_attention)
 
@@ -116,7 +120,9 @@ struct PageMath {
   __device__ __forceinline__ int offset(int j) const { return shift >= 0 ? j & (size - 1) : j % size; }
 };
 
-template <int D>
+// CLUSTER: the splits of one (row, kv head) are the blocks of a thread-block cluster and add
+// themselves up through distributed shared memory; else through global partial sums and a counter.
+template <int D, bool CLUSTER>
 __global__ void __launch_bounds__(128)
 attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kc,
                    const __nv_bfloat16* __restrict__ vc, __nv_bfloat16* __restrict__ out,
@@ -132,8 +138,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   __shared__ int bt_s[BT_STAGE];
   LSE_TL_BEGIN(6)
   pdl_launch_dependents();
-  pdl_wait();
-  LSE_TL_MARK(2)
+  // The step's metadata (segments, positions, block tables) was copied to the device before the
+  // step's first kernel started: it is read before waiting for the kernels that produce q, k and v.
   const int t = blockIdx.x;
   const int group = n_q / n_kv;
   const int gchunks = (group + 15) / 16;
@@ -160,6 +166,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   const bool staged = n_pages <= BT_STAGE;
   if (staged)
     for (int i = tid; i < n_pages; i += 128) bt_s[i] = bt[first_page + i];
+  pdl_wait();
+  LSE_TL_MARK(2)
   // queries of the group -> shared memory (rows beyond the group are zero)
   for (int e = tid; e < 16 * CH; e += 128) {
     const int r = e / CH, c = e % CH;
@@ -292,6 +300,9 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   float* mg_acc = reinterpret_cast<float*>(kv_s);                // [4][16][D]
   float* mg_m = mg_acc + 4 * 16 * D;                             // [4][16]
   float* mg_l = mg_m + 4 * 16;                                   // [4][16]
+  float* c_o = mg_l + 4 * 16;                                    // [16][D]  this block's sums, read by the cluster
+  float* c_m = c_o + 16 * D;                                     // [16]
+  float* c_l = c_m + 16;                                         // [16]
   {
     const int r0 = lane >> 2, r1 = r0 + 8;
 #pragma unroll
@@ -324,6 +335,9 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     const int head = first_head + g;
     if (num_splits == 1) {
       out[((size_t)t * n_q + head) * D + d] = __float2bfloat16_rn(O / L);
+    } else if (CLUSTER) {
+      c_o[g * D + d] = O;
+      if (d == 0) { c_m[g] = M; c_l[g] = L; }
     } else {
       const size_t pidx = ((size_t)t * n_q + head) * num_splits + split;
       part_o[pidx * D + d] = O;
@@ -332,6 +346,42 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   }
   LSE_TL_MARK(3)
   if (num_splits == 1) return;
+  if (CLUSTER) {
+    // every split of this (row, kv head) has its sums in its own shared memory; block r of the cluster
+    // reads all of them (in split order) for its share of the outputs
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();
+    const int rank = (int)cluster.block_rank();
+    const int items = gcount * D;
+    const int per = (items + num_splits - 1) / num_splits;
+    const int hi = min(items, (rank + 1) * per);
+    for (int e = rank * per + tid; e < hi; e += 128) {
+      const int g = e / D, d = e % D;
+      float mr[8], lr[8], orr[8];
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        if (r < num_splits) {
+          mr[r] = cluster.map_shared_rank(c_m, r)[g];
+          lr[r] = cluster.map_shared_rank(c_l, r)[g];
+          orr[r] = cluster.map_shared_rank(c_o, r)[g * D + d];
+        } else { mr[r] = -INFINITY; lr[r] = 0.f; orr[r] = 0.f; }
+      }
+      float M = mr[0];
+#pragma unroll
+      for (int r = 1; r < 8; ++r) M = fmaxf(M, mr[r]);
+      float L = 0.f, O = 0.f;
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        const float w = mr[r] == -INFINITY ? 0.f : exp2f(mr[r] - M);
+        L += lr[r] * w;
+        O += orr[r] * w;
+      }
+      out[((size_t)t * n_q + first_head + g) * D + d] = __float2bfloat16_rn(O / L);
+    }
+    LSE_TL_MARK_ANY(5, tid == 0 && blockIdx.x == 0 && blockIdx.y == 0 && rank == 0)
+    cluster.sync();   // nobody leaves while its shared memory may still be read
+    return;
+  }
 
   // The split that finishes last adds up all of them (in split order, so the sum does not depend
   // on which one that is).  `arrivals` counts finished splits per (row, block column) and is put
@@ -415,11 +465,11 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   unsigned char* kv_s = smem + PF_BM * D * 2;      // [2 stages][K|V][64][D]
   __shared__ int bt_s[BT_STAGE];
   pdl_launch_dependents();
-  pdl_wait();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int kvh = blockIdx.y;
   const int group = n_q / n_kv;
 
+  // (the step's metadata is read before waiting for the kernels that produce q, k and v)
   // which tile of which request is this block's (blocks beyond the last tile leave)
   int seg = -1, r0 = 0, cnt = 0;
   {
@@ -444,6 +494,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   const bool staged = n_pages <= BT_STAGE;
   if (staged)
     for (int i = tid; i < n_pages; i += 128) bt_s[i] = bt[i];
+  pdl_wait();
 
   for (int e = tid; e < PF_BM * CH; e += 128) {
     const int m = e / CH, c = e % CH;
@@ -603,24 +654,37 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
 template <int D> size_t decode_smem() { return (size_t)DEC_TILE * D * 2 * (1 + 4 * DEC_STAGES * 2); }
 template <int D> size_t prefill_smem() { return (size_t)PF_BM * D * 2 + (size_t)2 * 2 * PF_BN * D * 2; }
 
-template <int D>
-int launch_decode(const void* q, const void* kc, const void* vc, void* out, float* part_o, float* part_ml,
-                  int* arrivals, const int* block_tables, int bt_stride, const int* seg, const int* positions,
-                  int tokens, int n_q, int n_kv, int page_size, float scale, int num_splits, cudaStream_t stream) {
+template <int D, bool CLUSTER>
+int launch_decode_as(const void* q, const void* kc, const void* vc, void* out, float* part_o, float* part_ml,
+                     int* arrivals, const int* block_tables, int bt_stride, const int* seg, const int* positions,
+                     int tokens, int n_q, int n_kv, int page_size, float scale, int num_splits, cudaStream_t stream) {
   const size_t smem = decode_smem<D>();
   static bool configured = false;   // once per process: not repeated while a stream is captured
   if (!configured) {
-    cudaError_t err = cudaFuncSetAttribute(attn_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t err = cudaFuncSetAttribute(attn_decode_kernel<D, CLUSTER>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (err != cudaSuccess) return (int)err;
     configured = true;
   }
   const int group = n_q / n_kv;
   dim3 grid(tokens, n_kv * ((group + 15) / 16), num_splits);
-  cudaError_t err = lse_launch(attn_decode_kernel<D>, grid, 128, smem, stream,
+  cudaError_t err = lse_launch_cluster(attn_decode_kernel<D, CLUSTER>, grid, 128, smem, stream,
+      CLUSTER ? (unsigned)num_splits : 1u,
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, (__nv_bfloat16*)out, part_o,
       part_ml, arrivals, block_tables, bt_stride, seg, positions, n_q, n_kv, page_size, scale * LOG2E, num_splits);
   if (err != cudaSuccess) return (int)err;
   return (int)cudaGetLastError();
+}
+
+template <int D>
+int launch_decode(const void* q, const void* kc, const void* vc, void* out, float* part_o, float* part_ml,
+                  int* arrivals, const int* block_tables, int bt_stride, const int* seg, const int* positions,
+                  int tokens, int n_q, int n_kv, int page_size, float scale, int num_splits, int cluster,
+                  cudaStream_t stream) {
+  if (cluster && num_splits > 1 && num_splits <= 8)
+    return launch_decode_as<D, true>(q, kc, vc, out, part_o, part_ml, arrivals, block_tables, bt_stride, seg, positions,
+                                     tokens, n_q, n_kv, page_size, scale, num_splits, stream);
+  return launch_decode_as<D, false>(q, kc, vc, out, part_o, part_ml, arrivals, block_tables, bt_stride, seg, positions,
+                                    tokens, n_q, n_kv, page_size, scale, num_splits, stream);
 }
 
 template <int D>
@@ -658,24 +722,27 @@ extern "C" long long lse_attention_decode_scratch_floats(int tokens, int n_q, in
   return (long long)tokens * n_q * num_splits * (head_dim + 2);
 }
 
-// `arrivals`: tokens * n_kv * ceil(group / 16) ints that are zero before the first launch (the kernel
-// leaves them zero); needed when num_splits > 1.
+// `cluster` != 0 and 2 <= num_splits <= 8: the splits form a thread-block cluster and need neither
+// `scratch` nor `arrivals`.  Else `scratch` holds the partial sums and `arrivals` is tokens * n_kv *
+// ceil(group / 16) ints that are zero before the first launch (the kernel leaves them zero).
 extern "C" int lse_paged_attention_decode(const void* q, const void* k_cache, const void* v_cache, void* out,
-                                          float* scratch, int* arrivals, const int* block_tables, int bt_stride,
+                                          float* scratch, int* arrivals, int cluster, const int* block_tables,
+                                          int bt_stride,
                                           const int* segment_of_token, const int* positions, int tokens,
                                           int n_q, int n_kv, int head_dim, int page_size, float scale,
                                           int num_splits, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (!lse_attention_mma_supported(head_dim, n_q, n_kv) || page_size <= 0 || num_splits < 1 || num_splits > 32)
     return LSE_ERR_BAD_ARGUMENT;
-  if (num_splits > 1 && (scratch == nullptr || arrivals == nullptr)) return LSE_ERR_BAD_ARGUMENT;
+  const bool by_cluster = cluster && num_splits > 1 && num_splits <= 8;
+  if (num_splits > 1 && !by_cluster && (scratch == nullptr || arrivals == nullptr)) return LSE_ERR_BAD_ARGUMENT;
   float* part_o = scratch;
   float* part_ml = scratch ? scratch + (size_t)tokens * n_q * num_splits * head_dim : nullptr;
   if (head_dim == 128)
     return launch_decode<128>(q, k_cache, v_cache, out, part_o, part_ml, arrivals, block_tables, bt_stride,
-                              segment_of_token, positions, tokens, n_q, n_kv, page_size, scale, num_splits, stream);
+                              segment_of_token, positions, tokens, n_q, n_kv, page_size, scale, num_splits, cluster, stream);
   return launch_decode<64>(q, k_cache, v_cache, out, part_o, part_ml, arrivals, block_tables, bt_stride,
-                           segment_of_token, positions, tokens, n_q, n_kv, page_size, scale, num_splits, stream);
+                           segment_of_token, positions, tokens, n_q, n_kv, page_size, scale, num_splits, cluster, stream);
 }
 
 extern "C" int lse_paged_attention_prefill(const void* q, const void* k_cache, const void* v_cache, void* out,

@@ -77,20 +77,34 @@ inline int lse_pdl_enabled = 1;
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 
+// cluster_z > 1: the blocks (x, y, 0 .. cluster_z-1) form a thread-block cluster (distributed shared memory).
 template <typename... KArgs, typename... Args>
-inline cudaError_t lse_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                              Args&&... args) {
+inline cudaError_t lse_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                      cudaStream_t stream, unsigned cluster_z, Args&&... args) {
   cudaLaunchConfig_t config = {};
   config.gridDim = grid;
   config.blockDim = block;
   config.dynamicSmemBytes = smem;
   config.stream = stream;
-  cudaLaunchAttribute attribute[1];
+  cudaLaunchAttribute attribute[2];
   attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attribute[0].val.programmaticStreamSerializationAllowed = lse_pdl_enabled ? 1 : 0;
   config.attrs = attribute;
   config.numAttrs = 1;
+  if (cluster_z > 1) {
+    attribute[1].id = cudaLaunchAttributeClusterDimension;
+    attribute[1].val.clusterDim.x = 1;
+    attribute[1].val.clusterDim.y = 1;
+    attribute[1].val.clusterDim.z = cluster_z;
+    config.numAttrs = 2;
+  }
   return cudaLaunchKernelEx(&config, kernel, static_cast<Args&&>(args)...);
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t lse_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args&&... args) {
+  return lse_launch_cluster(kernel, grid, block, smem, stream, 1u, static_cast<Args&&>(args)...);
 }
 
 

@@ -250,17 +250,26 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, int n_partials,
   const int e0 = pairing == 0 ? 8 * c : 4 * c;
   const int e1 = pairing == 0 ? 8 * c + 4 : half + 4 * c;
   const size_t col = (size_t)head * head_dim;
-  // frequencies and bias do not depend on earlier kernels: fetch them before waiting for those
+  // Frequencies, bias, the row's position and cache slot do not come from the kernels before this one
+  // (the step's metadata is copied to the device before its first kernel starts): fetch them, and work
+  // out sines and cosines, before waiting for those kernels.
   float freq[4] = {0.f, 0.f, 0.f, 0.f}, ba[4] = {0.f, 0.f, 0.f, 0.f}, bb[4] = {0.f, 0.f, 0.f, 0.f};
+  float sn[4] = {0.f, 0.f, 0.f, 0.f}, cs[4] = {1.f, 1.f, 1.f, 1.f};
+  int slot = -1;
+  const bool is_q = head < n_q, is_k = !is_q && head < n_q + n_kv;
   if (in_range) {
     load4<float>(inv_freq + 4 * c, freq);
     if (bias) { load4<float>(bias + col + e0, ba); load4<float>(bias + col + e1, bb); }
+    slot = slot_mapping[t];
+    if (is_q || is_k) {
+      const float pos = (float)positions[t];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) sincosf(pos * freq[j], &sn[j], &cs[j]);
+    }
   }
   pdl_wait();
   LSE_TL_MARK(2)
   if (!in_range) return;
-  const int slot = slot_mapping[t];
-  const bool is_q = head < n_q, is_k = !is_q && head < n_q + n_kv;
   if (!is_q && slot < 0) return;   // padding row: nothing is cached
   const TI* row = qkv + (size_t)t * qkv_stride + col;
   float g0[4] = {0.f, 0.f, 0.f, 0.f}, g1[4] = {0.f, 0.f, 0.f, 0.f};
@@ -292,7 +301,6 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, int n_partials,
     dst = (is_k ? k_cache : v_cache) + ((page * n_kv + kv_head) * page_size + off) * head_dim;
   }
   if (is_q || is_k) {
-    const float pos = (float)positions[t];
     float xa[4], xb[4];
     if (pairing == 0) { xa[0] = g0[0]; xb[0] = g0[1]; xa[1] = g0[2]; xb[1] = g0[3]; xa[2] = g1[0]; xb[2] = g1[1]; xa[3] = g1[2]; xb[3] = g1[3]; }
     else {
@@ -301,9 +309,7 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, int n_partials,
     }
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      float sn, cs;
-      sincosf(pos * freq[j], &sn, &cs);
-      const float ya = xa[j] * cs - xb[j] * sn, yb = xb[j] * cs + xa[j] * sn;
+      const float ya = xa[j] * cs[j] - xb[j] * sn[j], yb = xb[j] * cs[j] + xa[j] * sn[j];
       xa[j] = ya; xb[j] = yb;
     }
     if (pairing == 0) { g0[0] = xa[0]; g0[1] = xb[0]; g0[2] = xa[1]; g0[3] = xb[1]; g1[0] = xa[2]; g1[1] = xb[2]; g1[2] = xa[3]; g1[3] = xb[3]; }

@@ -28,7 +28,7 @@ _SIGNATURES = {
     "lse_paged_attention_generic": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
                                     c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
                                     c_int, c_void_p],
-    "lse_paged_attention_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+    "lse_paged_attention_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
                                    c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "lse_paged_attention_prefill": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                     c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],

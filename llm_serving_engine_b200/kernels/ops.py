@@ -198,7 +198,7 @@ def _arrival_counters(device, count: int) -> torch.Tensor:
 
 def paged_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
                            block_tables: torch.Tensor, segment_of_token: torch.Tensor, positions: torch.Tensor,
-                           scale: float, num_splits: int) -> torch.Tensor:
+                           scale: float, num_splits: int, cluster: bool = True) -> torch.Tensor:
     """Attention of single decoded tokens (one row per request) with the keys split over
     ``num_splits`` blocks; bfloat16, head size 64 or 128."""
     _need_cuda(q, k_cache, v_cache, out, block_tables, segment_of_token, positions)
@@ -208,12 +208,14 @@ def paged_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
     assert q.is_contiguous() and out.is_contiguous() and k_cache.is_contiguous() and v_cache.is_contiguous()
     assert block_tables.dtype == torch.int32 and block_tables.stride(1) == 1
     scratch = arrivals = None
-    if num_splits > 1:
+    by_cluster = cluster and 1 < num_splits <= 8      # the splits add up through distributed shared memory
+    if num_splits > 1 and not by_cluster:
         scratch = torch.empty(tokens * n_q * num_splits * (head_dim + 2), dtype=torch.float32, device=q.device)
         arrivals = _arrival_counters(q.device, tokens * n_kv * ((n_q // n_kv + 15) // 16))
     lib = library.load()
     check(lib.lse_paged_attention_decode(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
-                                         _ptr(scratch), _ptr(arrivals), block_tables.data_ptr(), block_tables.stride(0),
+                                         _ptr(scratch), _ptr(arrivals), int(by_cluster), block_tables.data_ptr(),
+                                         block_tables.stride(0),
                                          segment_of_token.data_ptr(), positions.data_ptr(), tokens, n_q, n_kv,
                                          head_dim, page_size, float(scale), int(num_splits), _stream()),
           "paged_attention_decode")
@@ -269,7 +271,7 @@ def gemm_bf16_skinny_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
 
 
 def gemm_bf16_skinny(x: torch.Tensor, weight: torch.Tensor, splits: int | None = None, stages: int = 6,
-                     kboxes: int = 1) -> torch.Tensor:
+                     kboxes: int = 1, max_splits: int | None = None) -> torch.Tensor:
     """Partial sums [P, M, N] (float32) of x[M, K] @ weight[N, K]^T for M <= 256, bfloat16 operands;
     the k range is cut into P splits so that enough blocks stream the weights."""
     _need_cuda(x, weight)
@@ -282,7 +284,7 @@ def gemm_bf16_skinny(x: torch.Tensor, weight: torch.Tensor, splits: int | None =
         # about two blocks per SM (more of the weights are fetched ahead while earlier kernels run), but no
         # more splits than keep the partial sums (4 bytes per row, column and split) well below the weight bytes
         n_tiles = -(-n // 128)
-        splits = max(1, min(-(-k // 128), _GEMM_TARGET_BLOCKS // n_tiles, max(1, k // (4 * m)), _GEMM_MAX_SPLITS)) if n_tiles < 148 else 1
+        splits = max(1, min(-(-k // 128), _GEMM_TARGET_BLOCKS // n_tiles, max(1, k // (4 * m)), max_splits or _GEMM_MAX_SPLITS)) if n_tiles < 148 else 1
     splits = lib.lse_gemm_bf16_skinny_splits(k, int(splits), int(kboxes))
     out = torch.empty((splits, m, n), dtype=torch.float32, device=x.device)
     check(lib.lse_gemm_bf16_skinny(x.data_ptr(), weight.data_ptr(), out.data_ptr(), m, n, k, splits, int(stages),

@@ -66,7 +66,8 @@ class GroupedQueryAttention(Mixer):
 
     def forward(self, x, step, cache):
         tokens = x.shape[0]
-        qkv = linear_partials(x, self.qkv_weight)  # bias is added with the rotation, in float32
+        # bias is added with the rotation, in float32; at most 8 partial sums: the rotary kernel fetches them in one go
+        qkv = linear_partials(x, self.qkv_weight, max_splits=8)
         q = torch.empty((tokens, self.n_q, self.head_dim), dtype=x.dtype, device=x.device)
         self.position.encode_and_store(qkv, self.qkv_bias, step, cache, q, self.n_q, self.n_kv, self.head_dim)
         attended = torch.empty_like(q)

@@ -26,12 +26,12 @@ def reduce_partials(y: torch.Tensor) -> torch.Tensor:
     return y
 
 
-def linear_partials(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+def linear_partials(x: torch.Tensor, weight: torch.Tensor, max_splits: int | None = None) -> torch.Tensor:
     """x W^T as [rows, out] or, for few bfloat16 rows, as a float32 stack of partial sums
     [P, rows, out].  For callers whose consumer kernel adds the partials itself."""
     if (x.is_cuda and weight.dtype == torch.bfloat16 and x.shape[0] <= SKINNY_MAX_ROWS
             and ops.gemm_bf16_skinny_ok(x, weight)):
-        return ops.gemm_bf16_skinny(x, weight)
+        return ops.gemm_bf16_skinny(x, weight, max_splits=max_splits)
     return linear(x, weight)
 
 

@@ -345,9 +345,9 @@ def test_sampling_follows_the_distribution():
 MMA_SHAPES = [(64, 6, 2, 16), (128, 12, 2, 16), (128, 7, 1, 8), (64, 4, 4, 1), (128, 40, 2, 64), (64, 3, 1, 32)]
 
 
-@pytest.mark.parametrize("splits", [1, 3, 32])
+@pytest.mark.parametrize("splits, cluster", [(1, True), (3, True), (8, True), (3, False), (32, False)])
 @pytest.mark.parametrize("head_dim, n_q, n_kv, page", MMA_SHAPES)
-def test_decode_attention_split_keys(head_dim, n_q, n_kv, page, splits):
+def test_decode_attention_split_keys(head_dim, n_q, n_kv, page, splits, cluster):
     rng = random.Random(head_dim + n_q + splits)
     torch.manual_seed(n_q * splits)
     contexts = [1, 15, 16, 17, 63, 64, 65, 130, 1000, 2049]
@@ -358,7 +358,7 @@ def test_decode_attention_split_keys(head_dim, n_q, n_kv, page, splits):
     out = torch.empty_like(q)
     scale = 1.0 / math.sqrt(head_dim)
     assert ops().attention_mma_supported(head_dim, n_q, n_kv, torch.bfloat16)
-    ops().paged_attention_decode(q, k_cache, v_cache, out, tables, segs, positions, scale, splits)
+    ops().paged_attention_decode(q, k_cache, v_cache, out, tables, segs, positions, scale, splits, cluster)
     for r, ctx in enumerate(contexts):
         k, v = dense[r]
         want = dense_attention(q[r], k, v, scale)
@@ -367,7 +367,7 @@ def test_decode_attention_split_keys(head_dim, n_q, n_kv, page, splits):
     # a padding row (segment -1) is left alone
     segs[2] = -1
     out.fill_(7.0)
-    ops().paged_attention_decode(q, k_cache, v_cache, out, tables, segs, positions, scale, splits)
+    ops().paged_attention_decode(q, k_cache, v_cache, out, tables, segs, positions, scale, splits, cluster)
     assert float((out[2].float() - 7.0).abs().max()) == 0.0 and float((out[3].float() - 7.0).abs().max()) > 0.0
 
 
