@@ -21,10 +21,8 @@
 LSE_TL_DEFINE(lse_timeline_gemm)
 
 namespace {
-constexpr int BLOCK_N = 128;  // rows of w per block (UMMA M)
 constexpr int BLOCK_K = 64;   // k-values per stage: 128-byte rows
 constexpr int UMMA_K = 16;
-constexpr uint32_t A_BYTES = BLOCK_N * BLOCK_K * 2;
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
 
 __device__ int lse_gemm_error;
@@ -82,12 +80,18 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
 }
 
-// grid: (ceil(N / 128), splits); block: 128 threads; dynamic shared memory:
-// stages * (16 KiB + m_pad * 128 B) + alignment slack + barriers.
+// BLOCK_N rows of w per block (the M side of the instruction): 128, or 64 for twice as many blocks.
+// With 64 the accumulator rows lie in lanes 0-15 of each 32-lane quarter of tensor memory
+// (row r -> lane (r % 16) + 32 * (r / 16)).
+// grid: (ceil(N / BLOCK_N), splits); block: 128 threads; dynamic shared memory:
+// stages * kboxes * (BLOCK_N * 128 B + m_pad * 128 B) + alignment slack + barriers.
+template <int BLOCK_N>
 __global__ void __launch_bounds__(128)
 gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                         float* __restrict__ out, int M, int N, int k_tiles, int tiles_per_split, int m_pad,
-                        int stages, int kboxes) {
+                        int stages, int kboxes, __nv_bfloat16* __restrict__ gated_out) {
+  constexpr uint32_t A_BYTES = BLOCK_N * BLOCK_K * 2;
+  constexpr int ROWS_PER_WARP = BLOCK_N / 4;   // valid accumulator rows in a warp's quarter of tensor memory
   extern __shared__ unsigned char smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   // a stage holds `kboxes` adjacent 64-wide k-boxes of w, then the same boxes of x: one row of w is
@@ -196,8 +200,44 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
   pdl_wait();   // nothing is written, and no bounded wait starts, before the earlier kernels are done
   const bool ready = mbar_wait(accum_bar, 0, abort_flag);
   asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-  if (ready) {
-    const int n = n0 + warp * 32 + lane;
+  if (ready && gated_out != nullptr) {
+    // SiLU gate in the epilogue (one split only): the 128 rows of this block are 64 gate rows, then the
+    // 64 up rows of the same outputs.  Warps 2 and 3 hand their (up) values over through shared
+    // memory; warps 0 and 1 write silu(gate) * up as bfloat16: gated_out[m][blockIdx.x * 64 + lane].
+    float* hand = reinterpret_cast<float*>(smem_raw + (base - smem_u32(smem_raw)));   // stage 0 is free now
+    const int pitch = m_pad + 1;
+    const int row = (warp & 1) * ROWS_PER_WARP + lane;     // index among the block's BLOCK_N / 2 outputs
+    const bool lane_valid = lane < ROWS_PER_WARP;
+    float g[8];
+    for (int c0 = 0; c0 < m_pad; c0 += 8) {
+      uint32_t r[8];
+      const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0;
+      asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];\n"
+                   : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                   : "r"(taddr));
+      asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+      if (warp >= 2 && lane_valid) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) hand[row * pitch + c0 + i] = __uint_as_float(r[i]);
+      }
+      __syncthreads();
+      if (warp < 2 && lane_valid) {
+        const int col = blockIdx.x * (BLOCK_N / 2) + row;
+        if (col < N / 2) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            if (c0 + i < M) {
+              g[i] = __uint_as_float(r[i]);
+              const float u = hand[row * pitch + c0 + i];
+              gated_out[(size_t)(c0 + i) * (N / 2) + col] = __float2bfloat16_rn((g[i] / (1.0f + expf(-g[i]))) * u);
+            }
+          }
+        }
+      }
+      __syncthreads();
+    }
+  } else if (ready) {
+    const int n = n0 + warp * ROWS_PER_WARP + lane;
     float* dst = out + (size_t)blockIdx.y * M * N + n;
     for (int c0 = 0; c0 < m_pad; c0 += 8) {
       uint32_t r[8];
@@ -206,7 +246,7 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
                    : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
                    : "r"(taddr));
       asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-      if (n < N) {
+      if (n < N && lane < ROWS_PER_WARP) {
 #pragma unroll
         for (int i = 0; i < 8; ++i)
           if (c0 + i < M) dst[(size_t)(c0 + i) * N] = __uint_as_float(r[i]);
@@ -279,16 +319,22 @@ extern "C" int lse_gemm_bf16_skinny_status(void) {
 
 // out[split][m][n] (float32, splits * M * N values) = partial sums of x[M, K] * w[N, K]^T.
 // x, w bfloat16 row-major, 16-byte aligned, K a multiple of 8, M <= 256.
-extern "C" int lse_gemm_bf16_skinny(const void* x, const void* w, float* out, int M, int N, int K, int splits,
-                                    int stages, int kboxes, cudaStream_t stream) {
+namespace {
+template <int BLOCK_N>
+int launch_skinny(const void* x, const void* w, float* out, int M, int N, int K, int splits, int stages, int kboxes,
+                  void* gated_out, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   const int m_pad = lse_gemm_bf16_skinny_pad(M);
   if (m_pad == 0 || K <= 0 || K % 8 || (((uintptr_t)x | (uintptr_t)w) & 15)) return LSE_ERR_BAD_ARGUMENT;
   if (kboxes != 1 && kboxes != 2 && kboxes != 4) return LSE_ERR_BAD_ARGUMENT;
+  if (gated_out != nullptr) {
+    if (N % BLOCK_N) return LSE_ERR_BAD_ARGUMENT;
+    splits = 1;
+  }
   const int k_tiles = (K + BLOCK_K * kboxes - 1) / (BLOCK_K * kboxes);
   splits = lse_gemm_bf16_skinny_splits(K, splits, kboxes);
   const int per = (k_tiles + splits - 1) / splits;
-  const uint32_t stage_bytes = (uint32_t)kboxes * (A_BYTES + (uint32_t)m_pad * BLOCK_K * 2);
+  const uint32_t stage_bytes = (uint32_t)kboxes * ((uint32_t)BLOCK_N * BLOCK_K * 2 + (uint32_t)m_pad * BLOCK_K * 2);
   if (stages < 2) stages = 2;
   while (stages > 2 && (size_t)stages * stage_bytes + 2048 > 200 * 1024) --stages;
   if (stages > per + 1) stages = per + 1 < 2 ? 2 : per + 1;
@@ -297,13 +343,25 @@ extern "C" int lse_gemm_bf16_skinny(const void* x, const void* w, float* out, in
   if (!make_map(&map_w, w, N, K, BLOCK_N) || !make_map(&map_x, x, M, K, m_pad)) return LSE_ERR_BAD_ARGUMENT;
   static size_t configured = 0;   // largest dynamic shared memory asked for so far
   if (smem > configured) {
-    cudaError_t err = cudaFuncSetAttribute(gemm_bf16_skinny_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t err = cudaFuncSetAttribute(gemm_bf16_skinny_kernel<BLOCK_N>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (err != cudaSuccess) return (int)err;
     configured = smem;
   }
   dim3 grid((N + BLOCK_N - 1) / BLOCK_N, splits);
-  cudaError_t err = lse_launch(gemm_bf16_skinny_kernel, grid, 128, smem, stream, map_w, map_x, out, M, N, k_tiles, per,
-                               m_pad, stages, kboxes);
+  cudaError_t err = lse_launch(gemm_bf16_skinny_kernel<BLOCK_N>, grid, 128, smem, stream, map_w, map_x, out, M, N,
+                               k_tiles, per, m_pad, stages, kboxes, (__nv_bfloat16*)gated_out);
   if (err != cudaSuccess) return (int)err;
   return (int)cudaGetLastError();
+}
+}  // namespace
+
+// block_n: rows of w per block, 128 or 64.
+// gated_out != null: w holds, per block of block_n rows, block_n / 2 gate rows then the block_n / 2 up rows
+// of the same outputs; one split is used and gated_out[M, N / 2] (bfloat16) = silu(gate) * up; `out` is
+// not written.
+extern "C" int lse_gemm_bf16_skinny(const void* x, const void* w, float* out, int M, int N, int K, int splits,
+                                    int stages, int kboxes, int block_n, void* gated_out, cudaStream_t stream) {
+  if (block_n == 64) return launch_skinny<64>(x, w, out, M, N, K, splits, stages, kboxes, gated_out, stream);
+  if (block_n == 128) return launch_skinny<128>(x, w, out, M, N, K, splits, stages, kboxes, gated_out, stream);
+  return LSE_ERR_BAD_ARGUMENT;
 }

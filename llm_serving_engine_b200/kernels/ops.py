@@ -245,16 +245,17 @@ def paged_attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
     return out
 
 
-def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]; ``gate_up`` is [T, 2I] or a float32
-    stack of partial sums [P, T, 2I]."""
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, interleave: int = 0) -> torch.Tensor:
+    """out[t, i] = silu(gate_i) * up_i; ``gate_up`` is [T, 2I] or a float32 stack of partial sums
+    [P, T, 2I].  ``interleave`` 0: the row is [gate (I) | up (I)]; n > 0: blocks of n gate values
+    followed by the n up values of the same outputs."""
     _need_cuda(gate_up, out)
     tokens, two_i = gate_up.shape[-2], gate_up.shape[-1]
     assert two_i % 2 == 0 and out.shape == (tokens, two_i // 2) and out.is_contiguous()
     gate_up, n_partials, stride = _partials(gate_up, tokens, two_i)
     lib = library.load()
     check(lib.lse_silu_mul(gate_up.data_ptr(), dtype_code(gate_up.dtype), n_partials, stride, out.data_ptr(),
-                           dtype_code(out.dtype), tokens, two_i // 2, _stream()), "silu_mul")
+                           dtype_code(out.dtype), tokens, two_i // 2, int(interleave), _stream()), "silu_mul")
     return out
 
 
@@ -271,7 +272,7 @@ def gemm_bf16_skinny_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
 
 
 def gemm_bf16_skinny(x: torch.Tensor, weight: torch.Tensor, splits: int | None = None, stages: int = 6,
-                     kboxes: int = 1, max_splits: int | None = None) -> torch.Tensor:
+                     kboxes: int = 1, max_splits: int | None = None, block_n: int = 128) -> torch.Tensor:
     """Partial sums [P, M, N] (float32) of x[M, K] @ weight[N, K]^T for M <= 256, bfloat16 operands;
     the k range is cut into P splits so that enough blocks stream the weights."""
     _need_cuda(x, weight)
@@ -283,12 +284,43 @@ def gemm_bf16_skinny(x: torch.Tensor, weight: torch.Tensor, splits: int | None =
     if splits is None:
         # about two blocks per SM (more of the weights are fetched ahead while earlier kernels run), but no
         # more splits than keep the partial sums (4 bytes per row, column and split) well below the weight bytes
-        n_tiles = -(-n // 128)
+        n_tiles = -(-n // block_n)
         splits = max(1, min(-(-k // 128), _GEMM_TARGET_BLOCKS // n_tiles, max(1, k // (4 * m)), max_splits or _GEMM_MAX_SPLITS)) if n_tiles < 148 else 1
     splits = lib.lse_gemm_bf16_skinny_splits(k, int(splits), int(kboxes))
     out = torch.empty((splits, m, n), dtype=torch.float32, device=x.device)
     check(lib.lse_gemm_bf16_skinny(x.data_ptr(), weight.data_ptr(), out.data_ptr(), m, n, k, splits, int(stages),
-                                   int(kboxes), _stream()), "gemm_bf16_skinny")
+                                   int(kboxes), int(block_n), None, _stream()), "gemm_bf16_skinny")
+    return out
+
+
+GATED_INTERLEAVE = 32      # gate and up rows alternate in blocks of 32: blocks of 64 weight rows per thread block
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, interleave: int = GATED_INTERLEAVE) -> torch.Tensor:
+    """[2I, K] weight for ``gemm_bf16_skinny_gated``: ``interleave`` gate rows, then the ``interleave`` up
+    rows of the same outputs, and so on (I a multiple of ``interleave``)."""
+    inter, k = gate.shape
+    assert inter % interleave == 0 and up.shape == gate.shape
+    blocks = inter // interleave
+    stacked = torch.stack([gate.view(blocks, interleave, k), up.view(blocks, interleave, k)], dim=1)
+    return stacked.reshape(2 * inter, k).contiguous()
+
+
+def gemm_bf16_skinny_gated(x: torch.Tensor, weight: torch.Tensor, interleave: int = GATED_INTERLEAVE,
+                           stages: int = 8) -> torch.Tensor:
+    """silu(x @ gate^T) * (x @ up^T) as bfloat16 [M, I] in one kernel; ``weight`` is the interleaved
+    [2I, K] matrix of ``interleave_gate_up`` (interleave 32 or 64); M <= 256."""
+    _need_cuda(x, weight)
+    m, k = x.shape
+    n = weight.shape[0]
+    block_n = 2 * interleave
+    if block_n not in (64, 128) or not gemm_bf16_skinny_ok(x, weight) or weight.shape[1] != k or n % block_n:
+        raise KernelError("gemm_bf16_skinny_gated: contiguous bfloat16 operands, K % 8 == 0, I a multiple of the "
+                          "interleave (32 or 64), M <= 256")
+    lib = library.load()
+    out = torch.empty((m, n // 2), dtype=torch.bfloat16, device=x.device)
+    check(lib.lse_gemm_bf16_skinny(x.data_ptr(), weight.data_ptr(), None, m, n, k, 1, int(stages), 1, block_n,
+                                   out.data_ptr(), _stream()), "gemm_bf16_skinny_gated")
     return out
 
 

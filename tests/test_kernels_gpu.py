@@ -448,11 +448,12 @@ def test_prefill_attention_keeps_the_causal_edge():
 @pytest.mark.parametrize("m, n, k, splits", [(1, 128, 64, 1), (8, 2048, 1536, 12), (3, 1536, 8960, 24), (16, 1000, 776, 3),
                                              (32, 17920, 1536, None), (7, 151936, 1536, None), (200, 384, 520, 2),
                                              (256, 130, 72, 5), (17, 96, 8, 4)])
-def test_few_rows_product_on_tensor_cores(m, n, k, splits):
+@pytest.mark.parametrize("block_n", [128, 64])
+def test_few_rows_product_on_tensor_cores(m, n, k, splits, block_n):
     torch.manual_seed(m + n + k)
     x = torch.randn(m, k, device=DEV).bfloat16()
     w = (torch.randn(n, k, device=DEV) * 0.05).bfloat16()
-    parts = ops().gemm_bf16_skinny(x, w, splits)
+    parts = ops().gemm_bf16_skinny(x, w, splits, block_n=block_n)
     assert parts.dtype == torch.float32 and parts.shape[1:] == (m, n)
     got = parts.double().sum(0)
     want = x.double() @ w.double().t()
@@ -521,3 +522,24 @@ def test_rope_and_silu_of_partial_sums():
         ops().silu_mul(gate_up, out)
         total = gate_up.double().sum(0)
         assert rel_err(out, torch.nn.functional.silu(total[:, :inter]) * total[:, inter:]) < TOL[torch.bfloat16] * 2
+
+
+@pytest.mark.parametrize("interleave", [32, 64])
+@pytest.mark.parametrize("m, inter, k", [(1, 64, 64), (8, 8960, 1536), (5, 256, 96), (16, 192, 520), (33, 128, 72)])
+def test_gated_product_and_interleaved_silu(m, inter, k, interleave):
+    """silu(x gate^T) * (x up^T) from the interleaved weight: in one kernel, and through the separate
+    SiLU kernel reading the interleaved columns."""
+    torch.manual_seed(m + inter)
+    x = torch.randn(m, k, device=DEV).bfloat16()
+    gate = (torch.randn(inter, k, device=DEV) * 0.1).bfloat16()
+    up = (torch.randn(inter, k, device=DEV) * 0.1).bfloat16()
+    weight = ops().interleave_gate_up(gate, up, interleave)
+    assert torch.equal(weight[:interleave], gate[:interleave]) and torch.equal(weight[interleave:2 * interleave], up[:interleave])
+    want = torch.nn.functional.silu(x.double() @ gate.double().t()) * (x.double() @ up.double().t())
+    got = ops().gemm_bf16_skinny_gated(x, weight, interleave)
+    assert got.dtype == torch.bfloat16 and rel_err(got, want) < TOL[torch.bfloat16] * 2
+    columns = torch.mm(x, weight.t())                       # library product, interleaved columns
+    out = torch.empty(m, inter, device=DEV, dtype=torch.bfloat16)
+    ops().silu_mul(columns, out, interleave=interleave)
+    assert rel_err(out, want) < TOL[torch.bfloat16] * 4     # its input was rounded to bfloat16 once more
+    assert ops().gemm_bf16_skinny_status() == 0

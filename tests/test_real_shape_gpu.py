@@ -1,0 +1,60 @@
+"""The layer sizes of the benchmark model (Qwen2.5-1.5B: hidden 1536, 12 query and 2 key/value heads of
+128, feed-forward 8960, vocabulary 151936) with two layers and random weights: the kernels run at the
+shapes they were tuned for (tcgen05 product with k = 8960, tensor-core attention with six heads per
+group, the wide LM head), through prompts cut into portions, decoding from CUDA graphs and a mixed
+step, against the plain implementation."""
+import json
+import random
+import tempfile
+from pathlib import Path
+
+import pytest
+import torch
+
+import helpers
+from plain import qwen2_plain
+
+pytestmark = pytest.mark.gpu
+
+CONFIG = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "vocab_size": 151936, "hidden_size": 1536, "intermediate_size": 8960, "num_hidden_layers": 2,
+    "num_attention_heads": 12, "num_key_value_heads": 2, "max_position_embeddings": 1024,
+    "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": True,
+}
+
+
+@pytest.fixture(scope="module")
+def folder():
+    from llm_serving_engine_b200.weights import write_random_model
+    with tempfile.TemporaryDirectory(prefix="real_shape_") as name:
+        write_random_model(name, CONFIG, seed=11, dtype="bfloat16")
+        yield Path(name)
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_benchmark_shapes_against_the_plain_implementation(folder, dtype):
+    from llm_serving_engine_b200.engine.trace_replay import replay
+
+    rng = random.Random(4)
+    a = helpers.random_tokens(rng, CONFIG["vocab_size"], 150)
+    b = helpers.random_tokens(rng, CONFIG["vocab_size"], 41)
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": a[:100], "want": [0, 63, 64, 99]}], "end": []},
+        {"step": 1, "entries": [{"id": "a", "tokens": a[100:130], "want": [29]}, {"id": "b", "tokens": b[:40], "want": [39]}], "end": []},
+        {"step": 2, "entries": [{"id": "a", "tokens": [a[130]], "want": [0]}, {"id": "b", "tokens": [b[40]], "want": [0]}], "end": ["b"]},
+    ]
+    steps += [{"step": 3 + i, "entries": [{"id": "a", "tokens": [a[131 + i]], "want": [0]}], "end": []} for i in range(19)]
+    with tempfile.TemporaryDirectory(prefix="real_out_") as out:
+        replay(folder, dtype, out, 256, [json.dumps(step) for step in steps])
+        got = helpers.collect(steps, Path(out))
+    cfg, weights = qwen2_plain.load_folder(folder)          # the matrices are stored in bfloat16 already
+    want_a = qwen2_plain.forward_full(cfg, weights, a)
+    want_b = qwen2_plain.forward_full(cfg, weights, b)
+    rows_a = [0, 63, 64, 99, 129] + list(range(130, 150))
+    for name, got_rows, want_rows in (("a", got["a"], want_a[rows_a]), ("b", got["b"], want_b[[39, 40]])):
+        limit = helpers.tolerance(dtype, want_rows)
+        error = (got_rows - want_rows).abs().max(dim=1).values
+        assert float(error.max()) <= limit, f"{name} ({dtype}): max error {float(error.max()):.3e} > {limit:.3e} at row {int(error.argmax())}"
+    from llm_serving_engine_b200.kernels import ops
+    assert ops.gemm_bf16_skinny_status() == 0
