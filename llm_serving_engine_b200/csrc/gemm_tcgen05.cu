@@ -336,7 +336,9 @@ int launch_skinny(const void* x, const void* w, float* out, int M, int N, int K,
   const int per = (k_tiles + splits - 1) / splits;
   const uint32_t stage_bytes = (uint32_t)kboxes * ((uint32_t)BLOCK_N * BLOCK_K * 2 + (uint32_t)m_pad * BLOCK_K * 2);
   if (stages < 2) stages = 2;
-  while (stages > 2 && (size_t)stages * stage_bytes + 2048 > 200 * 1024) --stages;
+  // two blocks must fit on an SM (beside each other, or beside a block of the kernel before): at most
+  // about 110 KB of stages per block
+  while (stages > 2 && (size_t)stages * stage_bytes + 2048 > 112 * 1024) --stages;
   if (stages > per + 1) stages = per + 1 < 2 ? 2 : per + 1;
   const size_t smem = (size_t)stages * stage_bytes + 1024 + 16 * (size_t)stages + 64;
   CUtensorMap map_w, map_x;

@@ -16,7 +16,7 @@ from ..kernels import ops
 import os
 
 # above this many rows the library product is faster (LSE_SKINNY_MAX_ROWS overrides, for comparisons)
-SKINNY_MAX_ROWS = int(os.environ.get("LSE_SKINNY_MAX_ROWS", "8"))
+SKINNY_MAX_ROWS = int(os.environ.get("LSE_SKINNY_MAX_ROWS", "32"))
 
 
 def reduce_partials(y: torch.Tensor) -> torch.Tensor:
