@@ -229,6 +229,14 @@ extern "C" int lse_add_rmsnorm(float* residual, const void* delta, int delta_dty
 // grid: (tokens, groups of heads); a thread owns four pairs of one head: eight consecutive
 // elements (pairs (2i, 2i+1)) or four elements of each half (pairs (i, i + D/2)); either way the
 // pairs have the frequency indices 4c .. 4c+3, c being the thread's index inside the head.
+// One pair turned by its angle.  Products and sums are rounded one by one (no contraction into
+// fused multiply-adds that the compiler might choose differently from kernel to kernel), so both
+// kernels below give the same bits.
+__device__ __forceinline__ void rope_rotate(float& xa, float& xb, float cs, float sn) {
+  const float ya = __fsub_rn(__fmul_rn(xa, cs), __fmul_rn(xb, sn));
+  const float yb = __fadd_rn(__fmul_rn(xb, cs), __fmul_rn(xa, sn));
+  xa = ya; xb = yb;
+}
 template <typename T> __device__ __forceinline__ void rope_load4(const T* p, float (&v)[4]) { load4<T>(p, v); }
 
 template <typename TI, typename TO>
@@ -264,7 +272,7 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, int n_partials,
     if (is_q || is_k) {
       const float pos = (float)positions[t];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) sincosf(pos * freq[j], &sn[j], &cs[j]);
+      for (int j = 0; j < 4; ++j) sincosf(__fmul_rn(pos, freq[j]), &sn[j], &cs[j]);
     }
   }
   pdl_wait();
@@ -308,10 +316,7 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, int n_partials,
       for (int j = 0; j < 4; ++j) { xa[j] = g0[j]; xb[j] = g1[j]; }
     }
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float ya = xa[j] * cs[j] - xb[j] * sn[j], yb = xb[j] * cs[j] + xa[j] * sn[j];
-      xa[j] = ya; xb[j] = yb;
-    }
+    for (int j = 0; j < 4; ++j) rope_rotate(xa[j], xb[j], cs[j], sn[j]);
     if (pairing == 0) { g0[0] = xa[0]; g0[1] = xb[0]; g0[2] = xa[1]; g0[3] = xb[1]; g1[0] = xa[2]; g1[1] = xb[2]; g1[2] = xa[3]; g1[3] = xb[3]; }
     else {
 #pragma unroll
@@ -321,6 +326,121 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, int n_partials,
   store4<TO>(dst + e0, g0);
   store4<TO>(dst + e1, g1);
   LSE_TL_MARK(3)
+}
+
+// Many tokens (portions of prompts), one set of sums: a thread owns eight pairs (frequency indices
+// 8c .. 8c+7) of ROPE_WIDE_HEADS heads of one token, so that the sines and cosines are worked out
+// once for those heads and sixteen-byte loads of all of them are in flight together.  The values
+// are those of the kernel above: the same angle, the same products.
+constexpr int ROPE_WIDE_HEADS = 4;
+template <typename T> __device__ __forceinline__ void load8(const T* p, float (&v)[8]);
+template <> __device__ __forceinline__ void load8<float>(const float* p, float (&v)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <> __device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[8]) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162*>(&w[e]);
+    v[2 * e] = __low2float(h); v[2 * e + 1] = __high2float(h);
+  }
+}
+template <typename T> __device__ __forceinline__ void store8(T* p, const float (&v)[8]);
+template <> __device__ __forceinline__ void store8<float>(float* p, const float (&v)[8]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+template <> __device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* p, const float (&v)[8]) {
+  uint32_t w[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
+    w[e] = *reinterpret_cast<const uint32_t*>(&h);
+  }
+  *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+template <typename TI, typename TO>
+__global__ void rope_kv_write_wide_kernel(const TI* __restrict__ qkv, const float* __restrict__ bias,
+                                          const int* __restrict__ positions, const int* __restrict__ slot_mapping,
+                                          const float* __restrict__ inv_freq, TO* __restrict__ q_out,
+                                          TO* __restrict__ k_cache, TO* __restrict__ v_cache, int tokens, int n_q,
+                                          int n_kv, int head_dim, int page_size, int pairing, long long qkv_stride,
+                                          int head_groups) {
+  pdl_launch_dependents();
+  const int per_head = head_dim >> 4;            // threads per head
+  const int per_token = per_head * head_groups;  // threads per token
+  const int local = threadIdx.x % per_token;
+  const int t = blockIdx.x * (blockDim.x / per_token) + threadIdx.x / per_token;
+  const int c = local % per_head, group = local / per_head;
+  const int heads = n_q + 2 * n_kv;
+  const bool live = t < tokens && threadIdx.x < (blockDim.x / per_token) * per_token;
+  const int e0 = pairing == 0 ? 16 * c : 8 * c;
+  const int e1 = pairing == 0 ? 16 * c + 8 : (head_dim >> 1) + 8 * c;
+  // position, cache slot and frequencies are the step's own data: fetched, and the sines and
+  // cosines worked out, before waiting for the kernel that makes the projections
+  float sn[8], cs[8];
+  int slot = -1;
+  if (live) {
+    float freq[8];
+    load8<float>(inv_freq + 8 * c, freq);
+    slot = slot_mapping[t];
+    const float pos = (float)positions[t];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) sincosf(__fmul_rn(pos, freq[j]), &sn[j], &cs[j]);
+  }
+  pdl_wait();
+  if (!live) return;
+  const TI* row = qkv + (size_t)t * qkv_stride;
+  float a[ROPE_WIDE_HEADS][8], b[ROPE_WIDE_HEADS][8];
+#pragma unroll
+  for (int k = 0; k < ROPE_WIDE_HEADS; ++k) {
+    const int head = group + k * head_groups;   // neighbouring threads read neighbouring heads
+    if (head < heads && (head < n_q || slot >= 0)) {
+      load8<TI>(row + (size_t)head * head_dim + e0, a[k]);
+      load8<TI>(row + (size_t)head * head_dim + e1, b[k]);
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < ROPE_WIDE_HEADS; ++k) {
+    const int head = group + k * head_groups;
+    const bool is_q = head < n_q, is_k = !is_q && head < n_q + n_kv;
+    if (head >= heads || (!is_q && slot < 0)) continue;   // padding row: nothing is cached
+    float g0[8], g1[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { g0[j] = 0.f + a[k][j]; g1[j] = 0.f + b[k][j]; }
+    if (bias) {
+      float ba[8], bb[8];
+      load8<float>(bias + (size_t)head * head_dim + e0, ba);
+      load8<float>(bias + (size_t)head * head_dim + e1, bb);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { g0[j] += ba[j]; g1[j] += bb[j]; }
+    }
+    if (is_q || is_k) {
+      if (pairing == 0) {   // pairs (2i, 2i+1): pair j of this thread lies in g0 (j < 4) or g1
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          rope_rotate(g0[2 * j], g0[2 * j + 1], cs[j], sn[j]);
+          rope_rotate(g1[2 * j], g1[2 * j + 1], cs[4 + j], sn[4 + j]);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) rope_rotate(g0[j], g1[j], cs[j], sn[j]);
+      }
+    }
+    TO* dst;
+    if (is_q) {
+      dst = q_out + ((size_t)t * n_q + head) * head_dim;
+    } else {
+      const size_t page = slot / page_size, off = slot % page_size;
+      const int kv_head = is_k ? head - n_q : head - n_q - n_kv;
+      dst = (is_k ? k_cache : v_cache) + ((page * n_kv + kv_head) * page_size + off) * head_dim;
+    }
+    store8<TO>(dst + e0, g0);
+    store8<TO>(dst + e1, g1);
+  }
 }
 
 extern "C" int lse_rope_kv_write(const void* qkv, int in_dtype, int n_partials, long long partial_stride,
@@ -334,8 +454,28 @@ extern "C" int lse_rope_kv_write(const void* qkv, int in_dtype, int n_partials, 
       (pairing != 0 && pairing != 1) || n_partials < 1 || qkv_stride % 4 || partial_stride % 4 ||
       (((uintptr_t)qkv | (uintptr_t)bias | (uintptr_t)inv_freq | (uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15))
     return LSE_ERR_BAD_ARGUMENT;
-  const int per_head = head_dim / 8;
   const int heads = n_q + 2 * n_kv;
+  const int in_vec = in_dtype == LSE_DTYPE_BF16 ? 8 : 4;   // elements of a sixteen-byte load
+  if (tokens >= 64 && n_partials == 1 && head_dim % 16 == 0 && head_dim <= 1024 && qkv_stride % in_vec == 0) {
+    const int per_head = head_dim / 16;
+    const int head_groups = (heads + ROPE_WIDE_HEADS - 1) / ROPE_WIDE_HEADS;
+    const int per_token = per_head * head_groups;
+    if (per_token <= 128) {
+      const int threads = 128, per_block = threads / per_token;
+      const unsigned blocks = (unsigned)((tokens + per_block - 1) / per_block);
+#define LSE_ROPE_WIDE_CASE(TI, TO)                                                                              \
+  lse_launch(rope_kv_write_wide_kernel<TI, TO>, blocks, threads, 0, stream, (const TI*)qkv, bias, positions,    \
+      slot_mapping, inv_freq, (TO*)q_out, (TO*)k_cache, (TO*)v_cache, tokens, n_q, n_kv, head_dim, page_size,   \
+      pairing, qkv_stride, head_groups)
+      if (in_dtype == LSE_DTYPE_F32 && out_dtype == LSE_DTYPE_F32) LSE_ROPE_WIDE_CASE(float, float);
+      else if (in_dtype == LSE_DTYPE_BF16 && out_dtype == LSE_DTYPE_BF16) LSE_ROPE_WIDE_CASE(__nv_bfloat16, __nv_bfloat16);
+      else if (in_dtype == LSE_DTYPE_F32 && out_dtype == LSE_DTYPE_BF16) LSE_ROPE_WIDE_CASE(float, __nv_bfloat16);
+      else return LSE_ERR_BAD_ARGUMENT;
+#undef LSE_ROPE_WIDE_CASE
+      LSE_LAUNCH_CHECK();
+    }
+  }
+  const int per_head = head_dim / 8;
   int per_block = (tokens >= 64 ? 256 : 64) / per_head;   // heads per block: few tokens -> more, smaller blocks
   if (per_block < 1) per_block = 1;
   if (per_block > heads) per_block = heads;

@@ -132,6 +132,45 @@ def test_rope_bias_and_cache_write(dtype, head_dim, n_q, n_kv, page, pairing):
     assert float((q2.float().cpu() - want_q2).abs().max()) < tol * float(want_q2.abs().max())
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("tokens, head_dim, n_q, n_kv, page, pairing", [
+    (64, 16, 4, 2, 16, "interleaved"), (131, 48, 10, 2, 8, "half"), (300, 128, 12, 2, 16, "interleaved"),
+    (77, 256, 3, 1, 4, "half"), (200, 32, 7, 7, 16, "half"), (97, 64, 33, 3, 16, "interleaved")])
+def test_rope_of_many_tokens(dtype, tokens, head_dim, n_q, n_kv, page, pairing):
+    """Portions of prompts take the kernel that shares sines and cosines among heads: it has to
+    give what the few-token kernel gives (same angles, same products) and leave padding rows alone."""
+    torch.manual_seed(tokens)
+    theta = 1e4
+    width = (n_q + 2 * n_kv) * head_dim
+    pages = (tokens + page - 1) // page + 3
+    qkv = torch.randn(tokens, width, device=DEV).to(dtype)
+    bias = torch.randn(width, device=DEV) * 0.1
+    positions = (torch.arange(tokens, dtype=torch.int32) * 37 % 5000).to(DEV)
+    order = torch.randperm(pages * page)[:tokens].to(torch.int32)
+    order[5] = -1
+    order[tokens - 1] = -1
+    slots = order.to(DEV)
+    inv_freq = qwen2_plain.rope_inverse_frequencies(head_dim, theta).to(DEV)
+    code = 0 if pairing == "interleaved" else 1
+    q_out = torch.zeros(tokens, n_q, head_dim, device=DEV, dtype=dtype)
+    k_cache = torch.zeros(pages, n_kv, page, head_dim, device=DEV, dtype=dtype)
+    v_cache = torch.zeros_like(k_cache)
+    ops().rope_kv_write(qkv, bias, positions, slots, inv_freq, q_out, k_cache, v_cache, n_q, n_kv, head_dim, code)
+    # the same rows, nine at a time, through the few-token kernel
+    q_few = torch.zeros_like(q_out)
+    k_few, v_few = torch.zeros_like(k_cache), torch.zeros_like(v_cache)
+    for start in range(0, tokens, 9):
+        stop = min(tokens, start + 9)
+        ops().rope_kv_write(qkv[start:stop], bias, positions[start:stop], slots[start:stop], inv_freq,
+                            q_few[start:stop], k_few, v_few, n_q, n_kv, head_dim, code)
+    for got, few in ((q_out, q_few), (k_cache, k_few), (v_cache, v_few)):
+        assert torch.equal(got, few)   # bit for bit, padding rows included
+    x = (qkv.float() + bias).cpu()
+    want_q = qwen2_plain.rope(x[:, :n_q * head_dim].reshape(tokens, n_q, head_dim), positions.cpu(), theta, pairing)
+    tol = 3e-5 if dtype == torch.float32 else 2.0 ** -7
+    assert float((q_out.float().cpu() - want_q).abs().max()) < tol * float(want_q.abs().max())
+
+
 def dense_attention(q, k, v, scale, window=0):
     """q [Hq, D] at the last position of k, v [ctx, Hkv, D]; float64."""
     n_q, n_kv = q.shape[0], k.shape[1]
