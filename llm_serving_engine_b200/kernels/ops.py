@@ -245,6 +245,43 @@ def paged_attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
     return out
 
 
+def attention_tc_supported(head_dim: int, n_q: int, n_kv: int, page_size: int, dtype: torch.dtype,
+                           window: int = 0) -> bool:
+    """Whether the tcgen05 prefill kernel takes this shape (bfloat16, head size 64 or 128, pages of
+    8 to 128 keys that divide 128, no window)."""
+    if dtype != torch.bfloat16 or window > 0:
+        return False
+    return bool(library.load().lse_attention_tc_supported(head_dim, n_q, n_kv, page_size))
+
+
+def paged_attention_prefill_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
+                               block_tables: torch.Tensor, segment_start: torch.Tensor,
+                               segment_first_position: torch.Tensor, scale: float) -> torch.Tensor:
+    """Attention of prompt portions on the 5th-generation tensor cores: the arguments and the
+    result of :func:`paged_attention_prefill`; blocks of 128 rows of one head, keys in tiles of 128
+    brought in by TMA page by page, scores and outputs accumulated in tensor memory."""
+    _need_cuda(q, k_cache, v_cache, out, block_tables, segment_start, segment_first_position)
+    tokens, n_q, head_dim = q.shape
+    pages, n_kv, page_size = k_cache.shape[0], k_cache.shape[1], k_cache.shape[2]
+    segments = segment_first_position.shape[0]
+    assert q.dtype == out.dtype == k_cache.dtype == v_cache.dtype == torch.bfloat16
+    assert q.is_contiguous() and out.is_contiguous() and k_cache.is_contiguous() and v_cache.is_contiguous()
+    assert v_cache.shape == k_cache.shape and k_cache.shape[3] == head_dim
+    assert block_tables.dtype == torch.int32 and block_tables.stride(1) == 1 and segment_start.shape[0] == segments + 1
+    lib = library.load()
+    check(lib.lse_paged_attention_prefill_tc(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
+                                             block_tables.data_ptr(), block_tables.stride(0), segment_start.data_ptr(),
+                                             segment_first_position.data_ptr(), segments, tokens, pages, n_q, n_kv,
+                                             head_dim, page_size, float(scale), _stream()),
+          "paged_attention_prefill_tc")
+    return out
+
+
+def attention_tc_status() -> int:
+    """0 while no bounded wait of the tcgen05 attention kernel has given up (synchronises the device)."""
+    return int(library.load().lse_attention_tc_status())
+
+
 def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, interleave: int = 0) -> torch.Tensor:
     """out[t, i] = silu(gate_i) * up_i; ``gate_up`` is [T, 2I] or a float32 stack of partial sums
     [P, T, 2I].  ``interleave`` 0: the row is [gate (I) | up (I)]; n > 0: blocks of n gate values

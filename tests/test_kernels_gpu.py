@@ -483,6 +483,121 @@ def test_prefill_attention_keeps_the_causal_edge():
         assert float((out[local].double() - want).abs().max()) < 2.0 ** -6, local
 
 
+TC_SHAPES = [(128, 12, 2, 16), (64, 6, 2, 16), (128, 7, 1, 8), (64, 4, 4, 32), (128, 40, 2, 64), (64, 3, 1, 128)]
+
+
+def dense_causal(q, k, v, before, scale):
+    """q [rows, Hq, D] at positions before .. before+rows-1 of k, v [ctx, Hkv, D]; float64."""
+    rows, n_q = q.shape[0], q.shape[1]
+    group = n_q // k.shape[1]
+    kk, vv = k.double().repeat_interleave(group, dim=1), v.double().repeat_interleave(group, dim=1)
+    scores = torch.einsum("rhd,chd->hrc", q.double(), kk) * scale
+    position = before + torch.arange(rows, device=q.device)
+    hidden = torch.arange(k.shape[0], device=q.device)[None, :] > position[:, None]
+    scores = scores.masked_fill(hidden[None], float("-inf"))
+    return torch.einsum("hrc,chd->rhd", torch.softmax(scores, -1), vv)
+
+
+@pytest.mark.parametrize("head_dim, n_q, n_kv, page", TC_SHAPES)
+def test_tcgen05_prefill_attention(head_dim, n_q, n_kv, page):
+    """Every row of every portion against dense attention: portions shorter and longer than a block
+    of 128 rows, with and without earlier keys, starting off the tile grid; the cache pages that no
+    request owns hold NaN, which must never reach a result."""
+    rng = random.Random(head_dim * n_kv + page)
+    torch.manual_seed(head_dim + page)
+    portions = [(0, 1), (0, 70), (5, 2), (63, 3), (64, 64), (100, 129), (1000, 1), (300, 11), (0, 200), (37, 300), (128, 128)]
+    contexts = [before + rows for before, rows in portions]
+    k_cache, v_cache, tables, dense = paged_setup(rng, contexts, n_kv, head_dim, page, torch.bfloat16)
+    owned = torch.zeros(k_cache.shape[0], dtype=torch.bool)
+    owned[tables[tables >= 0].long().cpu()] = True
+    k_cache[~owned] = float("nan")
+    v_cache[~owned] = float("nan")
+    for s, ctx in enumerate(contexts):       # so does the unused end of every last page
+        if ctx % page:
+            last = int(tables[s, (ctx - 1) // page])
+            k_cache[last, :, ctx % page:] = float("nan")
+            v_cache[last, :, ctx % page:] = float("nan")
+    total = sum(rows for _, rows in portions)
+    q = torch.randn(total, n_q, head_dim, device=DEV).bfloat16()
+    starts = [0]
+    for _, rows in portions:
+        starts.append(starts[-1] + rows)
+    out = torch.full_like(q, 9.0)
+    scale = 1.0 / math.sqrt(head_dim)
+    assert ops().attention_tc_supported(head_dim, n_q, n_kv, page, torch.bfloat16)
+    ops().paged_attention_prefill_tc(q, k_cache, v_cache, out, tables, torch.tensor(starts, dtype=torch.int32, device=DEV),
+                                     torch.tensor([b for b, _ in portions], dtype=torch.int32, device=DEV), scale)
+    assert ops().attention_tc_status() == 0
+    for s, (before, rows) in enumerate(portions):
+        want = dense_causal(q[starts[s]:starts[s + 1]], dense[s][0], dense[s][1], before, scale)
+        err = (out[starts[s]:starts[s + 1]].double() - want).abs()
+        assert float(err.max()) < 2.0 ** -7 * max(1.0, float(want.abs().max())), (s, before, rows, float(err.max()))
+
+
+def test_tcgen05_prefill_attention_when_the_maximum_grows():
+    """Scores that grow by far more than 2^8 from tile to tile (keys scaled up along the sequence):
+    the outputs in tensor memory have to be rescaled on the way, and a far, dominant key found."""
+    rng = random.Random(11)
+    torch.manual_seed(11)
+    n_q, n_kv, head_dim, page = 4, 2, 128, 16
+    before, rows = 200, 700
+    k_cache, v_cache, tables, dense = paged_setup(rng, [before + rows], n_kv, head_dim, page, torch.bfloat16)
+    k, v = dense[0]
+    q = torch.randn(rows, n_q, head_dim, device=DEV).bfloat16()
+    growth = (1.0 + torch.arange(before + rows, device=DEV).float() / 40.0)[:, None, None]   # up to about 23 times
+    k[:] = (k.float().abs() * growth * q[0, 0].float().sign()).bfloat16()     # scores of row 0, head 0 rise steadily
+    needle = 77                                                                 # and one early key dominates row 500
+    k[needle] = (q[500, 1].float() * 6)[None, :].bfloat16()
+    for position in range(before + rows):
+        k_cache[int(tables[0, position // page]), :, position % page] = k[position]
+    out = torch.empty_like(q)
+    scale = 1.0 / math.sqrt(head_dim)
+    ops().paged_attention_prefill_tc(q, k_cache, v_cache, out, tables, torch.tensor([0, rows], dtype=torch.int32, device=DEV),
+                                     torch.tensor([before], dtype=torch.int32, device=DEV), scale)
+    assert ops().attention_tc_status() == 0
+    want = dense_causal(q, k, v, before, scale)
+    err = (out.double() - want).abs()
+    assert float(err.max()) < 2.0 ** -6 * max(1.0, float(want.abs().max())), float(err.max())
+    assert float((out[500, 1].double() - v[needle, 0].double()).abs().max()) < 0.05
+
+
+def test_tcgen05_prefill_attention_keeps_the_causal_edge():
+    """The key right after a row's own position is made to match the query: it must not be read."""
+    rng = random.Random(5)
+    torch.manual_seed(5)
+    n_q, n_kv, head_dim, page = 6, 2, 64, 16
+    before, rows = 37, 300
+    k_cache, v_cache, tables, dense = paged_setup(rng, [before + rows], n_kv, head_dim, page, torch.bfloat16)
+    q = torch.randn(rows, n_q, head_dim, device=DEV).bfloat16()
+    k, v = dense[0]
+    for local in range(rows - 1):          # key pos+1 looks like the query of row `local`
+        pos = before + local
+        k[pos + 1, :] = (q[local, 0].float() * 4).bfloat16()
+        k_cache[int(tables[0, (pos + 1) // page]), :, (pos + 1) % page] = k[pos + 1]
+    out = torch.empty_like(q)
+    scale = 1.0 / math.sqrt(head_dim)
+    ops().paged_attention_prefill_tc(q, k_cache, v_cache, out, tables, torch.tensor([0, rows], dtype=torch.int32, device=DEV),
+                                     torch.tensor([before], dtype=torch.int32, device=DEV), scale)
+    want = dense_causal(q, k, v, before, scale)
+    assert float((out.double() - want).abs().max()) < 2.0 ** -6
+
+
+def test_tcgen05_prefill_attention_refuses_what_it_cannot_run():
+    assert not ops().attention_tc_supported(80, 4, 2, 16, torch.bfloat16)
+    assert not ops().attention_tc_supported(128, 4, 2, 4, torch.bfloat16)      # pages below 8 keys
+    assert not ops().attention_tc_supported(128, 4, 2, 48, torch.bfloat16)     # 48 does not divide 128
+    assert not ops().attention_tc_supported(128, 5, 2, 16, torch.bfloat16)
+    assert not ops().attention_tc_supported(128, 4, 2, 16, torch.float32)
+    assert not ops().attention_tc_supported(128, 4, 2, 16, torch.bfloat16, window=64)
+    from llm_serving_engine_b200.kernels.library import KernelError
+    q = torch.zeros(4, 4, 128, device=DEV, dtype=torch.bfloat16)
+    cache = torch.zeros(3, 2, 4, 128, device=DEV, dtype=torch.bfloat16)
+    with pytest.raises(KernelError):
+        ops().paged_attention_prefill_tc(q, cache, cache.clone(), torch.empty_like(q), torch.zeros(1, 1, dtype=torch.int32, device=DEV),
+                                         torch.tensor([0, 4], dtype=torch.int32, device=DEV),
+                                         torch.tensor([0], dtype=torch.int32, device=DEV), 0.1)
+
+
 # ------------------------------------------------------------------ tcgen05 product and partial-sum inputs
 @pytest.mark.parametrize("m, n, k, splits", [(1, 128, 64, 1), (8, 2048, 1536, 12), (3, 1536, 8960, 24), (16, 1000, 776, 3),
                                              (32, 17920, 1536, None), (7, 151936, 1536, None), (200, 384, 520, 2),
