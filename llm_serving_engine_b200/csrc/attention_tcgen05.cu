@@ -2,22 +2,28 @@
 // (bfloat16, head size 64 or 128, pages of 8, 16, 32, 64 or 128 keys).
 //
 // One block = 128 consecutive rows of one request x one query head.  It walks the keys in
-// tiles of 128 (causal: up to the position of its last row):
+// tiles of 128 (causal: up to the position of its last row).  The tiles go alternately to two
+// groups of four softmax warps; a group has its own key and value stage, score and output
+// accumulators in tensor memory, probability tile, running maxima and sums, and the two
+// partial results are merged at the end.  While one group works out exponentials the other
+// waits for its scores or writes probabilities, so the units of the SM overlap.
 //
-//   loader warp   TMA brings the query tile once, then the key and value tiles page by page
-//                 (the block table gives the page of every 128-byte-swizzled box) into two
-//                 stages each.
-//   MMA warp      one thread issues  S = Q K^T  (tcgen05.mma, accumulator in tensor memory,
-//                 two S buffers) and, when the probabilities of a tile are ready,  O += P V
-//                 (V is the MN-major operand: its rows are keys).  S of tile j+1 is issued
-//                 before P V of tile j, so the tensor cores work while the softmax runs.
-//   softmax       eight warps; a thread owns half a row (64 keys) of S: tcgen05.ld, mask, row
-//                 maximum (exchanged with the thread of the other half through shared memory),
-//                 exp2 in float32, bfloat16 probabilities written to shared memory in the
-//                 swizzled K-major layout the tensor cores read.  O stays in tensor memory and
-//                 is only rescaled when a row maximum grows by more than 2^8 (the sums carry
-//                 the same factor, so the quotient is exact either way); at the end
-//                 O / sum is written out as bfloat16.
+//   loader warp   TMA brings the query tile once, then the key and value tiles, one copy per page
+//                 (the block table gives the page; a four-dimensional tensor map lays the two
+//                 64-column halves of every 8 keys side by side, 128-byte swizzled), into the
+//                 stage of the tile's group.
+//   MMA warps     one thread issues  S = Q K^T  (tcgen05.mma, accumulator in tensor memory) for the
+//                 group whose turn it is, a thread of another warp  O += P V  (V is the MN-major
+//                 operand: its rows are keys), so that neither product waits behind the other's
+//                 barrier.
+//   softmax       a thread owns one row of its group's tiles: it reads S (tcgen05.ld), masks, finds
+//                 the row maximum, takes exp2 in float32 and writes bfloat16 probabilities to shared memory in the swizzled K-major
+//                 layout the tensor cores read.  After a group's first tile the probabilities
+//                 are taken relative to the maximum in use, in one pass; O stays in tensor memory
+//                 and is only rescaled when a row maximum has grown by more than 2^8 (the sums
+//                 carry the same factor, so the quotient is exact either way).  At the end the two groups' outputs
+//                 are weighted by 2^(their maximum - the common maximum), added, divided by the
+//                 sum and written out as bfloat16.
 //
 // Softmax, maxima and sums are float32.  Every wait is bounded (see tcgen05.cuh); after a
 // wait that gave up the block writes nothing, frees its tensor memory and returns, and
@@ -29,25 +35,38 @@ using namespace tc;
 
 constexpr int BM = 128;        // rows of a block
 constexpr int BN = 128;        // keys per tile
-constexpr int SOFTMAX_WARPS = 8;
-constexpr int MMA_WARP = 8, LOADER_WARP = 9;
-constexpr int THREADS = 320;
+constexpr int GROUPS = 2;      // softmax groups (tiles j with j % 2 == g go to group g)
+constexpr int GROUP_THREADS = 128;
+constexpr int MMA_WARP = 8, LOADER_WARP = 9, PV_WARP = 10;
+constexpr int THREADS = 352;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float RESCALE_STEP = 8.0f;   // in powers of two
+constexpr float REDO_STEP = 64.0f;
 constexpr uint32_t HALF_BYTES = 128 * 128;   // a box of 128 rows x 64 bfloat16
 
 __device__ int lse_attn_tc_error;
 
 // Tuning builds (-DLSE_TRACE): the block of the last tile of the first request, head 0, records clock
-// stamps of its first softmax thread (slots 0-5 of a tile) and of its MMA thread (slots 6, 7).
+// stamps of the first thread of each softmax group (slots 0-5 of a tile) and of its MMA thread (6, 7).
 #ifdef LSE_TRACE
-__device__ long long lse_attn_tc_stamps[128 * 8];
+__device__ long long lse_attn_tc_stamps[2 * 128 * 8];
 #define TC_STAMP(tile, k) if (traced && (tile) < 128) lse_attn_tc_stamps[(tile) * 8 + (k)] = clock64();
+#define TC_STAMP2(tile, k) if (traced && (tile) < 128) lse_attn_tc_stamps[1024 + (tile) * 8 + (k)] = clock64();
+// start and end of every block (nanoseconds of the global timer), its SM and its number of tiles
+__device__ unsigned long long lse_attn_tc_blocks[4096 * 4];
+__device__ __forceinline__ unsigned long long global_ns() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+__device__ __forceinline__ unsigned sm_id() { unsigned v; asm volatile("mov.u32 %0, %%smid;" : "=r"(v)); return v; }
+// what-if switches (wrong results): 1 no probability writes, 2 no P V products, 4 no score products, 8 no exponentials, 16 no key and value loads
+__device__ int lse_attn_tc_what_if;
+#define TC_WHAT_IF(bit) ((what_if & (bit)) != 0)
 #else
 #define TC_STAMP(tile, k)
+#define TC_STAMP2(tile, k)
+#define TC_WHAT_IF(bit) false
 #endif
 
-enum Bar { B_Q = 0, B_KF = 1, B_KE = 3, B_VF = 5, B_VE = 7, B_SF = 9, B_SE = 11, B_PF = 13, B_OD = 14, B_COUNT = 15 };
+// per group g: index + g
+enum Bar { B_Q = 0, B_KF = 1, B_KE = 3, B_VF = 5, B_VE = 7, B_SF = 9, B_PF = 11, B_OD = 13, B_COUNT = 15 };
 
 __device__ __forceinline__ float exp2_fast(float x) {   // 2^x, 2^-inf = 0
   float y;
@@ -58,17 +77,27 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<const uint32_t*>(&v);
 }
-__device__ __forceinline__ void pair_barrier(int quarter) {   // the two warps that share 32 rows
+__device__ __forceinline__ void pair_barrier(int quarter) {   // the warps of the two groups that own the same 32 rows
   asm volatile("bar.sync %0, %1;\n" ::"r"(1 + quarter), "r"(64) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {   // has that phase completed? (no waiting)
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}\n"
+      : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+  return done != 0;
 }
 
 template <int D>
 constexpr size_t attn_tc_smem() {
-  return 1024 + (size_t)(D / 64) * HALF_BYTES * 5 + 2 * HALF_BYTES + 256 + 3 * 1024;
+  // alignment slack, Q, a key and a value stage and a probability tile per group, barriers
+  return 1024 + (size_t)(D / 64) * HALF_BYTES * (1 + 2 * GROUPS) + (size_t)GROUPS * 2 * HALF_BYTES + 256;
 }
 
 template <int D>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
                        const int* __restrict__ block_tables, int bt_stride, const int* __restrict__ segment_start,
@@ -76,21 +105,23 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        float scale_log2e) {
   constexpr int HALVES = D / 64;
   constexpr uint32_t Q_BYTES = HALVES * HALF_BYTES, KV_BYTES = HALVES * HALF_BYTES, P_BYTES = 2 * HALF_BYTES;
-  constexpr uint32_t S_COLS = BN, O_COL = 2 * BN;
-  constexpr int OD = D / 2;   // output columns of one softmax thread
+  constexpr uint32_t GROUP_BYTES = HALVES * 1024;   // 8 keys (or values) in a stage: 8 rows x 128 bytes for every 64 columns
+  constexpr uint32_t S_COLS = BN, O_COL = GROUPS * BN;   // tensor memory: S of group 0, S of group 1, O of group 0, O of group 1
+  constexpr int OD = D / 2;   // output columns that one thread writes at the end
   extern __shared__ unsigned char smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char* gbase = smem_raw + (base - smem_u32(smem_raw));
-  const uint32_t q_s = base, k_s = q_s + Q_BYTES, v_s = k_s + 2 * KV_BYTES, p_s = v_s + 2 * KV_BYTES;
-  const uint32_t bars = p_s + P_BYTES;
+  const uint32_t q_s = base, k_s = q_s + Q_BYTES, v_s = k_s + GROUPS * KV_BYTES, p_s = v_s + GROUPS * KV_BYTES;
+  const uint32_t bars = p_s + GROUPS * P_BYTES;
   unsigned char* tail = gbase + (bars - base);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail + 8 * B_COUNT);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 8 * B_COUNT + 4);
-  float* exchange = reinterpret_cast<float*>(tail + 256);   // [2 tiles in flight][2 halves][128 rows], then sums [2][128]
   auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int head = blockIdx.y;
+  // blocks are numbered tile by tile, all heads of a tile side by side: the blocks that walk the most
+  // keys (the last tiles) start first, whatever their head
+  const int head = blockIdx.x % n_q;
   const int kvh = head / (n_q / n_kv);
   pdl_launch_dependents();
 
@@ -99,7 +130,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   int seg = -1, r0 = 0, cnt = 0;
   {
     int before = 0;
-    const int tile = gridDim.x - 1 - blockIdx.x;
+    const int tile = (int)(gridDim.x / n_q) - 1 - (int)(blockIdx.x / n_q);
     for (int s = 0; s < num_segments; ++s) {
       const int c = segment_start[s + 1] - segment_start[s];
       const int nt = (c + BM - 1) / BM;
@@ -107,6 +138,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       before += nt;
     }
   }
+#ifdef LSE_TRACE
+  const int block_linear = blockIdx.x;
+  if (tid == 0 && block_linear < 4096) { lse_attn_tc_blocks[block_linear * 4] = global_ns(); lse_attn_tc_blocks[block_linear * 4 + 2] = sm_id(); lse_attn_tc_blocks[block_linear * 4 + 3] = 0; }
+#endif
   if (seg < 0) return;
   const int nrows = min(BM, cnt - r0);
   const int row_base = segment_start[seg] + r0;
@@ -116,15 +151,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const int n_pages = last_pos / page_size + 1;
   const int* bt = block_tables + (size_t)seg * bt_stride;
 #ifdef LSE_TRACE
-  const bool traced = seg == 0 && head == 0 && r0 + BM >= cnt && (tid == 0 || tid == MMA_WARP * 32);
+  const int what_if = lse_attn_tc_what_if;
+  const bool traced = seg == 0 && head == 0 && r0 + BM >= cnt && (tid == 0 || tid == GROUP_THREADS || tid == MMA_WARP * 32 || tid == PV_WARP * 32);
 #endif
 
   if (tid == 0) {
-    for (int i = 0; i < B_COUNT; ++i) mbar_init(bar(i), (i == B_SE || i == B_SE + 1 || i == B_PF) ? SOFTMAX_WARPS * 32 : 1);
+    for (int i = 0; i < B_COUNT; ++i)
+      mbar_init(bar(i), (i >= B_PF && i < B_PF + 2) ? GROUP_THREADS : 1);
     *abort_flag = 0;
     mbar_init_fence();
   }
-  if (warp == MMA_WARP) tmem_alloc(tmem_slot, 512);   // S twice (256 columns), O (D columns)
+  if (warp == MMA_WARP) tmem_alloc(tmem_slot, 512);   // S and O (at most 128 columns each) of both groups
   fence_before_sync();
   __syncthreads();
   fence_after_sync();
@@ -134,210 +171,284 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   pdl_wait();   // queries, keys and values come from the kernel before; no bounded wait starts earlier
 
   if (warp == LOADER_WARP) {
+    // Order: K of tile j + 1 goes before V of tile j (the scores are wanted first).  A lane owns one
+    // page of the tile.
     const int ppt = BN / page_size;   // pages per tile, at most 16
     if (lane == 0) {
       mbar_expect_tx(bar(B_Q), Q_BYTES);
       for (int h = 0; h < HALVES; ++h) tma_load_3d(q_s + h * HALF_BYTES, &map_q, bar(B_Q), h * 64, head, row_base);
     }
-    int page_next = lane < min(ppt, n_pages) ? bt[lane] : 0;
-    for (int j = 0; j < n_tiles; ++j) {
-      const int st = j & 1;
+    auto page_of = [&](int j) { return (j < n_tiles && lane < min(ppt, n_pages - j * ppt)) ? bt[j * ppt + lane] : 0; };
+    auto load = [&](int j, int page, uint32_t dst, const CUtensorMap* map, int full, int empty) -> bool {
+      const int g = j & 1;
       const uint32_t parity = (uint32_t)(j >> 1) & 1u;
       const int np = min(ppt, n_pages - j * ppt);
-      const int page = page_next;
-      if (j + 1 < n_tiles) page_next = lane < min(ppt, n_pages - (j + 1) * ppt) ? bt[(j + 1) * ppt + lane] : 0;
-      const int y = (page * n_kv + kvh) * page_size;
-      const uint32_t box = (uint32_t)(lane * page_size) * 128u;
-      const uint32_t bytes = (uint32_t)(np * page_size) * 128u * HALVES;
       int ok = 1;
-      if (lane == 0) ok = mbar_wait(bar(B_KE + st), parity ^ 1u, abort_flag, err) ? 1 : 0;
-      if (!__shfl_sync(0xffffffffu, ok, 0)) break;
-      if (lane == 0) mbar_expect_tx(bar(B_KF + st), bytes);
+      if (lane == 0) ok = mbar_wait(bar(empty + g), parity ^ 1u, abort_flag, err) ? 1 : 0;
+      if (!__shfl_sync(0xffffffffu, ok, 0)) return false;
+      if (TC_WHAT_IF(16)) {   // no key and value loads
+        if (lane == 0) mbar_arrive(bar(full + g));
+        return true;
+      }
+      if (lane == 0) mbar_expect_tx(bar(full + g), (uint32_t)(np * page_size) * 128u * HALVES);
       __syncwarp();
-      if (lane < np)
-        for (int h = 0; h < HALVES; ++h)
-          tma_load_2d(k_s + st * KV_BYTES + h * HALF_BYTES + box, &map_k, bar(B_KF + st), h * 64, y);
-      if (lane == 0) ok = mbar_wait(bar(B_VE + st), parity ^ 1u, abort_flag, err) ? 1 : 0;
-      if (!__shfl_sync(0xffffffffu, ok, 0)) break;
-      if (lane == 0) mbar_expect_tx(bar(B_VF + st), bytes);
-      __syncwarp();
-      if (lane < np)
-        for (int h = 0; h < HALVES; ++h)
-          tma_load_2d(v_s + st * KV_BYTES + h * HALF_BYTES + box, &map_v, bar(B_VF + st), h * 64, y);
+      if (lane < np)   // one copy per page: its groups of 8 keys, the two halves of the head size side by side
+        tma_load_4d(dst + g * KV_BYTES + (uint32_t)(lane * page_size) * 128u * HALVES, map, bar(full + g), 0, 0, 0,
+                    (page * n_kv + kvh) * (page_size / 8));
+      return true;
+    };
+    int page_k = page_of(0), page_v = page_k;
+    bool ok = load(0, page_k, k_s, &map_k, B_KF, B_KE);
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      page_k = page_of(j + 1);
+      if (j + 1 < n_tiles) ok = load(j + 1, page_k, k_s, &map_k, B_KF, B_KE);
+      if (ok) ok = load(j, page_v, v_s, &map_v, B_VF, B_VE);
+      page_v = page_k;
     }
   } else if (warp == MMA_WARP) {
     if (lane == 0) {
+      // S_j = Q K_j^T as soon as the group of tile j has read the scores of its tile before (it has, when
+      // its probabilities are written).  The keys are waited for first: they have long arrived, and the
+      // wait that matters then comes last.
       const uint32_t idesc_s = instr_desc_bf16(BM, BN, false, false);
-      const uint32_t idesc_o = instr_desc_bf16(BM, D, false, true);
       bool ok = mbar_wait(bar(B_Q), 0, abort_flag, err);
-      for (int j = 0; j <= n_tiles && ok; ++j) {
-        if (j < n_tiles) {   // S_j = Q K_j^T
-          const int st = j & 1;
-          const uint32_t parity = (uint32_t)(j >> 1) & 1u;
-          ok = mbar_wait(bar(B_KF + st), parity, abort_flag, err) && mbar_wait(bar(B_SE + st), parity ^ 1u, abort_flag, err);
-          if (!ok) break;
-          fence_after_sync();
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int g = j & 1;
+        const uint32_t parity = (uint32_t)(j >> 1) & 1u;
+        TC_STAMP2(j, 1)
+        ok = mbar_wait(bar(B_KF + g), parity, abort_flag, err);
+        TC_STAMP2(j, 2)
+        if (ok && j >= GROUPS) ok = mbar_wait(bar(B_PF + g), parity ^ 1u, abort_flag, err);
+        if (!ok) break;
+        fence_after_sync();
+        TC_STAMP2(j, 6)
 #pragma unroll
-          for (int ks = 0; ks < D / 16; ++ks) {
-            const uint32_t off = (uint32_t)(ks / 4) * HALF_BYTES + (uint32_t)(ks % 4) * 32u;
-            umma_bf16(tmem_base + st * S_COLS, smem_desc_k_major(q_s + off),
-                      smem_desc_k_major(k_s + st * KV_BYTES + off), idesc_s, ks != 0 ? 1u : 0u);
-          }
-          umma_commit(bar(B_KE + st));
-          umma_commit(bar(B_SF + st));
-          TC_STAMP(j, 6)
+        for (int ks = 0; ks < D / 16 && !TC_WHAT_IF(4); ++ks) {
+          const uint32_t off = (uint32_t)(ks / 4) * HALF_BYTES + (uint32_t)(ks % 4) * 32u;
+          const uint32_t k_off = (uint32_t)(ks / 4) * 1024u + (uint32_t)(ks % 4) * 32u;
+          umma_bf16(tmem_base + g * S_COLS, smem_desc_k_major(q_s + off),
+                    smem_desc_k_major(k_s + g * KV_BYTES + k_off, GROUP_BYTES), idesc_s, ks != 0 ? 1u : 0u);
         }
-        if (j >= 1) {        // O += P_i V_i
-          const int i = j - 1, st = i & 1;
-          ok = mbar_wait(bar(B_PF), (uint32_t)i & 1u, abort_flag, err) &&
-               mbar_wait(bar(B_VF + st), (uint32_t)(i >> 1) & 1u, abort_flag, err);
-          if (!ok) break;
-          fence_after_sync();
+        TC_STAMP2(j, 7)
+        umma_commit(bar(B_KE + g));
+        umma_commit(bar(B_SF + g));
+        TC_STAMP(j, 6)
+      }
+    }
+    __syncwarp();
+  } else if (warp == PV_WARP) {
+    if (lane == 0) {
+      // O_g += P_i V_i as soon as the probabilities of tile i are written
+      const uint32_t idesc_o = instr_desc_bf16(BM, D, false, true);
+      bool ok = true;
+      for (int i = 0; i < n_tiles && ok; ++i) {
+        const int g = i & 1;
+        const uint32_t parity = (uint32_t)(i >> 1) & 1u;
+        TC_STAMP2(i, 0)
+        ok = mbar_wait(bar(B_VF + g), parity, abort_flag, err) && mbar_wait(bar(B_PF + g), parity, abort_flag, err);
+        // the scores of the group's next tile go first (the group waits for them; this product is wanted later)
+        if (ok && i + GROUPS < n_tiles) ok = mbar_wait(bar(B_KE + g), parity ^ 1u, abort_flag, err);
+        if (!ok) break;
+        fence_after_sync();
+        TC_STAMP2(i, 3)
 #pragma unroll
-          for (int ks = 0; ks < BN / 16; ++ks) {
-            const uint32_t p_off = (uint32_t)(ks / 4) * HALF_BYTES + (uint32_t)(ks % 4) * 32u;
-            umma_bf16(tmem_base + O_COL, smem_desc_k_major(p_s + p_off),
-                      smem_desc_mn_major(v_s + st * KV_BYTES + (uint32_t)ks * 2048u, HALF_BYTES), idesc_o,
-                      (i | ks) != 0 ? 1u : 0u);
-          }
-          umma_commit(bar(B_VE + st));
-          umma_commit(bar(B_OD));
-          TC_STAMP(i, 7)
+        for (int ks = 0; ks < BN / 16 && !TC_WHAT_IF(2); ++ks) {
+          const uint32_t p_off = (uint32_t)(ks / 4) * HALF_BYTES + (uint32_t)(ks % 4) * 32u;
+          umma_bf16(tmem_base + O_COL + g * D, smem_desc_k_major(p_s + g * P_BYTES + p_off),
+                    smem_desc_mn_major(v_s + g * KV_BYTES + (uint32_t)ks * 2u * GROUP_BYTES, 1024u, GROUP_BYTES), idesc_o,
+                    (i >= GROUPS || ks != 0) ? 1u : 0u);
         }
+        TC_STAMP2(i, 4)
+        umma_commit(bar(B_VE + g));
+        umma_commit(bar(B_OD + g));
+        TC_STAMP2(i, 5)
+        TC_STAMP(i, 7)
       }
     }
     __syncwarp();
   } else {
     // ---------------------------------------------------------------- softmax
-    const int quarter = warp & 3, half = warp >> 2;
+    const int g = warp >> 2, quarter = warp & 3;
     const int row = quarter * 32 + lane;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    const uint32_t s_addr = lane_addr + g * S_COLS, o_addr = lane_addr + O_COL + g * D;
     const int my_pos = pos0 + min(row, nrows - 1);
-    float m_used = -INFINITY, l = 0.f;
+    unsigned char* prow = gbase + (p_s - base) + g * P_BYTES + row * 128;
+    float m_used = -INFINITY, m_seen = -INFINITY, l = 0.f;   // the maximum that O and l are relative to; the largest score seen
+    bool pending = false;                                    // m_seen has outgrown m_used: O and l are to be rescaled
     // `ok` is the same in all lanes of a warp (a vote after every wait).  A warp whose wait gave up
-    // keeps meeting its partner warp at the pair barriers, which have no time limit of their own.
+    // still meets the warp of the other group at the pair barrier, which has no time limit of its own.
     bool ok = true;
     auto wait_all = [&](int which, uint32_t parity) {
-      return __all_sync(0xffffffffu, mbar_wait(bar(which), parity, abort_flag, err) ? 1 : 0) != 0;
+      const bool done = mbar_test(bar(which), parity) || mbar_wait(bar(which), parity, abort_flag, err);
+      return __all_sync(0xffffffffu, done ? 1 : 0) != 0;
     };
-    for (int j = 0; j < n_tiles; ++j) {
-      const int st = j & 1;
-      uint32_t sa[32], sb[32];
-      float mx = -INFINITY;
+    for (int j = g; j < n_tiles && ok; j += GROUPS) {
+      const uint32_t parity = (uint32_t)(j >> 1) & 1u;
       TC_STAMP(j, 0)
-      if (ok) ok = wait_all(B_SF + st, (uint32_t)(j >> 1) & 1u);
+      ok = wait_all(B_SF + g, parity);
+      if (!ok) break;
       TC_STAMP(j, 1)
-      if (ok) {
-        fence_after_sync();
-        tmem_ld32(lane_addr + st * S_COLS + half * 64, sa);
-        tmem_ld32(lane_addr + st * S_COLS + half * 64 + 32, sb);
-        tmem_ld_wait();
-        fence_before_sync();
-        mbar_arrive(bar(B_SE + st));   // the buffer may take the tile after next
-        const int kv0 = j * BN + half * 64;
-        if (kv0 + 63 > my_pos) {   // the diagonal runs through these keys
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            if (kv0 + i > my_pos) sa[i] = 0xff800000u;
-            if (kv0 + 32 + i > my_pos) sb[i] = 0xff800000u;
-          }
-        }
-#pragma unroll
-        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fmaxf(__uint_as_float(sa[i]), __uint_as_float(sb[i])));
-      }
-      float* slot = exchange + (j & 1) * 256;
-      slot[half * 128 + row] = mx;
-      pair_barrier(quarter);
-      TC_STAMP(j, 2)
-      if (!ok) continue;
-      mx = fmaxf(mx, slot[(half ^ 1) * 128 + row]);
-      const float m_new = fmaxf(m_used, mx * scale_log2e);   // finite: key 0 is visible to every row
+      fence_after_sync();
+      const int kv0 = j * BN;
+      const bool diagonal = kv0 + BN - 1 > my_pos;   // some keys of this tile lie beyond this row's position
+      const bool first = j < GROUPS;                 // this group's first tile
       bool rescale = false;
       float alpha = 1.f;
-      if (j == 0) {
-        m_used = m_new;
-      } else if (__any_sync(0xffffffffu, m_new > m_used + RESCALE_STEP)) {   // the same vote in both warps of the rows
-        rescale = true;
-        alpha = exp2_fast(m_used - m_new);
-        m_used = m_new;
-        l *= alpha;
-      }
-      const float neg = -m_used;
-      uint32_t pk[32];
+      if (first) {
+        // the row maximum of the first tile is found before anything is exponentiated
+        float mx = -INFINITY;
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const float p0 = exp2_fast(fmaf(__uint_as_float(sa[2 * i]), scale_log2e, neg));
-        const float p1 = exp2_fast(fmaf(__uint_as_float(sa[2 * i + 1]), scale_log2e, neg));
-        const float p2 = exp2_fast(fmaf(__uint_as_float(sb[2 * i]), scale_log2e, neg));
-        const float p3 = exp2_fast(fmaf(__uint_as_float(sb[2 * i + 1]), scale_log2e, neg));
-        l += (p0 + p1) + (p2 + p3);
-        pk[i] = pack_bf16(p0, p1);
-        pk[16 + i] = pack_bf16(p2, p3);
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t s[32];
+          tmem_ld32(s_addr + c, s);
+          tmem_ld_wait();
+          if (diagonal) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (kv0 + c + i > my_pos) s[i] = 0xff800000u;
+          }
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) mx = fmaxf(mx, fmaxf(__uint_as_float(s[i]), __uint_as_float(s[i + 1])));
+        }
+        // a row of tile 0 always sees key 0; tile 1 may be hidden entirely (-inf: nothing is added then)
+        m_used = m_seen = mx * scale_log2e;
+      } else if (pending) {   // the tile before raised the maximum by more than the step: O and the sum follow now
+        rescale = true;
+        alpha = m_used == -INFINITY ? 0.f : exp2_fast(m_used - m_seen);
+        m_used = m_seen;
+        l *= alpha;
+        pending = false;
       }
-      TC_STAMP(j, 3)
-      if (j > 0) {   // P V of the tile before has read the probabilities and added to O
-        ok = wait_all(B_OD, (uint32_t)(j - 1) & 1u);
-        if (!ok) continue;
+      TC_STAMP(j, 2)
+      if (j >= GROUPS) {   // P V of this group's tile before has read the probabilities and added to O
+        ok = wait_all(B_OD + g, parity ^ 1u);
+        if (!ok) break;
         fence_after_sync();
       }
-      TC_STAMP(j, 4)
-      if (rescale) {
+      TC_STAMP(j, 3)
+      // Later tiles take their probabilities relative to the maximum in use, in one pass, and find their
+      // own maximum on the way.  A maximum that grew by more than 2^8 is taken over before the next
+      // tile; one that grew by more than 2^64 (bfloat16 and float32 would run out of range a little
+      // further on) is taken over at once and the tile is done again.
+#pragma unroll 1
+      for (int attempt = 0; attempt < 2; ++attempt) {
+        if (rescale) {
 #pragma unroll
-        for (int c = 0; c < OD; c += 32) {
-          uint32_t o[32];
-          tmem_ld32(lane_addr + O_COL + half * OD + c, o);
-          tmem_ld_wait();
+          for (int c = 0; c < D; c += 32) {
+            uint32_t o[32];
+            tmem_ld32(o_addr + c, o);
+            tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-          tmem_st32(lane_addr + O_COL + half * OD + c, o);
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st32(o_addr + c, o);
+          }
+          tmem_st_wait();
+          rescale = false;
         }
-        tmem_st_wait();
-      }
-      // 64 probabilities = 8 chunks of 16 bytes of row `row` in the box of this half
-      unsigned char* prow = gbase + (p_s - base) + half * HALF_BYTES + row * 128;
+        const float neg = m_used == -INFINITY ? 0.f : -m_used;   // every score is -inf then as well: p = 0
+        float mx = -INFINITY, sum = 0.f;
 #pragma unroll
-      for (int c = 0; c < 8; ++c)
-        *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) =
-            make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+        for (int c = 0; c < BN; c += 32) {   // 32 keys = 4 chunks of 16 bytes at a time
+          uint32_t s[32];
+          tmem_ld32(s_addr + c, s);
+          tmem_ld_wait();
+          if (diagonal) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (kv0 + c + i > my_pos) s[i] = 0xff800000u;
+          }
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 16; i += 2) {
+            const float s0 = __uint_as_float(s[2 * i]), s1 = __uint_as_float(s[2 * i + 1]);
+            const float s2 = __uint_as_float(s[2 * i + 2]), s3 = __uint_as_float(s[2 * i + 3]);
+            mx = fmaxf(mx, fmaxf(fmaxf(s0, s1), fmaxf(s2, s3)));
+            float p0 = fmaf(s0, scale_log2e, neg), p1 = fmaf(s1, scale_log2e, neg);
+            float p2 = fmaf(s2, scale_log2e, neg), p3 = fmaf(s3, scale_log2e, neg);
+            if (!TC_WHAT_IF(8)) { p0 = exp2_fast(p0); p1 = exp2_fast(p1); p2 = exp2_fast(p2); p3 = exp2_fast(p3); }
+            sum += (p0 + p1) + (p2 + p3);
+            pk[i] = pack_bf16(p0, p1);
+            pk[i + 1] = pack_bf16(p2, p3);
+          }
+          unsigned char* box = prow + (c / 64) * HALF_BYTES;
+#pragma unroll
+          for (int k = 0; k < 4 && !TC_WHAT_IF(1); ++k) {
+            const int chunk = (c % 64) / 8 + k;
+            *reinterpret_cast<uint4*>(box + ((chunk ^ (row & 7)) << 4)) = make_uint4(pk[4 * k], pk[4 * k + 1], pk[4 * k + 2], pk[4 * k + 3]);
+          }
+        }
+        const float m_tile = mx * scale_log2e;
+        if (first || !__any_sync(0xffffffffu, m_tile > m_used + REDO_STEP)) {
+          l += sum;
+          m_seen = fmaxf(m_seen, m_tile);
+          pending = __any_sync(0xffffffffu, m_seen > m_used + RESCALE_STEP) != 0;
+          break;
+        }
+        rescale = true;
+        alpha = m_used == -INFINITY ? 0.f : exp2_fast(m_used - fmaxf(m_used, m_tile));
+        m_used = fmaxf(m_used, m_tile);
+        m_seen = fmaxf(m_seen, m_used);
+        l *= alpha;
+      }
+      TC_STAMP(j, 4)
       if (j == n_tiles - 1 && last_pos + 1 - j * BN < BN) {
         // rows of V beyond the last key: whatever lies there (stale keys, unwritten shared memory)
         // must not meet the zero probabilities as NaN or infinity
-        ok = wait_all(B_VF + st, (uint32_t)(j >> 1) & 1u);
-        if (!ok) continue;
+        ok = wait_all(B_VF + g, parity);
+        if (!ok) break;
         const int valid = last_pos + 1 - j * BN, chunks = (BN - valid) * 8;
-        for (int idx = tid; idx < chunks * HALVES; idx += SOFTMAX_WARPS * 32) {
+        for (int idx = tid - g * GROUP_THREADS; idx < chunks * HALVES; idx += GROUP_THREADS) {
           const int h = idx / chunks, rem = idx % chunks;
-          *reinterpret_cast<uint4*>(gbase + (v_s - base) + st * KV_BYTES + h * HALF_BYTES + (valid + rem / 8) * 128 + (rem % 8) * 16) =
+          const int r = valid + rem / 8;
+          *reinterpret_cast<uint4*>(gbase + (v_s - base) + g * KV_BYTES + (r / 8) * GROUP_BYTES + h * 1024 + (r % 8) * 128 + (rem % 8) * 16) =
               make_uint4(0, 0, 0, 0);
         }
       }
       fence_async_smem();
       fence_before_sync();
-      mbar_arrive(bar(B_PF));
+      mbar_arrive(bar(B_PF + g));
       TC_STAMP(j, 5)
     }
-    if (ok) ok = wait_all(B_OD, (uint32_t)(n_tiles - 1) & 1u);
-    float* sums = exchange + 512;
-    sums[half * 128 + row] = l;
+    // ---------------------------------------------------------------- merge of the two groups
+    // A group hands its maxima and sums over in its own key stage: the group has seen the scores of
+    // its last tile, so nothing reads or writes that stage any more.
+    float* mine = reinterpret_cast<float*>(gbase + (k_s - base) + g * KV_BYTES);
+    const float* other = reinterpret_cast<const float*>(gbase + (k_s - base) + (g ^ 1) * KV_BYTES);
+    mine[row] = m_used;
+    mine[128 + row] = l;
     pair_barrier(quarter);
+    const float m_other = other[row], l_other = other[128 + row];
+    const float m_all = fmaxf(m_used, m_other);                      // finite: group 0 saw key 0
+    const float w_mine = m_used == -INFINITY ? 0.f : exp2_fast(m_used - m_all);
+    const float w_other = m_other == -INFINITY ? 0.f : exp2_fast(m_other - m_all);
+    const float inv = 1.0f / (l * w_mine + l_other * w_other);
+    const float w0 = (g == 0 ? w_mine : w_other) * inv, w1 = (g == 0 ? w_other : w_mine) * inv;
+    // both groups' last products must have landed (group 1 has none when there is a single tile)
+    const int n0 = (n_tiles + 1) / 2, n1 = n_tiles / 2;
+    if (ok) ok = wait_all(B_OD + 0, (uint32_t)(n0 - 1) & 1u);
+    if (ok && n1 > 0) ok = wait_all(B_OD + 1, (uint32_t)(n1 - 1) & 1u);
     if (ok) {
       fence_after_sync();
-      const float inv = 1.0f / (l + sums[(half ^ 1) * 128 + row]);
-      __nv_bfloat16* dst = out + ((size_t)(row_base + row) * n_q + head) * D + half * OD;
+      // this thread writes columns g * D/2 .. of its row: the same columns of both groups' outputs
+      __nv_bfloat16* dst = out + ((size_t)(row_base + row) * n_q + head) * D + g * OD;
 #pragma unroll
       for (int c = 0; c < OD; c += 32) {
-        uint32_t o[32];
-        tmem_ld32(lane_addr + O_COL + half * OD + c, o);
+        uint32_t a[32], b[32];
+        tmem_ld32(lane_addr + O_COL + g * OD + c, a);
+        if (n1 > 0) tmem_ld32(lane_addr + O_COL + D + g * OD + c, b);
         tmem_ld_wait();
         if (row < nrows) {
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            uint4 w;
-            w.x = pack_bf16(__uint_as_float(o[8 * i]) * inv, __uint_as_float(o[8 * i + 1]) * inv);
-            w.y = pack_bf16(__uint_as_float(o[8 * i + 2]) * inv, __uint_as_float(o[8 * i + 3]) * inv);
-            w.z = pack_bf16(__uint_as_float(o[8 * i + 4]) * inv, __uint_as_float(o[8 * i + 5]) * inv);
-            w.w = pack_bf16(__uint_as_float(o[8 * i + 6]) * inv, __uint_as_float(o[8 * i + 7]) * inv);
-            *reinterpret_cast<uint4*>(dst + c + 8 * i) = w;
+            float v[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              v[e] = __uint_as_float(a[8 * i + e]) * w0;
+              if (n1 > 0) v[e] = fmaf(__uint_as_float(b[8 * i + e]), w1, v[e]);
+            }
+            *reinterpret_cast<uint4*>(dst + c + 8 * i) =
+                make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
           }
         }
       }
@@ -350,6 +461,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   fence_before_sync();
   __syncthreads();
   if (warp == MMA_WARP) tmem_dealloc(tmem_base, 512);
+#ifdef LSE_TRACE
+  if (tid == 0 && block_linear < 4096) { lse_attn_tc_blocks[block_linear * 4 + 1] = global_ns(); lse_attn_tc_blocks[block_linear * 4 + 3] = n_tiles; }
+#endif
 }
 
 template <int D>
@@ -365,11 +479,11 @@ int launch_prefill_tc(const void* q, const void* kc, const void* vc, void* out, 
   }
   CUtensorMap map_q, map_k, map_v;
   if (!make_map_3d(&map_q, q, tokens, n_q, D, BM) ||
-      !make_map_2d(&map_k, kc, num_pages * n_kv * page_size, D, page_size) ||
-      !make_map_2d(&map_v, vc, num_pages * n_kv * page_size, D, page_size))
+      !make_map_row_groups(&map_k, kc, num_pages * n_kv * page_size, D, page_size) ||
+      !make_map_row_groups(&map_v, vc, num_pages * n_kv * page_size, D, page_size))
     return LSE_ERR_BAD_ARGUMENT;
   const int tiles = (tokens + BM - 1) / BM + num_segments;   // upper bound
-  dim3 grid(tiles, n_q);
+  dim3 grid(tiles * n_q);
   cudaError_t err = lse_launch(attn_prefill_tc_kernel<D>, grid, THREADS, smem, stream, map_q, map_k, map_v,
                                (__nv_bfloat16*)out, block_tables, bt_stride, segment_start, segment_first_pos,
                                num_segments, n_q, n_kv, page_size, scale * LOG2E);
@@ -386,8 +500,14 @@ extern "C" int lse_attention_tc_supported(int head_dim, int n_q, int n_kv, int p
 }
 
 #ifdef LSE_TRACE
+extern "C" int lse_attention_tc_set_what_if(int bits) {
+  return (int)cudaMemcpyToSymbol(lse_attn_tc_what_if, &bits, sizeof(int));
+}
+extern "C" int lse_attention_tc_blocks(unsigned long long* host_out) {
+  return (int)cudaMemcpyFromSymbol(host_out, lse_attn_tc_blocks, sizeof(unsigned long long) * 4096 * 4);
+}
 extern "C" int lse_attention_tc_stamps(long long* host_out) {
-  return (int)cudaMemcpyFromSymbol(host_out, lse_attn_tc_stamps, sizeof(long long) * 128 * 8);
+  return (int)cudaMemcpyFromSymbol(host_out, lse_attn_tc_stamps, sizeof(long long) * 2 * 128 * 8);
 }
 #endif
 

@@ -54,6 +54,11 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
       ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
 }
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z, int w) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];\n"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z) {
   asm volatile(
       "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n"
@@ -69,23 +74,24 @@ __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.a
 // K-major operand: a row of the tile is a row (M or N index) of the operand and holds 64
 // consecutive k.  An instruction takes 16 k = 32 bytes of every row: the start address moves by 32
 // bytes per k-step inside the 128-byte row.
-__device__ __forceinline__ uint64_t smem_desc_k_major(uint32_t addr) {
+// `group_bytes`: distance between consecutive groups of 8 rows (1024 when the groups lie back to back).
+__device__ __forceinline__ uint64_t smem_desc_k_major(uint32_t addr, uint32_t group_bytes = 1024) {
   uint64_t d = 0;
   d |= (uint64_t)((addr & 0x3FFFFu) >> 4);   // start address, 16-byte units           bits [0,14)
   d |= (uint64_t)1 << 16;                    // leading byte offset (not used here)    bits [16,30)
-  d |= (uint64_t)(1024 >> 4) << 32;          // stride byte offset between row groups  bits [32,46)
+  d |= (uint64_t)(group_bytes >> 4) << 32;   // stride byte offset between row groups  bits [32,46)
   d |= (uint64_t)1 << 46;                    // descriptor version of sm_100           bits [46,48)
   d |= (uint64_t)2 << 61;                    // SWIZZLE_128B                           bits [61,64)
   return d;
 }
 // MN-major operand: a row of the tile is one k and holds 64 consecutive M (or N) indices.  Groups
-// of 8 k lie 1024 bytes apart (stride byte offset); the next 64 M/N indices lie `next_64_bytes`
-// further (leading byte offset).  An instruction takes 16 k = 16 rows = 2048 bytes.
-__device__ __forceinline__ uint64_t smem_desc_mn_major(uint32_t addr, uint32_t next_64_bytes) {
+// of 8 k lie `group_bytes` apart (stride byte offset); the next 64 M/N indices lie `next_64_bytes`
+// further (leading byte offset).  An instruction takes 16 k = two groups of rows.
+__device__ __forceinline__ uint64_t smem_desc_mn_major(uint32_t addr, uint32_t next_64_bytes, uint32_t group_bytes = 1024) {
   uint64_t d = 0;
   d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
   d |= (uint64_t)((next_64_bytes >> 4) & 0x3FFFu) << 16;
-  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)(group_bytes >> 4) << 32;
   d |= (uint64_t)1 << 46;
   d |= (uint64_t)2 << 61;
   return d;
@@ -187,6 +193,22 @@ inline bool make_map_3d(CUtensorMap* map, const void* ptr, long long outer, int 
   const cuuint32_t box[3] = {64u, 1u, (cuuint32_t)box_outer};
   const cuuint32_t elem[3] = {1, 1, 1};
   return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Tensor map of a row-major bfloat16 matrix [rows, cols] (rows a multiple of 8, cols 64 or 128) seen as
+// [rows / 8][cols / 64][8 rows][64 columns]; box = box_rows rows, all columns.  One copy leaves, for every
+// group of 8 rows, the 8 x 128-byte pieces of the first 64 columns and then those of the next 64:
+// 128-byte-swizzled groups of 8 rows lie cols / 64 * 1024 bytes apart, the column halves 1024 bytes apart.
+inline bool make_map_row_groups(CUtensorMap* map, const void* ptr, long long rows, int cols, int box_rows) {
+  EncodeTiledFn fn = encode_tiled();
+  if (fn == nullptr || rows % 8 || box_rows % 8 || (cols != 64 && cols != 128)) return false;
+  const cuuint64_t dims[4] = {64u, 8u, (cuuint64_t)(cols / 64), (cuuint64_t)(rows / 8)};
+  const cuuint64_t strides[3] = {(cuuint64_t)cols * 2, 128u, (cuuint64_t)cols * 2 * 8};
+  const cuuint32_t box[4] = {64u, 8u, (cuuint32_t)(cols / 64), (cuuint32_t)(box_rows / 8)};
+  const cuuint32_t elem[4] = {1, 1, 1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, elem,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }

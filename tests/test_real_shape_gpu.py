@@ -58,3 +58,36 @@ def test_benchmark_shapes_against_the_plain_implementation(folder, dtype):
         assert float(error.max()) <= limit, f"{name} ({dtype}): max error {float(error.max()):.3e} > {limit:.3e} at row {int(error.argmax())}"
     from llm_serving_engine_b200.kernels import ops
     assert ops.gemm_bf16_skinny_status() == 0
+
+
+def test_long_portions_take_the_tcgen05_attention(folder):
+    """Steps of 128 rows and more run the tcgen05 attention kernel: a prompt whole, the same prompt in
+    long portions (the second with earlier keys, starting off the tile grid), and two requests in one
+    step; all against the plain implementation, and no bounded wait may have given up."""
+    from llm_serving_engine_b200.engine.trace_replay import replay
+    from llm_serving_engine_b200.kernels import ops
+
+    rng = random.Random(8)
+    a = helpers.random_tokens(rng, CONFIG["vocab_size"], 420)
+    b = helpers.random_tokens(rng, CONFIG["vocab_size"], 180)
+    want_rows_a = [0, 127, 128, 300, 419]
+    steps = [
+        {"step": 0, "entries": [{"id": "whole", "tokens": a, "want": want_rows_a}], "end": ["whole"]},
+        {"step": 1, "entries": [{"id": "cut", "tokens": a[:150], "want": [0, 127, 128]}], "end": []},
+        {"step": 2, "entries": [{"id": "cut", "tokens": a[150:390], "want": [150]},
+                                {"id": "b", "tokens": b[:170], "want": [0, 169]}], "end": []},
+        {"step": 3, "entries": [{"id": "cut", "tokens": a[390:], "want": [29]},
+                                {"id": "b", "tokens": b[170:], "want": [9]}], "end": ["cut", "b"]},
+    ]
+    with tempfile.TemporaryDirectory(prefix="real_out_") as out:
+        replay(folder, "bfloat16", out, 1024, [json.dumps(step) for step in steps])
+        got = helpers.collect(steps, Path(out))
+    assert ops.attention_tc_status() == 0
+    cfg, weights = qwen2_plain.load_folder(folder)
+    want_a = qwen2_plain.forward_full(cfg, weights, a)
+    want_b = qwen2_plain.forward_full(cfg, weights, b)
+    for name, got_rows, want_rows in (("whole", got["whole"], want_a[want_rows_a]), ("cut", got["cut"], want_a[want_rows_a]),
+                                      ("b", got["b"], want_b[[0, 169, 179]])):
+        limit = helpers.tolerance("bfloat16", want_rows)
+        error = (got_rows - want_rows).abs().max(dim=1).values
+        assert float(error.max()) <= limit, f"{name}: max error {float(error.max()):.3e} > {limit:.3e} at row {int(error.argmax())}"
