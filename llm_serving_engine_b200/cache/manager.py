@@ -200,6 +200,34 @@ class CacheManager:
                 need[index] += pages
         return all(n <= group.pool.free_pages for n, group in zip(need, self.groups))
 
+    def grow(self, request_id: str, count: int) -> bool:
+        """Take the pages that the request's next ``count`` tokens need, without counting the tokens
+        in: a later ``reserve`` finds them there.  Pages taken early are the request's like any other
+        and go back with it.  False, and nothing changed, when a group has too few free pages or the
+        request would outgrow its table."""
+        request = self.requests[request_id]
+        after = (request.length + count + self.page_size - 1) // self.page_size
+        if after > self.max_pages_per_request:
+            return False
+        for group, table in zip(self.groups, request.tables):
+            if after - len(table) > group.pool.free_pages:
+                return False
+        self._extend(request, after)
+        return True
+
+    def _extend(self, request: RequestCache, after: int) -> None:
+        request_id = request.request_id
+        for index, (group, table) in enumerate(zip(self.groups, request.tables)):
+            while len(table) < after:
+                page = group.pool.allocate(request_id)
+                mirror = request.tables_np[index]
+                if len(table) >= mirror.shape[0]:
+                    grown = np.full(max(2 * mirror.shape[0], after), -1, dtype=np.int32)
+                    grown[:mirror.shape[0]] = mirror
+                    request.tables_np[index] = mirror = grown
+                mirror[len(table)] = page
+                table.append(page)
+
     def reserve(self, request_id: str, count: int) -> int:
         """Make room for the request's next ``count`` tokens and return the position of
         the first.  Either every page is had or nothing changes."""
@@ -212,16 +240,7 @@ class CacheManager:
         for group, table in zip(self.groups, request.tables):
             if after - len(table) > group.pool.free_pages:
                 raise CacheFullError("paged KV cache has no free blocks")
-        for index, (group, table) in enumerate(zip(self.groups, request.tables)):
-            while len(table) < after:
-                page = group.pool.allocate(request_id)
-                mirror = request.tables_np[index]
-                if len(table) >= mirror.shape[0]:
-                    grown = np.full(max(2 * mirror.shape[0], after), -1, dtype=np.int32)
-                    grown[:mirror.shape[0]] = mirror
-                    request.tables_np[index] = mirror = grown
-                mirror[len(table)] = page
-                table.append(page)
+        self._extend(request, after)
         first = request.length
         request.length += count
         used = sum(group.pool.used_pages for group in self.groups)

@@ -61,6 +61,8 @@ class LLMEngine:
         self._incoming: asyncio.Queue | None = None
         self._worker: asyncio.Task | None = None
         self._closed = False
+        self._ahead = None   # the next decode step, packed while the device ran the last one
+        self.pack_ahead = True
         self._pending_callbacks: list[tuple[RequestState, int]] = []
         self._just_finished: list[tuple[RequestState, Exception | None]] = []
         self._cpu_ms = {"prefill": 0.0, "decode": 0.0, "mixed": 0.0}
@@ -183,22 +185,31 @@ class LLMEngine:
 
     @torch.inference_mode()
     def _step(self) -> None:
-        phase = self._phase()
-        started = time.perf_counter()
         events = None
         if self.collect_iteration_metrics:
+            phase = self._phase()
+            started = time.perf_counter()
             events = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
             events[0].record()
-        planned = plan_iteration(list(self.scheduler.active), self.scheduler_config.max_tokens_per_step,
-                                 self.prefill_chunk_size)
-        def preempt(victim: RequestState) -> None:
-            self.cache.free(victim.request_id)
-            self.scheduler.preempt(victim)
+        ahead, self._ahead = self._ahead, None
+        active = self.scheduler.active
+        if (ahead is not None and len(ahead[1]) == len(active) and all(a is b for a, b in zip(ahead[1], active))
+                and all(r.total_tokens - r.processed_tokens == 1 for r in active)):
+            # the step that was packed ahead: the same requests, one token each; their pages are there
+            planned = [(request, 1) for request in active]
+            ahead = ahead[0]
+        else:
+            ahead = None
+            planned = plan_iteration(list(active), self.scheduler_config.max_tokens_per_step, self.prefill_chunk_size)
 
-        planned, _, failed = resolve_page_pressure(
-            planned, lambda plan: self.cache.fits([(r.request_id, n) for r, n in plan]), preempt)
-        if failed is not None:
-            self._finish(failed, CacheFullError("one sequence exceeds total KV cache capacity"))
+            def preempt(victim: RequestState) -> None:
+                self.cache.free(victim.request_id)
+                self.scheduler.preempt(victim)
+
+            planned, _, failed = resolve_page_pressure(
+                planned, lambda plan: self.cache.fits([(r.request_id, n) for r, n in plan]), preempt)
+            if failed is not None:
+                self._finish(failed, CacheFullError("one sequence exceeds total KV cache capacity"))
         if planned:
             entries, sampled = [], []
             for request, count in planned:
@@ -208,13 +219,23 @@ class LLMEngine:
                 entries.append(StepEntry(request.request_id, tokens, [count - 1] if done else []))
                 if done:
                     sampled.append(request)
-            logits = self.runner.run(entries)
+            logits = self.runner.run_ahead(ahead, entries) if ahead is not None else None
+            if logits is None:
+                logits = self.runner.run(entries)
             for request, count in planned:
                 request.processed_tokens += count
             if sampled:
                 configs = [self._configs[r.request_id] for r in sampled]
                 counters = [len(r.generated_token_ids) for r in sampled]
-                tokens = self.sampler.sample(logits, configs, counters)
+                self.sampler.launch(logits, configs, counters)
+                # While the device works: if the next step will be these same requests with one token
+                # each (nobody waits, nobody reaches its token limit), pack it now but for the tokens.
+                if (self.pack_ahead and len(sampled) == len(planned) and not self.scheduler.waiting
+                        and all(len(r.generated_token_ids) + 1 < r.max_new_tokens for r in sampled)):
+                    packed = self.runner.prepare_ahead([r.request_id for r, _ in planned])
+                    if packed is not None:
+                        self._ahead = (packed, [r for r, _ in planned])
+                tokens = self.sampler.collect()
                 for request, config, token in zip(sampled, configs, tokens):
                     request.generated_token_ids.append(token)
                     if request.callback:
@@ -252,6 +273,7 @@ class LLMEngine:
         for request in self.scheduler.active + self.scheduler.waiting:
             if error is not None and request.future is not None and not request.future.done():
                 request.future.set_exception(error)
+        self._ahead = None
         self.cache.free_all()
         self.scheduler.active.clear()
         self.scheduler.waiting.clear()

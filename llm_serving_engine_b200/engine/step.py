@@ -106,6 +106,13 @@ class _Graph:
         self.launches = 0        # launches of the engine's own kernels inside the graph
 
 
+class _Ahead:
+    """A decode step packed before its tokens were known: the graph it goes to, and what it assumed."""
+
+    def __init__(self, key, request_ids: list[str], firsts: list[int]) -> None:
+        self.key, self.request_ids, self.firsts = key, request_ids, firsts
+
+
 class StepRunner:
     """Packs a step, runs the model on it and keeps the cache manager in step."""
 
@@ -136,6 +143,7 @@ class StepRunner:
         self._arange = np.arange(max(self.GRAPH_BUCKETS), dtype=np.int32)
         self.steps_run = 0
         self.graph_replays = 0
+        self.ahead_steps = 0             # decode steps whose packing ran beside the step before
         self.graph_kernel_launches = 0
         self.last_h2d_bytes = 0
 
@@ -343,6 +351,95 @@ class StepRunner:
         if not rows:
             return slot.logits[:0]
         return slot.logits[torch.tensor(rows, device=self.device)]
+
+    # -- a decode step packed before its tokens are known ----------------------------
+    def prepare_ahead(self, request_ids: list[str]) -> "_Ahead | None":
+        """Pack, while the device still works on the step before, the decode step in which each of
+        these requests will bring one token that is not known yet: positions, cache slots and block
+        tables follow from the cache as it stands.  A request whose token opens a page takes that
+        page now (it keeps it whatever happens next); no token is counted in, so the result may simply
+        be dropped.  None when such a step cannot be packed ahead: no captured graph for it yet, or
+        no free page."""
+        count = len(request_ids)
+        if not self.use_graphs or count == 0 or count > self.max_segments:
+            return None
+        bucket = next((b for b in self.GRAPH_BUCKETS if b >= count), None)
+        if bucket is None:
+            return None
+        cache = self.cache
+        page_size = cache.page_size
+        firsts = []
+        for rid in request_ids:
+            request = cache.requests.get(rid)
+            if request is None:
+                return None
+            first = request.length
+            if any(first // page_size >= len(table) for table in request.tables) and not cache.grow(rid, 1):
+                return None          # the token opens a page and none is free: the ordinary path decides
+            firsts.append(first)
+        pages = max(1, max(first // page_size + 1 for first in firsts))
+        key = (bucket, self._graph_width(pages))
+        slot = self._graphs.get(key)
+        if slot is None or slot.graph is None:
+            return None
+        if self._copy_pending:
+            self._copied.synchronize()
+            self._copy_pending = False
+        host, lay = slot.host_np, slot.layout
+        for lo, hi in lay.tables:
+            host[lo:hi] = -1
+        slots_of = []
+        group_slots = [[] for _ in range(self._groups)]
+        for index, (rid, first) in enumerate(zip(request_ids, firsts)):
+            request = cache.requests[rid]
+            slots_of.append(request.state_slot)
+            for g in range(self._groups):
+                table = request.tables[g]
+                group_slots[g].append(table[first // page_size] * page_size + first % page_size)
+                base = lay.tables[g][0] + index * lay.table_width
+                host[base: base + len(table)] = request.tables_np[g][:len(table)]
+        pad = lay.tokens - count
+        rows = list(range(count))
+        host[lay.pos[0]:lay.pos[1]] = firsts + [0] * pad
+        host[lay.seg[0]:lay.seg[1]] = rows + [-1] * pad
+        host[lay.start[0]:lay.start[1]] = rows + [count] * (lay.segments + 1 - count)
+        host[lay.first[0]:lay.first[1]] = firsts + [0] * pad
+        host[lay.ctx[0]:lay.ctx[1]] = [first + 1 for first in firsts] + [0] * pad
+        host[lay.slot[0]:lay.slot[1]] = slots_of + [0] * pad
+        host[lay.want[0]:lay.want[1]] = self._arange[:lay.wanted]
+        for g in range(self._groups):
+            host[lay.maps[g][0]:lay.maps[g][1]] = group_slots[g] + [-1] * pad
+        return _Ahead(key, list(request_ids), firsts)
+
+    def run_ahead(self, ahead: "_Ahead", entries: list[StepEntry]) -> torch.Tensor | None:
+        """Run the step that :meth:`prepare_ahead` packed, now that the tokens are known.  None
+        (and nothing done) when the entries are not the ones it was packed for."""
+        cache = self.cache
+        if [entry.request_id for entry in entries] != ahead.request_ids:
+            return None
+        vocab = self.model.vocab_size
+        for entry, first in zip(entries, ahead.firsts):
+            request = cache.requests.get(entry.request_id)
+            if (request is None or request.length != first or len(entry.tokens) != 1 or entry.want != [0]
+                    or not 0 <= entry.tokens[0] < vocab):
+                return None
+        slot = self._graphs[ahead.key]
+        for entry, first in zip(entries, ahead.firsts):
+            if cache.reserve(entry.request_id, 1) != first:
+                raise RuntimeError("the cache moved under a step that was packed ahead")
+        lay = slot.layout
+        count = len(entries)
+        slot.host_np[lay.tok[0]:lay.tok[1]] = [entry.tokens[0] for entry in entries] + [0] * (lay.tokens - count)
+        slot.device.copy_(slot.host, non_blocking=True)
+        self.last_h2d_bytes = lay.size * 4
+        self._copied.record()
+        self._copy_pending = True
+        slot.graph.replay()
+        self.graph_replays += 1
+        self.ahead_steps += 1
+        self.graph_kernel_launches += slot.launches
+        self.finish(entries)
+        return slot.logits[:count]
 
     def _graph_width(self, pages_needed: int) -> int:
         """Block-table width of a captured step: the whole table of a request when that is at most

@@ -57,10 +57,17 @@ class Sampler:
         self._out = torch.empty(max_rows, dtype=torch.int32, device=self.device)
         self._host_out = torch.empty(max_rows, dtype=torch.int32, pin_memory=pinned)
         self._scratch = None
+        self._pending_rows = 0
 
     def sample(self, logits: torch.Tensor, configs: list[GenerationConfig], counters: list[int]) -> list[int]:
         """One token per row of ``logits`` (float32 [R, V]); ``counters[r]`` is the index of
         the token being generated for row r's request.  One device-to-host transfer."""
+        self.launch(logits, configs, counters)
+        return self.collect()
+
+    def launch(self, logits: torch.Tensor, configs: list[GenerationConfig], counters: list[int]) -> None:
+        """Start sampling and the copy of the tokens to the host; :meth:`collect` waits for them.
+        What the host does in between runs beside the device's work."""
         rows = logits.shape[0]
         if rows != len(configs) or rows != len(counters) or rows > self.max_rows:
             raise ValueError("batched sampling inputs must have matching rows")
@@ -80,5 +87,9 @@ class Sampler:
             ops.sample(logits, self._dev_f[0, :rows], self._dev_f[1, :rows], self._dev_i[0, :rows],
                        self._dev_i[1, :rows], self._scratch, out)
         self._host_out[:rows].copy_(out, non_blocking=True)
+        self._pending_rows = rows
+
+    def collect(self) -> list[int]:
+        """The tokens of the last :meth:`launch` (waits for the device)."""
         torch.cuda.current_stream().synchronize()
-        return self._host_out[:rows].tolist()
+        return self._host_out[:self._pending_rows].tolist()

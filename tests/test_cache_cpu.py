@@ -15,7 +15,9 @@ def make(requirements, pages=12, page=4, max_pos=64, slots=4):
                         max_pos, num_state_slots=slots)
 
 
-def check_invariants(cache: CacheManager) -> None:
+def check_invariants(cache: CacheManager, grown: dict | None = None) -> None:
+    """``grown``: per request, tokens whose pages were taken early (``grow``) and not yet reserved."""
+    grown = grown or {}
     for index, group in enumerate(cache.groups):
         held = [page for request in cache.requests.values() for page in request.tables[index] if page >= 0]
         assert len(held) == len(set(held)), "a page is held twice"
@@ -29,7 +31,7 @@ def check_invariants(cache: CacheManager) -> None:
                     assert group.pool.owner_of(page) == request.request_id
             assert cache.block_table_array(index, request.request_id).tolist() == request.tables[index]
             live = [p for p in request.tables[index] if p >= 0]
-            needed = -(-request.length // cache.page_size) - request.released[index]
+            needed = -(-(request.length + grown.get(request.request_id, 0)) // cache.page_size) - request.released[index]
             assert len(live) == needed
     slots = [request.state_slot for request in cache.requests.values()]
     assert len(slots) == len(set(slots)) and len(slots) + len(cache._free_slots) == cache.num_state_slots
@@ -153,6 +155,56 @@ def test_random_orders_of_requests_keep_the_books(seed):
     for rid in live:
         cache.free(rid)
     assert all(group.pool.free_pages == 10 for group in cache.groups) and len(cache._free_slots) == 5
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_pages_taken_early_are_found_by_the_next_reserve_or_go_back_with_the_request(seed):
+    """``grow`` takes the page of a request's next token before the token is counted in (a decode step
+    packed ahead): the next ``reserve`` must give that position in that page and take nothing more;
+    a request that ends instead gives the page back; nothing changes when no page is free."""
+    rng = random.Random(seed)
+    cache = make([PagedKV(2, 16), PagedKV(1, 32)], pages=9, page=4, max_pos=120, slots=4)
+    live: list[str] = []
+    grown: dict[str, int] = {}
+    counter = 0
+    for _ in range(500):
+        action = rng.random()
+        if action < 0.15 and len(live) < 4:
+            counter += 1
+            live.append(f"r{counter}")
+            cache.create(live[-1])
+            try:
+                cache.reserve(live[-1], rng.randrange(1, 9))
+            except CacheFullError:
+                pass
+        elif action < 0.5 and live:
+            rid = rng.choice(live)
+            before = [list(t) for t in cache.requests[rid].tables]
+            free_before = cache.free_pages()
+            if cache.grow(rid, 1):
+                grown[rid] = 1
+                assert all(len(t) * cache.page_size > cache.requests[rid].length for t in cache.requests[rid].tables)
+            else:
+                assert [list(t) for t in cache.requests[rid].tables] == before and cache.free_pages() == free_before
+        elif action < 0.85 and live:
+            rid = rng.choice(live)
+            request = cache.requests[rid]
+            free_before = cache.free_pages()
+            length, tables = request.length, [list(t) for t in request.tables]
+            try:
+                assert cache.reserve(rid, 1) == length
+                if grown.pop(rid, 0):     # the page was there already
+                    assert cache.free_pages() == free_before and [list(t) for t in request.tables] == tables
+            except CacheFullError:
+                assert not grown.get(rid) and request.length == length
+        elif live:
+            rid = live.pop(rng.randrange(len(live)))
+            grown.pop(rid, None)
+            cache.free(rid)
+        check_invariants(cache, grown)
+    for rid in live:
+        cache.free(rid)
+    assert all(group.pool.free_pages == 9 for group in cache.groups)
 
 
 def test_stats_report_usage():

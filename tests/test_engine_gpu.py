@@ -200,6 +200,33 @@ def test_warmup_captures_decode_graphs_and_leaves_the_cache_empty():
     assert cold.generate_many(prompts, GenerationConfig(max_new_tokens=12)) == warm       # graphs change nothing
 
 
+def test_decode_steps_packed_ahead_give_the_same_tokens():
+    """While the device runs a decode step the host packs the next one but for its tokens.  The tokens
+    must be those of an engine that packs every step after reading the last one: through page edges
+    (a new page is reserved by the ordinary path), requests that stop at different lengths, stop
+    tokens that nobody could foresee, and sampling with a temperature."""
+    from llm_serving_engine_b200 import GenerationConfig
+    prompts = prompts_for("D", (9, 30, 4, 17), seed=6)
+    configs = [GenerationConfig(max_new_tokens=40), GenerationConfig(max_new_tokens=23, temperature=0.7, seed=3),
+               GenerationConfig(max_new_tokens=40), GenerationConfig(max_new_tokens=31)]
+    plain = engine_for("D", dtype="bfloat16", batch=4, pages=128)
+    plain.pack_ahead = False
+    want = plain.generate_many(prompts, configs)
+    assert plain.runner.ahead_steps == 0
+    ahead = engine_for("D", dtype="bfloat16", batch=4, pages=128)
+    assert ahead.generate_many(prompts, configs) == want
+    assert ahead.runner.ahead_steps > 20
+    assert not ahead.cache.requests and ahead.cache.groups[0].pool.used_pages == 0
+    # a stop token that ends one request early: the step packed ahead for all four is dropped
+    stop = want[2][10]
+    configs[2] = GenerationConfig(max_new_tokens=40, stop_token_ids=(stop,))
+    again = engine_for("D", dtype="bfloat16", batch=4, pages=128)
+    got = again.generate_many(prompts, configs)
+    cut = want[2].index(stop) + 1
+    assert got == [want[0], want[1], want[2][:cut], want[3]]
+    assert again.runner.ahead_steps > 10 and not again.cache.requests
+
+
 def test_dependent_launch_off_gives_the_same_logits(tmp_path):
     """LSE_PDL=0 launches every kernel fully serialised; the logits must not change."""
     name = "D"
