@@ -526,7 +526,11 @@ __global__ void silu_mul_kernel(const TI* __restrict__ gate_up, int n_partials, 
   }
   float y[4];
 #pragma unroll
-  for (int e = 0; e < VEC; ++e) y[e] = (g[e] / (1.0f + expf(-g[e]))) * u[e];
+  for (int e = 0; e < VEC; ++e) {
+    // a bfloat16 result is rounded far more coarsely than the fast exponential and division err
+    if (sizeof(TO) == 2) y[e] = __fdividef(g[e], 1.0f + __expf(-g[e])) * u[e];
+    else y[e] = (g[e] / (1.0f + expf(-g[e]))) * u[e];
+  }
   TO* dst = out + (size_t)t * inter + i;
   if (VEC == 4) store4<TO>(dst, y);
   else dst[0] = from_f32<TO>(y[0]);

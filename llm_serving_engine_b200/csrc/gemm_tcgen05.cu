@@ -35,11 +35,18 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) { return smem_desc_
 // (row r -> lane (r % 16) + 32 * (r / 16)).
 // grid: (ceil(N / BLOCK_N), splits); block: 128 threads; dynamic shared memory:
 // stages * kboxes * (BLOCK_N * 128 B + m_pad * 128 B) + alignment slack + barriers.
-template <int BLOCK_N>
-__global__ void __launch_bounds__(128)
+//
+// GATED_IN: x is not read from memory but made on the way: x[m, k] = silu(gate) * up of the float32
+// partial sums gate_up[p][m][k] and gate_up[p][m][inter + k] (the output of the gate/up product,
+// K = inter).  Four more warps work the values out (as the SiLU kernel does), write them into the
+// stage in the swizzled layout that TMA would leave, and arrive on the stage's barrier beside the
+// TMA bytes of w; the same warps read the accumulator back at the end.  Block: 192 threads; at most 16 rows.
+template <int BLOCK_N, bool GATED_IN>
+__global__ void __launch_bounds__(GATED_IN ? 192 : 128)
 gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                         float* __restrict__ out, int M, int N, int k_tiles, int tiles_per_split, int m_pad,
-                        int stages, int kboxes, __nv_bfloat16* __restrict__ gated_out) {
+                        int stages, int kboxes, __nv_bfloat16* __restrict__ gated_out,
+                        const float* __restrict__ gate_up, int n_partials, long long partial_stride, int inter) {
   constexpr uint32_t A_BYTES = BLOCK_N * BLOCK_K * 2;
   constexpr int ROWS_PER_WARP = BLOCK_N / 4;   // valid accumulator rows in a warp's quarter of tensor memory
   extern __shared__ unsigned char smem_raw[];
@@ -65,7 +72,7 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
   pdl_launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
-      mbar_init(bars + 8u * s, 1);
+      mbar_init(bars + 8u * s, GATED_IN ? 5 : 1);   // the TMA bytes (and the four warps that make x)
       mbar_init(bars + 8u * (stages + s), 1);
     }
     mbar_init(accum_bar, 1);
@@ -89,16 +96,17 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
       // fetched at once, while the kernel before may still run.  The rows of x are its
       // output and are fetched after pdl_wait().
       const int early = n_tiles < stages ? n_tiles : stages;
+      const uint32_t tma_bytes = GATED_IN ? (uint32_t)kboxes * A_BYTES : stage_bytes;
       for (int it = 0; it < early; ++it) {
         const uint32_t full = bars + 8u * it;
-        mbar_expect_tx(full, stage_bytes);
+        mbar_expect_tx(full, tma_bytes);
         for (int b = 0; b < kboxes; ++b)
           tma_load_2d(base + (uint32_t)it * stage_bytes + (uint32_t)b * A_BYTES, &map_w, full,
                       ((tile_lo + it) * kboxes + b) * BLOCK_K, n0);
       }
       pdl_wait();
       LSE_TL_MARK(2)
-      for (int it = 0; it < early; ++it)
+      for (int it = 0; it < early && !GATED_IN; ++it)
         for (int b = 0; b < kboxes; ++b)
           tma_load_2d(base + (uint32_t)it * stage_bytes + b_base + (uint32_t)b * b_bytes, &map_x, bars + 8u * it,
                       ((tile_lo + it) * kboxes + b) * BLOCK_K, 0);
@@ -107,12 +115,12 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
         const uint32_t parity = (uint32_t)(it / stages) & 1u;
         if (!mbar_wait(bars + 8u * (stages + s), parity ^ 1u, abort_flag)) break;
         const uint32_t full = bars + 8u * s;
-        mbar_expect_tx(full, stage_bytes);
+        mbar_expect_tx(full, tma_bytes);
         const uint32_t a_dst = base + (uint32_t)s * stage_bytes;
         for (int b = 0; b < kboxes; ++b) {
           const int k = ((tile_lo + it) * kboxes + b) * BLOCK_K;
           tma_load_2d(a_dst + (uint32_t)b * A_BYTES, &map_w, full, k, n0);
-          tma_load_2d(a_dst + b_base + (uint32_t)b * b_bytes, &map_x, full, k, 0);
+          if (!GATED_IN) tma_load_2d(a_dst + b_base + (uint32_t)b * b_bytes, &map_x, full, k, 0);
         }
       }
     }
@@ -146,11 +154,94 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
     __syncwarp();
   }
 
+  if (GATED_IN && warp >= 2) {
+    // x of every stage: thread -> (row m, 8 consecutive k) = one 16-byte chunk of the row's 128 bytes
+    pdl_wait();   // the partial sums come from the kernel before
+    const int maker = (int)threadIdx.x - 64;
+    unsigned char* stage0 = smem_raw + (base - smem_u32(smem_raw));
+    // The partial sums of MAKE_AHEAD stages are fetched together (one round trip to the L2 instead of one
+    // per stage).  m_pad is 16 here (the launcher sees to it): 16 rows x 8 chunks = one chunk per thread.
+    constexpr int MAKE_AHEAD = 3;
+    bool ok = true;
+    {
+      const int m = maker >> 3, c = maker & 7;
+      const float* row = gate_up + (size_t)m * 2 * inter;
+      for (int it0 = 0; it0 < n_tiles && ok; it0 += MAKE_AHEAD) {
+        float g[MAKE_AHEAD][8], u[MAKE_AHEAD][8];
+#pragma unroll
+        for (int t = 0; t < MAKE_AHEAD; ++t)
+#pragma unroll
+          for (int e = 0; e < 8; ++e) g[t][e] = u[t][e] = 0.f;
+        for (int p0 = 0; p0 < n_partials; p0 += 2) {   // two partial sums of every stage in flight, added in index order
+          float4 v[MAKE_AHEAD][2][4];
+#pragma unroll
+          for (int t = 0; t < MAKE_AHEAD; ++t) {
+            const int k = (tile_lo + it0 + t) * BLOCK_K + c * 8;
+            const bool live = it0 + t < n_tiles && m < M && k < inter;   // inter is a multiple of 8: the chunk lies inside the row
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+              if (live && p0 + q < n_partials) {
+                const float* src = row + (size_t)(p0 + q) * partial_stride + k;
+                v[t][q][0] = *reinterpret_cast<const float4*>(src);
+                v[t][q][1] = *reinterpret_cast<const float4*>(src + 4);
+                v[t][q][2] = *reinterpret_cast<const float4*>(src + inter);
+                v[t][q][3] = *reinterpret_cast<const float4*>(src + inter + 4);
+              } else {
+                v[t][q][0] = v[t][q][1] = v[t][q][2] = v[t][q][3] = make_float4(0.f, 0.f, 0.f, 0.f);
+              }
+            }
+          }
+#pragma unroll
+          for (int t = 0; t < MAKE_AHEAD; ++t)
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+              if (p0 + q < n_partials) {
+                g[t][0] += v[t][q][0].x; g[t][1] += v[t][q][0].y; g[t][2] += v[t][q][0].z; g[t][3] += v[t][q][0].w;
+                g[t][4] += v[t][q][1].x; g[t][5] += v[t][q][1].y; g[t][6] += v[t][q][1].z; g[t][7] += v[t][q][1].w;
+                u[t][0] += v[t][q][2].x; u[t][1] += v[t][q][2].y; u[t][2] += v[t][q][2].z; u[t][3] += v[t][q][2].w;
+                u[t][4] += v[t][q][3].x; u[t][5] += v[t][q][3].y; u[t][6] += v[t][q][3].z; u[t][7] += v[t][q][3].w;
+              }
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < MAKE_AHEAD; ++t) {
+          const int it = it0 + t;
+          if (it >= n_tiles || !ok) break;
+          const int s = it % stages;
+          if (it >= stages) {   // one lane waits until the stage is free again and tells the others
+            int freed = 1;
+            if (lane == 0) freed = mbar_wait(bars + 8u * (stages + s), (((uint32_t)(it / stages)) & 1u) ^ 1u, abort_flag) ? 1 : 0;
+            ok = __shfl_sync(0xffffffffu, freed, 0) != 0;
+          }
+          if (!ok) break;
+          uint32_t w[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            // rounded to bfloat16 next: the fast exponential and division are far below that (the SiLU
+            // kernel takes the same ones when it writes bfloat16)
+            const float a = __fdividef(g[t][2 * e], 1.0f + __expf(-g[t][2 * e])) * u[t][2 * e];
+            const float b = __fdividef(g[t][2 * e + 1], 1.0f + __expf(-g[t][2 * e + 1])) * u[t][2 * e + 1];
+            const __nv_bfloat162 v2 = __floats2bfloat162_rn(a, b);
+            w[e] = *reinterpret_cast<const uint32_t*>(&v2);
+          }
+          unsigned char* x_tile = stage0 + (size_t)s * stage_bytes + b_base;
+          *reinterpret_cast<uint4*>(x_tile + m * 128 + ((c ^ (m & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bars + 8u * s);   // one arrival per warp
+        }
+      }
+    }
+  }
+
   // epilogue: warp w reads TMEM lanes 32w .. 32w+31 (rows n0 + 32w + lane of w), all m_pad columns
+  // (GATED_IN: the four extra warps do, each the quarter of tensor memory that its number gives)
+  const int quarter = warp & 3;
+  const bool reader = !GATED_IN || warp >= 2;
   pdl_wait();   // nothing is written, and no bounded wait starts, before the earlier kernels are done
-  const bool ready = mbar_wait(accum_bar, 0, abort_flag);
+  const bool ready = reader && mbar_wait(accum_bar, 0, abort_flag);
   asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-  if (ready && gated_out != nullptr) {
+  if (!GATED_IN && ready && gated_out != nullptr) {
     // SiLU gate in the epilogue (one split only): the 128 rows of this block are 64 gate rows, then the
     // 64 up rows of the same outputs.  Warps 2 and 3 hand their (up) values over through shared
     // memory; warps 0 and 1 write silu(gate) * up as bfloat16: gated_out[m][blockIdx.x * 64 + lane].
@@ -187,11 +278,11 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
       __syncthreads();
     }
   } else if (ready) {
-    const int n = n0 + warp * ROWS_PER_WARP + lane;
+    const int n = n0 + quarter * ROWS_PER_WARP + lane;
     float* dst = out + (size_t)blockIdx.y * M * N + n;
     for (int c0 = 0; c0 < m_pad; c0 += 8) {
       uint32_t r[8];
-      const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
       asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];\n"
                    : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
                    : "r"(taddr));
@@ -202,7 +293,7 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
           if (c0 + i < M) dst[(size_t)(c0 + i) * N] = __uint_as_float(r[i]);
       }
     }
-  } else if (threadIdx.x == 0) {
+  } else if (threadIdx.x == 0 && *abort_flag) {
     // a wait gave up: give copies that may still be in flight time to land before the block leaves
     for (int i = 0; i < 2000; ++i) __nanosleep(100);
   }
@@ -245,12 +336,17 @@ extern "C" int lse_gemm_bf16_skinny_status(void) {
 // out[split][m][n] (float32, splits * M * N values) = partial sums of x[M, K] * w[N, K]^T.
 // x, w bfloat16 row-major, 16-byte aligned, K a multiple of 8, M <= 256.
 namespace {
-template <int BLOCK_N>
+// GATED_IN: x is null; gate_up[n_partials][M][2 K] float32 (partials `partial_stride` floats apart) gives it.
+template <int BLOCK_N, bool GATED_IN = false>
 int launch_skinny(const void* x, const void* w, float* out, int M, int N, int K, int splits, int stages, int kboxes,
-                  void* gated_out, cudaStream_t stream) {
+                  void* gated_out, cudaStream_t stream, const float* gate_up = nullptr, int n_partials = 0,
+                  long long partial_stride = 0) {
   if (M <= 0 || N <= 0) return 0;
   const int m_pad = lse_gemm_bf16_skinny_pad(M);
   if (m_pad == 0 || K <= 0 || K % 8 || (((uintptr_t)x | (uintptr_t)w) & 15)) return LSE_ERR_BAD_ARGUMENT;
+  if (GATED_IN && (gate_up == nullptr || n_partials < 1 || kboxes != 1 || gated_out != nullptr || m_pad != 16 ||
+                   partial_stride % 4 || ((uintptr_t)gate_up & 15)))
+    return LSE_ERR_BAD_ARGUMENT;
   if (kboxes != 1 && kboxes != 2 && kboxes != 4) return LSE_ERR_BAD_ARGUMENT;
   if (gated_out != nullptr) {
     if (N % BLOCK_N) return LSE_ERR_BAD_ARGUMENT;
@@ -267,16 +363,19 @@ int launch_skinny(const void* x, const void* w, float* out, int M, int N, int K,
   if (stages > per + 1) stages = per + 1 < 2 ? 2 : per + 1;
   const size_t smem = (size_t)stages * stage_bytes + 1024 + 16 * (size_t)stages + 64;
   CUtensorMap map_w, map_x;
-  if (!make_map(&map_w, w, N, K, BLOCK_N) || !make_map(&map_x, x, M, K, m_pad)) return LSE_ERR_BAD_ARGUMENT;
+  if (!make_map(&map_w, w, N, K, BLOCK_N)) return LSE_ERR_BAD_ARGUMENT;
+  if (GATED_IN) map_x = map_w;   // not used
+  else if (!make_map(&map_x, x, M, K, m_pad)) return LSE_ERR_BAD_ARGUMENT;
   static size_t configured = 0;   // largest dynamic shared memory asked for so far
   if (smem > configured) {
-    cudaError_t err = cudaFuncSetAttribute(gemm_bf16_skinny_kernel<BLOCK_N>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t err = cudaFuncSetAttribute(gemm_bf16_skinny_kernel<BLOCK_N, GATED_IN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (err != cudaSuccess) return (int)err;
     configured = smem;
   }
   dim3 grid((N + BLOCK_N - 1) / BLOCK_N, splits);
-  cudaError_t err = lse_launch(gemm_bf16_skinny_kernel<BLOCK_N>, grid, 128, smem, stream, map_w, map_x, out, M, N,
-                               k_tiles, per, m_pad, stages, kboxes, (__nv_bfloat16*)gated_out);
+  cudaError_t err = lse_launch(gemm_bf16_skinny_kernel<BLOCK_N, GATED_IN>, grid, GATED_IN ? 192 : 128, smem, stream,
+                               map_w, map_x, out, M, N, k_tiles, per, m_pad, stages, kboxes,
+                               (__nv_bfloat16*)gated_out, gate_up, n_partials, partial_stride, K);
   if (err != cudaSuccess) return (int)err;
   return (int)cudaGetLastError();
 }
@@ -291,4 +390,15 @@ extern "C" int lse_gemm_bf16_skinny(const void* x, const void* w, float* out, in
   if (block_n == 64) return launch_skinny<64>(x, w, out, M, N, K, splits, stages, kboxes, gated_out, stream);
   if (block_n == 128) return launch_skinny<128>(x, w, out, M, N, K, splits, stages, kboxes, gated_out, stream);
   return LSE_ERR_BAD_ARGUMENT;
+}
+
+// out[split][m][n] = partial sums of x[M, K] * w[N, K]^T where x[m, k] = silu(g) * u (rounded to bfloat16),
+// g = sum over p of gate_up[p][m][k], u = sum over p of gate_up[p][m][K + k]: the SiLU gate of the
+// feed-forward made inside the product that consumes it.  gate_up: float32, n_partials stacks of [M, 2 K],
+// `partial_stride` floats apart, 16-byte aligned; K a multiple of 8; M <= 16 (one chunk of x per thread and stage).
+extern "C" int lse_gemm_bf16_skinny_gated_in(const float* gate_up, int n_partials, long long partial_stride,
+                                             const void* w, float* out, int M, int N, int K, int splits, int stages,
+                                             cudaStream_t stream) {
+  return launch_skinny<128, true>(nullptr, w, out, M, N, K, splits, stages, 1, nullptr, stream, gate_up, n_partials,
+                                  partial_stride);
 }

@@ -361,6 +361,42 @@ def gemm_bf16_skinny_gated(x: torch.Tensor, weight: torch.Tensor, interleave: in
     return out
 
 
+GATED_IN_MAX_ROWS = 16      # one 16-byte chunk of the activations per thread and stage
+
+
+def gemm_bf16_skinny_gated_in_ok(gate_up: torch.Tensor, weight: torch.Tensor) -> bool:
+    """Whether ``gemm_bf16_skinny_gated_in`` takes these operands."""
+    return (gate_up.dim() == 3 and gate_up.dtype == torch.float32 and weight.dtype == torch.bfloat16
+            and gate_up.shape[1] <= GATED_IN_MAX_ROWS and gate_up.shape[2] == 2 * weight.shape[1]
+            and weight.shape[1] % 8 == 0 and gate_up.is_contiguous() and weight.is_contiguous()
+            and gate_up.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
+
+
+def gemm_bf16_skinny_gated_in(gate_up: torch.Tensor, weight: torch.Tensor, splits: int | None = None,
+                              stages: int = 6, max_splits: int | None = None) -> torch.Tensor:
+    """Partial sums [P, M, N] (float32) of act @ weight[N, I]^T where act = silu(gate) * up, rounded to
+    bfloat16, is made inside the kernel from ``gate_up``: a float32 stack of partial sums [Q, M, 2I] whose
+    rows are [gate (I) | up (I)].  The result equals ``silu_mul`` followed by ``gemm_bf16_skinny`` bit for
+    bit (the same values meet the tensor cores in the same order); one kernel and one round trip through
+    memory less."""
+    _need_cuda(gate_up, weight)
+    if not gemm_bf16_skinny_gated_in_ok(gate_up, weight):
+        raise KernelError("gemm_bf16_skinny_gated_in: float32 partial sums [Q, M, 2I], contiguous bfloat16 weight "
+                          "[N, I], I a multiple of 8, at most 16 rows")
+    parts, m, two_i = gate_up.shape
+    k = two_i // 2
+    n = weight.shape[0]
+    lib = library.load()
+    if splits is None:
+        n_tiles = -(-n // 128)
+        splits = max(1, min(-(-k // 128), _GEMM_TARGET_BLOCKS // n_tiles, max(1, k // (4 * m)), max_splits or _GEMM_MAX_SPLITS)) if n_tiles < 148 else 1
+    splits = lib.lse_gemm_bf16_skinny_splits(k, int(splits), 1)
+    out = torch.empty((splits, m, n), dtype=torch.float32, device=weight.device)
+    check(lib.lse_gemm_bf16_skinny_gated_in(gate_up.data_ptr(), parts, m * two_i, weight.data_ptr(), out.data_ptr(),
+                                            m, n, k, splits, int(stages), _stream()), "gemm_bf16_skinny_gated_in")
+    return out
+
+
 def gemm_bf16_skinny_status() -> int:
     """0 unless a bounded wait inside the kernel has given up (synchronises the device)."""
     return int(library.load().lse_gemm_bf16_skinny_status())

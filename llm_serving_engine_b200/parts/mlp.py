@@ -14,6 +14,12 @@ from .linear import SKINNY_MAX_ROWS, linear_partials
 # Qwen2.5-1.5B shape at batch 8, the separate kernel behind a two-split product is faster (more blocks
 # fetch weights ahead), so the fused form is off unless the part's ``fuse_gate`` parameter asks for it.
 FUSE_GATE = 0
+# With at most 16 rows the gate can also be worked out inside the down product, from the partial sums of
+# the gate/up product (no SiLU kernel, no activations in memory).  Measured on the same shape it is
+# slower as well (1.56 against 1.48 ms a step): making the activations sits on the product's critical
+# path, while the separate SiLU kernel runs beside the product's first weight loads.  Off unless
+# LSE_FUSE_GATE_INTO_DOWN=1.
+FUSE_GATE_INTO_DOWN = __import__("os").environ.get("LSE_FUSE_GATE_INTO_DOWN", "0") == "1"
 
 
 @register_feed_forward("swiglu")
@@ -49,6 +55,10 @@ class SwiGLU(FeedForward):
             act = ops.gemm_bf16_skinny_gated(x, self.gate_up_weight, self.interleave)   # product and gate in one kernel
         else:
             gate_up = linear_partials(x, self.gate_up_weight)
+            if (FUSE_GATE_INTO_DOWN and not self.interleave
+                    and ops.gemm_bf16_skinny_gated_in_ok(gate_up, self.down_weight)):
+                # few rows: the gate is worked out inside the down product, from the partial sums
+                return ops.gemm_bf16_skinny_gated_in(gate_up, self.down_weight)
             act = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
             ops.silu_mul(gate_up, act, self.interleave)
         return linear_partials(act, self.down_weight)

@@ -617,6 +617,27 @@ def test_few_rows_product_on_tensor_cores(m, n, k, splits, block_n):
     assert ops().gemm_bf16_skinny_status() == 0
 
 
+@pytest.mark.parametrize("m, inter, n, parts, splits", [(8, 8960, 1536, 2, None), (8, 8960, 1536, 2, 2), (3, 4096, 200, 1, 1),
+                                                       (1, 64, 128, 1, 1), (5, 1000, 130, 3, 4),
+                                                       (16, 256, 384, 1, 2), (11, 520, 96, 2, 3), (16, 2048, 257, 5, 2)])
+def test_product_that_makes_the_gated_activations_itself(m, inter, n, parts, splits):
+    """The down product fed with the partial sums of the gate/up product gives, bit for bit, what the SiLU
+    kernel followed by the plain product gives; and both agree with float64."""
+    torch.manual_seed(m + inter)
+    gate_up = torch.randn(parts, m, 2 * inter, device=DEV)
+    w = (torch.randn(n, inter, device=DEV) * 0.05).bfloat16()
+    fused = ops().gemm_bf16_skinny_gated_in(gate_up, w, splits)
+    act = torch.empty(m, inter, device=DEV, dtype=torch.bfloat16)
+    ops().silu_mul(gate_up, act)
+    plain = ops().gemm_bf16_skinny(act, w, fused.shape[0])
+    assert fused.shape == plain.shape and torch.equal(fused, plain)
+    g, u = gate_up.double().sum(0).split(inter, dim=1)
+    want = (torch.nn.functional.silu(g) * u) @ w.double().t()
+    bound = ((torch.nn.functional.silu(g) * u).abs() @ w.abs().double().t()) * 2.0 ** -8 + 1e-6   # activations rounded to bfloat16
+    assert bool(((fused.double().sum(0) - want).abs() <= bound).all())
+    assert ops().gemm_bf16_skinny_status() == 0
+
+
 def test_few_rows_product_refuses_what_it_cannot_run():
     from llm_serving_engine_b200.kernels.library import KernelError
     x = torch.randn(4, 100, device=DEV).bfloat16()      # k not a multiple of 8
