@@ -177,13 +177,79 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __res
   }
 }
 
+// Many rows (portions of prompts), one set of sums, bfloat16 out: a warp owns a row and keeps it in
+// registers (C float4 chunks per lane), so that no block-wide barrier stands between the loads and
+// the stores and eight rows are in flight per block.  hidden % 4 == 0, hidden <= 128 * C.
+template <typename TD, int C>
+__global__ void __launch_bounds__(256)
+add_rmsnorm_rows_kernel(float* __restrict__ residual, const TD* __restrict__ delta, const float* __restrict__ weight,
+                        __nv_bfloat16* __restrict__ out, int n_rows, int hidden, float eps) {
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31;
+  const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int chunks = hidden >> 2;
+  float w[C][4];
+#pragma unroll
+  for (int c = 0; c < C; ++c) {
+    const int i = c * 32 + lane;
+    if (i < chunks) load4<float>(weight + 4 * i, w[c]);
+  }
+  pdl_wait();
+  if (r >= n_rows) return;
+  float* res = residual + (size_t)r * hidden;
+  const TD* del = delta + (size_t)r * hidden;
+  float x[C][4], d[C][4];
+#pragma unroll
+  for (int c = 0; c < C; ++c) {
+    const int i = c * 32 + lane;
+    if (i < chunks) {
+      load4<float>(res + 4 * i, x[c]);
+      load4<TD>(del + 4 * i, d[c]);
+    }
+  }
+  float sq = 0.f;
+#pragma unroll
+  for (int c = 0; c < C; ++c) {
+    const int i = c * 32 + lane;
+    if (i < chunks) {
+      x[c][0] += d[c][0]; x[c][1] += d[c][1]; x[c][2] += d[c][2]; x[c][3] += d[c][3];
+      store4<float>(res + 4 * i, x[c]);
+      sq = fmaf(x[c][0], x[c][0], sq); sq = fmaf(x[c][1], x[c][1], sq);
+      sq = fmaf(x[c][2], x[c][2], sq); sq = fmaf(x[c][3], x[c][3], sq);
+    }
+  }
+  const float inv = 1.0f / sqrtf(warp_sum(sq) / (float)hidden + eps);
+  __nv_bfloat16* dst = out + (size_t)r * hidden;
+#pragma unroll
+  for (int c = 0; c < C; ++c) {
+    const int i = c * 32 + lane;
+    if (i < chunks) {
+      float y[4];
+      y[0] = (x[c][0] * inv) * w[c][0]; y[1] = (x[c][1] * inv) * w[c][1];
+      y[2] = (x[c][2] * inv) * w[c][2]; y[3] = (x[c][3] * inv) * w[c][3];
+      store4<__nv_bfloat16>(dst + 4 * i, y);
+    }
+  }
+}
+
 template <typename TD, typename TO>
 static void launch_add_rmsnorm(float* residual, const void* delta, int n_partials, long long partial_stride,
                                const float* weight, void* out, const int* rows, int n_rows, int hidden, float eps,
                                int write_residual, cudaStream_t stream) {
   const bool aligned = (((uintptr_t)residual | (uintptr_t)delta | (uintptr_t)weight | (uintptr_t)out) & 15) == 0 &&
                        (partial_stride % 4) == 0;
-  if (hidden % 4 == 0 && hidden <= NORM_THREADS * NORM_CHUNKS * 4 && aligned) {
+  if (sizeof(TO) == 2 && n_rows >= 256 && n_partials == 1 && delta != nullptr && rows == nullptr && write_residual &&
+      hidden % 4 == 0 && hidden <= 2048 && aligned) {
+    const unsigned blocks = (unsigned)((n_rows + 7) / 8);
+#define LSE_NORM_ROWS(C)                                                                                        \
+  lse_launch(add_rmsnorm_rows_kernel<TD, C>, blocks, 256, 0, stream, residual, (const TD*)delta, weight,        \
+             (__nv_bfloat16*)out, n_rows, hidden, eps)
+    if (hidden <= 512) LSE_NORM_ROWS(4);
+    else if (hidden <= 1024) LSE_NORM_ROWS(8);
+    else if (hidden <= 1536) LSE_NORM_ROWS(12);
+    else LSE_NORM_ROWS(16);
+#undef LSE_NORM_ROWS
+  } else if (hidden % 4 == 0 && hidden <= NORM_THREADS * NORM_CHUNKS * 4 && aligned) {
     // few rows (decoding): one float4 chunk per thread, the shortest chain; many rows (prompts): up to
     // four chunks per thread, so that more rows are in flight on an SM
     const int per_thread = n_rows >= 256 ? NORM_CHUNKS : 1;

@@ -35,6 +35,25 @@ def test_embedding(dtype):
     assert torch.equal(out, table[ids.long()].float())
 
 
+@pytest.mark.parametrize("rows, hidden", [(256, 80), (300, 1536), (1000, 2048), (257, 516), (513, 1028), (256, 2052)])
+@pytest.mark.parametrize("delta_dtype", [torch.float32, torch.bfloat16])
+def test_add_rmsnorm_of_many_rows(rows, hidden, delta_dtype):
+    """Portions of prompts (256 rows and more, bfloat16 out) take the kernel that gives a warp a row;
+    widths at and beyond its limit of 2,048 included."""
+    torch.manual_seed(rows + hidden)
+    residual = torch.randn(rows, hidden, device=DEV) * 3
+    residual[5] *= 100       # rows of very different size: every row has its own scale
+    delta = torch.randn(rows, hidden, device=DEV).to(delta_dtype)
+    weight = 1 + 0.1 * torch.randn(hidden, device=DEV)
+    want_residual = residual.double() + delta.double()
+    want = qwen2_plain.rms_norm(want_residual, weight.double(), 1e-6)
+    out = torch.empty(rows, hidden, device=DEV, dtype=torch.bfloat16)
+    got_residual = residual.clone()
+    ops().add_rmsnorm(got_residual, delta, weight, 1e-6, out)
+    assert rel_err(got_residual, want_residual) < 1e-6
+    assert float(((out.double() - want).abs() / (want.abs() + 1e-3)).max()) < 2.0 ** -7
+
+
 @pytest.mark.parametrize("hidden", [80, 1536, 3000])
 @pytest.mark.parametrize("delta_dtype, out_dtype", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16)])
 def test_add_rmsnorm(hidden, delta_dtype, out_dtype):
