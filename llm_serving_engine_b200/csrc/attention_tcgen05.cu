@@ -348,11 +348,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
         const float neg = m_used == -INFINITY ? 0.f : -m_used;   // every score is -inf then as well: p = 0
         float mx = -INFINITY, sum = 0.f;
-#pragma unroll
-        for (int c = 0; c < BN; c += 32) {   // 32 keys = 4 chunks of 16 bytes at a time
-          uint32_t s[32];
-          tmem_ld32(s_addr + c, s);
-          tmem_ld_wait();
+        // 32 keys = 4 chunks of 16 bytes at a time; the next 32 scores are on their way from tensor memory
+        // while these are worked on
+        auto take = [&](uint32_t (&s)[32], int c) {
           if (diagonal) {
 #pragma unroll
             for (int i = 0; i < 32; ++i)
@@ -377,6 +375,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             const int chunk = (c % 64) / 8 + k;
             *reinterpret_cast<uint4*>(box + ((chunk ^ (row & 7)) << 4)) = make_uint4(pk[4 * k], pk[4 * k + 1], pk[4 * k + 2], pk[4 * k + 3]);
           }
+        };
+        uint32_t sa[32], sb[32];
+        tmem_ld32(s_addr, sa);
+#pragma unroll
+        for (int c = 0; c < BN; c += 64) {
+          tmem_ld_wait();
+          tmem_ld32(s_addr + c + 32, sb);
+          take(sa, c);
+          tmem_ld_wait();
+          if (c + 64 < BN) tmem_ld32(s_addr + c + 64, sa);
+          take(sb, c + 32);
         }
         const float m_tile = mx * scale_log2e;
         if (first || !__any_sync(0xffffffffu, m_tile > m_used + REDO_STEP)) {
