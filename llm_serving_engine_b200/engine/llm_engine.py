@@ -63,6 +63,8 @@ class LLMEngine:
         self._closed = False
         self._ahead = None   # the next decode step, packed while the device ran the last one
         self.pack_ahead = True
+        self.launch_ahead = True
+        self._flying = None  # (requests, configs, sampling ticket) of a decode step that is queued on the device
         self._pending_callbacks: list[tuple[RequestState, int]] = []
         self._just_finished: list[tuple[RequestState, Exception | None]] = []
         self._cpu_ms = {"prefill": 0.0, "decode": 0.0, "mixed": 0.0}
@@ -142,6 +144,7 @@ class LLMEngine:
         except Exception:
             self._fail_all(None)
             raise
+        self._drop_flying()   # a step queued for requests that have all ended meanwhile
         for state in states:
             if state.request_id in errors:
                 raise errors[state.request_id]
@@ -183,8 +186,61 @@ class LLMEngine:
         decode = any(r.processed_tokens >= len(r.prompt_token_ids) for r in active)
         return "mixed" if prefill and decode else "prefill" if prefill else "decode"
 
+    # -- a decode step in flight ---------------------------------------------------------
+    # In a run of decode steps over the same requests the engine keeps one step queued on the device
+    # ahead of the host: the step is launched before the tokens of the step before have reached the
+    # host (it takes them on the device), so packing, planning and book-keeping run beside the
+    # device's work.  A request that ends by a stop token is found out one step late: its row of the
+    # step in flight is dropped (its pages are freed with it).  Requests that will reach their token
+    # limit, waiting requests, a new page that cannot be had or iteration metrics end the run: the
+    # step in flight is collected and the ordinary path goes on.
+    def _may_fly(self, requests: list[RequestState]) -> bool:
+        return (self.pack_ahead and self.launch_ahead and not self.collect_iteration_metrics
+                and not self.scheduler.waiting
+                and all(len(r.generated_token_ids) + 2 <= r.max_new_tokens for r in requests))
+
+    def _launch_flying(self, requests: list[RequestState], ticket: int):
+        """Queue the next decode step of ``requests`` behind the sampling launch ``ticket`` whose tokens
+        it consumes.  Returns (requests, configs, ticket of its own sampling) or None."""
+        packed = self.runner.prepare_ahead([r.request_id for r in requests])
+        if packed is None:
+            return None
+        logits = self.runner.launch_ahead(packed, self.sampler.device_tokens(ticket))
+        if logits is None:
+            return None
+        configs = [self._configs[r.request_id] for r in requests]
+        counters = [len(r.generated_token_ids) + 1 for r in requests]   # the token before is still on its way
+        return requests, configs, self.sampler.launch(logits, configs, counters)
+
+    def _take_tokens(self, requests, configs, tokens, fed: bool) -> None:
+        """Book the sampled tokens; ``fed``: the step consumed one token of every request on the device."""
+        for request, config, token in zip(requests, configs, tokens):
+            if request not in self.scheduler.active:
+                continue          # ended a step ago (a stop token): this row was computed for nothing
+            if fed:
+                request.processed_tokens += 1
+            request.generated_token_ids.append(token)
+            if request.callback:
+                self._pending_callbacks.append((request, token))
+            if len(request.generated_token_ids) >= request.max_new_tokens or token in config.stop_token_ids:
+                self._finish(request)
+
+    def _drop_flying(self) -> None:
+        flying, self._flying = self._flying, None
+        if flying is not None:
+            self.sampler.collect(flying[2])   # its buffers are free again; the tokens are not wanted
+
     @torch.inference_mode()
     def _step(self) -> None:
+        flying, self._flying = self._flying, None
+        if flying is not None:
+            requests, configs, ticket = flying
+            active = self.scheduler.active
+            same = len(requests) == len(active) and all(a is b for a, b in zip(requests, active))
+            following = self._launch_flying(requests, ticket) if same and self._may_fly(requests) else None
+            self._take_tokens(requests, configs, self.sampler.collect(ticket), fed=True)
+            self._flying = following
+            return
         events = None
         if self.collect_iteration_metrics:
             phase = self._phase()
@@ -227,21 +283,21 @@ class LLMEngine:
             if sampled:
                 configs = [self._configs[r.request_id] for r in sampled]
                 counters = [len(r.generated_token_ids) for r in sampled]
-                self.sampler.launch(logits, configs, counters)
+                ticket = self.sampler.launch(logits, configs, counters)
                 # While the device works: if the next step will be these same requests with one token
-                # each (nobody waits, nobody reaches its token limit), pack it now but for the tokens.
+                # each (nobody waits, nobody reaches its token limit), launch it now on the tokens that
+                # are still on the device, or at least pack it but for the tokens.
+                following = None
                 if (self.pack_ahead and len(sampled) == len(planned) and not self.scheduler.waiting
                         and all(len(r.generated_token_ids) + 1 < r.max_new_tokens for r in sampled)):
-                    packed = self.runner.prepare_ahead([r.request_id for r, _ in planned])
-                    if packed is not None:
-                        self._ahead = (packed, [r for r, _ in planned])
-                tokens = self.sampler.collect()
-                for request, config, token in zip(sampled, configs, tokens):
-                    request.generated_token_ids.append(token)
-                    if request.callback:
-                        self._pending_callbacks.append((request, token))
-                    if len(request.generated_token_ids) >= request.max_new_tokens or token in config.stop_token_ids:
-                        self._finish(request)
+                    if len(sampled) == len(self.scheduler.active) and self._may_fly(sampled):
+                        following = self._launch_flying(sampled, ticket)
+                    if following is None:
+                        packed = self.runner.prepare_ahead([r.request_id for r, _ in planned])
+                        if packed is not None:
+                            self._ahead = (packed, [r for r, _ in planned])
+                self._take_tokens(sampled, configs, self.sampler.collect(ticket), fed=False)
+                self._flying = following
         if self.collect_iteration_metrics:
             events[1].record()
             self._events[phase].append(events)
@@ -274,6 +330,7 @@ class LLMEngine:
             if error is not None and request.future is not None and not request.future.done():
                 request.future.set_exception(error)
         self._ahead = None
+        self._drop_flying()
         self.cache.free_all()
         self.scheduler.active.clear()
         self.scheduler.waiting.clear()

@@ -20,6 +20,7 @@ whose mixers all say ``graph_safe`` are captured; others run launch by launch.
 """
 from __future__ import annotations
 
+import gc
 from dataclasses import dataclass, field
 
 import numpy as np
@@ -144,6 +145,7 @@ class StepRunner:
         self.steps_run = 0
         self.graph_replays = 0
         self.ahead_steps = 0             # decode steps whose packing ran beside the step before
+        self.flying_steps = 0            # of these, steps queued before the tokens of the step before reached the host
         self.graph_kernel_launches = 0
         self.last_h2d_bytes = 0
 
@@ -441,6 +443,39 @@ class StepRunner:
         self.finish(entries)
         return slot.logits[:count]
 
+    def launch_ahead(self, ahead: "_Ahead", device_tokens: torch.Tensor) -> torch.Tensor | None:
+        """Queue the step that :meth:`prepare_ahead` packed behind the work already on the stream, with
+        its token ids taken on the device (int32, one per request: the tokens that the step before is
+        still sampling).  The host does not wait for them.  None (and nothing done) when the cache no
+        longer is what the step was packed for."""
+        cache = self.cache
+        count = len(ahead.request_ids)
+        if device_tokens.dtype != torch.int32 or device_tokens.shape[0] != count:
+            return None
+        for rid, first in zip(ahead.request_ids, ahead.firsts):
+            request = cache.requests.get(rid)
+            if request is None or request.length != first:
+                return None
+        slot = self._graphs[ahead.key]
+        for rid, first in zip(ahead.request_ids, ahead.firsts):
+            if cache.reserve(rid, 1) != first:
+                raise RuntimeError("the cache moved under a step that was packed ahead")
+        lay = slot.layout
+        slot.device[lay.tok[0]:lay.tok[0] + count].copy_(device_tokens, non_blocking=True)
+        slot.device[lay.tok[1]:lay.size].copy_(slot.host[lay.tok[1]:lay.size], non_blocking=True)   # all but the token ids
+        self.last_h2d_bytes = (lay.size - lay.tok[1]) * 4
+        self._copied.record()
+        self._copy_pending = True
+        slot.graph.replay()
+        self.graph_replays += 1
+        self.ahead_steps += 1
+        self.flying_steps += 1
+        self.graph_kernel_launches += slot.launches
+        for rid in ahead.request_ids:
+            cache.release_passed(rid)
+        self.steps_run += 1
+        return slot.logits[:count]
+
     def _graph_width(self, pages_needed: int) -> int:
         """Block-table width of a captured step: the whole table of a request when that is at most
         2,048 entries (one graph per batch bucket), else the next power of two."""
@@ -467,12 +502,22 @@ class StepRunner:
         before = library.launches()
         graph = torch.cuda.CUDAGraph()
         self._capture_stream.wait_stream(current)
-        with torch.cuda.stream(self._capture_stream):
-            graph.capture_begin(pool=self._graph_pool)
-            try:
-                slot.logits = self.model.forward(step, caches)
-            finally:
-                graph.capture_end()
+        # No garbage collection while the stream is capturing: the collector may destroy CUDA objects of
+        # engines that are no longer used (their graphs, their events), and such a call from this thread
+        # would invalidate the capture.
+        collecting = gc.isenabled()
+        gc.collect()
+        gc.disable()
+        try:
+            with torch.cuda.stream(self._capture_stream):
+                graph.capture_begin(pool=self._graph_pool)
+                try:
+                    slot.logits = self.model.forward(step, caches)
+                finally:
+                    graph.capture_end()
+        finally:
+            if collecting:
+                gc.enable()
         current.wait_stream(self._capture_stream)
         slot.launches = library.launches() - before
         slot.graph = graph

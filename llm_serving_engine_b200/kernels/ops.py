@@ -171,11 +171,14 @@ def attention_mma_supported(head_dim: int, n_q: int, n_kv: int, dtype: torch.dty
     return bool(library.load().lse_attention_mma_supported(head_dim, n_q, n_kv))
 
 
+_DECODE_MAX_SPLITS = int(__import__("os").environ.get("LSE_DECODE_MAX_SPLITS", "8"))
+
+
 def decode_splits(tokens: int, n_q: int, n_kv: int, max_context: int | None) -> int:
     """How many splits of the keys a decode launch uses: enough blocks to fill the GPU,
     at least one 16-key tile per warp and split."""
     base = tokens * n_kv * ((n_q // n_kv + 15) // 16)
-    splits = max(1, min(8, 148 // base))        # about one block per SM; at most 8, which the last block adds up in one go
+    splits = max(1, min(_DECODE_MAX_SPLITS, 148 // base))   # about one block per SM; at most 8: one cluster adds them up
     if max_context is not None:
         splits = min(splits, max(1, -(-max_context // 64)))
     return splits

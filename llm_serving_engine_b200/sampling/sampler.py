@@ -43,6 +43,21 @@ def uniform01(seed: int, counter: int) -> float:
     return (mixed >> 40) / 16777216.0
 
 
+class _Turn:
+    """The buffers of one sampling launch.  There are two, used in turn, so that a launch may be queued
+    while the tokens of the one before have not been read yet."""
+
+    def __init__(self, max_rows: int, device, pinned: bool) -> None:
+        self.host_f = torch.empty((2, max_rows), dtype=torch.float32, pin_memory=pinned)
+        self.host_i = torch.empty((2, max_rows), dtype=torch.int64, pin_memory=pinned)
+        self.dev_f = torch.empty((2, max_rows), dtype=torch.float32, device=device)
+        self.dev_i = torch.empty((2, max_rows), dtype=torch.int64, device=device)
+        self.out = torch.empty(max_rows, dtype=torch.int32, device=device)
+        self.host_out = torch.empty(max_rows, dtype=torch.int32, pin_memory=pinned)
+        self.done = torch.cuda.Event() if pinned else None
+        self.rows = 0
+
+
 class Sampler:
     """Reusable buffers for sampling up to ``max_rows`` rows of ``vocab`` logits."""
 
@@ -50,46 +65,54 @@ class Sampler:
         self.vocab, self.max_rows = vocab, max_rows
         self.device = torch.device(device)
         pinned = self.device.type == "cuda"
-        self._host_f = torch.empty((2, max_rows), dtype=torch.float32, pin_memory=pinned)
-        self._host_i = torch.empty((2, max_rows), dtype=torch.int64, pin_memory=pinned)
-        self._dev_f = torch.empty((2, max_rows), dtype=torch.float32, device=self.device)
-        self._dev_i = torch.empty((2, max_rows), dtype=torch.int64, device=self.device)
-        self._out = torch.empty(max_rows, dtype=torch.int32, device=self.device)
-        self._host_out = torch.empty(max_rows, dtype=torch.int32, pin_memory=pinned)
+        self._turns = [_Turn(max_rows, self.device, pinned), _Turn(max_rows, self.device, pinned)]
+        self._last = 1
         self._scratch = None
-        self._pending_rows = 0
 
     def sample(self, logits: torch.Tensor, configs: list[GenerationConfig], counters: list[int]) -> list[int]:
         """One token per row of ``logits`` (float32 [R, V]); ``counters[r]`` is the index of
         the token being generated for row r's request.  One device-to-host transfer."""
-        self.launch(logits, configs, counters)
-        return self.collect()
+        return self.collect(self.launch(logits, configs, counters))
 
-    def launch(self, logits: torch.Tensor, configs: list[GenerationConfig], counters: list[int]) -> None:
-        """Start sampling and the copy of the tokens to the host; :meth:`collect` waits for them.
-        What the host does in between runs beside the device's work."""
+    def launch(self, logits: torch.Tensor, configs: list[GenerationConfig], counters: list[int]) -> int:
+        """Start sampling and the copy of the tokens to the host; returns a ticket for :meth:`collect`,
+        which waits for them.  What the host does in between runs beside the device's work.  At most
+        two launches may be outstanding."""
         rows = logits.shape[0]
         if rows != len(configs) or rows != len(counters) or rows > self.max_rows:
             raise ValueError("batched sampling inputs must have matching rows")
-        out = self._out[:rows]
+        ticket = self._last ^ 1
+        turn = self._turns[ticket]
+        out = turn.out[:rows]
         if all(config.temperature <= 0 for config in configs):
             ops.argmax(logits, out)
         else:
             if self._scratch is None:
                 self._scratch = torch.empty(self.max_rows * self.vocab, dtype=torch.float32, device=self.device)
             for row, (config, counter) in enumerate(zip(configs, counters)):
-                self._host_f[0, row] = config.temperature
-                self._host_f[1, row] = config.top_p
-                self._host_i[0, row] = config.seed
-                self._host_i[1, row] = counter
-            self._dev_f.copy_(self._host_f, non_blocking=True)
-            self._dev_i.copy_(self._host_i, non_blocking=True)
-            ops.sample(logits, self._dev_f[0, :rows], self._dev_f[1, :rows], self._dev_i[0, :rows],
-                       self._dev_i[1, :rows], self._scratch, out)
-        self._host_out[:rows].copy_(out, non_blocking=True)
-        self._pending_rows = rows
+                turn.host_f[0, row] = config.temperature
+                turn.host_f[1, row] = config.top_p
+                turn.host_i[0, row] = config.seed
+                turn.host_i[1, row] = counter
+            turn.dev_f.copy_(turn.host_f, non_blocking=True)
+            turn.dev_i.copy_(turn.host_i, non_blocking=True)
+            ops.sample(logits, turn.dev_f[0, :rows], turn.dev_f[1, :rows], turn.dev_i[0, :rows],
+                       turn.dev_i[1, :rows], self._scratch, out)
+        turn.host_out[:rows].copy_(out, non_blocking=True)
+        if turn.done is not None:
+            turn.done.record()
+        turn.rows = rows
+        self._last = ticket
+        return ticket
 
-    def collect(self) -> list[int]:
-        """The tokens of the last :meth:`launch` (waits for the device)."""
-        torch.cuda.current_stream().synchronize()
-        return self._host_out[:self._pending_rows].tolist()
+    def device_tokens(self, ticket: int) -> torch.Tensor:
+        """The tokens of that launch on the device (int32 [rows]), for a step that is queued behind it."""
+        turn = self._turns[ticket]
+        return turn.out[:turn.rows]
+
+    def collect(self, ticket: int | None = None) -> list[int]:
+        """The tokens of that launch (default: the last one); waits until the device has delivered them."""
+        turn = self._turns[self._last if ticket is None else ticket]
+        if turn.done is not None:
+            turn.done.synchronize()
+        return turn.host_out[:turn.rows].tolist()

@@ -215,7 +215,11 @@ def test_decode_steps_packed_ahead_give_the_same_tokens():
     assert plain.runner.ahead_steps == 0
     ahead = engine_for("D", dtype="bfloat16", batch=4, pages=128)
     assert ahead.generate_many(prompts, configs) == want
-    assert ahead.runner.ahead_steps > 20
+    assert ahead.runner.ahead_steps > 20 and ahead.runner.flying_steps > 20   # most of them queued before the tokens were read
+    packed_only = engine_for("D", dtype="bfloat16", batch=4, pages=128)
+    packed_only.launch_ahead = False
+    assert packed_only.generate_many(prompts, configs) == want
+    assert packed_only.runner.ahead_steps > 20 and packed_only.runner.flying_steps == 0
     assert not ahead.cache.requests and ahead.cache.groups[0].pool.used_pages == 0
     # a stop token that ends one request early: the step packed ahead for all four is dropped
     stop = want[2][10]
@@ -224,7 +228,8 @@ def test_decode_steps_packed_ahead_give_the_same_tokens():
     got = again.generate_many(prompts, configs)
     cut = want[2].index(stop) + 1
     assert got == [want[0], want[1], want[2][:cut], want[3]]
-    assert again.runner.ahead_steps > 10 and not again.cache.requests
+    assert again.runner.flying_steps > 10 and not again.cache.requests
+    assert again.cache.groups[0].pool.used_pages == 0 and again._flying is None
 
 
 def test_dependent_launch_off_gives_the_same_logits(tmp_path):
