@@ -289,7 +289,9 @@ def run_ours(args) -> dict:
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / peak["hbm_gbs"], 4), "peaks": peak["source"]},
         "points": points,
-        "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "pipeline": "one decode step in flight: every step copies its metadata from pinned host memory and its "
+                            "tokens to the host; the tokens feed the next step on the device"},
         "gpu_launches": launches,
         "clocks": clocks.summary(),
     }
