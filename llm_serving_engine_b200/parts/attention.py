@@ -12,9 +12,12 @@ from ..weights.tensor_spec import TensorSpec
 from .base import POSITION_ENCODINGS, Mixer, PagedKV, register_mixer
 from .linear import linear_partials
 
-# portions with at least this many rows go to the tcgen05 kernel (blocks of 128 rows); fewer rows
-# to the mma.sync kernel, whose blocks are smaller.  LSE_PREFILL_ATTENTION=mma turns the former off.
+# Steps with at least this many rows, and at least 64 rows per request on average, go to the tcgen05
+# kernel (a block = 128 rows of one request and one head); steps of fewer rows, or of many short
+# portions, to the mma.sync kernel, whose blocks hold about ten rows of all heads of a group.
+# LSE_PREFILL_ATTENTION=mma turns the former off.
 TCGEN05_MIN_ROWS = int(os.environ.get("LSE_TCGEN05_MIN_ROWS", "128"))
+TCGEN05_MIN_ROWS_PER_REQUEST = 64
 TCGEN05_PREFILL = os.environ.get("LSE_PREFILL_ATTENTION", "tcgen05") != "mma"
 
 
@@ -82,7 +85,8 @@ class GroupedQueryAttention(Mixer):
                 splits = ops.decode_splits(tokens, self.n_q, self.n_kv, step.max_context)
                 ops.paged_attention_decode(q, cache.keys, cache.values, attended, cache.block_tables,
                                            step.segment_of_token, step.positions, self.scale, splits)
-            elif (TCGEN05_PREFILL and tokens >= TCGEN05_MIN_ROWS and ops.attention_tc_supported(
+            elif (TCGEN05_PREFILL and tokens >= TCGEN05_MIN_ROWS
+                  and tokens >= TCGEN05_MIN_ROWS_PER_REQUEST * step.num_segments and ops.attention_tc_supported(
                     self.head_dim, self.n_q, self.n_kv, cache.keys.shape[2], x.dtype, self.window)):
                 ops.paged_attention_prefill_tc(q, cache.keys, cache.values, attended, cache.block_tables,
                                                step.segment_start, step.segment_first_position, self.scale)
