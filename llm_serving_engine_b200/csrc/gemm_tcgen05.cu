@@ -46,7 +46,8 @@ __global__ void __launch_bounds__(GATED_IN ? 192 : 128)
 gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                         float* __restrict__ out, int M, int N, int k_tiles, int tiles_per_split, int m_pad,
                         int stages, int kboxes, __nv_bfloat16* __restrict__ gated_out,
-                        const float* __restrict__ gate_up, int n_partials, long long partial_stride, int inter) {
+                        const float* __restrict__ gate_up, int n_partials, long long partial_stride, int inter,
+                        int* __restrict__ arrivals, __nv_bfloat16* __restrict__ finished_out) {
   constexpr uint32_t A_BYTES = BLOCK_N * BLOCK_K * 2;
   constexpr int ROWS_PER_WARP = BLOCK_N / 4;   // valid accumulator rows in a warp's quarter of tensor memory
   extern __shared__ unsigned char smem_raw[];
@@ -297,6 +298,35 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
     // a wait gave up: give copies that may still be in flight time to land before the block leaves
     for (int i = 0; i < 2000; ++i) __nanosleep(100);
   }
+  if (!GATED_IN && arrivals != nullptr) {
+    // The split of this block column that finishes last (an arrival counter, nobody waits) adds the
+    // partial sums of the column's 128 weight rows up in split order: 64 gate rows, then the 64 up
+    // rows of the same outputs, and writes silu(gate) * up as bfloat16.  The counter goes back to
+    // zero for the next launch.
+    __shared__ int last_split;
+    __threadfence();
+    const int all_ready = __syncthreads_and(ready ? 1 : 0);
+    if (threadIdx.x == 0) last_split = all_ready && atomicAdd(&arrivals[blockIdx.x], 1) == (int)gridDim.y - 1;
+    __syncthreads();
+    if (last_split) {
+      __threadfence();
+      constexpr int HALF = BLOCK_N / 2;
+      const int n_out = N / 2;
+      for (int idx = threadIdx.x; idx < M * HALF; idx += 128) {
+        const int m = idx / HALF, j = idx % HALF;
+        if (n0 + HALF + j >= N) continue;
+        float g = 0.f, u = 0.f;
+        for (int p = 0; p < (int)gridDim.y; ++p) {
+          const float* row = out + ((size_t)p * M + m) * N + n0;
+          g += __ldcg(row + j);
+          u += __ldcg(row + HALF + j);
+        }
+        finished_out[(size_t)m * n_out + blockIdx.x * HALF + j] =
+            __float2bfloat16_rn(__fdividef(g, 1.0f + __expf(-g)) * u);
+      }
+      if (threadIdx.x == 0) arrivals[blockIdx.x] = 0;
+    }
+  }
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
   __syncthreads();
   LSE_TL_MARK(3)
@@ -340,7 +370,7 @@ namespace {
 template <int BLOCK_N, bool GATED_IN = false>
 int launch_skinny(const void* x, const void* w, float* out, int M, int N, int K, int splits, int stages, int kboxes,
                   void* gated_out, cudaStream_t stream, const float* gate_up = nullptr, int n_partials = 0,
-                  long long partial_stride = 0) {
+                  long long partial_stride = 0, int* arrivals = nullptr, void* finished_out = nullptr) {
   if (M <= 0 || N <= 0) return 0;
   const int m_pad = lse_gemm_bf16_skinny_pad(M);
   if (m_pad == 0 || K <= 0 || K % 8 || (((uintptr_t)x | (uintptr_t)w) & 15)) return LSE_ERR_BAD_ARGUMENT;
@@ -352,6 +382,8 @@ int launch_skinny(const void* x, const void* w, float* out, int M, int N, int K,
     if (N % BLOCK_N) return LSE_ERR_BAD_ARGUMENT;
     splits = 1;
   }
+  if ((arrivals != nullptr) != (finished_out != nullptr) || (arrivals != nullptr && (N % BLOCK_N || gated_out != nullptr || GATED_IN)))
+    return LSE_ERR_BAD_ARGUMENT;
   const int k_tiles = (K + BLOCK_K * kboxes - 1) / (BLOCK_K * kboxes);
   splits = lse_gemm_bf16_skinny_splits(K, splits, kboxes);
   const int per = (k_tiles + splits - 1) / splits;
@@ -375,7 +407,8 @@ int launch_skinny(const void* x, const void* w, float* out, int M, int N, int K,
   dim3 grid((N + BLOCK_N - 1) / BLOCK_N, splits);
   cudaError_t err = lse_launch(gemm_bf16_skinny_kernel<BLOCK_N, GATED_IN>, grid, GATED_IN ? 192 : 128, smem, stream,
                                map_w, map_x, out, M, N, k_tiles, per, m_pad, stages, kboxes,
-                               (__nv_bfloat16*)gated_out, gate_up, n_partials, partial_stride, K);
+                               (__nv_bfloat16*)gated_out, gate_up, n_partials, partial_stride, K, arrivals,
+                               (__nv_bfloat16*)finished_out);
   if (err != cudaSuccess) return (int)err;
   return (int)cudaGetLastError();
 }
@@ -401,4 +434,17 @@ extern "C" int lse_gemm_bf16_skinny_gated_in(const float* gate_up, int n_partial
                                              cudaStream_t stream) {
   return launch_skinny<128, true>(nullptr, w, out, M, N, K, splits, stages, 1, nullptr, stream, gate_up, n_partials,
                                   partial_stride);
+}
+
+// The product of lse_gemm_bf16_skinny (128 weight rows per block, any number of splits; `out` gets the
+// partial sums as usual) whose last-arriving split of every block column also applies the SiLU gate:
+// w holds, per 128 rows, 64 gate rows then the 64 up rows of the same outputs (N a multiple of 128);
+// finished_out[M, N / 2] (bfloat16) = silu(sum of gate partials) * (sum of up partials), the sums in
+// split order.  `arrivals`: ceil(N / 128) ints that are zero before the first launch (the kernel
+// leaves them zero).  One launch at a time may use the same `arrivals`.
+extern "C" int lse_gemm_bf16_skinny_finish_gate(const void* x, const void* w, float* out, int* arrivals,
+                                                void* finished_out, int M, int N, int K, int splits, int stages,
+                                                cudaStream_t stream) {
+  if (arrivals == nullptr || finished_out == nullptr) return LSE_ERR_BAD_ARGUMENT;
+  return launch_skinny<128>(x, w, out, M, N, K, splits, stages, 1, nullptr, stream, nullptr, 0, 0, arrivals, finished_out);
 }

@@ -23,6 +23,8 @@ _SIGNATURES = {
                              c_void_p],
     "lse_gemm_bf16_skinny_gated_in": [c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                       c_void_p],
+    "lse_gemm_bf16_skinny_finish_gate": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                         c_int, c_void_p],
     "lse_gemm_bf16_skinny_pad": [c_int],
     "lse_gemm_bf16_skinny_splits": [c_int, c_int, c_int],
     "lse_gemm_bf16_skinny_status": [],

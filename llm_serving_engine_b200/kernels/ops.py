@@ -364,6 +364,37 @@ def gemm_bf16_skinny_gated(x: torch.Tensor, weight: torch.Tensor, interleave: in
     return out
 
 
+FINISH_GATE_INTERLEAVE = 64     # 128 weight rows per block: 64 gate rows, then the 64 up rows of the same outputs
+
+
+def gemm_bf16_skinny_finish_gate(x: torch.Tensor, weight: torch.Tensor, arrivals: torch.Tensor,
+                                 splits: int | None = None, stages: int = 6,
+                                 max_splits: int | None = None) -> tuple[torch.Tensor, torch.Tensor]:
+    """The split-k product of ``gemm_bf16_skinny`` on a gate/up matrix interleaved in blocks of 64
+    (``interleave_gate_up(gate, up, 64)``) whose last-arriving split of every block column also
+    applies the gate: returns (partial sums [P, M, 2I] float32, silu(gate) * up [M, I] bfloat16),
+    the latter bit for bit what ``silu_mul`` gives on the former.  ``arrivals``: int32 zeros, one
+    per 128 weight rows, that only this product uses."""
+    _need_cuda(x, weight, arrivals)
+    m, k = x.shape
+    n = weight.shape[0]
+    if (not gemm_bf16_skinny_ok(x, weight) or weight.shape[1] != k or n % 128 or arrivals.dtype != torch.int32
+            or arrivals.shape[0] < n // 128):
+        raise KernelError("gemm_bf16_skinny_finish_gate: contiguous bfloat16 operands, K % 8 == 0, 2I a multiple of 128, "
+                          "M <= 256, one int32 counter per 128 weight rows")
+    lib = library.load()
+    if splits is None:
+        n_tiles = n // 128
+        splits = max(1, min(-(-k // 128), _GEMM_TARGET_BLOCKS // n_tiles, max(1, k // (4 * m)), max_splits or _GEMM_MAX_SPLITS)) if n_tiles < 148 else 1
+    splits = lib.lse_gemm_bf16_skinny_splits(k, int(splits), 1)
+    out = torch.empty((splits, m, n), dtype=torch.float32, device=x.device)
+    act = torch.empty((m, n // 2), dtype=torch.bfloat16, device=x.device)
+    check(lib.lse_gemm_bf16_skinny_finish_gate(x.data_ptr(), weight.data_ptr(), out.data_ptr(), arrivals.data_ptr(),
+                                               act.data_ptr(), m, n, k, splits, int(stages), _stream()),
+          "gemm_bf16_skinny_finish_gate")
+    return out, act
+
+
 GATED_IN_MAX_ROWS = 16      # one 16-byte chunk of the activations per thread and stage
 
 

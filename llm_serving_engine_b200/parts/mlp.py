@@ -20,6 +20,11 @@ FUSE_GATE = 0
 # path, while the separate SiLU kernel runs beside the product's first weight loads.  Off unless
 # LSE_FUSE_GATE_INTO_DOWN=1.
 FUSE_GATE_INTO_DOWN = __import__("os").environ.get("LSE_FUSE_GATE_INTO_DOWN", "0") == "1"
+# A third form: the gate applied by the split of the gate/up product that finishes last in its block
+# column (the product keeps its splits; gate and up rows interleaved in blocks of 64).  Measured slower
+# too (1.53 against 1.48 ms a step at batch 8, 2.21 against 1.95 at batch 32): the last split's extra
+# round trips are serial, the SiLU kernel's are not.  Off unless LSE_FINISH_GATE=1.
+FINISH_GATE = __import__("os").environ.get("LSE_FINISH_GATE", "0") == "1"
 
 
 @register_feed_forward("swiglu")
@@ -33,8 +38,14 @@ class SwiGLU(FeedForward):
         # bfloat16 and I a multiple of 32: gate and up rows are interleaved in blocks of 32, the layout
         # whose few-rows product applies the SiLU gate in its epilogue; else gate rows, then up rows
         self.interleave = 0
+        self.arrivals = None
         wish = int(params.get("fuse_gate", FUSE_GATE))
-        if ctx.dtype == torch.bfloat16 and wish and self.inter % wish == 0:
+        if (ctx.dtype == torch.bfloat16 and not wish and FINISH_GATE and not FUSE_GATE_INTO_DOWN
+                and self.inter % ops.FINISH_GATE_INTERLEAVE == 0):
+            self.interleave = ops.FINISH_GATE_INTERLEAVE
+            self.gate_up_weight = ops.interleave_gate_up(weights["gate_proj.weight"], weights["up_proj.weight"], self.interleave)
+            self.arrivals = torch.zeros(2 * self.inter // 128, dtype=torch.int32, device=ctx.device)   # this product's own
+        elif ctx.dtype == torch.bfloat16 and wish and self.inter % wish == 0:
             self.interleave = wish
             self.gate_up_weight = ops.interleave_gate_up(weights["gate_proj.weight"], weights["up_proj.weight"], wish)
         else:
@@ -51,7 +62,11 @@ class SwiGLU(FeedForward):
         }
 
     def forward(self, x):
-        if self.interleave and x.shape[0] <= SKINNY_MAX_ROWS and ops.gemm_bf16_skinny_ok(x, self.gate_up_weight):
+        if self.arrivals is not None and x.shape[0] <= SKINNY_MAX_ROWS and ops.gemm_bf16_skinny_ok(x, self.gate_up_weight):
+            # few rows: the split that finishes last in a block column applies the gate to the column's sums
+            _, act = ops.gemm_bf16_skinny_finish_gate(x, self.gate_up_weight, self.arrivals)
+        elif (self.interleave and self.arrivals is None and x.shape[0] <= SKINNY_MAX_ROWS
+              and ops.gemm_bf16_skinny_ok(x, self.gate_up_weight)):
             act = ops.gemm_bf16_skinny_gated(x, self.gate_up_weight, self.interleave)   # product and gate in one kernel
         else:
             gate_up = linear_partials(x, self.gate_up_weight)

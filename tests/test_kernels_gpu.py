@@ -657,6 +657,30 @@ def test_product_that_makes_the_gated_activations_itself(m, inter, n, parts, spl
     assert ops().gemm_bf16_skinny_status() == 0
 
 
+@pytest.mark.parametrize("m, inter, k, splits", [(8, 8960, 1536, None), (1, 64, 64, 1), (5, 192, 520, 3), (16, 1024, 776, 7),
+                                                 (32, 8960, 1536, None), (200, 320, 264, 2)])
+def test_product_whose_last_split_applies_the_gate(m, inter, k, splits):
+    """Bit for bit the SiLU kernel's result on the same partial sums, launch after launch (the arrival
+    counters have to be back at zero), and the partial sums themselves are those of the plain product."""
+    torch.manual_seed(m + inter)
+    x = torch.randn(m, k, device=DEV).bfloat16()
+    gate = (torch.randn(inter, k, device=DEV) * 0.05).bfloat16()
+    up = (torch.randn(inter, k, device=DEV) * 0.05).bfloat16()
+    w = ops().interleave_gate_up(gate, up, 64)
+    arrivals = torch.zeros(2 * inter // 128, dtype=torch.int32, device=DEV)
+    for _ in range(3):
+        parts, act = ops().gemm_bf16_skinny_finish_gate(x, w, arrivals, splits)
+        assert int(arrivals.abs().sum()) == 0
+        want = torch.empty(m, inter, device=DEV, dtype=torch.bfloat16)
+        ops().silu_mul(parts, want, 64)
+        assert torch.equal(act, want)
+        assert torch.equal(parts, ops().gemm_bf16_skinny(x, w, parts.shape[0]))
+    g, u = x.double() @ gate.double().t(), x.double() @ up.double().t()
+    exact = torch.nn.functional.silu(g) * u
+    assert float((act.double() - exact).abs().max()) <= 2.0 ** -7 * float(exact.abs().max()) + 1e-6
+    assert ops().gemm_bf16_skinny_status() == 0
+
+
 def test_few_rows_product_refuses_what_it_cannot_run():
     from llm_serving_engine_b200.kernels.library import KernelError
     x = torch.randn(4, 100, device=DEV).bfloat16()      # k not a multiple of 8
