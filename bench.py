@@ -297,6 +297,75 @@ def run_ours(args) -> dict:
     }
 
 
+def timeline(args) -> int:
+    """One decode step seen from the device: the tuning variant of the kernel library (built with
+    ``-DLSE_TRACE``) lets block 0 of every kernel record when it started, when its wait for the kernels
+    before returned and when it ended (nanoseconds of the global timer).  Prints the kernels of the first
+    layers in order and the sums per kind of kernel."""
+    import ctypes
+
+    import torch
+
+    os.environ["LSE_TRACE"] = "1"   # before the library is loaded
+    from llm_serving_engine_b200.cache.manager import CacheManager
+    from llm_serving_engine_b200.config.runtime_config import CacheConfig
+    from llm_serving_engine_b200.engine.step import StepEntry, StepRunner
+    from llm_serving_engine_b200.kernels import library
+    from llm_serving_engine_b200.models import cache_requirements
+
+    torch.cuda.set_device(0)
+    lib = library.load()
+    model, _ = build_model(args.layers or FULL_LAYERS)
+    batch = args.batch
+    context = model.spec.max_position_embeddings
+    cache = CacheManager(cache_requirements(model.spec), CacheConfig(BLOCK, batch * (context // BLOCK)), model.dtype,
+                         model.device, context, num_state_slots=batch)
+    runner = StepRunner(model, cache, max(PROMPT, batch), batch, use_graphs=USE_GRAPHS)
+    generator = torch.Generator().manual_seed(1)
+    names = {1: "embedding", 2: "add+norm", 3: "rope+cache", 4: "silu", 5: "product", 6: "attention"}
+
+    def read_all(reset: int):
+        rows = []
+        for reader in ("lse_timeline_elementwise", "lse_timeline_gemm", "lse_timeline_attention"):
+            function = getattr(lib, reader)
+            function.argtypes = [ctypes.c_void_p, ctypes.c_int]
+            function.restype = ctypes.c_int
+            buffer = (ctypes.c_ulonglong * (4096 * 8))()
+            count = function(buffer, reset)
+            rows += [tuple(int(buffer[i * 8 + k]) for k in range(4)) for i in range(count)]
+        return sorted(rows, key=lambda row: row[1])
+
+    ids = [f"r{index}" for index in range(batch)]
+    with torch.inference_mode():
+        for rid in ids:
+            cache.create(rid)
+            runner.run([StepEntry(rid, torch.randint(0, model.vocab_size, (PROMPT,), generator=generator).tolist(), [])])
+        for _ in range(max(args.warmup, 3)):
+            runner.run([StepEntry(rid, [5], [0]) for rid in ids])
+        torch.cuda.synchronize()
+        read_all(1)
+        runner.run([StepEntry(rid, [5], [0]) for rid in ids])
+        torch.cuda.synchronize()
+    rows = read_all(1)
+    origin = rows[0][1]
+    print(f"decode step, batch {batch}, {len(rows)} kernels, {(max(row[3] for row in rows) - origin) / 1000:.1f} us "
+          f"from the first kernel's start to the last kernel's end (block 0 of each; microseconds)")
+    print(f"{'#':>3} {'kernel':10} {'started':>9} {'wait over':>10} {'ended':>9} {'after wait':>11} {'since the kernel before ended':>30}")
+    before = origin
+    for index, (kind, started, waited, ended) in enumerate(rows[:2 + 9 * args.timeline]):
+        print(f"{index:3d} {names.get(kind, str(kind)):10} {(started - origin) / 1000:9.2f} {(waited - origin) / 1000:10.2f} "
+              f"{(ended - origin) / 1000:9.2f} {(ended - waited) / 1000:11.2f} {(waited - before) / 1000:30.2f}")
+        before = ended
+    totals: dict[str, list] = {}
+    for kind, started, waited, ended in rows:
+        entry = totals.setdefault(names.get(kind, str(kind)), [0, 0.0])
+        entry[0] += 1
+        entry[1] += (ended - waited) / 1000
+    for name, (count, active) in totals.items():
+        print(f"{name:10} x{count:4d}: {active:8.1f} us after the wait in total, {active / count:6.2f} us each")
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -308,9 +377,14 @@ def main() -> int:
     parser.add_argument("--only", choices=("all", "decode", "prefill"), default="all",
                         help="run one part only (a small case for ncu; no bench line)")
     parser.add_argument("--no-graphs", action="store_true", help="decode launch by launch instead of from CUDA graphs")
+    parser.add_argument("--timeline", type=int, default=0, metavar="LAYERS",
+                        help="print the device-side timeline of one decode step (the first LAYERS layers kernel by "
+                             "kernel) from the tuning variant of the kernel library; no bench line")
     args = parser.parse_args()
     global USE_GRAPHS
     USE_GRAPHS = not args.no_graphs
+    if args.timeline:
+        return timeline(args)
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
                           "offline pip install of the reference fails: its build backend (hatchling) is not in the wheelhouse"}))

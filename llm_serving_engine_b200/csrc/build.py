@@ -47,9 +47,9 @@ def _nvcc() -> str:
     raise BuildError("nvcc not found: the CUDA kernels cannot be built (set NVCC or add it to PATH)")
 
 
-def _key() -> str:
+def _key(flags: list[str]) -> str:
     digest = hashlib.sha256()
-    digest.update(" ".join(NVCC_FLAGS).encode())
+    digest.update(" ".join(flags).encode())
     for path in sorted(list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h"))):
         digest.update(path.name.encode())
         digest.update(path.read_bytes())
@@ -75,12 +75,16 @@ def _log(message: str, verbose: bool) -> None:
         print(f"[llm_serving_engine_b200] {message}", file=sys.stderr, flush=True)
 
 
-def library_path(verbose: bool = True, force: bool = False) -> Path:
-    """Path of the built library; compiles it first when it is missing or stale."""
+def library_path(verbose: bool = True, force: bool = False, trace: bool = False) -> Path:
+    """Path of the built library; compiles it first when it is missing or stale.
+
+    ``trace``: the tuning variant (``-DLSE_TRACE``), in which block 0 of every kernel records when it
+    started, when its wait for the kernels before returned and when it ended; a library of its own."""
     build_dir = _build_dir()
-    key = _key()
-    lib = build_dir / LIB_NAME
-    stamp = build_dir / "build.key"
+    flags = NVCC_FLAGS + (["-DLSE_TRACE"] if trace else [])
+    key = _key(flags)
+    lib = build_dir / (LIB_NAME.replace(".so", "_trace.so") if trace else LIB_NAME)
+    stamp = build_dir / ("build_trace.key" if trace else "build.key")
     if not force and lib.exists() and stamp.exists() and stamp.read_text().strip() == key:
         return lib
     nvcc = _nvcc()
@@ -99,7 +103,7 @@ def library_path(verbose: bool = True, force: bool = False) -> Path:
     try:
         def compile_one(src: Path) -> Path:
             obj = build_dir / (src.stem + f".{os.getpid()}.o")
-            cmd = [nvcc, *NVCC_FLAGS, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+            cmd = [nvcc, *flags, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
             result = subprocess.run(cmd, capture_output=True, text=True)
             if result.returncode != 0:
                 raise BuildError(f"nvcc failed on {src.name}:\n{result.stdout}\n{result.stderr}")
@@ -108,7 +112,7 @@ def library_path(verbose: bool = True, force: bool = False) -> Path:
 
         with ThreadPoolExecutor(max_workers=min(8, len(srcs), os.cpu_count() or 1)) as pool:
             objects = list(pool.map(compile_one, srcs))
-        tmp_lib = build_dir / f"{LIB_NAME}.{os.getpid()}.tmp"
+        tmp_lib = build_dir / f"{lib.name}.{os.getpid()}.tmp"
         cmd = [nvcc, "-shared", "-o", str(tmp_lib), *map(str, objects)]
         result = subprocess.run(cmd, capture_output=True, text=True)
         if result.returncode != 0:

@@ -57,13 +57,13 @@ def load(verbose: bool = True):
     """The ctypes handle of the kernel library (built at the first call)."""
     global _lib
     if _lib is None:
-        path = build.library_path(verbose=verbose)
+        import os
+        path = build.library_path(verbose=verbose, trace=os.environ.get("LSE_TRACE", "0") == "1")   # 1: the tuning variant
         lib = ctypes.CDLL(str(path))
         for name, argtypes in _SIGNATURES.items():
             fn = getattr(lib, name)
             fn.argtypes = argtypes
             fn.restype = c_int
-        import os
         if os.environ.get("LSE_PDL", "1") == "0":   # programmatic dependent launch off (for comparisons)
             lib.lse_set_pdl(0)
         _lib = lib
