@@ -91,3 +91,42 @@ def test_long_portions_take_the_tcgen05_attention(folder):
         limit = helpers.tolerance("bfloat16", want_rows)
         error = (got_rows - want_rows).abs().max(dim=1).values
         assert float(error.max()) <= limit, f"{name}: max error {float(error.max()):.3e} > {limit:.3e} at row {int(error.argmax())}"
+
+
+CONFIG_7B_LAYER = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "vocab_size": 2048, "hidden_size": 3584, "intermediate_size": 18944, "num_hidden_layers": 1,
+    "num_attention_heads": 28, "num_key_value_heads": 4, "max_position_embeddings": 1024,
+    "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": False,
+}
+
+
+def test_layer_sizes_of_a_larger_model(tmp_path):
+    """One layer of the Qwen2.5-7B sizes (hidden 3584, 28 query and 4 key/value heads, feed-forward 18944; a small
+    vocabulary keeps it light): sizes the kernels were not tuned on: seven heads a group, a width beyond the
+    warp-per-row norm, k = 18944 in the few-rows product, in a long portion, a short one, decoding and a mixed step."""
+    from llm_serving_engine_b200.engine.trace_replay import replay
+    from llm_serving_engine_b200.kernels import ops
+    from llm_serving_engine_b200.weights import write_random_model
+
+    write_random_model(tmp_path / "model", CONFIG_7B_LAYER, seed=5, dtype="bfloat16")
+    rng = random.Random(6)
+    a = helpers.random_tokens(rng, CONFIG_7B_LAYER["vocab_size"], 330)
+    b = helpers.random_tokens(rng, CONFIG_7B_LAYER["vocab_size"], 50)
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": a[:300], "want": [0, 128, 299]}], "end": []},
+        {"step": 1, "entries": [{"id": "a", "tokens": a[300:320], "want": [19]}, {"id": "b", "tokens": b[:40], "want": [39]}], "end": []},
+    ]
+    steps += [{"step": 2 + i, "entries": [{"id": "a", "tokens": [a[320 + i]], "want": [0]}, {"id": "b", "tokens": [b[40 + i]], "want": [0]}],
+               "end": []} for i in range(10)]
+    with tempfile.TemporaryDirectory(prefix="real_out_") as out:
+        replay(tmp_path / "model", "bfloat16", out, 512, [json.dumps(step) for step in steps])
+        got = helpers.collect(steps, Path(out))
+    assert ops.attention_tc_status() == 0 and ops.gemm_bf16_skinny_status() == 0
+    cfg, weights = qwen2_plain.load_folder(tmp_path / "model")
+    want_a = qwen2_plain.forward_full(cfg, weights, a)[[0, 128, 299, 319] + list(range(320, 330))]
+    want_b = qwen2_plain.forward_full(cfg, weights, b)[[39] + list(range(40, 50))]
+    for name, got_rows, want_rows in (("a", got["a"], want_a), ("b", got["b"], want_b)):
+        limit = helpers.tolerance("bfloat16", want_rows)
+        error = (got_rows - want_rows).abs().max(dim=1).values
+        assert float(error.max()) <= limit, f"{name}: max error {float(error.max()):.3e} > {limit:.3e} at row {int(error.argmax())}"
