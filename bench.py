@@ -31,6 +31,9 @@ QWEN25_1P5B = {
     "num_attention_heads": 12, "num_key_value_heads": 2, "max_position_embeddings": 4096,
     "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "attention_bias": True, "tie_word_embeddings": True,
 }
+# layer sizes of a larger model of the same architecture, for `--sizes 7b --only decode|prefill` (no bench line)
+QWEN25_7B_SIZES = {"hidden_size": 3584, "intermediate_size": 18944, "num_attention_heads": 28, "num_key_value_heads": 4,
+                   "vocab_size": 152064, "tie_word_embeddings": False}
 FULL_LAYERS = QWEN25_1P5B["num_hidden_layers"]
 USE_GRAPHS = True     # --no-graphs: launch by launch (for profilers)
 PROMPT = 2048
@@ -254,10 +257,13 @@ def run_ours(args) -> dict:
     batch = args.batch
 
     if args.only == "decode":     # a short run of one part, for profilers; prints no bench line
-        ms, _, _ = time_decode(model, batch, args.steps, args.warmup)
-        return {"only": "decode", "batch": batch, "layers": layers, "ms_per_step": round(ms, 4)}
+        ms, kv_bytes, _ = time_decode(model, batch, args.steps, args.warmup)
+        return {"only": "decode", "batch": batch, "layers": layers, "ms_per_step": round(ms, 4),
+                "gb_per_s": round((weight_bytes + kv_bytes) / (ms / 1000) / 1e9, 1)}
     if args.only == "prefill":
-        return {"only": "prefill", "layers": layers, "ms": round(time_prefill(model, repeats=max(1, args.steps)), 4)}
+        ms = time_prefill(model, repeats=max(1, args.steps))
+        return {"only": "prefill", "layers": layers, "ms": round(ms, 4),
+                "tflops": round(prefill_flops(config, layers, PROMPT) / (ms / 1000) / 1e12, 1)}
     with ClockSampler() as clocks:
         ms, kv_bytes, launches = time_decode(model, batch, args.steps, args.warmup)
     value = batch / (ms / 1e3)
@@ -377,12 +383,19 @@ def main() -> int:
     parser.add_argument("--only", choices=("all", "decode", "prefill"), default="all",
                         help="run one part only (a small case for ncu; no bench line)")
     parser.add_argument("--no-graphs", action="store_true", help="decode launch by launch instead of from CUDA graphs")
+    parser.add_argument("--sizes", choices=("1.5b", "7b"), default="1.5b",
+                        help="layer sizes (7b: those of Qwen2.5-7B; only with --only, give --layers to fit the time)")
     parser.add_argument("--timeline", type=int, default=0, metavar="LAYERS",
                         help="print the device-side timeline of one decode step (the first LAYERS layers kernel by "
                              "kernel) from the tuning variant of the kernel library; no bench line")
     args = parser.parse_args()
     global USE_GRAPHS
     USE_GRAPHS = not args.no_graphs
+    if args.sizes == "7b":
+        if args.only == "all" and not args.timeline:
+            print("--sizes 7b measures one part only: add --only decode or --only prefill")
+            return 2
+        QWEN25_1P5B.update(QWEN25_7B_SIZES)
     if args.timeline:
         return timeline(args)
     if args.impl == "reference":
