@@ -348,6 +348,8 @@ class LLMEngine:
         if self._worker:
             self._worker.cancel()
             await asyncio.gather(self._worker, return_exceptions=True)
+        self._ahead = None
+        self._drop_flying()   # a decode step that was still queued on the device
 
     async def __aenter__(self) -> "LLMEngine":
         return self
