@@ -90,6 +90,18 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {   // 
   return done != 0;
 }
 
+// Bounded wait that polls without letting the thread be suspended (for the two issuing threads, which
+// have nothing else to do: they see the arrival sooner).
+__device__ __forceinline__ bool mbar_poll(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* error_word) {
+  for (uint32_t i = 0; i < SPIN_LIMIT * 16u; ++i) {
+    if (mbar_test(bar, parity)) return true;
+    if ((i & 63u) == 63u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  atomicExch(error_word, 1);
+  return false;
+}
+
 template <int D>
 constexpr size_t attn_tc_smem() {
   // alignment slack, Q, a key and a value stage and a probability tile per group, barriers
@@ -211,14 +223,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       // its probabilities are written).  The keys are waited for first: they have long arrived, and the
       // wait that matters then comes last.
       const uint32_t idesc_s = instr_desc_bf16(BM, BN, false, false);
-      bool ok = mbar_wait(bar(B_Q), 0, abort_flag, err);
+      bool ok = mbar_poll(bar(B_Q), 0, abort_flag, err);
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int g = j & 1;
         const uint32_t parity = (uint32_t)(j >> 1) & 1u;
         TC_STAMP2(j, 1)
-        ok = mbar_wait(bar(B_KF + g), parity, abort_flag, err);
+        ok = mbar_poll(bar(B_KF + g), parity, abort_flag, err);
         TC_STAMP2(j, 2)
-        if (ok && j >= GROUPS) ok = mbar_wait(bar(B_PF + g), parity ^ 1u, abort_flag, err);
+        if (ok && j >= GROUPS) ok = mbar_poll(bar(B_PF + g), parity ^ 1u, abort_flag, err);
         if (!ok) break;
         fence_after_sync();
         TC_STAMP2(j, 6)
@@ -245,9 +257,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const int g = i & 1;
         const uint32_t parity = (uint32_t)(i >> 1) & 1u;
         TC_STAMP2(i, 0)
-        ok = mbar_wait(bar(B_VF + g), parity, abort_flag, err) && mbar_wait(bar(B_PF + g), parity, abort_flag, err);
+        ok = mbar_poll(bar(B_VF + g), parity, abort_flag, err) && mbar_poll(bar(B_PF + g), parity, abort_flag, err);
         // the scores of the group's next tile go first (the group waits for them; this product is wanted later)
-        if (ok && i + GROUPS < n_tiles) ok = mbar_wait(bar(B_KE + g), parity ^ 1u, abort_flag, err);
+        if (ok && i + GROUPS < n_tiles) ok = mbar_poll(bar(B_KE + g), parity ^ 1u, abort_flag, err);
         if (!ok) break;
         fence_after_sync();
         TC_STAMP2(i, 3)
