@@ -80,28 +80,6 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 __device__ __forceinline__ void pair_barrier(int quarter) {   // the warps of the two groups that own the same 32 rows
   asm volatile("bar.sync %0, %1;\n" ::"r"(1 + quarter), "r"(64) : "memory");
 }
-__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {   // has that phase completed? (no waiting)
-  uint32_t done;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}\n"
-      : "=r"(done) : "r"(bar), "r"(parity) : "memory");
-  return done != 0;
-}
-
-// Bounded wait that polls without letting the thread be suspended (for the two issuing threads, which
-// have nothing else to do: they see the arrival sooner).
-__device__ __forceinline__ bool mbar_poll(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* error_word) {
-  for (uint32_t i = 0; i < SPIN_LIMIT * 16u; ++i) {
-    if (mbar_test(bar, parity)) return true;
-    if ((i & 63u) == 63u && *abort_flag) return false;
-  }
-  *abort_flag = 1;
-  atomicExch(error_word, 1);
-  return false;
-}
-
 template <int D>
 constexpr size_t attn_tc_smem() {
   // alignment slack, Q, a key and a value stage and a probability tile per group, barriers

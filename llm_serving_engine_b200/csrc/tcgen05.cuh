@@ -47,6 +47,28 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   return false;
 }
 
+// Has that phase completed?  (No waiting.)
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}\n"
+      : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+  return done != 0;
+}
+// Bounded wait that polls without letting the thread be suspended: for threads that have nothing else
+// to do and sit on a kernel's critical path (they see the arrival a few hundred cycles sooner).
+__device__ __forceinline__ bool mbar_poll(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* error_word) {
+  for (uint32_t i = 0; i < SPIN_LIMIT * 16u; ++i) {
+    if (mbar_test(bar, parity)) return true;
+    if ((i & 63u) == 63u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  atomicExch(error_word, 1);
+  return false;
+}
+
 // ------------------------------------------------------------------ TMA
 // Tile loads; the innermost coordinate times the element size is a multiple of 16 bytes at every call.
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
