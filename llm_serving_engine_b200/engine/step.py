@@ -21,6 +21,7 @@ whose mixers all say ``graph_safe`` are captured; others run launch by launch.
 from __future__ import annotations
 
 import gc
+import os
 from dataclasses import dataclass, field
 
 import numpy as np
@@ -118,6 +119,11 @@ class StepRunner:
     """Packs a step, runs the model on it and keeps the cache manager in step."""
 
     GRAPH_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256)
+    # size classes of steps with prompt portions: tokens (steps of a quarter to a half, so that at most a third
+    # of a graph's rows is padding) and requests (few classes: every class is a capture)
+    PORTION_BUCKETS = (16, 32, 48, 64, 96, 128, 160, 192, 256, 320, 384, 512, 640, 768, 1024, 1280, 1536, 2048,
+                       2560, 3072, 4096, 5120, 6144, 8192)
+    PORTION_REQUEST_BUCKETS = (1, 8, 32, 128, 256)
 
     def __init__(self, model, cache: CacheManager, max_tokens_per_step: int, max_segments: int,
                  use_graphs: bool = True) -> None:
@@ -142,6 +148,10 @@ class StepRunner:
         self._graph_pool = None          # one memory pool for all graphs: only one of them runs at a time
         self._capture_stream = None
         self._arange = np.arange(max(self.GRAPH_BUCKETS), dtype=np.int32)
+        self.graph_portions = os.environ.get("LSE_PORTION_GRAPHS", "1") != "0"
+        self._portion_classes_seen: dict = {}
+        self._portion_graphs: dict = {}
+        self.portion_graph_replays = 0
         self.steps_run = 0
         self.graph_replays = 0
         self.ahead_steps = 0             # decode steps whose packing ran beside the step before
@@ -155,9 +165,12 @@ class StepRunner:
         order of the entries and of each entry's ``want``.  The tensor may be a view of a
         buffer that the next step overwrites: use or copy it before the next ``run``."""
         self._validate(entries)
+        logits = None
         if self.use_graphs and all(len(entry.tokens) == 1 for entry in entries):
             logits = self._run_graph(entries)
-        else:
+        elif self.use_graphs and self.graph_portions:
+            logits = self._run_portion_graph(entries)
+        if logits is None:
             step, caches = self.prepare(entries, validated=True)
             logits = self.model.forward(step, caches)
         self.finish(entries)
@@ -203,6 +216,7 @@ class StepRunner:
         host[lay.first[0]:lay.first[1]] = 0
         host[lay.ctx[0]:lay.ctx[1]] = 0
         host[lay.slot[0]:lay.slot[1]] = 0
+        host[lay.want[0]:lay.want[1]] = 0      # wanted places beyond the entries' point at row 0
         for lo, hi in lay.maps:
             host[lo:hi] = -1
         for lo, hi in lay.tables:
@@ -353,6 +367,52 @@ class StepRunner:
         if not rows:
             return slot.logits[:0]
         return slot.logits[torch.tensor(rows, device=self.device)]
+
+    # -- steps with prompt portions from CUDA graphs --------------------------------------
+    def _run_portion_graph(self, entries: list[StepEntry]) -> torch.Tensor | None:
+        """A step with prompt portions (alone or beside decoding requests) replayed from a graph that was
+        captured for its size class: tokens, requests and wanted places rounded up to the class, the
+        rest padding (rows of segment -1 that every kernel skips, empty segments, wanted places that
+        point at row 0).  A class is captured the second time a step falls into it; until then, and for
+        steps beyond the largest class, None: the caller launches kernel by kernel.  Launching some 250
+        kernels from the host takes longer than a small step takes on the device; a replay does not."""
+        total = sum(len(entry.tokens) for entry in entries)
+        wanted = sum(len(entry.want) for entry in entries)
+        tokens = next((b for b in self.PORTION_BUCKETS if b >= total), None)
+        segments = next((b for b in self.PORTION_REQUEST_BUCKETS if b >= len(entries)), None)
+        if tokens is None or segments is None:
+            return None
+        segments = min(segments, self.max_segments, tokens)
+        places = 0 if wanted == 0 else (segments if wanted <= segments else tokens)   # none, at most one a request, or any
+        if wanted > places:
+            return None
+        longest = max(len(entry.tokens) for entry in entries)
+        # (the attention part picks its kernel by the longest portion: steps with and without a long one get graphs of their own)
+        key = ("portions", tokens, segments, places, self._graph_width(self._pages_after(entries)), longest >= 128)
+        slot = self._portion_graphs.get(key)
+        if slot is None:
+            seen = self._portion_classes_seen.get(key, 0) + 1
+            self._portion_classes_seen[key] = seen
+            if seen < 2:
+                return None
+            slot = _Graph(_Layout(tokens, segments, places, key[4], self._groups), self.device, True)
+            self._portion_graphs[key] = slot
+        if self._copy_pending:
+            self._copied.synchronize()
+            self._copy_pending = False
+        step = self._pack(entries, slot.host_np, slot.layout, wanted_all_rows=False)
+        step.max_context = None
+        slot.device.copy_(slot.host, non_blocking=True)
+        self.last_h2d_bytes = slot.layout.size * 4
+        self._copied.record()
+        self._copy_pending = True
+        if slot.graph is None:
+            self._capture(slot, step)
+        slot.graph.replay()
+        self.graph_replays += 1
+        self.portion_graph_replays += 1
+        self.graph_kernel_launches += slot.launches
+        return slot.logits[:wanted]
 
     # -- a decode step packed before its tokens are known ----------------------------
     def prepare_ahead(self, request_ids: list[str]) -> "_Ahead | None":

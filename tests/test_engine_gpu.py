@@ -232,6 +232,31 @@ def test_decode_steps_packed_ahead_give_the_same_tokens():
     assert again.cache.groups[0].pool.used_pages == 0 and again._flying is None
 
 
+def test_steps_with_prompt_portions_replayed_from_graphs_give_the_same_tokens():
+    """Steps with prompt portions fall into size classes (tokens, requests, wanted places rounded up, the rest
+    padding); a class is captured in a CUDA graph the second time it is met.  Prompts fed in small portions
+    beside decoding requests meet few classes many times: the tokens must be those of an engine that launches
+    every such step kernel by kernel, and the cache must come back empty."""
+    from llm_serving_engine_b200 import GenerationConfig
+    prompts = prompts_for("D", (70, 33, 5, 58, 41, 64), seed=8)
+    config = GenerationConfig(max_new_tokens=20, temperature=0.6, seed=5)
+    plain = engine_for("D", dtype="bfloat16", batch=4, pages=160, budget=24, chunk=16)
+    plain.runner.graph_portions = False
+    want = plain.generate_many(prompts, config)
+    assert plain.runner.portion_graph_replays == 0
+    graphs = engine_for("D", dtype="bfloat16", batch=4, pages=160, budget=24, chunk=16)
+    assert graphs.generate_many(prompts, config) == want
+    assert graphs.runner.portion_graph_replays > 10 and len(graphs.runner._portion_graphs) >= 2
+    assert not graphs.cache.requests and graphs.cache.groups[0].pool.used_pages == 0
+    # float32 too (the general attention kernel): bit for bit the same logits with and without padding rows
+    one = engine_for("B", dtype="float32", batch=3, budget=20, chunk=8)
+    two = engine_for("B", dtype="float32", batch=3, budget=20, chunk=8)
+    two.runner.graph_portions = False
+    few = prompts_for("B", (30, 9, 44), seed=2)
+    assert one.generate_many(few, GenerationConfig(max_new_tokens=6)) == two.generate_many(few, GenerationConfig(max_new_tokens=6))
+    assert one.runner.portion_graph_replays > 0
+
+
 def test_dependent_launch_off_gives_the_same_logits(tmp_path):
     """LSE_PDL=0 launches every kernel fully serialised; the logits must not change."""
     name = "D"
