@@ -175,10 +175,12 @@ _DECODE_MAX_SPLITS = int(__import__("os").environ.get("LSE_DECODE_MAX_SPLITS", "
 
 
 def decode_splits(tokens: int, n_q: int, n_kv: int, max_context: int | None) -> int:
-    """How many splits of the keys a decode launch uses: enough blocks to fill the GPU,
-    at least one 16-key tile per warp and split."""
+    """How many splits of the keys a decode launch uses: enough blocks to fill the GPU and a little
+    more (a block that ends early makes room for the next kernel's blocks), at least one 16-key
+    tile per warp and split."""
     base = tokens * n_kv * ((n_q // n_kv + 15) // 16)
-    splits = max(1, min(_DECODE_MAX_SPLITS, 148 // base))   # about one block per SM; at most 8: one cluster adds them up
+    # about 200 blocks (measured best from 12 to 64 rows: 192 blocks beat 128 and 256); at most 8 splits: one cluster adds them up
+    splits = max(1, min(_DECODE_MAX_SPLITS, 208 // base))
     if max_context is not None:
         splits = min(splits, max(1, -(-max_context // 64)))
     return splits
