@@ -14,6 +14,7 @@ the measured copy bandwidth, ``points`` decoding at batch 1 and 64.
 from __future__ import annotations
 
 import argparse
+import gc
 import json
 import os
 import subprocess
@@ -282,14 +283,7 @@ def run_ours(args) -> dict:
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic (random weights, uniform random token ids)", "impl": "ours",
-        "config": {
-            "model": "Qwen2.5-1.5B shape", "layers": layers, "layers_full": FULL_LAYERS, "hidden": config["hidden_size"],
-            "heads": config["num_attention_heads"], "kv_heads": config["num_key_value_heads"],
-            "head_dim": config["hidden_size"] // config["num_attention_heads"],
-            "intermediate": config["intermediate_size"], "vocab": config["vocab_size"], "tied": True,
-            "global_batch": batch, "seq_len": PROMPT, "context": config["max_position_embeddings"],
-            "kv_block": BLOCK, "parallelism": "single GPU", "l2": "inputs larger than L2 (weights 3 GB per step)",
-        },
+        "config": bench_config(config, layers, batch),
         "prefill": {"value": round(PROMPT / (prefill_ms / 1e3), 1), "tokens": PROMPT, "ms": round(prefill_ms, 3),
                     "frac": round(flops / (prefill_ms / 1e3) / (peak["bf16_tflops"] * 1e12), 4)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak["hbm_gbs"], "unit": "GB/s",
@@ -299,6 +293,223 @@ def run_ours(args) -> dict:
                 "pipeline": "one decode step in flight: every step copies its metadata from pinned host memory and its "
                             "tokens to the host; the tokens feed the next step on the device"},
         "gpu_launches": launches,
+        "clocks": clocks.summary(),
+    }
+
+
+def bench_config(config: dict, layers: int, batch: int) -> dict:
+    """The ``config`` of the bench line: every size, flat; the same dict in both arms."""
+    return {
+        "model": "Qwen2.5-1.5B shape", "layers": layers, "layers_full": FULL_LAYERS, "hidden": config["hidden_size"],
+        "heads": config["num_attention_heads"], "kv_heads": config["num_key_value_heads"],
+        "head_dim": config["hidden_size"] // config["num_attention_heads"],
+        "intermediate": config["intermediate_size"], "vocab": config["vocab_size"], "tied": True,
+        "global_batch": batch, "seq_len": PROMPT, "context": config["max_position_embeddings"],
+        "kv_block": BLOCK, "parallelism": "single GPU", "l2": "inputs larger than L2 (weights 3 GB per step)",
+    }
+
+
+# -- the reference arm -----------------------------------------------------------------------
+REFERENCE_DIR = os.path.join(ROOT, "baseline", "_ref")
+
+
+def install_reference() -> str:
+    """Put the unmodified reference into ``baseline/_ref`` (once, where its source tree is at hand) and
+    return how.  The offline ``pip install`` is tried first; the reference's build backend (hatchling) is
+    not in the wheelhouse, and its wheel is nothing but the pure-Python package ``src/llmserve``
+    (``pyproject.toml``: ``packages = ["src/llmserve"]``), so a plain copy of that folder is the install."""
+    import shutil
+
+    if os.path.exists(os.path.join(REFERENCE_DIR, "llmserve", "engine.py")):
+        return "present"
+    source = os.environ.get("LLMSERVE_REFERENCE", "/root/reference")
+    if not os.path.isdir(os.path.join(source, "src", "llmserve")):
+        return ""
+    os.makedirs(REFERENCE_DIR, exist_ok=True)
+    pip = subprocess.run([sys.executable, "-m", "pip", "install", "--no-index", "--no-build-isolation", "--no-deps",
+                          "--find-links", "/opt/wheelhouse", "--target", REFERENCE_DIR, source],
+                         capture_output=True, text=True)
+    if pip.returncode == 0 and os.path.exists(os.path.join(REFERENCE_DIR, "llmserve", "engine.py")):
+        return "pip"
+    shutil.copytree(os.path.join(source, "src", "llmserve"), os.path.join(REFERENCE_DIR, "llmserve"),
+                    ignore=shutil.ignore_patterns("__pycache__"), dirs_exist_ok=True)
+    return "copy of src/llmserve (pip: no hatchling in the wheelhouse)"
+
+
+def run_reference(args) -> dict:
+    """The same metric and configuration through the UNMODIFIED reference: ``llmserve`` imported from
+    ``baseline/_ref`` and nowhere else, its ``Transformer(ModelConfig(...))`` with its own random
+    initialisation (``src/llmserve/cli.py:39-41``), its stock CUDA path (float16, ``cli.py:34``; Triton paged
+    attention, ``engine.py:140-155``) and its public API (``LLMEngine.generate`` with per-token callbacks,
+    ``engine.py:188-221``).  Nothing of this repository's package is imported.
+
+    Device time per step comes from the CUDA event pairs that the reference records around every
+    iteration when ``collect_iteration_metrics`` is on (the list behind its ``iteration_stats``,
+    ``engine.py:246-254,358-370,438-458``): the decode iterations in which all requests decode together,
+    the first ``--warmup`` of them left out, the next ``--steps`` taken.  ``e2e`` is measured from the
+    callbacks' time stamps over the same iterations, as in this repository's own arm."""
+    how = install_reference()
+    if not how:
+        return {"impl": "reference", "unavailable": "baseline/_ref holds no install of the reference and its source tree is not at hand"}
+    sys.path.insert(0, REFERENCE_DIR)
+    try:
+        import asyncio
+
+        import torch
+        import llmserve
+        from llmserve.config import CacheConfig, ModelConfig, SchedulerConfig
+        from llmserve.engine import GenerationConfig, LLMEngine
+        from llmserve.model import Transformer
+        from llmserve.tokenizer import ByteTokenizer
+        from llmserve.triton_kernels import is_triton_paged_attention_available
+    except Exception as error:   # a missing dependency of the reference
+        return {"impl": "reference", "unavailable": f"the reference does not import: {type(error).__name__}: {error}"}
+    if not os.path.abspath(llmserve.__file__).startswith(REFERENCE_DIR):
+        return {"impl": "reference", "unavailable": f"llmserve was imported from {llmserve.__file__}, not from baseline/_ref"}
+    if "llm_serving_engine_b200" in sys.modules:
+        raise RuntimeError("the reference arm must not load this repository's package")
+    torch.cuda.set_device(0)
+    device = torch.device("cuda")
+    layers = args.layers or FULL_LAYERS
+    config = dict(QWEN25_1P5B, num_hidden_layers=layers)
+    peak = peaks()
+    torch.manual_seed(0)
+    model = Transformer(ModelConfig.from_dict(config))
+    model = model.to(device=device, dtype=torch.float16).eval()
+    backend = "triton" if is_triton_paged_attention_available(device) else "pytorch"
+    if backend == "pytorch":
+        return {"impl": "reference", "unavailable": "the reference's Triton paged attention reports itself unavailable on this GPU; "
+                "its PyTorch block loop walks every (row, block) pair in Python: hours for 2,048-token prompts"}
+    weight_bytes = sum(p.numel() * p.element_size() for p in model.parameters())   # tied head counted once
+    kv_bytes_per_token = 2 * layers * config["num_key_value_heads"] * (config["hidden_size"] // config["num_attention_heads"]) * 2
+
+    def make_engine(batch: int):
+        return LLMEngine(model, ByteTokenizer(), cache_config=CacheConfig(BLOCK, batch * (config["max_position_embeddings"] // BLOCK)),
+                         scheduler_config=SchedulerConfig(max_batch_size=batch, max_tokens_per_step=max(PROMPT, batch)),
+                         paged_attention_backend=backend, prefill_chunk_size=PROMPT, collect_iteration_metrics=True,
+                         device=device, dtype=torch.float16)
+
+    def decode_run(batch: int, steps: int, warmup: int, inference_mode: bool = False):
+        """(device ms per full-batch decode step, its median, end-to-end tokens/s over the same steps, the
+        engine's stats).  ``inference_mode``: the driver wraps the run in ``torch.inference_mode()``."""
+        with torch.inference_mode(inference_mode):
+            return _decode_run(batch, steps, warmup)
+
+    def _decode_run(batch: int, steps: int, warmup: int):
+        engine = make_engine(batch)
+        generator = torch.Generator().manual_seed(3)
+        prompts = [torch.randint(0, config["vocab_size"], (PROMPT,), generator=generator).tolist() for _ in range(batch)]
+        new_tokens = warmup + steps + 2 * batch + 2
+        stamps: list[tuple[float, int]] = []
+
+        def make_callback(index: int):
+            def callback(_token: int) -> None:
+                stamps.append((time.perf_counter(), index))
+            return callback
+
+        async def drive():
+            try:
+                await asyncio.gather(*[engine.generate(prompt, GenerationConfig(max_new_tokens=new_tokens, temperature=0.0),
+                                                       make_callback(index)) for index, prompt in enumerate(prompts)])
+                return engine.iteration_stats
+            finally:
+                await engine.close()
+
+        stats = asyncio.run(drive())
+        # iterations in which all requests decode together: from the one after the last request got its first
+        # token to the one in which the first request got its last token; one stamp per request and iteration
+        counts = [0] * batch
+        first_full = last_full = None
+        for position, (_, index) in enumerate(stamps):
+            counts[index] += 1
+            if first_full is None and min(counts) >= 1:
+                first_full = position + 1
+            if last_full is None and max(counts) >= new_tokens:
+                last_full = position        # the first request's last token opens an iteration: that one is left out
+        full = stamps[first_full:last_full]
+        iterations = len(full) // batch
+        if len(full) != iterations * batch or iterations < warmup + steps:
+            raise RuntimeError(f"reference arm: {len(full)} stamps in the all-decoding window do not make {warmup + steps} steps of {batch}")
+        events = engine._iteration_cuda_events["decode"][:iterations]    # the list behind iteration_stats
+        times = sorted(a.elapsed_time(b) for a, b in events[warmup:warmup + steps])
+        ms = sum(times) / len(times)
+        begin = full[warmup * batch - 1][0] if warmup else stamps[first_full - 1][0]
+        end = full[(warmup + steps) * batch - 1][0]
+        e2e = steps * batch / max(end - begin, 1e-9)
+        del engine, drive, make_callback
+        gc.collect()
+        torch.cuda.empty_cache()
+        return ms, times[len(times) // 2], e2e, stats
+
+    def prefill_run(repeats: int = 5):
+        engine = make_engine(1)
+        generator = torch.Generator().manual_seed(2)
+        prompt = torch.randint(0, config["vocab_size"], (PROMPT,), generator=generator).tolist()
+
+        async def drive():
+            try:
+                for _ in range(repeats + 2):
+                    await engine.generate(prompt, GenerationConfig(max_new_tokens=1, temperature=0.0))
+                return engine.iteration_stats
+            finally:
+                await engine.close()
+
+        asyncio.run(drive())
+        times = sorted(a.elapsed_time(b) for a, b in engine._iteration_cuda_events["prefill"][2:])
+        del engine, drive
+        gc.collect()
+        torch.cuda.empty_cache()
+        return times[len(times) // 2]
+
+    # The reference decorates its async ``_step`` with ``@torch.inference_mode()`` (``engine.py:244``); on a
+    # coroutine function that only covers the creation of the coroutine, so its stock path runs with autograd on:
+    # the in-place cache write (``kv_cache.py:265-266``) chains every step's graph to the cache tensor and the
+    # activations of all earlier steps stay allocated (about 3 GB per 2,048-token step here).  ``value`` and ``e2e``
+    # are that stock path; the same run under the driver's ``torch.inference_mode()`` is given beside it.  Batch 64
+    # (65 prompt steps) runs out of 180 GB on the stock path and is measured under inference mode only.
+    batch = args.batch
+    stock = batch <= 16
+    with ClockSampler() as clocks:
+        ms, median_ms, e2e_value, stats = decode_run(batch, args.steps, args.warmup, inference_mode=not stock)
+    guarded = None
+    if stock:
+        guarded_ms, _, guarded_e2e, _ = decode_run(batch, args.steps, args.warmup, inference_mode=True)
+        guarded = {"value": round(batch / (guarded_ms / 1e3), 1), "ms_per_step": round(guarded_ms, 4), "e2e": round(guarded_e2e, 1)}
+    kv_bytes = batch * (PROMPT + args.warmup + args.steps // 2 + batch) * kv_bytes_per_token
+    achieved = (weight_bytes + kv_bytes) / (ms / 1e3) / 1e9
+    prefill_ms = prefill_run()
+    flops = prefill_flops(config, layers, PROMPT)
+    points, notes = {}, {}
+    for point_batch in (1, 64):
+        try:
+            point_ms, _, _, _ = decode_run(point_batch, max(args.steps // 2, 8), args.warmup, inference_mode=point_batch > 16)
+            points[f"decode_b{point_batch}"] = round(point_batch / (point_ms / 1e3), 1)
+            if point_batch > 16:
+                notes[f"decode_b{point_batch}"] = "under the driver's torch.inference_mode()"
+        except Exception as error:
+            points[f"decode_b{point_batch}"] = None
+            notes[f"decode_b{point_batch}"] = f"{type(error).__name__}: {str(error)[:160]}"
+            torch.cuda.empty_cache()
+    return {
+        "metric": "decode tok/s at batch 8 (Qwen2.5-1.5B shape, 2,048-token prompts)",
+        "value": round(batch / (ms / 1e3), 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms, 4), "ms_per_step_median": round(median_ms, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "fp16", "data": "synthetic (random weights, uniform random token ids)",
+        "impl": "reference", "install": how, "attention_backend": backend,
+        "config": bench_config(config, layers, batch),
+        "prefill": {"value": round(PROMPT / (prefill_ms / 1e3), 1), "tokens": PROMPT, "ms": round(prefill_ms, 3),
+                    "frac": round(flops / (prefill_ms / 1e3) / (peak["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / peak["hbm_gbs"], 4), "peaks": peak["source"]},
+        "points": points, "points_notes": notes,
+        "autograd": "on (stock: the reference's inference_mode decorator sits on an async function and has no effect)" if stock
+                    else "off (driver's torch.inference_mode())",
+        "under_inference_mode": guarded,
+        "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s",
+                "h2d_bytes_per_step": batch * (8 + 8 + 4 * 4), "d2h_bytes_per_step": batch * 8,
+                "pipeline": "the reference's own loop: token ids, positions (int64) and four int32 metadata arrays from pinned "
+                            "host memory every step, sampled ids back through .tolist()"},
+        "iteration_stats": {key: (round(value, 3) if isinstance(value, float) else value) for key, value in stats.items()},
         "clocks": clocks.summary(),
     }
 
@@ -398,13 +609,13 @@ def main() -> int:
         QWEN25_1P5B.update(QWEN25_7B_SIZES)
     if args.timeline:
         return timeline(args)
-    if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "offline pip install of the reference fails: its build backend (hatchling) is not in the wheelhouse"}))
-        return 0
     if args.gpus != 1:
         print(f"bench.py measures a single-GPU engine; --gpus {args.gpus} is not supported")
         return 2
+    if args.impl == "reference":
+        args.warmup = max(args.warmup, 3)
+        print(json.dumps(run_reference(args)))
+        return 0
     if args.only == "all":
         args.warmup = max(args.warmup, 3)
     print(json.dumps(run_ours(args)))

@@ -11,18 +11,15 @@ from ..parts.base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, BuildContext, Re
 from ..parts.linear import linear
 from ..weights.tensor_spec import TensorSpec
 
-_MIXER_PREFIX = "self_attn."
-_FF_PREFIX = "mlp."
+_PART_ROLES = ("mixer_norm", "mixer", "feed_forward_norm", "feed_forward")
 
 
 def _layer_part_prefixes(layer: LayerSpec) -> dict[str, str]:
+    """Full tensor prefix of each part of a layer: the layer's own prefix followed by the part's,
+    which the architecture's builder gives in ``block.params["tensor_prefixes"]`` (a role that is
+    not named there is called by its role: ``mixer.``, ``feed_forward_norm.`` and so on)."""
     names = dict(layer.block.params.get("tensor_prefixes", {}))
-    return {
-        "mixer": layer.prefix + names.get("mixer", _MIXER_PREFIX),
-        "feed_forward": layer.prefix + names.get("feed_forward", _FF_PREFIX),
-        "mixer_norm": layer.prefix + names.get("mixer_norm", "input_layernorm."),
-        "feed_forward_norm": layer.prefix + names.get("feed_forward_norm", "post_attention_layernorm."),
-    }
+    return {role: layer.prefix + names.get(role, role + ".") for role in _PART_ROLES}
 
 
 def _layer_parts(layer: LayerSpec) -> list[tuple[str, type, PartSpec]]:
@@ -98,8 +95,14 @@ class DecoderModel:
 
     @property
     def graph_safe(self) -> bool:
-        """Whether a decode step of this model can be captured in a CUDA graph."""
-        return all(getattr(block.mixer, "graph_safe", False) for block in self.blocks)
+        """Whether a step of this model can be captured in a CUDA graph: every block, every part of
+        every block (mixer, its position encoding, feed-forward, both norms) and the final norm say so."""
+        for block in self.blocks:
+            if not getattr(block, "graph_safe", False):
+                return False
+            if not all(getattr(part, "graph_safe", False) for part in block.parts()):
+                return False
+        return bool(getattr(self.final_norm, "graph_safe", False))
 
     @property
     def vocab_size(self) -> int:

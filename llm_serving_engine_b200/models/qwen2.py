@@ -29,7 +29,10 @@ def build_qwen2_spec(config: Qwen2Config) -> ModelSpec:
         "position": position,
     })
     feed_forward = PartSpec("swiglu", {"intermediate_size": config.intermediate_size})
-    block = PartSpec("prenorm_residual", {})
+    block = PartSpec("prenorm_residual", {"tensor_prefixes": {
+        "mixer_norm": "input_layernorm.", "mixer": "self_attn.",
+        "feed_forward_norm": "post_attention_layernorm.", "feed_forward": "mlp.",
+    }})
     layers = tuple(
         LayerSpec(prefix=f"model.layers.{index}.", block=block, mixer=mixer, feed_forward=feed_forward,
                   mixer_norm=norm, feed_forward_norm=norm)

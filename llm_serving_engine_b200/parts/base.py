@@ -71,6 +71,12 @@ class ResidualStream:
 
 
 class Part:
+    # True when the part only launches work whose shape depends on the number of rows and reads
+    # everything else (positions, segments, tables, routing decisions) from device memory, without
+    # waiting for the device: a step made of such parts can be captured in a CUDA graph and
+    # replayed with other contents.  A model is captured only if every part of it says so.
+    graph_safe = False
+
     def __init__(self, params: dict[str, Any], weights: dict[str, torch.Tensor], ctx: BuildContext) -> None:
         self.params = params
         self.ctx = ctx
@@ -91,11 +97,6 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
-    # True when ``forward`` only launches work whose shape depends on the number of rows and
-    # reads everything else (positions, segments, tables) from device memory: such a step
-    # can be captured in a CUDA graph and replayed with other contents.
-    graph_safe = False
-
     @classmethod
     def cache_requirement(cls, params: dict[str, Any], hidden_size: int):
         """``PagedKV``, ``RequestState`` or ``None``."""
@@ -111,11 +112,21 @@ class FeedForward(Part):
 
 
 class Block:
+    graph_safe = False     # as for ``Part``: the arrangement itself launches nothing that depends on the step's contents
+
     def __init__(self, params, mixer_norm: Norm, mixer: Mixer, feed_forward_norm: Norm,
                  feed_forward: FeedForward) -> None:
         self.params = params
         self.mixer_norm, self.mixer = mixer_norm, mixer
         self.feed_forward_norm, self.feed_forward = feed_forward_norm, feed_forward
+
+    def parts(self) -> list:
+        """Every part this block runs (a mixer's position encoding included)."""
+        found = [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward]
+        position = getattr(self.mixer, "position", None)
+        if position is not None:
+            found.append(position)
+        return found
 
     def forward(self, stream: ResidualStream, step, cache) -> None:
         raise NotImplementedError

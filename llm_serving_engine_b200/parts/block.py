@@ -10,6 +10,8 @@ class PreNormResidualBlock(Block):
     (reference ``src/llmserve/model.py:199-201,233-234``).  Each branch output
     stays pending in the stream; the next norm adds it to the float32 residual."""
 
+    graph_safe = True
+
     def forward(self, stream: ResidualStream, step, cache) -> None:
         x = self.mixer_norm.forward(stream)
         stream.delta = self.mixer.forward(x, step, cache)

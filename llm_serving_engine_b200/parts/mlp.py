@@ -32,6 +32,8 @@ class SwiGLU(FeedForward):
     """params: ``intermediate_size``, optional ``fuse_gate`` (0, 32 or 64).  y = down(silu(gate(x)) * up(x)),
     no biases; gate and up are stacked into one matrix when the part is built."""
 
+    graph_safe = True
+
     def __init__(self, params, weights, ctx) -> None:
         super().__init__(params, weights, ctx)
         self.inter = int(params["intermediate_size"])

@@ -13,6 +13,8 @@ class RMSNorm(Norm):
     """params: ``eps``.  y = (x * rsqrt(mean(x^2) + eps)) * weight, where x is the
     float32 residual after the pending branch output has been added to it."""
 
+    graph_safe = True
+
     def __init__(self, params, weights, ctx) -> None:
         super().__init__(params, weights, ctx)
         self.eps = float(params["eps"])

@@ -14,6 +14,8 @@ class RotaryEncoding(PositionEncoding):
     (i, i + D/2)).  Angles are position * 1/theta^(2i/D) in float32
     (``src/llmserve/model.py:29-31``), computed in the kernel from the position."""
 
+    graph_safe = True
+
     def __init__(self, params, weights, ctx) -> None:
         super().__init__(params, weights, ctx)
         head_dim = int(params["head_dim"])

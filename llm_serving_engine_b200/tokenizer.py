@@ -1,5 +1,6 @@
-"""Tokenizers in the reference's manner (``src/llmserve/tokenizer.py``): the engine
-works on token ids; these turn text into ids for the command line."""
+"""The byte tokenizer of the reference (``src/llmserve/tokenizer.py:15-28``): the engine
+works on token ids; this turns text into ids for the command line's demo model.
+Text tokenizers of real checkpoints are outside this engine: it takes token ids."""
 from __future__ import annotations
 
 
@@ -16,21 +17,3 @@ class ByteTokenizer:
 
     def decode(self, token_ids: list[int]) -> str:
         return bytes(token - 4 for token in token_ids if 4 <= token < 260).decode("utf-8", errors="replace")
-
-
-class HuggingFaceTokenizer:
-    """The tokenizer files of a model folder, through ``transformers.AutoTokenizer``
-    (tokenization only; no model code of that package is used)."""
-
-    def __init__(self, model_path: str) -> None:
-        from transformers import AutoTokenizer
-
-        self.inner = AutoTokenizer.from_pretrained(model_path, trust_remote_code=False)
-        self.eos_token_id = int(self.inner.eos_token_id)
-        self.vocab_size = int(self.inner.vocab_size)
-
-    def encode(self, text: str) -> list[int]:
-        return list(self.inner.encode(text, add_special_tokens=False))
-
-    def decode(self, token_ids: list[int]) -> str:
-        return self.inner.decode(token_ids, skip_special_tokens=True)
