@@ -1,9 +1,15 @@
-"""The ``llmserve`` command line, in the reference's manner (``src/llmserve/cli.py``).
+"""The ``llmserve`` command line.
 
-``benchmark`` keeps the reference's option names and meanings (``cli.py:248-275``);
-options of parts this engine does not have (the HTTP service, quantized linear
-layers, the choice of an attention backend, rebuilt device metadata) are left
-out.  ``generate`` is this engine's own: ids in, ids out.
+``benchmark`` has the option names and meanings of the reference's subcommand
+(``src/llmserve/cli.py:244-316``): ``--config {naive,paged,static,continuous}``, ``--policy``,
+``--profile``, ``--model``, ``--device``, ``--requests``, ``--arrival-rate``, ``--batch-size``,
+``--block-size``, ``--num-blocks``, ``--prefill-chunk-size``, ``--max-tokens-per-step``, ``--seed``,
+``--output``.  Options of parts this engine does not have are absent (the HTTP service, quantized
+linear layers, a choice of attention backend, rebuilt device metadata).  ``generate`` (token ids in,
+token ids out) and ``replay`` (the trace replay program) are this engine's own.
+
+Without ``--model`` a small random model stands in, as in the reference (``cli.py:39-41``);
+``--random NAME`` picks which one (``tiny`` is the reference's bundled demo size).
 """
 from __future__ import annotations
 
@@ -11,50 +17,63 @@ import argparse
 import asyncio
 import json
 import sys
-from dataclasses import replace
 from pathlib import Path
 
+# Random stand-in models by name: config.json contents of the architecture, sizes only.
+RANDOM_MODELS = {
+    # the reference's ModelConfig.tiny (src/llmserve/config.py:34-44) over the byte tokenizer's vocabulary
+    "tiny": dict(vocab_size=260, hidden_size=128, intermediate_size=352, num_hidden_layers=4, num_attention_heads=4,
+                 num_key_value_heads=2, max_position_embeddings=1024, rope_theta=10000.0, rms_norm_eps=1e-6),
+    "small": dict(vocab_size=4096, hidden_size=512, intermediate_size=1376, num_hidden_layers=8, num_attention_heads=8,
+                  num_key_value_heads=2, max_position_embeddings=4096, rope_theta=10000.0, rms_norm_eps=1e-6),
+}
 
-def tiny_config(vocab_size: int = 260) -> dict:
-    """The bundled demo model of the reference (``ModelConfig.tiny``, ``src/llmserve/config.py:34-44``)."""
-    return {
-        "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "vocab_size": vocab_size,
-        "hidden_size": 128, "intermediate_size": 352, "num_hidden_layers": 4, "num_attention_heads": 4,
-        "num_key_value_heads": 2, "max_position_embeddings": 1024, "rope_theta": 10000.0,
-        "rms_norm_eps": 1e-6, "attention_bias": True, "tie_word_embeddings": True,
-    }
+
+def tiny_config(vocab_size: int = 260, name: str = "tiny") -> dict:
+    """config.json of a random stand-in model."""
+    return {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "attention_bias": True,
+            "tie_word_embeddings": True, **RANDOM_MODELS[name], "vocab_size": vocab_size}
 
 
-def _device(name: str) -> str:
-    import torch
+class _Runtime:
+    """What the subcommands share: the model, a tokenizer if text can be handled, engine settings."""
 
-    if name in ("auto", "cuda") or name.startswith("cuda:"):
+    def __init__(self, args) -> None:
+        import torch
+
+        from .models import load_model, random_model
+        from .tokenizer import ByteTokenizer
+
+        if args.device not in ("auto", "cuda") and not args.device.startswith("cuda:"):
+            raise SystemExit(f"llmserve: device {args.device!r}: this engine runs on CUDA devices only")
         if not torch.cuda.is_available():
             raise SystemExit("llmserve: no CUDA device; this engine has no CPU path")
-        return "cuda" if name == "auto" else name
-    raise SystemExit(f"llmserve: device {name!r} is not supported; this engine runs on CUDA only")
+        device = "cuda" if args.device == "auto" else args.device
+        self.args = args
+        if args.model:
+            self.model = load_model(args.model, dtype=args.dtype, device=device)
+            self.tokenizer = None        # a model folder is served by token ids; text tokenizers are outside this engine
+        else:
+            self.tokenizer = ByteTokenizer()
+            vocab = max(self.tokenizer.vocab_size, RANDOM_MODELS[args.random]["vocab_size"])
+            self.model = random_model(tiny_config(vocab, args.random), args.seed, dtype=args.dtype, device=device)
 
+    def engine(self, *, batch_size=None, mode="continuous", policy="fcfs", metrics=False):
+        from .config.runtime_config import CacheConfig, SchedulerConfig
+        from .engine.llm_engine import LLMEngine
 
-def _load_runtime(args):
-    from .models import load_model, random_model
-    from .tokenizer import ByteTokenizer, HuggingFaceTokenizer
-
-    device = _device(args.device)
-    if args.model:
-        model = load_model(args.model, dtype=args.dtype, device=device)
-        try:
-            tokenizer = HuggingFaceTokenizer(args.model)
-        except Exception:
-            tokenizer = None  # a folder without tokenizer files still serves token ids
-    else:
-        tokenizer = ByteTokenizer()
-        model = random_model(tiny_config(tokenizer.vocab_size), args.seed, dtype=args.dtype, device=device)
-    return model, tokenizer
+        args = self.args
+        return LLMEngine(self.model, self.tokenizer,
+                         cache_config=CacheConfig(block_size=args.block_size, num_blocks=args.num_blocks),
+                         scheduler_config=SchedulerConfig(max_batch_size=batch_size or args.batch_size,
+                                                          max_tokens_per_step=args.max_tokens_per_step, policy=policy),
+                         scheduler_mode=mode, prefill_chunk_size=args.prefill_chunk_size,
+                         collect_iteration_metrics=metrics)
 
 
 class NaiveDecoder:
-    """Sequential baseline: recompute the whole prefix for every token
-    (``src/llmserve/engine.py:75-105``), through the same step function."""
+    """The sequential baseline of ``--config naive``: every token recomputes its whole prefix
+    (``src/llmserve/engine.py:75-105``), here as one whole-prompt step of the same step function."""
 
     def __init__(self, model) -> None:
         from .cache.manager import CacheManager
@@ -68,111 +87,97 @@ class NaiveDecoder:
                                   model.device, limit, num_state_slots=1)
         self.runner = StepRunner(model, self.cache, limit, 1)
         self.sampler = Sampler(model.vocab_size, 1, model.device)
-        self._lock = asyncio.Lock()
+        self._turn = asyncio.Lock()
 
     async def generate(self, prompt_token_ids, config, callback=None) -> list[int]:
         from .engine.step import StepEntry
 
-        async with self._lock:
-            output: list[int] = []
-            for _ in range(config.max_new_tokens):
-                tokens = list(prompt_token_ids) + output
+        produced: list[int] = []
+        async with self._turn:
+            while len(produced) < config.max_new_tokens:
+                prefix = [*prompt_token_ids, *produced]
                 self.cache.create("naive")
                 try:
-                    logits = self.runner.run([StepEntry("naive", tokens, [len(tokens) - 1])])
-                    token = self.sampler.sample(logits, [config], [len(output)])[0]
+                    logits = self.runner.run([StepEntry("naive", prefix, [len(prefix) - 1])])
+                    token = self.sampler.sample(logits, [config], [len(produced)])[0]
                 finally:
                     self.cache.free("naive")
-                output.append(token)
-                if callback:
+                produced.append(token)
+                if callback is not None:
                     callback(token)
                 if token in config.stop_token_ids:
                     break
                 await asyncio.sleep(0)
-            return output
+        return produced
 
 
-async def _benchmark(args) -> None:
-    from .config.runtime_config import CacheConfig, SchedulerConfig
-    from .engine.llm_engine import LLMEngine
+def run_benchmark(args) -> dict:
+    """``llmserve benchmark``: synthetic traffic of the profile against one of four serving set-ups."""
     from .sampling.sampler import GenerationConfig
-    from .workload import LoadProfile, run_open_loop
+    from .workload import TrafficProfile, make_traffic, replay_traffic, summarise
 
-    model, tokenizer = _load_runtime(args)
-    profile = LoadProfile.from_yaml(args.profile) if args.profile and Path(args.profile).exists() else LoadProfile()
-    limit = model.spec.max_position_embeddings
-    profile = replace(
-        profile,
-        requests=args.requests or profile.requests,
-        arrival_rate=args.arrival_rate or profile.arrival_rate,
-        vocabulary_size=model.vocab_size,
-        prompt=replace(profile.prompt, maximum=min(profile.prompt.maximum, limit - profile.output.maximum)),
-    )
+    runtime = _Runtime(args)
+    model = runtime.model
+    profile = TrafficProfile.from_file(args.profile) if args.profile and Path(args.profile).exists() else TrafficProfile()
+    overrides = {key: value for key, value in (("requests", args.requests), ("arrival_rate", args.arrival_rate)) if value}
+    profile = TrafficProfile(**{**vars(profile), **overrides}).fitted_to(model.vocab_size, model.spec.max_position_embeddings)
+    traffic = make_traffic(profile)
 
-    def generation_for(spec):
-        return GenerationConfig(max_new_tokens=spec.max_new_tokens, temperature=0.0, seed=args.seed)
+    def sampling(item):
+        return GenerationConfig(max_new_tokens=item.max_new_tokens, temperature=0.0, seed=args.seed)
 
-    engine = None
-    if args.config == "naive":
-        decoder = NaiveDecoder(model)
+    async def drive():
+        if args.config == "naive":
+            decoder = NaiveDecoder(model)
+            return await replay_traffic(f"naive-{args.policy}", traffic, lambda item, on_token: decoder.generate(
+                item.prompt_token_ids, sampling(item), on_token)), None
+        engine = runtime.engine(batch_size=1 if args.config == "paged" else None, policy=args.policy, metrics=True,
+                                mode="static" if args.config == "static" else "continuous")
+        async with engine:
+            result = await replay_traffic(f"{args.config}-{args.policy}", traffic, lambda item, on_token: engine.generate(
+                list(item.prompt_token_ids), sampling(item), on_token, request_id=item.request_id))
+            result.cache = engine.cache_stats
+            result.extra["engine"] = engine.iteration_stats
+        return result, engine
 
-        async def generate(spec, callback):
-            return await decoder.generate(list(spec.prompt_token_ids), generation_for(spec), callback)
-    else:
-        engine = LLMEngine(
-            model, tokenizer,
-            cache_config=CacheConfig(block_size=args.block_size, num_blocks=args.num_blocks),
-            scheduler_config=SchedulerConfig(max_batch_size=1 if args.config == "paged" else args.batch_size,
-                                             max_tokens_per_step=args.max_tokens_per_step, policy=args.policy),
-            scheduler_mode="static" if args.config == "static" else "continuous",
-            prefill_chunk_size=args.prefill_chunk_size, collect_iteration_metrics=True)
-
-        async def generate(spec, callback):
-            return await engine.generate(list(spec.prompt_token_ids), generation_for(spec), callback,
-                                         request_id=spec.request_id)
-
-    report = await run_open_loop(f"{args.config}-{args.policy}", profile, generate)
-    if engine:
-        report.cache = engine.cache_stats
-        report.metadata["engine"] = engine.iteration_stats
-        await engine.close()
-    output = Path(args.output)
-    output.parent.mkdir(parents=True, exist_ok=True)
-    output.write_text(json.dumps(report.to_dict(), indent=2) + "\n")
-    print(json.dumps(report.summary, indent=2))
+    result, _ = asyncio.run(drive())
+    result.extra["profile"] = {**{k: v for k, v in vars(profile).items() if k not in ("prompt", "output")},
+                               "prompt": vars(profile.prompt), "output": vars(profile.output)}
+    target = Path(args.output)
+    target.parent.mkdir(parents=True, exist_ok=True)
+    target.write_text(json.dumps(result.as_dict(), indent=2) + "\n")
+    summary = summarise(result)
+    print(json.dumps(summary, indent=2))
+    return summary
 
 
-def _generate(args) -> None:
-    from .config.runtime_config import CacheConfig, SchedulerConfig
-    from .engine.llm_engine import LLMEngine
+def run_generate(args) -> list[dict]:
+    """``llmserve generate``: one JSON line per prompt with its ids and the generated ids."""
     from .sampling.sampler import GenerationConfig
 
-    model, tokenizer = _load_runtime(args)
-    prompts = []
-    for text in args.prompt_ids or []:
-        prompts.append([int(item) for item in text.replace(",", " ").split()])
+    runtime = _Runtime(args)
+    prompts = [[int(item) for item in text.replace(",", " ").split()] for text in args.prompt_ids or []]
     for text in args.prompt or []:
-        if tokenizer is None:
-            raise SystemExit("llmserve: --prompt needs a tokenizer; pass --prompt-ids")
-        prompts.append(tokenizer.encode(text))
+        if runtime.tokenizer is None:
+            raise SystemExit("llmserve generate: --prompt needs a tokenizer (the random model has one); give --prompt-ids")
+        prompts.append(runtime.tokenizer.encode(text))
     if not prompts:
         raise SystemExit("llmserve generate: give --prompt-ids or --prompt")
-    engine = LLMEngine(model, tokenizer,
-                       cache_config=CacheConfig(block_size=args.block_size, num_blocks=args.num_blocks),
-                       scheduler_config=SchedulerConfig(max_batch_size=args.batch_size,
-                                                        max_tokens_per_step=args.max_tokens_per_step),
-                       prefill_chunk_size=args.prefill_chunk_size)
-    config = GenerationConfig(max_new_tokens=args.max_new_tokens, temperature=args.temperature, top_p=args.top_p,
-                              seed=args.seed, stop_token_ids=tuple(args.stop_token_ids or ()))
-    for prompt, output in zip(prompts, engine.generate_many(prompts, config)):
+    sampling = GenerationConfig(max_new_tokens=args.max_new_tokens, temperature=args.temperature, top_p=args.top_p,
+                                seed=args.seed, stop_token_ids=tuple(args.stop_token_ids or ()))
+    records = []
+    for prompt, output in zip(prompts, runtime.engine().generate_many(prompts, sampling)):
         record = {"prompt_ids": prompt, "output_ids": output}
-        if tokenizer is not None:
-            record["text"] = tokenizer.decode(output)
+        if runtime.tokenizer is not None:
+            record["text"] = runtime.tokenizer.decode(output)
         print(json.dumps(record))
+        records.append(record)
+    return records
 
 
 def _engine_options(parser: argparse.ArgumentParser) -> None:
-    parser.add_argument("--model", help="folder with config.json and safetensors (default: a random tiny model)")
+    parser.add_argument("--model", help="folder with config.json and safetensors (default: a random stand-in model)")
+    parser.add_argument("--random", choices=sorted(RANDOM_MODELS), default="tiny", help="which random stand-in model")
     parser.add_argument("--device", default="auto")
     parser.add_argument("--dtype", choices=("bfloat16", "float32"), default="bfloat16")
     parser.add_argument("--batch-size", type=int, default=16)
@@ -186,7 +191,7 @@ def _engine_options(parser: argparse.ArgumentParser) -> None:
 def build_parser() -> argparse.ArgumentParser:
     parser = argparse.ArgumentParser(prog="llmserve")
     commands = parser.add_subparsers(dest="command", required=True)
-    benchmark = commands.add_parser("benchmark", help="run the open-loop workload harness")
+    benchmark = commands.add_parser("benchmark", help="synthetic traffic against the engine; latency and throughput report")
     benchmark.add_argument("--config", choices=("naive", "paged", "static", "continuous"), default="continuous")
     benchmark.add_argument("--policy", choices=("fcfs", "sjf", "priority"), default="fcfs")
     benchmark.add_argument("--profile", default="configs/benchmark-sharegpt.yaml")
@@ -202,15 +207,31 @@ def build_parser() -> argparse.ArgumentParser:
     generate.add_argument("--top-p", type=float, default=1.0)
     generate.add_argument("--stop-token-ids", type=int, nargs="*")
     _engine_options(generate)
+    replay = commands.add_parser("replay", help="trace replay: steps of token ids from standard input, logits to files "
+                                                "(the same program as bin/trace_run)")
+    replay.description = "every option after `replay` goes to trace_run: --model --dtype --out --max-tokens"
     return parser
 
 
+def parse(argv=None):
+    """Arguments of the command line; ``rest`` holds what follows ``replay`` (trace_run's own options)."""
+    parser = build_parser()
+    args, rest = parser.parse_known_args(argv)
+    if rest and args.command != "replay":
+        parser.error("unrecognized arguments: " + " ".join(rest))
+    args.rest = rest
+    return args
+
+
 def main(argv=None) -> int:
-    args = build_parser().parse_args(argv)
+    args = parse(argv)
     if args.command == "benchmark":
-        asyncio.run(_benchmark(args))
+        run_benchmark(args)
+    elif args.command == "generate":
+        run_generate(args)
     else:
-        _generate(args)
+        from .engine.trace_replay import main as replay_main
+        return replay_main(args.rest)
     return 0
 
 

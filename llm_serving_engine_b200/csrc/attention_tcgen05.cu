@@ -517,6 +517,16 @@ extern "C" int lse_attention_tc_status(void) {
   return value;
 }
 
+// Queue a copy of the word to `host_dst` (pinned) on `stream`: the host reads it with the step's tokens,
+// without a synchronisation of its own.
+extern "C" int lse_attention_tc_status_async(int* host_dst, cudaStream_t stream) {
+  return (int)cudaMemcpyFromSymbolAsync(host_dst, lse_attn_tc_error, sizeof(int), 0, cudaMemcpyDeviceToHost, stream);
+}
+extern "C" int lse_attention_tc_status_reset(void) {
+  const int zero = 0;
+  return (int)cudaMemcpyToSymbol(lse_attn_tc_error, &zero, sizeof(int));
+}
+
 // q, out [tokens, n_q, D]; k_cache, v_cache [num_pages, n_kv, page_size, D], all bfloat16, contiguous,
 // 16-byte aligned.  segment_start [S + 1]: first row of each request's portion; segment_first_pos [S]:
 // the position of that row; block_tables [S, bt_stride].  Row r of a portion sees the keys 0 .. its position.

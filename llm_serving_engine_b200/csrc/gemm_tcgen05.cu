@@ -363,6 +363,16 @@ extern "C" int lse_gemm_bf16_skinny_status(void) {
   return value;
 }
 
+// Queue a copy of the word to `host_dst` (pinned) on `stream`: the host reads it with the step's tokens,
+// without a synchronisation of its own.
+extern "C" int lse_gemm_bf16_skinny_status_async(int* host_dst, cudaStream_t stream) {
+  return (int)cudaMemcpyFromSymbolAsync(host_dst, lse_gemm_error, sizeof(int), 0, cudaMemcpyDeviceToHost, stream);
+}
+extern "C" int lse_gemm_bf16_skinny_status_reset(void) {
+  const int zero = 0;
+  return (int)cudaMemcpyToSymbol(lse_gemm_error, &zero, sizeof(int));
+}
+
 // out[split][m][n] (float32, splits * M * N values) = partial sums of x[M, K] * w[N, K]^T.
 // x, w bfloat16 row-major, 16-byte aligned, K a multiple of 8, M <= 256.
 namespace {

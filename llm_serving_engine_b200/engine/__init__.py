@@ -1,5 +1,4 @@
-from .scheduler import IterationScheduler, RequestState, plan_iteration, resolve_page_pressure
+from .scheduler import GenerationRequest, Scheduler
 from .step import StepContext, StepEntry, StepRunner
 
-__all__ = ["IterationScheduler", "RequestState", "StepContext", "StepEntry", "StepRunner",
-           "plan_iteration", "resolve_page_pressure"]
+__all__ = ["GenerationRequest", "Scheduler", "StepContext", "StepEntry", "StepRunner"]

@@ -28,6 +28,10 @@ _SIGNATURES = {
     "lse_gemm_bf16_skinny_pad": [c_int],
     "lse_gemm_bf16_skinny_splits": [c_int, c_int, c_int],
     "lse_gemm_bf16_skinny_status": [],
+    "lse_gemm_bf16_skinny_status_async": [c_void_p, c_void_p],
+    "lse_gemm_bf16_skinny_status_reset": [],
+    "lse_attention_tc_status_async": [c_void_p, c_void_p],
+    "lse_attention_tc_status_reset": [],
     "lse_gemm_f32_nt": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong,
                         c_longlong, c_longlong, c_void_p],
     "lse_paged_attention_generic": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,

@@ -32,6 +32,19 @@ def _ptr(tensor: torch.Tensor | None) -> int | None:
     return None if tensor is None else tensor.data_ptr()
 
 
+_SM_COUNT: dict = {}
+
+
+def sm_count(device=None) -> int:
+    """Streaming multiprocessors of the device (the current one by default): launch heuristics size
+    their grids by it instead of carrying one GPU's number."""
+    index = torch.cuda.current_device() if device is None or torch.device(device).index is None else torch.device(device).index
+    count = _SM_COUNT.get(index)
+    if count is None:
+        count = _SM_COUNT[index] = int(torch.cuda.get_device_properties(index).multi_processor_count)
+    return count
+
+
 def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """out[t] = float32(table[ids[t]]); ids int32 [T], out float32 [T, H]."""
     _need_cuda(table, ids, out)
@@ -179,8 +192,9 @@ def decode_splits(tokens: int, n_q: int, n_kv: int, max_context: int | None) -> 
     more (a block that ends early makes room for the next kernel's blocks), at least one 16-key
     tile per warp and split."""
     base = tokens * n_kv * ((n_q // n_kv + 15) // 16)
-    # about 200 blocks (measured best from 12 to 64 rows: 192 blocks beat 128 and 256); at most 8 splits: one cluster adds them up
-    splits = max(1, min(_DECODE_MAX_SPLITS, 208 // base))
+    # about 1.4 blocks per SM (measured best from 12 to 64 rows on 148 SMs: 192 blocks beat 128 and 256); at most
+    # 8 splits: one cluster adds them up
+    splits = max(1, min(_DECODE_MAX_SPLITS, ((sm_count() * 7 + 4) // 5) // base))
     if max_context is not None:
         splits = min(splits, max(1, -(-max_context // 64)))
     return splits
@@ -302,8 +316,13 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, interleave: int = 0) -> t
 
 
 GEMM_SKINNY_MAX_ROWS = 256
-_GEMM_TARGET_BLOCKS = int(__import__("os").environ.get("LSE_GEMM_BLOCKS", "296"))
+_GEMM_BLOCKS_PER_SM = 2     # two blocks of the few-rows product fit on an SM; LSE_GEMM_BLOCKS overrides the total
 _GEMM_MAX_SPLITS = int(__import__("os").environ.get("LSE_GEMM_MAX_SPLITS", "16"))
+
+
+def _gemm_target_blocks() -> int:
+    override = __import__("os").environ.get("LSE_GEMM_BLOCKS")
+    return int(override) if override else _GEMM_BLOCKS_PER_SM * sm_count()
 
 
 def gemm_bf16_skinny_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
@@ -327,7 +346,7 @@ def gemm_bf16_skinny(x: torch.Tensor, weight: torch.Tensor, splits: int | None =
         # about two blocks per SM (more of the weights are fetched ahead while earlier kernels run), but no
         # more splits than keep the partial sums (4 bytes per row, column and split) well below the weight bytes
         n_tiles = -(-n // block_n)
-        splits = max(1, min(-(-k // 128), _GEMM_TARGET_BLOCKS // n_tiles, max(1, k // (4 * m)), max_splits or _GEMM_MAX_SPLITS)) if n_tiles < 148 else 1
+        splits = max(1, min(-(-k // 128), _gemm_target_blocks() // n_tiles, max(1, k // (4 * m)), max_splits or _GEMM_MAX_SPLITS)) if n_tiles < sm_count() else 1
     splits = lib.lse_gemm_bf16_skinny_splits(k, int(splits), int(kboxes))
     out = torch.empty((splits, m, n), dtype=torch.float32, device=x.device)
     check(lib.lse_gemm_bf16_skinny(x.data_ptr(), weight.data_ptr(), out.data_ptr(), m, n, k, splits, int(stages),
@@ -387,7 +406,7 @@ def gemm_bf16_skinny_finish_gate(x: torch.Tensor, weight: torch.Tensor, arrivals
     lib = library.load()
     if splits is None:
         n_tiles = n // 128
-        splits = max(1, min(-(-k // 128), _GEMM_TARGET_BLOCKS // n_tiles, max(1, k // (4 * m)), max_splits or _GEMM_MAX_SPLITS)) if n_tiles < 148 else 1
+        splits = max(1, min(-(-k // 128), _gemm_target_blocks() // n_tiles, max(1, k // (4 * m)), max_splits or _GEMM_MAX_SPLITS)) if n_tiles < sm_count() else 1
     splits = lib.lse_gemm_bf16_skinny_splits(k, int(splits), 1)
     out = torch.empty((splits, m, n), dtype=torch.float32, device=x.device)
     act = torch.empty((m, n // 2), dtype=torch.bfloat16, device=x.device)
@@ -425,7 +444,7 @@ def gemm_bf16_skinny_gated_in(gate_up: torch.Tensor, weight: torch.Tensor, split
     lib = library.load()
     if splits is None:
         n_tiles = -(-n // 128)
-        splits = max(1, min(-(-k // 128), _GEMM_TARGET_BLOCKS // n_tiles, max(1, k // (4 * m)), max_splits or _GEMM_MAX_SPLITS)) if n_tiles < 148 else 1
+        splits = max(1, min(-(-k // 128), _gemm_target_blocks() // n_tiles, max(1, k // (4 * m)), max_splits or _GEMM_MAX_SPLITS)) if n_tiles < sm_count() else 1
     splits = lib.lse_gemm_bf16_skinny_splits(k, int(splits), 1)
     out = torch.empty((splits, m, n), dtype=torch.float32, device=weight.device)
     check(lib.lse_gemm_bf16_skinny_gated_in(gate_up.data_ptr(), parts, m * two_i, weight.data_ptr(), out.data_ptr(),
@@ -436,6 +455,26 @@ def gemm_bf16_skinny_gated_in(gate_up: torch.Tensor, weight: torch.Tensor, split
 def gemm_bf16_skinny_status() -> int:
     """0 unless a bounded wait inside the kernel has given up (synchronises the device)."""
     return int(library.load().lse_gemm_bf16_skinny_status())
+
+
+def kernel_status_async(host_words: torch.Tensor) -> None:
+    """Queue, on the current stream, copies of the status words of the kernels with bounded waits (the
+    few-rows product, the tcgen05 prompt attention) into ``host_words`` (pinned int32 [2]).  Once the
+    stream has got there, a non-zero word says that a wait gave up: that block wrote nothing, and
+    what the step computed is not to be used."""
+    assert host_words.dtype == torch.int32 and host_words.numel() >= 2 and host_words.is_pinned()
+    lib = library.load()
+    stream = _stream()
+    if lib.lse_gemm_bf16_skinny_status_async(host_words.data_ptr(), stream) != 0 or \
+            lib.lse_attention_tc_status_async(host_words.data_ptr() + 4, stream) != 0:
+        raise KernelError("the kernels' status words could not be read")
+
+
+def kernel_status_reset() -> None:
+    """Clear both status words (after a failure has been reported)."""
+    lib = library.load()
+    lib.lse_gemm_bf16_skinny_status_reset()
+    lib.lse_attention_tc_status_reset()
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> torch.Tensor:

@@ -15,13 +15,12 @@ from .linear import linear_partials
 # Which kernel a step with prompt portions takes.  The tcgen05 kernel's block is 128 rows of one request
 # and one head; the mma.sync kernel's about ten rows of all heads of a group.  A step goes to the former
 # when its longest portion has at least TCGEN05_MIN_ROWS rows and either its blocks fit the GPU at once
-# (a long portion beside a few decoding requests: 31 against 46 us for 512 rows beside 8 requests) or
+# (one block per SM; a long portion beside a few decoding requests: 31 against 46 us for 512 rows beside 8 requests) or
 # its portions are long on average (at least 64 rows a request); many short portions or many decoding
 # requests beside a portion (90 against 64 us with 32 of them) stay on the mma.sync kernel.
 # LSE_PREFILL_ATTENTION=mma turns the tcgen05 kernel off.
 TCGEN05_MIN_ROWS = int(os.environ.get("LSE_TCGEN05_MIN_ROWS", "128"))
 TCGEN05_MIN_ROWS_PER_REQUEST = 64
-TCGEN05_BLOCKS_AT_ONCE = 148
 TCGEN05_PREFILL = os.environ.get("LSE_PREFILL_ATTENTION", "tcgen05") != "mma"
 
 
@@ -91,7 +90,7 @@ class GroupedQueryAttention(Mixer):
                                            step.segment_of_token, step.positions, self.scale, splits)
             elif (TCGEN05_PREFILL and step.max_segment_tokens >= TCGEN05_MIN_ROWS
                   and (tokens >= TCGEN05_MIN_ROWS_PER_REQUEST * step.num_segments
-                       or sum(-(-segment.count // 128) for segment in step.segments) * self.n_q <= TCGEN05_BLOCKS_AT_ONCE)
+                       or sum(-(-segment.count // 128) for segment in step.segments) * self.n_q <= ops.sm_count())
                   and ops.attention_tc_supported(
                     self.head_dim, self.n_q, self.n_kv, cache.keys.shape[2], x.dtype, self.window)):
                 ops.paged_attention_prefill_tc(q, cache.keys, cache.values, attended, cache.block_tables,

@@ -54,6 +54,7 @@ class _Turn:
         self.dev_i = torch.empty((2, max_rows), dtype=torch.int64, device=device)
         self.out = torch.empty(max_rows, dtype=torch.int32, device=device)
         self.host_out = torch.empty(max_rows, dtype=torch.int32, pin_memory=pinned)
+        self.host_status = torch.zeros(2, dtype=torch.int32, pin_memory=pinned) if pinned else None
         self.done = torch.cuda.Event() if pinned else None
         self.rows = 0
 
@@ -99,6 +100,8 @@ class Sampler:
             ops.sample(logits, turn.dev_f[0, :rows], turn.dev_f[1, :rows], turn.dev_i[0, :rows],
                        turn.dev_i[1, :rows], self._scratch, out)
         turn.host_out[:rows].copy_(out, non_blocking=True)
+        if turn.host_status is not None:
+            ops.kernel_status_async(turn.host_status)     # arrives with the tokens: no synchronisation of its own
         if turn.done is not None:
             turn.done.record()
         turn.rows = rows
@@ -115,4 +118,10 @@ class Sampler:
         turn = self._turns[self._last if ticket is None else ticket]
         if turn.done is not None:
             turn.done.synchronize()
+        if turn.host_status is not None and (turn.host_status[0] or turn.host_status[1]):
+            which = " and ".join(name for name, word in zip(("the few-rows product", "the tcgen05 prompt attention"),
+                                                            turn.host_status.tolist()) if word)
+            turn.host_status.zero_()
+            ops.kernel_status_reset()
+            raise ops.KernelError(f"a bounded wait inside {which} gave up: the step's results are not valid")
         return turn.host_out[:turn.rows].tolist()

@@ -1,173 +1,171 @@
-"""Synthetic open-loop workloads and the report of a run, after the reference's
-benchmark package (``src/llmserve/benchmark/workload.py``, ``metrics.py``,
-``runner.py``): clipped log-normal prompt and output lengths, exponential
-inter-arrival times, token ids uniform in [4, vocabulary), all from one seed;
-time to first token, time per output token and end-to-end latency percentiles."""
+"""Synthetic request traffic for the command line's ``benchmark`` and for ``bench.py``.
+
+The traffic has the statistics of the reference's generator
+(``src/llmserve/benchmark/workload.py:11-79``, ``configs/benchmark-sharegpt.yaml``): prompt and
+output lengths are log-normal around a median, clipped to a range; requests arrive with
+exponential gaps at a given rate; token ids are uniform over the vocabulary above the four
+reserved ids.  A profile file has the reference's keys (``requests``, ``arrival_rate``, ``seed``,
+``vocabulary_size``, and ``prompt`` / ``output`` with ``median``, ``sigma``, ``minimum``, ``maximum``).
+Everything is drawn from one NumPy generator, array by array, so a profile and a seed give the
+same traffic everywhere (not the reference's own stream of numbers).
+
+``replay_traffic`` plays such traffic against any ``async generate(request, on_token)`` and returns
+one timing row per request; ``summarise`` turns the rows into the usual latency figures (time to the
+first token, time per later token, total latency: median, 95th and 99th percentile).
+"""
 from __future__ import annotations
 
 import asyncio
-import math
-import random
 import time
-from dataclasses import asdict, dataclass, field
+from dataclasses import dataclass, field, replace
 from pathlib import Path
+
+import numpy as np
+
+RESERVED_IDS = 4       # pad, bos, eos, unk of the byte tokenizer: traffic never uses them
 
 
 @dataclass(frozen=True)
-class LengthDistribution:
+class ClippedLogNormal:
     median: int
     sigma: float
     minimum: int
     maximum: int
 
-    def sample(self, rng: random.Random) -> int:
-        value = round(rng.lognormvariate(math.log(self.median), self.sigma))
-        return max(self.minimum, min(self.maximum, value))
+    def draw(self, rng: np.random.Generator, count: int) -> np.ndarray:
+        values = np.rint(rng.lognormal(np.log(self.median), self.sigma, size=count)).astype(np.int64)
+        return np.clip(values, self.minimum, self.maximum)
 
 
 @dataclass(frozen=True)
-class LoadProfile:
+class TrafficProfile:
     requests: int = 100
-    arrival_rate: float = 2.0
-    prompt: LengthDistribution = LengthDistribution(128, 0.9, 8, 1_024)
-    output: LengthDistribution = LengthDistribution(64, 0.7, 4, 256)
+    arrival_rate: float = 2.0                  # requests per second; 0: all at once
+    prompt: ClippedLogNormal = ClippedLogNormal(128, 0.9, 8, 1024)
+    output: ClippedLogNormal = ClippedLogNormal(64, 0.7, 4, 256)
     seed: int = 7
     vocabulary_size: int = 32_000
 
-    @classmethod
-    def from_yaml(cls, path) -> "LoadProfile":
+    @staticmethod
+    def from_file(path) -> "TrafficProfile":
         import yaml
 
-        values = yaml.safe_load(Path(path).read_text())
-        return cls(requests=values["requests"], arrival_rate=values["arrival_rate"],
-                   prompt=LengthDistribution(**values["prompt"]), output=LengthDistribution(**values["output"]),
-                   seed=values.get("seed", 7), vocabulary_size=values.get("vocabulary_size", 32_000))
+        raw = yaml.safe_load(Path(path).read_text()) or {}
+        known = {"requests", "arrival_rate", "seed", "vocabulary_size"}
+        fields = {key: raw[key] for key in known if key in raw}
+        for key in ("prompt", "output"):
+            if key in raw:
+                fields[key] = ClippedLogNormal(**raw[key])
+        return TrafficProfile(**fields)
 
-    def to_dict(self) -> dict:
-        return asdict(self)
+    def fitted_to(self, vocabulary_size: int, max_positions: int) -> "TrafficProfile":
+        """The profile with the model's vocabulary, and prompts short enough that prompt + output fits."""
+        room = max(self.prompt.minimum, max_positions - self.output.maximum)
+        return replace(self, vocabulary_size=vocabulary_size,
+                       prompt=replace(self.prompt, maximum=min(self.prompt.maximum, room)))
 
 
 @dataclass(frozen=True)
-class RequestSpec:
+class TrafficRequest:
     request_id: str
-    arrival_offset_s: float
+    arrives_at: float                          # seconds after the start
     prompt_token_ids: tuple[int, ...]
     max_new_tokens: int
 
 
-def generate_workload(profile: LoadProfile) -> list[RequestSpec]:
-    if profile.arrival_rate <= 0:
-        raise ValueError("arrival_rate must be positive")
-    rng = random.Random(profile.seed)
-    elapsed = 0.0
-    out = []
-    for index in range(profile.requests):
-        if index:
-            elapsed += rng.expovariate(profile.arrival_rate)
-        prompt_length = profile.prompt.sample(rng)
-        output_length = profile.output.sample(rng)
-        tokens = tuple(rng.randrange(4, profile.vocabulary_size) for _ in range(prompt_length))
-        out.append(RequestSpec(f"request-{index:06d}", elapsed, tokens, output_length))
-    return out
-
-
-def percentile(values: list[float], quantile: float) -> float:
-    if not values:
-        return 0.0
-    ordered = sorted(values)
-    position = (len(ordered) - 1) * quantile
-    lower, upper = math.floor(position), math.ceil(position)
-    if lower == upper:
-        return ordered[lower]
-    return ordered[lower] * (upper - position) + ordered[upper] * (position - lower)
+def make_traffic(profile: TrafficProfile) -> list[TrafficRequest]:
+    if profile.requests <= 0:
+        return []
+    if profile.vocabulary_size <= RESERVED_IDS:
+        raise ValueError("the vocabulary has no ids beyond the reserved ones")
+    rng = np.random.default_rng(profile.seed)
+    count = profile.requests
+    prompt_lengths = profile.prompt.draw(rng, count)
+    output_lengths = profile.output.draw(rng, count)
+    arrivals = np.zeros(count)
+    if profile.arrival_rate > 0:
+        arrivals[1:] = np.cumsum(rng.exponential(1.0 / profile.arrival_rate, size=count - 1))
+    ids = rng.integers(RESERVED_IDS, profile.vocabulary_size, size=int(prompt_lengths.sum()))
+    ends = np.cumsum(prompt_lengths)
+    return [TrafficRequest(f"request-{index:06d}", float(arrivals[index]),
+                           tuple(int(token) for token in ids[ends[index] - prompt_lengths[index]:ends[index]]),
+                           int(output_lengths[index]))
+            for index in range(count)]
 
 
 @dataclass
-class RequestMetrics:
+class RequestTiming:
     request_id: str
-    arrival_s: float
     prompt_tokens: int
-    requested_output_tokens: int
-    first_token_s: float | None = None
-    finished_s: float | None = None
+    wanted_tokens: int
+    arrived: float
+    first_token: float | None = None
+    ended: float | None = None
     output_tokens: int = 0
     error: str | None = None
 
-    @property
-    def ttft_ms(self):
-        return None if self.first_token_s is None else (self.first_token_s - self.arrival_s) * 1e3
-
-    @property
-    def tpot_ms(self):
-        if self.first_token_s is None or self.finished_s is None or self.output_tokens < 2:
-            return None
-        return (self.finished_s - self.first_token_s) * 1e3 / (self.output_tokens - 1)
-
-    @property
-    def e2e_ms(self):
-        return None if self.finished_s is None else (self.finished_s - self.arrival_s) * 1e3
+    def figures(self) -> dict:
+        """ttft_ms, tpot_ms, e2e_ms (None where the request did not get that far)."""
+        ttft = None if self.first_token is None else (self.first_token - self.arrived) * 1e3
+        e2e = None if self.ended is None else (self.ended - self.arrived) * 1e3
+        tpot = None
+        if self.first_token is not None and self.ended is not None and self.output_tokens > 1:
+            tpot = (self.ended - self.first_token) * 1e3 / (self.output_tokens - 1)
+        return {"ttft_ms": ttft, "tpot_ms": tpot, "e2e_ms": e2e}
 
 
 @dataclass
-class BenchmarkReport:
-    config_name: str
-    duration_s: float
-    requests: list[RequestMetrics]
+class TrafficResult:
+    name: str
+    seconds: float
+    rows: list[RequestTiming]
     cache: dict = field(default_factory=dict)
-    metadata: dict = field(default_factory=dict)
+    extra: dict = field(default_factory=dict)
 
-    @property
-    def summary(self) -> dict:
-        good = [row for row in self.requests if row.error is None]
-        out = {
-            "config": self.config_name,
-            "requests": len(self.requests),
-            "successful_requests": len(good),
-            "duration_s": self.duration_s,
-            "throughput_tokens_per_s": sum(row.output_tokens for row in good) / max(self.duration_s, 1e-9),
-        }
-        for name in ("ttft_ms", "tpot_ms", "e2e_ms"):
-            values = [getattr(row, name) for row in good if getattr(row, name) is not None]
-            for label, q in (("p50", 0.5), ("p95", 0.95), ("p99", 0.99)):
-                out[f"{name}_{label}"] = percentile(values, q)
-        out.update({f"cache_{key}": value for key, value in self.cache.items()})
-        return out
-
-    def to_dict(self) -> dict:
-        rows = []
-        for row in self.requests:
-            item = asdict(row)
-            item.update(ttft_ms=row.ttft_ms, tpot_ms=row.tpot_ms, e2e_ms=row.e2e_ms)
-            rows.append(item)
-        return {"summary": self.summary, "metadata": self.metadata, "requests": rows}
+    def as_dict(self) -> dict:
+        rows = [dict(vars(row), **row.figures()) for row in self.rows]
+        return {"summary": summarise(self), "metadata": self.extra, "requests": rows}
 
 
-async def run_open_loop(name: str, profile: LoadProfile, generate) -> BenchmarkReport:
-    """Issue the profile's requests at their arrival times; ``generate(spec, on_token)`` is
-    an async callable that returns the generated ids.  Failures are kept in the rows."""
+def summarise(result: TrafficResult) -> dict:
+    served = [row for row in result.rows if row.error is None]
+    out = {"config": result.name, "requests": len(result.rows), "successful_requests": len(served),
+           "duration_s": result.seconds,
+           "throughput_tokens_per_s": sum(row.output_tokens for row in served) / max(result.seconds, 1e-9)}
+    figures = [row.figures() for row in served]
+    for key in ("ttft_ms", "tpot_ms", "e2e_ms"):
+        values = np.array([item[key] for item in figures if item[key] is not None], dtype=np.float64)
+        for label, q in (("p50", 50), ("p95", 95), ("p99", 99)):
+            out[f"{key}_{label}"] = float(np.percentile(values, q)) if values.size else 0.0
+    for key, value in result.cache.items():
+        out[f"cache_{key}"] = value
+    return out
+
+
+async def replay_traffic(name: str, traffic: list[TrafficRequest], generate) -> TrafficResult:
+    """Send every request at its arrival time to ``await generate(request, on_token)``; a request that
+    raises keeps its row, with the error's text."""
     loop = asyncio.get_running_loop()
-    start = loop.time()
-    rows: list[RequestMetrics] = []
+    origin = loop.time()
+    rows = {item.request_id: RequestTiming(item.request_id, len(item.prompt_token_ids), item.max_new_tokens, 0.0)
+            for item in traffic}
 
-    async def execute(spec: RequestSpec) -> None:
-        delay = start + spec.arrival_offset_s - loop.time()
-        if delay > 0:
-            await asyncio.sleep(delay)
-        row = RequestMetrics(spec.request_id, loop.time(), len(spec.prompt_token_ids), spec.max_new_tokens)
-        rows.append(row)
+    async def one(item: TrafficRequest) -> None:
+        await asyncio.sleep(max(0.0, origin + item.arrives_at - loop.time()))
+        row = rows[item.request_id]
+        row.arrived = loop.time()
 
-        def on_token(_: int) -> None:
-            if row.first_token_s is None:
-                row.first_token_s = loop.time()
+        def on_token(_token: int) -> None:
             row.output_tokens += 1
+            if row.output_tokens == 1:
+                row.first_token = loop.time()
 
         try:
-            await generate(spec, on_token)
-        except Exception as error:
+            await generate(item, on_token)
+        except Exception as error:   # the run goes on; the row says what happened
             row.error = f"{type(error).__name__}: {error}"
-        row.finished_s = loop.time()
+        row.ended = loop.time()
 
-    await asyncio.gather(*(asyncio.create_task(execute(spec)) for spec in generate_workload(profile)))
-    rows.sort(key=lambda row: row.request_id)
-    return BenchmarkReport(name, loop.time() - start, rows,
-                           metadata={"profile": profile.to_dict(), "wall_clock_unix_s": time.time()})
+    await asyncio.gather(*[one(item) for item in traffic])
+    return TrafficResult(name, loop.time() - origin, [rows[item.request_id] for item in traffic],
+                         extra={"wall_clock_unix_s": time.time()})

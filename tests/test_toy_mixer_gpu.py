@@ -64,10 +64,11 @@ def register_toy():
                                                     "pairing": "interleaved"}}})
         toy = PartSpec("toy_decayed_sum", {"decay": v["decay"]})
         feed_forward = PartSpec("swiglu", {"intermediate_size": v["intermediate_size"]})
-        block = PartSpec("prenorm_residual", {})
+        names = {"mixer_norm": "input_layernorm.", "mixer": "self_attn.", "feed_forward_norm": "post_attention_layernorm.", "feed_forward": "mlp."}
+        block = PartSpec("prenorm_residual", {"tensor_prefixes": names})
         layers = (
             LayerSpec("model.layers.0.", block, attention, feed_forward, norm, norm),
-            LayerSpec("model.layers.1.", PartSpec("prenorm_residual", {"tensor_prefixes": {"mixer": "toy."}}),
+            LayerSpec("model.layers.1.", PartSpec("prenorm_residual", {"tensor_prefixes": dict(names, mixer="toy.")}),
                       toy, feed_forward, norm, norm),
         )
         return ModelSpec("ToyHybridForCausalLM", v["vocab_size"], v["hidden_size"], layers, tuple(v["layer_order"]),

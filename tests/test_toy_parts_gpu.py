@@ -96,7 +96,8 @@ def register_toys():
             return PartSpec("gqa_attention", {"num_heads": v["num_attention_heads"], "num_kv_heads": v["num_key_value_heads"],
                                               "head_dim": v["head_dim"], "bias": True, "window": 0, "position": position})
         rotary = {"kind": "rope", "params": {"theta": v["rope_theta"], "head_dim": v["head_dim"], "pairing": "half"}}
-        block = PartSpec("prenorm_residual", {})
+        names = {"mixer_norm": "input_layernorm.", "mixer": "self_attn.", "feed_forward_norm": "post_attention_layernorm.", "feed_forward": "mlp."}
+        block = PartSpec("prenorm_residual", {"tensor_prefixes": names})
         layers = (
             LayerSpec("model.layers.0.", block, attention({"kind": "toy_wave", "params": {}}),
                       PartSpec("swiglu", {"intermediate_size": v["intermediate_size"]}), norm, norm),
@@ -157,7 +158,10 @@ def test_routed_feed_forward_and_another_position_encoding_run_through_the_uncha
     write_random_model(tmp_path, TOY, seed=9, dtype="float32")
     model = load_model(tmp_path, dtype="float32", device="cuda")
     cache = CacheManager(cache_requirements(model.spec), CacheConfig(8, 30), model.dtype, model.device, 128, num_state_slots=3)
-    runner = StepRunner(model, cache, 96, 3, use_graphs=False)   # the toy parts are plain tensor code, not made for capture
+    runner = StepRunner(model, cache, 96, 3)
+    # the toy parts are plain tensor code whose launches depend on the routing: they do not say ``graph_safe``,
+    # so the model does not either, although its attention does, and no step is captured
+    assert not model.graph_safe and not runner.use_graphs
     cfg, weights = qwen2_plain.load_folder(tmp_path)
     # router weights of the size of the others would send almost every row to the same expert: spread them
     rng = random.Random(1)
@@ -195,3 +199,21 @@ def test_routed_feed_forward_and_another_position_encoding_run_through_the_uncha
         assert float((whole[name] - want[name]).abs().max()) < bound, name
         assert float((mixed[name] - want[name]).abs().max()) < bound, name
     assert cache.groups[0].pool.used_pages == 0
+
+    # the same model through the entry point with everything at its default: greedy tokens equal the plain ones
+    from llm_serving_engine_b200 import GenerationConfig, LLMEngine, SchedulerConfig
+
+    engine = LLMEngine(model, None, cache_config=CacheConfig(8, 30), scheduler_config=SchedulerConfig(max_batch_size=3, max_tokens_per_step=32),
+                       prefill_chunk_size=16)
+    assert not engine.runner.use_graphs
+    prompts = [requests["b"][:19], requests["c"]]
+    got = engine.generate_many(prompts, GenerationConfig(max_new_tokens=5))
+    for prompt, tokens in zip(prompts, got):
+        sequence = list(prompt)
+        for token in tokens:
+            logits, _ = plain_forward(cfg, weights, sequence)
+            top = torch.topk(logits[-1], 2).values
+            if float(top[0] - top[1]) > 1e-4:     # a near tie may fall either way
+                assert token == int(logits[-1].argmax())
+            sequence.append(token)
+    assert engine.runner.graph_replays == 0
