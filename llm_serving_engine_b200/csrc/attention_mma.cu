@@ -103,7 +103,7 @@ struct SubTileCopy {
 // ---------------------------------------------------------------------------------------------
 // decode: one query row per request
 // ---------------------------------------------------------------------------------------------
-constexpr int DEC_STAGES = 3;
+constexpr int DEC_STAGES = 3;   // tiles of a warp in flight (more shared memory keeps the next kernel's blocks off the SM: measured slower)
 constexpr int DEC_TILE = 16;
 constexpr int BT_STAGE = 1024;   // block-table entries a block keeps in shared memory
 
@@ -129,7 +129,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
                    float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ arrivals,
                    const int* __restrict__ block_tables, int bt_stride,
                    const int* __restrict__ segment_of_token, const int* __restrict__ positions,
-                   int n_q, int n_kv, int page_size, float scale_log2e, int num_splits) {
+                   int n_q, int n_kv, int page_size, float scale_log2e, int num_splits, int dry_run) {
   constexpr int CH = D / 8;                 // 16-byte chunks per row
   constexpr int TILE_BYTES = DEC_TILE * D * 2;
   extern __shared__ __align__(128) unsigned char smem[];
@@ -166,27 +166,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   const bool staged = n_pages <= BT_STAGE;
   if (staged)
     for (int i = tid; i < n_pages; i += 128) bt_s[i] = bt[first_page + i];
-  pdl_wait();
-  LSE_TL_MARK(2)
-  // queries of the group -> shared memory (rows beyond the group are zero)
-  for (int e = tid; e < 16 * CH; e += 128) {
-    const int r = e / CH, c = e % CH;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (r < gcount) v = *reinterpret_cast<const uint4*>(q + ((size_t)t * n_q + first_head + r) * D + c * 8);
-    *reinterpret_cast<uint4*>(q_s + tile_off<D>(r, c)) = v;
-  }
   __syncthreads();
-  uint32_t qf[D / 16][4];
-  {
-    const int mi = lane >> 3, r = (lane & 7) + (mi & 1) * 8;
-#pragma unroll
-    for (int ks = 0; ks < D / 16; ++ks) ldmatrix_x4(qf[ks], smem_u32(q_s + tile_off<D>(r, ks * 2 + (mi >> 1))));
-  }
-
-  float acc[D / 8][4];
-#pragma unroll
-  for (int i = 0; i < D / 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
-  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
   unsigned char* my_s = kv_s + (size_t)warp * DEC_STAGES * 2 * TILE_BYTES;
   const uint32_t my_u32 = smem_u32(my_s);
@@ -223,33 +203,83 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   // this warp's tiles: tile_lo + warp, + 4, ...
   const int first = tile_lo + warp;
   const int n_mine = first < tile_hi ? (tile_hi - first + 3) / 4 : 0;
+  // Keys and values of earlier steps do not depend on the kernels before this one: the first tiles are
+  // fetched at once, while those kernels may still run.  Only the tile that holds the row's own position
+  // (its key and value were written just before this kernel) has to wait.
+  const int newest_tile = (ctx - 1) / DEC_TILE;
+  int deferred = -1;
 #pragma unroll
-  for (int s = 0; s < DEC_STAGES - 1; ++s) {
-    if (s < n_mine) load_tile(first + 4 * s, s);
+  for (int s = 0; s < DEC_STAGES; ++s) {
+    if (s < n_mine) {
+      if (first + 4 * s == newest_tile) deferred = s;
+      else load_tile(first + 4 * s, s);
+    }
     cp_async_commit();
   }
-  for (int it = 0; it < n_mine; ++it) {
-    const int pre = it + DEC_STAGES - 1;
-    if (pre < n_mine) load_tile(first + 4 * pre, pre % DEC_STAGES);
-    cp_async_commit();
-    cp_async_wait<DEC_STAGES - 1>();
+  // The loop over the tiles runs twice.  The first pass, before the wait for the kernels before this one,
+  // works one tile through with a zero query and throws the result away: it only brings the loop's
+  // instructions into the SM's instruction cache, which the other kernels of the step have emptied since
+  // this one last ran (a first pass through cold code was measured at about three times a warm one).
+  // `dry_run` is a kernel parameter so that the compiler keeps a single copy of the loop.
+  uint32_t qf[D / 16][4];
+#pragma unroll
+  for (int ks = 0; ks < D / 16; ++ks) qf[ks][0] = qf[ks][1] = qf[ks][2] = qf[ks][3] = 0u;
+  float acc[D / 8][4];
+  float m0, m1, l0, l1;
+#pragma unroll 1
+  for (int pass = dry_run ? 0 : 1; pass < 2; ++pass) {
+  if (pass == 1) {
+    pdl_wait();
+    LSE_TL_MARK(2)
+    if (deferred >= 0) {   // one warp of one split: the tile comes from the L2, and the warp waits for it here
+      load_tile(newest_tile, deferred);
+      cp_async_commit();
+      cp_async_wait<0>();
+    }
+    // queries of the group -> shared memory (rows beyond the group are zero)
+    for (int e = tid; e < 16 * CH; e += 128) {
+      const int r = e / CH, c = e % CH;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (r < gcount) v = *reinterpret_cast<const uint4*>(q + ((size_t)t * n_q + first_head + r) * D + c * 8);
+      *reinterpret_cast<uint4*>(q_s + tile_off<D>(r, c)) = v;
+    }
+    __syncthreads();
+    {
+      const int mi = lane >> 3, r = (lane & 7) + (mi & 1) * 8;
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) ldmatrix_x4(qf[ks], smem_u32(q_s + tile_off<D>(r, ks * 2 + (mi >> 1))));
+    }
+    LSE_TL_MARK(4)
+  }
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+  m0 = m1 = -INFINITY;
+  l0 = l1 = 0.f;
+  const int n_run = pass == 0 ? min(n_mine, 1) : n_mine;
+  for (int it = 0; it < n_run; ++it) {
+    cp_async_wait<DEC_STAGES - 1>();   // all but the newest DEC_STAGES - 1 groups have landed: tile `it` is there
     __syncwarp();
     const int tile = first + 4 * it;
     const uint32_t ks_ = my_u32 + (uint32_t)(it % DEC_STAGES) * 2 * TILE_BYTES;
     const uint32_t vs_ = ks_ + TILE_BYTES;
 
-    float s[2][4];
+    float s[2][4], s_odd[2][4];   // even and odd 16-column steps add up apart: two short chains of dependent MMAs instead of a long one
 #pragma unroll
-    for (int i = 0; i < 2; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+    for (int i = 0; i < 2; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = s_odd[i][0] = s_odd[i][1] = s_odd[i][2] = s_odd[i][3] = 0.f;
     {
       const int mi = lane >> 3, key = (lane & 7) + (mi >> 1) * 8;
 #pragma unroll
-      for (int ks = 0; ks < D / 16; ++ks) {
-        uint32_t b[4];
+      for (int ks = 0; ks < D / 16; ks += 2) {
+        uint32_t b[4], c[4];
         ldmatrix_x4(b, ks_ + tile_off<D>(key, ks * 2 + (mi & 1)));
+        ldmatrix_x4(c, ks_ + tile_off<D>(key, (ks + 1) * 2 + (mi & 1)));
         mma_bf16(s[0], qf[ks], b[0], b[1]);
         mma_bf16(s[1], qf[ks], b[2], b[3]);
+        mma_bf16(s_odd[0], qf[ks + 1], c[0], c[1]);
+        mma_bf16(s_odd[1], qf[ks + 1], c[2], c[3]);
       }
+#pragma unroll
+      for (int i = 0; i < 2; ++i) { s[i][0] += s_odd[i][0]; s[i][1] += s_odd[i][1]; s[i][2] += s_odd[i][2]; s[i][3] += s_odd[i][3]; }
     }
 #pragma unroll
     for (int nb = 0; nb < 2; ++nb)
@@ -290,7 +320,14 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
       }
     }
     __syncwarp();
+    // the stage is free: it takes the tile DEC_STAGES further on (one group per iteration, empty or not)
+    if (pass == 1) {
+      if (it + DEC_STAGES < n_mine) load_tile(first + 4 * (it + DEC_STAGES), it % DEC_STAGES);
+      cp_async_commit();
+      if (it == 0) { LSE_TL_MARK(7) }
+    }
   }
+  }   // pass
   cp_async_wait<0>();
   // row sums over the 4 lanes that share a row
   l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
@@ -670,7 +707,8 @@ int launch_decode_as(const void* q, const void* kc, const void* vc, void* out, f
   cudaError_t err = lse_launch_cluster(attn_decode_kernel<D, CLUSTER>, grid, 128, smem, stream,
       CLUSTER ? (unsigned)num_splits : 1u,
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, (__nv_bfloat16*)out, part_o,
-      part_ml, arrivals, block_tables, bt_stride, seg, positions, n_q, n_kv, page_size, scale * LOG2E, num_splits);
+      part_ml, arrivals, block_tables, bt_stride, seg, positions, n_q, n_kv, page_size, scale * LOG2E, num_splits,
+      lse_pdl_enabled ? 1 : 0);
   if (err != cudaSuccess) return (int)err;
   return (int)cudaGetLastError();
 }

@@ -12,34 +12,46 @@
 LSE_TL_DEFINE(lse_timeline_elementwise)
 
 // ------------------------------------------------------------------ embedding
-// residual[t, :] = float(table[ids[t], :])
+// residual[t, :] = float(table[ids[t], :]); sumsq[t] = sum of squares of that row (when sumsq is not null)
 template <typename T>
 __global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids,
-                                 float* __restrict__ out, int hidden, int vocab) {
+                                 float* __restrict__ out, float* __restrict__ sumsq, int hidden, int vocab) {
   LSE_TL_BEGIN(1)
   pdl_launch_dependents();
   pdl_wait();
   LSE_TL_MARK(2)
+  __shared__ float scratch[32];
   const int t = blockIdx.x;
   const int id = ids[t];
   float* dst = out + (size_t)t * hidden;
   if (id < 0 || id >= vocab) {  // padding row of a fixed-shape batch
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = 0.f;
+    if (sumsq != nullptr && threadIdx.x == 0) sumsq[t] = 0.f;
     return;
   }
   const T* src = table + (size_t)id * hidden;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_f32<T>(src[i]);
+  float sq = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float v = to_f32<T>(src[i]);
+    dst[i] = v;
+    sq = fmaf(v, v, sq);
+  }
+  if (sumsq != nullptr) {
+    const float total = block_sum(sq, scratch);
+    if (threadIdx.x == 0) sumsq[t] = total;
+  }
   LSE_TL_MARK(3)
 }
 
-extern "C" int lse_embedding(const void* table, int table_dtype, const int* ids, float* out,
+extern "C" int lse_embedding(const void* table, int table_dtype, const int* ids, float* out, float* sumsq,
                              int tokens, int hidden, int vocab, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   const int threads = hidden >= 1024 ? 256 : 128;
   if (table_dtype == LSE_DTYPE_F32)
-    lse_launch(embedding_kernel<float>, tokens, threads, 0, stream, (const float*)table, ids, out, hidden, vocab);
+    lse_launch(embedding_kernel<float>, tokens, threads, 0, stream, (const float*)table, ids, out, sumsq, hidden, vocab);
   else if (table_dtype == LSE_DTYPE_BF16)
-    lse_launch(embedding_kernel<__nv_bfloat16>, tokens, threads, 0, stream, (const __nv_bfloat16*)table, ids, out, hidden, vocab);
+    lse_launch(embedding_kernel<__nv_bfloat16>, tokens, threads, 0, stream, (const __nv_bfloat16*)table, ids, out, sumsq,
+               hidden, vocab);
   else
     return LSE_ERR_BAD_ARGUMENT;
   LSE_LAUNCH_CHECK();
@@ -109,16 +121,16 @@ add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* __restrict__ delt
     if (i < chunks) {
       load4<float>(res + 4 * i, x[c]);
       if (del) {
-        // eight partial sums are fetched together (one round trip), then added in index order
-        for (int p0 = 0; p0 < n_partials; p0 += 8) {
-          float d[8][4];
+        // sixteen partial sums are fetched together (one round trip), then added in index order
+        for (int p0 = 0; p0 < n_partials; p0 += 16) {
+          float d[16][4];
 #pragma unroll
-          for (int p = 0; p < 8; ++p) {
+          for (int p = 0; p < 16; ++p) {
             if (p0 + p < n_partials) load4<TD>(del + (size_t)(p0 + p) * partial_stride + 4 * i, d[p]);
             else d[p][0] = d[p][1] = d[p][2] = d[p][3] = 0.f;
           }
 #pragma unroll
-          for (int p = 0; p < 8; ++p) {
+          for (int p = 0; p < 16; ++p) {
             if (p0 + p < n_partials) { x[c][0] += d[p][0]; x[c][1] += d[p][1]; x[c][2] += d[p][2]; x[c][3] += d[p][3]; }
           }
         }

@@ -45,14 +45,17 @@ def sm_count(device=None) -> int:
     return count
 
 
-def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[t] = float32(table[ids[t]]); ids int32 [T], out float32 [T, H]."""
-    _need_cuda(table, ids, out)
+def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, sumsq: torch.Tensor | None = None) -> torch.Tensor:
+    """out[t] = float32(table[ids[t]]); ids int32 [T], out float32 [T, H].  ``sumsq`` (float32 [T]), when given,
+    receives the sum of squares of every row (what a ``NormedRows`` of these rows needs)."""
+    _need_cuda(table, ids, out, sumsq)
     vocab, hidden = table.shape
     assert ids.dtype == torch.int32 and out.dtype == torch.float32 and table.is_contiguous()
     assert out.shape == (ids.shape[0], hidden) and out.is_contiguous()
+    if sumsq is not None:
+        assert sumsq.dtype == torch.float32 and sumsq.numel() >= ids.shape[0] and sumsq.is_contiguous()
     lib = library.load()
-    check(lib.lse_embedding(table.data_ptr(), dtype_code(table.dtype), ids.data_ptr(), out.data_ptr(),
+    check(lib.lse_embedding(table.data_ptr(), dtype_code(table.dtype), ids.data_ptr(), out.data_ptr(), _ptr(sumsq),
                             ids.shape[0], hidden, vocab, _stream()), "embedding")
     return out
 
@@ -315,9 +318,12 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, interleave: int = 0) -> t
     return out
 
 
-GEMM_SKINNY_MAX_ROWS = 256
+GEMM_SKINNY_MAX_ROWS = 256      # rows of x the few-rows product takes when it writes partial sums
+GEMM_FUSED_MAX_ROWS = 32        # ... when its splits add themselves up (a cluster) or it makes x from the residual
 _GEMM_BLOCKS_PER_SM = 2     # two blocks of the few-rows product fit on an SM; LSE_GEMM_BLOCKS overrides the total
 _GEMM_MAX_SPLITS = int(__import__("os").environ.get("LSE_GEMM_MAX_SPLITS", "16"))
+PARTIALS, PLAIN, RESIDUAL, GATE = 0, 1, 2, 3
+GATE_INTERLEAVE = 64            # gate and up rows alternate in blocks of 64: 128 weight rows per thread block
 
 
 def _gemm_target_blocks() -> int:
@@ -332,8 +338,55 @@ def gemm_bf16_skinny_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
             and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
 
 
+def _wished_splits(m: int, n: int, k: int, block_n: int, max_splits: int | None) -> int:
+    """About two blocks per SM (more of the weights are fetched ahead while earlier kernels run), but no more
+    splits than keep the partial sums (4 bytes per row, column and split) well below the weight bytes."""
+    n_tiles = -(-n // block_n)
+    if n_tiles >= sm_count():
+        return 1
+    return max(1, min(-(-k // 128), _gemm_target_blocks() // n_tiles, max(1, k // (4 * m)), max_splits or _GEMM_MAX_SPLITS))
+
+
+class NormedRows:
+    """Rows that are not normalised yet: ``(residual[m] * inv[m]) * weight`` with ``inv[m] = rsqrt(sum_p sumsq[p][m] /
+    hidden + eps)``.  ``residual`` float32 [M, H] (everything already added), ``sumsq`` float32 [parts, M] partial sums
+    of squares of its rows (left by the kernel that wrote the residual), ``weight`` float32 [H].  The few-rows
+    product takes this in place of x and normalises on the way."""
+
+    __slots__ = ("residual", "sumsq", "weight", "eps")
+
+    def __init__(self, residual: torch.Tensor, sumsq: torch.Tensor, weight: torch.Tensor, eps: float) -> None:
+        self.residual, self.sumsq, self.weight, self.eps = residual, sumsq, weight, float(eps)
+
+    @property
+    def shape(self):
+        return self.residual.shape
+
+    def materialise(self, dtype: torch.dtype) -> torch.Tensor:
+        """The normalised rows as a tensor (the norm kernel; for consumers that need one)."""
+        out = torch.empty(self.residual.shape, dtype=dtype, device=self.residual.device)
+        return add_rmsnorm(self.residual, None, self.weight, self.eps, out, write_residual=False)
+
+
+def _launch_skinny(x, weight: torch.Tensor, m: int, n: int, k: int, splits: int, stages: int, block_n: int, epilogue: int,
+                   out=None, bias=None, residual=None, sumsq_out=None, act_out=None, name="gemm_bf16_skinny") -> None:
+    lib = library.load()
+    if isinstance(x, NormedRows):
+        assert x.residual.dtype == torch.float32 and x.residual.is_contiguous() and x.residual.shape == (m, k)
+        assert x.sumsq.dtype == torch.float32 and x.sumsq.dim() == 2 and x.sumsq.shape[1] >= m and x.sumsq.stride(1) == 1
+        assert x.weight.dtype == torch.float32 and x.weight.shape == (k,)
+        x_args = (None, x.residual.data_ptr(), x.sumsq.data_ptr(), x.sumsq.shape[0], x.sumsq.stride(0),
+                  x.weight.data_ptr(), x.eps)
+    else:
+        x_args = (x.data_ptr(), None, None, 0, 0, None, 0.0)
+    check(lib.lse_gemm_bf16_skinny(x_args[0], weight.data_ptr(), m, n, k, int(splits), int(stages), int(block_n), epilogue,
+                                   _ptr(out), _ptr(bias), _ptr(residual), _ptr(sumsq_out),
+                                   sumsq_out.stride(0) if sumsq_out is not None else 0, _ptr(act_out),
+                                   x_args[1], x_args[2], x_args[3], x_args[4], x_args[5], x_args[6], _stream()), name)
+
+
 def gemm_bf16_skinny(x: torch.Tensor, weight: torch.Tensor, splits: int | None = None, stages: int = 6,
-                     kboxes: int = 1, max_splits: int | None = None, block_n: int = 128) -> torch.Tensor:
+                     max_splits: int | None = None, block_n: int = 128) -> torch.Tensor:
     """Partial sums [P, M, N] (float32) of x[M, K] @ weight[N, K]^T for M <= 256, bfloat16 operands;
     the k range is cut into P splits so that enough blocks stream the weights."""
     _need_cuda(x, weight)
@@ -343,23 +396,71 @@ def gemm_bf16_skinny(x: torch.Tensor, weight: torch.Tensor, splits: int | None =
         raise KernelError("gemm_bf16_skinny: operands must be contiguous bfloat16, K a multiple of 8, at most 256 rows")
     lib = library.load()
     if splits is None:
-        # about two blocks per SM (more of the weights are fetched ahead while earlier kernels run), but no
-        # more splits than keep the partial sums (4 bytes per row, column and split) well below the weight bytes
-        n_tiles = -(-n // block_n)
-        splits = max(1, min(-(-k // 128), _gemm_target_blocks() // n_tiles, max(1, k // (4 * m)), max_splits or _GEMM_MAX_SPLITS)) if n_tiles < sm_count() else 1
-    splits = lib.lse_gemm_bf16_skinny_splits(k, int(splits), int(kboxes))
+        splits = _wished_splits(m, n, k, block_n, max_splits)
+    splits = lib.lse_gemm_bf16_skinny_splits(k, int(splits))
     out = torch.empty((splits, m, n), dtype=torch.float32, device=x.device)
-    check(lib.lse_gemm_bf16_skinny(x.data_ptr(), weight.data_ptr(), out.data_ptr(), m, n, k, splits, int(stages),
-                                   int(kboxes), int(block_n), None, _stream()), "gemm_bf16_skinny")
+    _launch_skinny(x, weight, m, n, k, splits, stages, block_n, PARTIALS, out=out)
     return out
 
 
-GATED_INTERLEAVE = 32      # gate and up rows alternate in blocks of 32: blocks of 64 weight rows per thread block
+def gemm_fused_ok(x, weight: torch.Tensor) -> bool:
+    """Whether the few-rows product with a cluster epilogue (or with x made from the residual) takes these."""
+    if weight.dtype != torch.bfloat16 or not weight.is_contiguous() or weight.data_ptr() % 16 or weight.shape[1] % 8:
+        return False
+    if isinstance(x, NormedRows):
+        return x.residual.shape[0] <= GEMM_FUSED_MAX_ROWS and x.residual.shape[1] == weight.shape[1]
+    return x.shape[0] <= GEMM_FUSED_MAX_ROWS and gemm_bf16_skinny_ok(x, weight) and x.shape[1] == weight.shape[1]
 
 
-def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, interleave: int = GATED_INTERLEAVE) -> torch.Tensor:
-    """[2I, K] weight for ``gemm_bf16_skinny_gated``: ``interleave`` gate rows, then the ``interleave`` up
-    rows of the same outputs, and so on (I a multiple of ``interleave``)."""
+def _fused_shape(x, weight, block_n, splits, max_splits):
+    m, k = x.shape
+    n = weight.shape[0]
+    if not gemm_fused_ok(x, weight):
+        raise KernelError("few-rows product: contiguous bfloat16 weight [N, K], K a multiple of 8, at most 32 rows")
+    if splits is None:
+        splits = _wished_splits(m, n, k, block_n, max_splits or 8)
+    return m, n, k, library.load().lse_gemm_bf16_skinny_cluster(k, int(splits))
+
+
+def gemm_bf16_plain(x, weight: torch.Tensor, bias: torch.Tensor | None = None, splits: int | None = None, stages: int = 6,
+                    block_n: int = 128) -> torch.Tensor:
+    """x @ weight^T (+ bias) as float32 [M, N], finished inside the kernel (the splits of a block column add
+    themselves up through distributed shared memory).  ``x``: bfloat16 [M, K] or ``NormedRows``."""
+    m, n, k, cluster = _fused_shape(x, weight, block_n, splits, None)
+    out = torch.empty((m, n), dtype=torch.float32, device=weight.device)
+    if bias is not None:
+        assert bias.dtype == torch.float32 and bias.shape == (n,)
+    _launch_skinny(x, weight, m, n, k, cluster, stages, block_n, PLAIN, out=out, bias=bias, name="gemm_bf16_plain")
+    return out
+
+
+def gemm_bf16_into_residual(x, weight: torch.Tensor, residual: torch.Tensor, splits: int | None = None, stages: int = 6,
+                            block_n: int = 128) -> torch.Tensor:
+    """residual[M, N] += x @ weight^T in place (float32); returns partial sums of squares of the new rows
+    [parts, M] for the ``NormedRows`` of the next product."""
+    m, n, k, cluster = _fused_shape(x, weight, block_n, splits, None)
+    assert residual.dtype == torch.float32 and residual.shape == (m, n) and residual.is_contiguous()
+    sumsq = torch.empty((-(-n // block_n) * cluster, m), dtype=torch.float32, device=weight.device)
+    _launch_skinny(x, weight, m, n, k, cluster, stages, block_n, RESIDUAL, residual=residual, sumsq_out=sumsq,
+                   name="gemm_bf16_into_residual")
+    return sumsq
+
+
+def gemm_bf16_gate(x, weight: torch.Tensor, splits: int | None = None, stages: int = 6,
+                   block_n: int = 2 * GATE_INTERLEAVE) -> torch.Tensor:
+    """silu(x @ gate^T) * (x @ up^T) as bfloat16 [M, I]; ``weight`` is the [2I, K] matrix of
+    ``interleave_gate_up(gate, up, block_n // 2)``."""
+    m, n, k, cluster = _fused_shape(x, weight, block_n, splits, None)
+    if n % block_n:
+        raise KernelError("gemm_bf16_gate: the interleaved weight must have a multiple of block_n rows")
+    act = torch.empty((m, n // 2), dtype=torch.bfloat16, device=weight.device)
+    _launch_skinny(x, weight, m, n, k, cluster, stages, block_n, GATE, act_out=act, name="gemm_bf16_gate")
+    return act
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, interleave: int = GATE_INTERLEAVE) -> torch.Tensor:
+    """[2I, K] weight whose rows alternate ``interleave`` gate rows and the ``interleave`` up rows of the same
+    outputs (I a multiple of ``interleave``)."""
     inter, k = gate.shape
     assert inter % interleave == 0 and up.shape == gate.shape
     blocks = inter // interleave
@@ -367,89 +468,11 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, interleave: int = G
     return stacked.reshape(2 * inter, k).contiguous()
 
 
-def gemm_bf16_skinny_gated(x: torch.Tensor, weight: torch.Tensor, interleave: int = GATED_INTERLEAVE,
-                           stages: int = 8) -> torch.Tensor:
-    """silu(x @ gate^T) * (x @ up^T) as bfloat16 [M, I] in one kernel; ``weight`` is the interleaved
-    [2I, K] matrix of ``interleave_gate_up`` (interleave 32 or 64); M <= 256."""
-    _need_cuda(x, weight)
-    m, k = x.shape
-    n = weight.shape[0]
-    block_n = 2 * interleave
-    if block_n not in (64, 128) or not gemm_bf16_skinny_ok(x, weight) or weight.shape[1] != k or n % block_n:
-        raise KernelError("gemm_bf16_skinny_gated: contiguous bfloat16 operands, K % 8 == 0, I a multiple of the "
-                          "interleave (32 or 64), M <= 256")
-    lib = library.load()
-    out = torch.empty((m, n // 2), dtype=torch.bfloat16, device=x.device)
-    check(lib.lse_gemm_bf16_skinny(x.data_ptr(), weight.data_ptr(), None, m, n, k, 1, int(stages), 1, block_n,
-                                   out.data_ptr(), _stream()), "gemm_bf16_skinny_gated")
-    return out
-
-
-FINISH_GATE_INTERLEAVE = 64     # 128 weight rows per block: 64 gate rows, then the 64 up rows of the same outputs
-
-
-def gemm_bf16_skinny_finish_gate(x: torch.Tensor, weight: torch.Tensor, arrivals: torch.Tensor,
-                                 splits: int | None = None, stages: int = 6,
-                                 max_splits: int | None = None) -> tuple[torch.Tensor, torch.Tensor]:
-    """The split-k product of ``gemm_bf16_skinny`` on a gate/up matrix interleaved in blocks of 64
-    (``interleave_gate_up(gate, up, 64)``) whose last-arriving split of every block column also
-    applies the gate: returns (partial sums [P, M, 2I] float32, silu(gate) * up [M, I] bfloat16),
-    the latter bit for bit what ``silu_mul`` gives on the former.  ``arrivals``: int32 zeros, one
-    per 128 weight rows, that only this product uses."""
-    _need_cuda(x, weight, arrivals)
-    m, k = x.shape
-    n = weight.shape[0]
-    if (not gemm_bf16_skinny_ok(x, weight) or weight.shape[1] != k or n % 128 or arrivals.dtype != torch.int32
-            or arrivals.shape[0] < n // 128):
-        raise KernelError("gemm_bf16_skinny_finish_gate: contiguous bfloat16 operands, K % 8 == 0, 2I a multiple of 128, "
-                          "M <= 256, one int32 counter per 128 weight rows")
-    lib = library.load()
-    if splits is None:
-        n_tiles = n // 128
-        splits = max(1, min(-(-k // 128), _gemm_target_blocks() // n_tiles, max(1, k // (4 * m)), max_splits or _GEMM_MAX_SPLITS)) if n_tiles < sm_count() else 1
-    splits = lib.lse_gemm_bf16_skinny_splits(k, int(splits), 1)
-    out = torch.empty((splits, m, n), dtype=torch.float32, device=x.device)
-    act = torch.empty((m, n // 2), dtype=torch.bfloat16, device=x.device)
-    check(lib.lse_gemm_bf16_skinny_finish_gate(x.data_ptr(), weight.data_ptr(), out.data_ptr(), arrivals.data_ptr(),
-                                               act.data_ptr(), m, n, k, splits, int(stages), _stream()),
-          "gemm_bf16_skinny_finish_gate")
-    return out, act
-
-
-GATED_IN_MAX_ROWS = 16      # one 16-byte chunk of the activations per thread and stage
-
-
-def gemm_bf16_skinny_gated_in_ok(gate_up: torch.Tensor, weight: torch.Tensor) -> bool:
-    """Whether ``gemm_bf16_skinny_gated_in`` takes these operands."""
-    return (gate_up.dim() == 3 and gate_up.dtype == torch.float32 and weight.dtype == torch.bfloat16
-            and gate_up.shape[1] <= GATED_IN_MAX_ROWS and gate_up.shape[2] == 2 * weight.shape[1]
-            and weight.shape[1] % 8 == 0 and gate_up.is_contiguous() and weight.is_contiguous()
-            and gate_up.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
-
-
-def gemm_bf16_skinny_gated_in(gate_up: torch.Tensor, weight: torch.Tensor, splits: int | None = None,
-                              stages: int = 6, max_splits: int | None = None) -> torch.Tensor:
-    """Partial sums [P, M, N] (float32) of act @ weight[N, I]^T where act = silu(gate) * up, rounded to
-    bfloat16, is made inside the kernel from ``gate_up``: a float32 stack of partial sums [Q, M, 2I] whose
-    rows are [gate (I) | up (I)].  The result equals ``silu_mul`` followed by ``gemm_bf16_skinny`` bit for
-    bit (the same values meet the tensor cores in the same order); one kernel and one round trip through
-    memory less."""
-    _need_cuda(gate_up, weight)
-    if not gemm_bf16_skinny_gated_in_ok(gate_up, weight):
-        raise KernelError("gemm_bf16_skinny_gated_in: float32 partial sums [Q, M, 2I], contiguous bfloat16 weight "
-                          "[N, I], I a multiple of 8, at most 16 rows")
-    parts, m, two_i = gate_up.shape
-    k = two_i // 2
-    n = weight.shape[0]
-    lib = library.load()
-    if splits is None:
-        n_tiles = -(-n // 128)
-        splits = max(1, min(-(-k // 128), _gemm_target_blocks() // n_tiles, max(1, k // (4 * m)), max_splits or _GEMM_MAX_SPLITS)) if n_tiles < sm_count() else 1
-    splits = lib.lse_gemm_bf16_skinny_splits(k, int(splits), 1)
-    out = torch.empty((splits, m, n), dtype=torch.float32, device=weight.device)
-    check(lib.lse_gemm_bf16_skinny_gated_in(gate_up.data_ptr(), parts, m * two_i, weight.data_ptr(), out.data_ptr(),
-                                            m, n, k, splits, int(stages), _stream()), "gemm_bf16_skinny_gated_in")
-    return out
+def gemm_bf16_skinny_test_hooks(spin_limit: int = 0, withhold: bool = False) -> None:
+    """For tests of the bounded waits: ``spin_limit`` iterations before a wait gives up (0: the default),
+    ``withhold``: every block leaves out its last weight tile, so that a wait runs out."""
+    torch.cuda.synchronize()
+    check(library.load().lse_gemm_bf16_skinny_test_hooks(int(spin_limit), int(bool(withhold))), "gemm test hooks")
 
 
 def gemm_bf16_skinny_status() -> int:

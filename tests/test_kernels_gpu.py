@@ -203,6 +203,20 @@ def dense_attention(q, k, v, scale, window=0):
     return out
 
 
+def poison_unowned(k_cache, v_cache, tables, contexts, page):
+    """NaN in every page that no request owns and in the unused end of every last page: none of it may
+    reach a result."""
+    owned = torch.zeros(k_cache.shape[0], dtype=torch.bool)
+    owned[tables[tables >= 0].long().cpu()] = True
+    k_cache[~owned] = float("nan")
+    v_cache[~owned] = float("nan")
+    for s, ctx in enumerate(contexts):
+        if ctx % page:
+            last = int(tables[s, (ctx - 1) // page])
+            k_cache[last, :, ctx % page:] = float("nan")
+            v_cache[last, :, ctx % page:] = float("nan")
+
+
 def paged_setup(rng, contexts, n_kv, head_dim, page, dtype, extra_pages=5):
     """Random keys/values of each request scattered over randomly permuted physical pages."""
     need = sum(-(-c // page) for c in contexts)
@@ -410,6 +424,7 @@ def test_decode_attention_split_keys(head_dim, n_q, n_kv, page, splits, cluster)
     torch.manual_seed(n_q * splits)
     contexts = [1, 15, 16, 17, 63, 64, 65, 130, 1000, 2049]
     k_cache, v_cache, tables, dense = paged_setup(rng, contexts, n_kv, head_dim, page, torch.bfloat16)
+    poison_unowned(k_cache, v_cache, tables, contexts, page)
     q = torch.randn(len(contexts), n_q, head_dim, device=DEV).bfloat16()
     segs = torch.arange(len(contexts), dtype=torch.int32, device=DEV)
     positions = torch.tensor([c - 1 for c in contexts], dtype=torch.int32, device=DEV)
@@ -458,6 +473,7 @@ def test_prefill_attention_portions_with_earlier_context(head_dim, n_q, n_kv, pa
     portions = [(0, 1), (0, 70), (5, 2), (63, 3), (64, 64), (100, 129), (1000, 1), (300, 11), (0, 200)]
     contexts = [before + rows for before, rows in portions]
     k_cache, v_cache, tables, dense = paged_setup(rng, contexts, n_kv, head_dim, page, torch.bfloat16)
+    poison_unowned(k_cache, v_cache, tables, contexts, page)
     total = sum(rows for _, rows in portions)
     q = torch.randn(total, n_q, head_dim, device=DEV).bfloat16()
     starts, firsts, cursor = [], [], 0
@@ -500,6 +516,68 @@ def test_prefill_attention_keeps_the_causal_edge():
         pos = before + local
         want = dense_attention(q[local], k[:pos + 1], v[:pos + 1], scale)
         assert float((out[local].double() - want).abs().max()) < 2.0 ** -6, local
+
+
+def test_attention_at_the_long_context_of_the_largest_shape():
+    """Five query heads a key/value head of 128, pages of 16: a 256-row portion on top of 6,144 earlier keys
+    (both prompt kernels) and single rows at context 8,191 and 8,192 (the decode kernel, one and eight splits)."""
+    rng = random.Random(14)
+    torch.manual_seed(14)
+    n_q, n_kv, head_dim, page = 10, 2, 128, 16
+    scale = 1.0 / math.sqrt(head_dim)
+    before, rows = 6144, 256
+    k_cache, v_cache, tables, dense = paged_setup(rng, [before + rows, 8191, 8192], n_kv, head_dim, page, torch.bfloat16)
+    poison_unowned(k_cache, v_cache, tables, [before + rows, 8191, 8192], page)
+    q = torch.randn(rows, n_q, head_dim, device=DEV).bfloat16()
+    starts = torch.tensor([0, rows], dtype=torch.int32, device=DEV)
+    firsts = torch.tensor([before], dtype=torch.int32, device=DEV)
+    want = dense_causal(q, dense[0][0], dense[0][1], before, scale)
+    for kernel in (ops().paged_attention_prefill, ops().paged_attention_prefill_tc):
+        out = torch.full_like(q, 9.0)
+        kernel(q, k_cache, v_cache, out, tables, starts, firsts, scale)
+        err = float((out.double() - want).abs().max())
+        assert err < 2.0 ** -7 * max(1.0, float(want.abs().max())), (kernel.__name__, err)
+    assert ops().attention_tc_status() == 0
+    q1 = torch.randn(2, n_q, head_dim, device=DEV).bfloat16()
+    segs = torch.tensor([1, 2], dtype=torch.int32, device=DEV)
+    positions = torch.tensor([8190, 8191], dtype=torch.int32, device=DEV)
+    for splits in (1, 8):
+        out = torch.empty_like(q1)
+        ops().paged_attention_decode(q1, k_cache, v_cache, out, tables, segs, positions, scale, splits)
+        for r in range(2):
+            want1 = dense_attention(q1[r], dense[1 + r][0], dense[1 + r][1], scale)
+            assert float((out[r].double() - want1).abs().max()) < 2.0 ** -7 * max(1.0, float(want1.abs().max())), (splits, r)
+
+
+def test_prompt_attention_with_more_pages_than_its_staged_block_table_holds():
+    """Pages of two keys: requests of more than 1,024 pages, beside a short one, on the mma.sync prompt kernel
+    (its block table no longer fits the shared-memory copy) and on the general kernel."""
+    rng = random.Random(15)
+    torch.manual_seed(15)
+    n_q, n_kv, head_dim, page = 6, 2, 64, 2
+    scale = 1.0 / math.sqrt(head_dim)
+    portions = [(2300, 21), (10, 5), (2051, 70)]
+    contexts = [before + rows for before, rows in portions]
+    k_cache, v_cache, tables, dense = paged_setup(rng, contexts, n_kv, head_dim, page, torch.bfloat16)
+    poison_unowned(k_cache, v_cache, tables, contexts, page)
+    assert tables.shape[1] > 1024
+    total = sum(rows for _, rows in portions)
+    q = torch.randn(total, n_q, head_dim, device=DEV).bfloat16()
+    starts = [0]
+    for _, rows in portions:
+        starts.append(starts[-1] + rows)
+    out = torch.full_like(q, 9.0)
+    ops().paged_attention_prefill(q, k_cache, v_cache, out, tables, torch.tensor(starts, dtype=torch.int32, device=DEV),
+                                  torch.tensor([b for b, _ in portions], dtype=torch.int32, device=DEV), scale)
+    segs = torch.cat([torch.full((rows,), s, dtype=torch.int32) for s, (_, rows) in enumerate(portions)]).to(DEV)
+    positions = torch.cat([torch.arange(before, before + rows, dtype=torch.int32) for before, rows in portions]).to(DEV)
+    general = torch.full_like(q, 9.0)
+    ops().paged_attention_generic(q, k_cache, v_cache, general, tables, segs, positions, scale)
+    for s, (before, rows) in enumerate(portions):
+        want = dense_causal(q[starts[s]:starts[s + 1]], dense[s][0], dense[s][1], before, scale)
+        for name, got in (("mma", out), ("general", general)):
+            err = float((got[starts[s]:starts[s + 1]].double() - want).abs().max())
+            assert err < 2.0 ** -7 * max(1.0, float(want.abs().max())), (name, s, err)
 
 
 TC_SHAPES = [(128, 12, 2, 16), (64, 6, 2, 16), (128, 7, 1, 8), (64, 4, 4, 32), (128, 40, 2, 64), (64, 3, 1, 128)]
@@ -635,53 +713,125 @@ def test_few_rows_product_on_tensor_cores(m, n, k, splits, block_n):
     got = parts.double().sum(0)
     want = x.double() @ w.double().t()
     # float32 accumulation of exact bfloat16 products
-    bound = (x.abs().double() @ w.abs().double().t()) * (k * 2.0 ** -24) + 1e-6
-    assert bool(((got - want).abs() <= bound).all()), float((got - want).abs().max())
+    assert bool(((got - want).abs() <= product_bound(x, w, k)).all()), float((got - want).abs().max())
     assert ops().gemm_bf16_skinny_status() == 0
 
 
-@pytest.mark.parametrize("m, inter, n, parts, splits", [(8, 8960, 1536, 2, None), (8, 8960, 1536, 2, 2), (3, 4096, 200, 1, 1),
-                                                       (1, 64, 128, 1, 1), (5, 1000, 130, 3, 4),
-                                                       (16, 256, 384, 1, 2), (11, 520, 96, 2, 3), (16, 2048, 257, 5, 2)])
-def test_product_that_makes_the_gated_activations_itself(m, inter, n, parts, splits):
-    """The down product fed with the partial sums of the gate/up product gives, bit for bit, what the SiLU
-    kernel followed by the plain product gives; and both agree with float64."""
-    torch.manual_seed(m + inter)
-    gate_up = torch.randn(parts, m, 2 * inter, device=DEV)
-    w = (torch.randn(n, inter, device=DEV) * 0.05).bfloat16()
-    fused = ops().gemm_bf16_skinny_gated_in(gate_up, w, splits)
-    act = torch.empty(m, inter, device=DEV, dtype=torch.bfloat16)
-    ops().silu_mul(gate_up, act)
-    plain = ops().gemm_bf16_skinny(act, w, fused.shape[0])
-    assert fused.shape == plain.shape and torch.equal(fused, plain)
-    g, u = gate_up.double().sum(0).split(inter, dim=1)
-    want = (torch.nn.functional.silu(g) * u) @ w.double().t()
-    bound = ((torch.nn.functional.silu(g) * u).abs() @ w.abs().double().t()) * 2.0 ** -8 + 1e-6   # activations rounded to bfloat16
-    assert bool(((fused.double().sum(0) - want).abs() <= bound).all())
+def product_bound(x, w, k):
+    """float32 accumulation of exact bfloat16 products."""
+    return (x.abs().double() @ w.abs().double().t()) * (k * 2.0 ** -24) + 1e-6
+
+
+@pytest.mark.parametrize("m, n, k, splits", [(1, 128, 64, 1), (8, 2048, 1536, 8), (3, 1536, 8960, 8), (16, 1000, 776, 3),
+                                             (32, 1536, 1536, None), (7, 200, 320, 4), (8, 96, 8, 2), (5, 130, 328, 8)])
+@pytest.mark.parametrize("block_n", [128, 64])
+def test_product_whose_splits_add_themselves_up(m, n, k, splits, block_n):
+    """The splits of a block column as a thread-block cluster: finished float32 sums with a bias; the same added to a
+    float32 residual in place, with the partial sums of squares of the new rows; launch after launch."""
+    torch.manual_seed(m + n + k)
+    x = torch.randn(m, k, device=DEV).bfloat16()
+    w = (torch.randn(n, k, device=DEV) * 0.05).bfloat16()
+    bias = torch.randn(n, device=DEV)
+    want = x.double() @ w.double().t()
+    bound = product_bound(x, w, k)
+    for _ in range(2):
+        got = ops().gemm_bf16_plain(x, w, bias, splits, block_n=block_n)
+        assert got.dtype == torch.float32 and got.shape == (m, n)
+        assert bool(((got.double() - (want + bias.double())).abs() <= bound + 1e-6 * bias.abs().double()).all())
+        assert torch.equal(ops().gemm_bf16_plain(x, w, None, splits, block_n=block_n) + bias, got)
+        residual = torch.randn(m, n, device=DEV)
+        before = residual.clone()
+        sumsq = ops().gemm_bf16_into_residual(x, w, residual, splits, block_n=block_n)
+        assert bool(((residual.double() - (before.double() + want)).abs() <= bound + 1e-6).all())
+        assert sumsq.shape[1] == m and rel_err(sumsq.double().sum(0), residual.double().pow(2).sum(1)) < 1e-5
     assert ops().gemm_bf16_skinny_status() == 0
 
 
-@pytest.mark.parametrize("m, inter, k, splits", [(8, 8960, 1536, None), (1, 64, 64, 1), (5, 192, 520, 3), (16, 1024, 776, 7),
-                                                 (32, 8960, 1536, None), (200, 320, 264, 2)])
-def test_product_whose_last_split_applies_the_gate(m, inter, k, splits):
-    """Bit for bit the SiLU kernel's result on the same partial sums, launch after launch (the arrival
-    counters have to be back at zero), and the partial sums themselves are those of the plain product."""
+@pytest.mark.parametrize("m, inter, k, splits", [(8, 8960, 1536, None), (1, 64, 64, 1), (5, 192, 520, 3), (16, 1024, 776, 8),
+                                                 (32, 8960, 1536, None), (3, 128, 72, 2)])
+@pytest.mark.parametrize("block_n", [128, 64])
+def test_product_that_applies_the_gate(m, inter, k, splits, block_n):
+    """silu(x gate^T) * (x up^T) from the interleaved weight in one kernel, for any number of splits; and through the
+    separate SiLU kernel reading the interleaved columns of a library product (the many-rows path)."""
     torch.manual_seed(m + inter)
     x = torch.randn(m, k, device=DEV).bfloat16()
     gate = (torch.randn(inter, k, device=DEV) * 0.05).bfloat16()
     up = (torch.randn(inter, k, device=DEV) * 0.05).bfloat16()
-    w = ops().interleave_gate_up(gate, up, 64)
-    arrivals = torch.zeros(2 * inter // 128, dtype=torch.int32, device=DEV)
-    for _ in range(3):
-        parts, act = ops().gemm_bf16_skinny_finish_gate(x, w, arrivals, splits)
-        assert int(arrivals.abs().sum()) == 0
-        want = torch.empty(m, inter, device=DEV, dtype=torch.bfloat16)
-        ops().silu_mul(parts, want, 64)
-        assert torch.equal(act, want)
-        assert torch.equal(parts, ops().gemm_bf16_skinny(x, w, parts.shape[0]))
+    half = block_n // 2
+    w = ops().interleave_gate_up(gate, up, half)
+    assert torch.equal(w[:half], gate[:half]) and torch.equal(w[half:2 * half], up[:half])
     g, u = x.double() @ gate.double().t(), x.double() @ up.double().t()
     exact = torch.nn.functional.silu(g) * u
-    assert float((act.double() - exact).abs().max()) <= 2.0 ** -7 * float(exact.abs().max()) + 1e-6
+    for _ in range(2):
+        act = ops().gemm_bf16_gate(x, w, splits, block_n=block_n)
+        assert act.dtype == torch.bfloat16 and act.shape == (m, inter)
+        assert float((act.double() - exact).abs().max()) <= 2.0 ** -7 * float(exact.abs().max()) + 1e-6
+    columns = torch.mm(x, w.t())                       # library product, interleaved columns
+    out = torch.empty(m, inter, device=DEV, dtype=torch.bfloat16)
+    ops().silu_mul(columns, out, interleave=half)
+    assert rel_err(out, exact) < TOL[torch.bfloat16] * 4     # its input was rounded to bfloat16 once more
+    assert ops().gemm_bf16_skinny_status() == 0
+
+
+@pytest.mark.parametrize("m, hidden, n, parts", [(8, 1536, 2048, 1), (8, 1536, 17920, 96), (1, 64, 128, 1), (5, 328, 130, 7),
+                                                 (32, 3584, 256, 224), (17, 8, 64, 2)])
+def test_product_that_normalises_its_rows_itself(m, hidden, n, parts):
+    """x = RMSNorm(residual) made inside the product from the residual rows and partial sums of squares: against
+    the norm kernel followed by the product (the same bfloat16 rows but for the last bit of 1/rms), and against float64;
+    in all three ways of finishing."""
+    torch.manual_seed(m + hidden)
+    residual = torch.randn(m, hidden, device=DEV) * 3
+    weight = 1 + 0.1 * torch.randn(hidden, device=DEV)
+    eps = 1e-5
+    exact_sq = residual.double().pow(2).sum(1)
+    shares = torch.rand(parts, m, device=DEV).double() + 0.1
+    sumsq = (shares / shares.sum(0) * exact_sq).float().contiguous()      # any split of the sums into parts
+    rows = ops().NormedRows(residual, sumsq, weight, eps)
+    normed = rows.materialise(torch.bfloat16)
+    want_x = qwen2_plain.rms_norm(residual.double(), weight.double(), eps)
+    assert rel_err(normed, want_x) < TOL[torch.bfloat16] * 2
+    w = (torch.randn(n, hidden, device=DEV) * 0.05).bfloat16()
+    want = want_x @ w.double().t()
+    slack = (want_x.abs() @ w.abs().double().t()) * 2.0 ** -8 + 1e-6      # the rows are rounded to bfloat16
+    got = ops().gemm_bf16_plain(rows, w)
+    assert bool(((got.double() - want).abs() <= slack).all())
+    assert rel_err(got, ops().gemm_bf16_plain(normed, w)) < 2e-3
+    target = torch.randn(m, n, device=DEV)
+    before = target.clone()
+    squares = ops().gemm_bf16_into_residual(rows, w, target)
+    assert bool(((target.double() - before.double() - want).abs() <= slack).all())
+    assert rel_err(squares.double().sum(0), target.double().pow(2).sum(1)) < 1e-5
+    if n % 128 == 0:
+        act = ops().gemm_bf16_gate(rows, w)
+        g, u = want.view(m, n // 128, 2, 64).unbind(2)
+        exact = (torch.nn.functional.silu(g) * u).reshape(m, n // 2)
+        assert float((act.double() - exact).abs().max()) <= 2.0 ** -6 * float(exact.abs().max()) + 1e-6
+    assert ops().gemm_bf16_skinny_status() == 0
+
+
+def test_a_wait_that_runs_out_is_reported_and_the_kernel_returns():
+    """Every block leaves out its last weight tile and gives up waiting for it after a few thousand tries: the kernel
+    returns, the status word says so (through the synchronous read and through the copy that is queued behind a
+    step's tokens), and after a reset the next launch is clean.  Nothing faults: a barrier simply gets no arrival."""
+    x = torch.randn(8, 512, device=DEV).bfloat16()
+    w = (torch.randn(256, 512, device=DEV) * 0.05).bfloat16()
+    assert ops().gemm_bf16_skinny_status() == 0
+    ops().gemm_bf16_skinny_test_hooks(spin_limit=2000, withhold=True)
+    try:
+        ops().gemm_bf16_skinny(x, w, 2)
+        torch.cuda.synchronize()
+        assert ops().gemm_bf16_skinny_status() == 1
+        ops().kernel_status_reset()
+        ops().gemm_bf16_into_residual(x, w, torch.zeros(8, 256, device=DEV), 4)       # the cluster form gives up and still meets its barriers
+        words = torch.zeros(2, dtype=torch.int32).pin_memory()
+        ops().kernel_status_async(words)
+        torch.cuda.synchronize()
+        assert words.tolist() == [1, 0]
+    finally:
+        ops().gemm_bf16_skinny_test_hooks()
+        ops().kernel_status_reset()
+    got = ops().gemm_bf16_plain(x, w)
+    assert bool(((got.double() - x.double() @ w.double().t()).abs() <= product_bound(x, w, 512)).all())
     assert ops().gemm_bf16_skinny_status() == 0
 
 
@@ -744,24 +894,3 @@ def test_rope_and_silu_of_partial_sums():
         ops().silu_mul(gate_up, out)
         total = gate_up.double().sum(0)
         assert rel_err(out, torch.nn.functional.silu(total[:, :inter]) * total[:, inter:]) < TOL[torch.bfloat16] * 2
-
-
-@pytest.mark.parametrize("interleave", [32, 64])
-@pytest.mark.parametrize("m, inter, k", [(1, 64, 64), (8, 8960, 1536), (5, 256, 96), (16, 192, 520), (33, 128, 72)])
-def test_gated_product_and_interleaved_silu(m, inter, k, interleave):
-    """silu(x gate^T) * (x up^T) from the interleaved weight: in one kernel, and through the separate
-    SiLU kernel reading the interleaved columns."""
-    torch.manual_seed(m + inter)
-    x = torch.randn(m, k, device=DEV).bfloat16()
-    gate = (torch.randn(inter, k, device=DEV) * 0.1).bfloat16()
-    up = (torch.randn(inter, k, device=DEV) * 0.1).bfloat16()
-    weight = ops().interleave_gate_up(gate, up, interleave)
-    assert torch.equal(weight[:interleave], gate[:interleave]) and torch.equal(weight[interleave:2 * interleave], up[:interleave])
-    want = torch.nn.functional.silu(x.double() @ gate.double().t()) * (x.double() @ up.double().t())
-    got = ops().gemm_bf16_skinny_gated(x, weight, interleave)
-    assert got.dtype == torch.bfloat16 and rel_err(got, want) < TOL[torch.bfloat16] * 2
-    columns = torch.mm(x, weight.t())                       # library product, interleaved columns
-    out = torch.empty(m, inter, device=DEV, dtype=torch.bfloat16)
-    ops().silu_mul(columns, out, interleave=interleave)
-    assert rel_err(out, want) < TOL[torch.bfloat16] * 4     # its input was rounded to bfloat16 once more
-    assert ops().gemm_bf16_skinny_status() == 0

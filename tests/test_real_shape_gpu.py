@@ -130,3 +130,85 @@ def test_layer_sizes_of_a_larger_model(tmp_path):
         limit = helpers.tolerance("bfloat16", want_rows)
         error = (got_rows - want_rows).abs().max(dim=1).values
         assert float(error.max()) <= limit, f"{name}: max error {float(error.max()):.3e} > {limit:.3e} at row {int(error.argmax())}"
+
+
+def test_tcgen05_attention_replayed_from_a_portion_graph(folder):
+    """Three steps of one size class (320 rows, up to 8 requests, every row wanted, a portion of 128 rows or more)
+    with different cuts: the first runs launch by launch, the second is captured and replayed, the third is a
+    replay of a graph that was captured for other portions (the kernel choice and the grid are frozen in the graph;
+    segment starts, first positions and block tables are read from device memory).  Portions start off the tile
+    grid, on top of earlier keys.  Every row against the plain implementation."""
+    from llm_serving_engine_b200.cache import CacheManager
+    from llm_serving_engine_b200.config import CacheConfig
+    from llm_serving_engine_b200.engine import StepEntry, StepRunner
+    from llm_serving_engine_b200.kernels import ops
+    from llm_serving_engine_b200.models import cache_requirements, load_model
+
+    model = load_model(folder, dtype="bfloat16", device="cuda")
+    cache = CacheManager(cache_requirements(model.spec), CacheConfig(16, 64), model.dtype, model.device, 1024, num_state_slots=8)
+    runner = StepRunner(model, cache, 512, 8)
+    assert runner.use_graphs and runner.graph_portions
+    cfg, weights = qwen2_plain.load_folder(folder)
+    rng = random.Random(12)
+    rounds = [[(0, 150), (37, 150)], [(5, 170), (0, 130)], [(21, 130), (0, 130), (3, 40)]]    # (earlier keys, rows of the portion)
+    with torch.inference_mode():
+        for number, portions in enumerate(rounds):
+            sequences, entries = [], []
+            for index, (before, rows) in enumerate(portions):
+                name = f"r{number}_{index}"
+                tokens = helpers.random_tokens(rng, CONFIG["vocab_size"], before + rows)
+                sequences.append(tokens)
+                cache.create(name)
+                if before:
+                    runner.run([StepEntry(name, tokens[:before], [])])
+                entries.append(StepEntry(name, tokens[before:], list(range(rows))))
+            replays = runner.portion_graph_replays
+            got = runner.run(entries).float().cpu()
+            assert runner.portion_graph_replays == replays + (1 if number else 0)
+            cursor = 0
+            for (before, rows), tokens in zip(portions, sequences):
+                want = qwen2_plain.forward_full(cfg, weights, tokens)[before:]
+                part = got[cursor:cursor + rows]
+                cursor += rows
+                limit = helpers.tolerance("bfloat16", want)
+                error = (part - want).abs().max(dim=1).values
+                assert float(error.max()) <= limit, f"round {number}, portion ({before}, {rows}): {float(error.max()):.3e} > {limit:.3e} at row {int(error.argmax())}"
+                assert helpers.rms_ratio(part, want) <= helpers.RMS_RATIO_LARGE_LAYERS
+            for entry in entries:
+                cache.free(entry.request_id)
+    assert runner.portion_graph_replays == 2 and ops.attention_tc_status() == 0
+
+
+def test_a_page_of_another_request_is_noticed(folder):
+    """That the comparison can fail: the same decode steps run twice, the second time with one entry of one
+    request's block table pointing at a page of the other live request (a host-side edit; every page is owned
+    and valid, nothing faults).  Sixteen wrong keys among 150 must fail the comparison; the undamaged run passes it."""
+    from llm_serving_engine_b200.cache import CacheManager
+    from llm_serving_engine_b200.config import CacheConfig
+    from llm_serving_engine_b200.engine import StepEntry, StepRunner
+    from llm_serving_engine_b200.models import cache_requirements, load_model
+
+    model = load_model(folder, dtype="bfloat16", device="cuda")
+    cfg, weights = qwen2_plain.load_folder(folder)
+    rng = random.Random(13)
+    a = helpers.random_tokens(rng, CONFIG["vocab_size"], 158)
+    b = helpers.random_tokens(rng, CONFIG["vocab_size"], 150)
+    want = qwen2_plain.forward_full(cfg, weights, a)[150:]
+    passed = []
+    for damaged in (False, True):
+        cache = CacheManager(cache_requirements(model.spec), CacheConfig(16, 64), model.dtype, model.device, 1024, num_state_slots=2)
+        runner = StepRunner(model, cache, 512, 2)
+        rows = []
+        with torch.inference_mode():
+            cache.create("a")
+            cache.create("b")
+            runner.run([StepEntry("a", a[:150], []), StepEntry("b", b, [])])
+            if damaged:
+                victim, other = cache.requests["a"], cache.requests["b"]
+                victim.tables[0][3], victim.tables_np[0][3] = other.tables[0][3], other.tables_np[0][3]   # keys 48 .. 63
+            for token in a[150:]:
+                rows.append(runner.run([StepEntry("a", [token], [0])]).float().cpu()[0])
+        got = torch.stack(rows)
+        passed.append(float((got - want).abs().max()) <= helpers.tolerance("bfloat16", want)
+                      and helpers.rms_ratio(got, want) <= helpers.RMS_RATIO_LARGE_LAYERS)
+    assert passed == [True, False], passed

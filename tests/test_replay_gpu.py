@@ -65,6 +65,22 @@ def test_mixed_with_page_reuse(name, dtype):
     helpers.assert_close(name, dtype, requests, got, "mixed batches with page reuse")
 
 
+@pytest.mark.parametrize("name, dtype", [("B", "float32"), ("D", "float32"), ("D", "bfloat16"), ("E", "bfloat16"), ("A", "bfloat16")])
+def test_dozens_of_live_requests(name, dtype):
+    """More than 32 rows of decoding and more than four live requests: decode-only steps of 33, 64 and 65 rows
+    (other products, other graph buckets, other splits of the decode attention than a handful of rows take),
+    prompt portions beside more than 32 decoding requests, and a pool so small that the pages of requests that
+    ended serve the ones that start; every logit row against the plain implementation."""
+    config, page, _ = ALL[name]
+    requests, steps, peak = helpers.trace_many_live(config["vocab_size"], seed=31)
+    assert max(len(step["entries"]) for step in steps) == 65
+    assert {len(step["entries"]) for step in steps if all(len(e["tokens"]) == 1 for e in step["entries"])} >= {33, 64, 65}
+    assert any(len(step["entries"]) > 40 and max(len(e["tokens"]) for e in step["entries"]) > 1 for step in steps)
+    assert peak < sum(-(-len(tokens) // 64) * 64 for tokens in requests.values()), "pages must be used again"
+    got = helpers.run_trace(name, dtype, steps, peak, page, max_requests=66)
+    helpers.assert_close(name, dtype, requests, got, "dozens of live requests")
+
+
 def test_float32_is_bitwise_the_same_however_it_is_cut():
     """In float32 every kernel sums in an order that depends on the row alone, so the
     logits of a position are the same bit for bit in every way of cutting and batching."""
@@ -81,6 +97,13 @@ def test_float32_is_bitwise_the_same_however_it_is_cut():
     for rid in requests:
         assert torch.equal(whole[rid], portions[rid]), f"{rid}: portions differ from whole"
         assert torch.equal(whole[rid], mixed[rid]), f"{rid}: mixed differs from whole"
+    # and with dozens of live requests: steps of 33 to 65 rows, replayed from graphs of other sizes
+    many, steps, peak = helpers.trace_many_live(config["vocab_size"], seed=32)
+    crowded = helpers.run_trace(name, "float32", steps, peak, page, max_requests=66)
+    some = {rid: many[rid] for rid in list(many)[::9]}
+    alone = helpers.run_trace(name, "float32", helpers.trace_whole(some), helpers.max_tokens_for(some), page)
+    for rid in some:
+        assert torch.equal(alone[rid], crowded[rid]), f"{rid}: differs among dozens of live requests"
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -111,3 +134,28 @@ def test_first_tokens_of_a_sequence(name, dtype):
                       "end": ["steps"] if index == 5 else []})
     got = helpers.run_trace(name, dtype, steps, 64, page)
     helpers.assert_close(name, dtype, requests, got, "first tokens")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_context_in_chunks_then_a_portion_then_decoding(dtype):
+    """The long-context schedule of the largest benchmark shape in small: a prompt fed in 2,048-token chunks, a
+    256-row portion on top of 6,144 earlier keys (512 pages a request), a long odd portion, and decoding at
+    contexts 8,191 and 8,192, the position limit.  Five query heads on one key/value head of 128."""
+    from tiny_configs import EXTRA
+
+    config, page, _ = EXTRA["L"]
+    rng = random.Random(41)
+    tokens = helpers.random_tokens(rng, config["vocab_size"], 8192)
+    cuts = [(0, 2048), (2048, 4096), (4096, 6144), (6144, 6400), (6400, 8190), (8190, 8191), (8191, 8192)]
+    steps, wanted = [], []
+    for number, (lo, hi) in enumerate(cuts):
+        want = list(range(hi - lo)) if hi - lo <= 256 else [0, 1, (hi - lo) // 2, hi - lo - 1]
+        wanted += [lo + index for index in want]
+        steps.append({"step": number, "entries": [{"id": "long", "tokens": tokens[lo:hi], "want": want}],
+                      "end": ["long"] if hi == 8192 else []})
+    got = helpers.run_trace("L", dtype, steps, 8192, page)["long"]
+    reference = helpers.plain_logits("L", dtype, tokens)[wanted]
+    error = (got - reference).abs().max(dim=1).values
+    limit = helpers.tolerance(dtype, reference)
+    assert float(error.max()) <= limit, f"max error {float(error.max()):.3e} > {limit:.3e} at position {wanted[int(error.argmax())]}"
+    assert helpers.rms_ratio(got, reference) <= helpers.RMS_RATIO[dtype]

@@ -51,3 +51,13 @@ TINY_E_PAGE = 8
 
 ALL = {"A": (TINY_A, TINY_A_PAGE, 0), "B": (TINY_B, TINY_B_PAGE, 1), "C": (TINY_C, TINY_C_PAGE, 2),
        "D": (TINY_D, TINY_D_PAGE, 3), "E": (TINY_E, TINY_E_PAGE, 4)}
+
+# Not one of the five above (the suites that run over ALL would take too long on it): a long context limit, five
+# query heads on one key/value head of 128 (the grouping of the Qwen2.5-14B shape), for the long-context replay.
+TINY_LONG = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "vocab_size": 300, "hidden_size": 48, "intermediate_size": 80, "num_hidden_layers": 1,
+    "num_attention_heads": 5, "num_key_value_heads": 1, "head_dim": 128, "max_position_embeddings": 8192,
+    "rope_theta": 1000000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": False,
+}
+EXTRA = {"L": (TINY_LONG, 16, 6)}
