@@ -12,46 +12,34 @@
 LSE_TL_DEFINE(lse_timeline_elementwise)
 
 // ------------------------------------------------------------------ embedding
-// residual[t, :] = float(table[ids[t], :]); sumsq[t] = sum of squares of that row (when sumsq is not null)
+// residual[t, :] = float(table[ids[t], :])
 template <typename T>
 __global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids,
-                                 float* __restrict__ out, float* __restrict__ sumsq, int hidden, int vocab) {
+                                 float* __restrict__ out, int hidden, int vocab) {
   LSE_TL_BEGIN(1)
   pdl_launch_dependents();
   pdl_wait();
   LSE_TL_MARK(2)
-  __shared__ float scratch[32];
   const int t = blockIdx.x;
   const int id = ids[t];
   float* dst = out + (size_t)t * hidden;
   if (id < 0 || id >= vocab) {  // padding row of a fixed-shape batch
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = 0.f;
-    if (sumsq != nullptr && threadIdx.x == 0) sumsq[t] = 0.f;
     return;
   }
   const T* src = table + (size_t)id * hidden;
-  float sq = 0.f;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-    const float v = to_f32<T>(src[i]);
-    dst[i] = v;
-    sq = fmaf(v, v, sq);
-  }
-  if (sumsq != nullptr) {
-    const float total = block_sum(sq, scratch);
-    if (threadIdx.x == 0) sumsq[t] = total;
-  }
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_f32<T>(src[i]);
   LSE_TL_MARK(3)
 }
 
-extern "C" int lse_embedding(const void* table, int table_dtype, const int* ids, float* out, float* sumsq,
+extern "C" int lse_embedding(const void* table, int table_dtype, const int* ids, float* out,
                              int tokens, int hidden, int vocab, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   const int threads = hidden >= 1024 ? 256 : 128;
   if (table_dtype == LSE_DTYPE_F32)
-    lse_launch(embedding_kernel<float>, tokens, threads, 0, stream, (const float*)table, ids, out, sumsq, hidden, vocab);
+    lse_launch(embedding_kernel<float>, tokens, threads, 0, stream, (const float*)table, ids, out, hidden, vocab);
   else if (table_dtype == LSE_DTYPE_BF16)
-    lse_launch(embedding_kernel<__nv_bfloat16>, tokens, threads, 0, stream, (const __nv_bfloat16*)table, ids, out, sumsq,
-               hidden, vocab);
+    lse_launch(embedding_kernel<__nv_bfloat16>, tokens, threads, 0, stream, (const __nv_bfloat16*)table, ids, out, hidden, vocab);
   else
     return LSE_ERR_BAD_ARGUMENT;
   LSE_LAUNCH_CHECK();
@@ -574,11 +562,9 @@ extern "C" int lse_rope_kv_write(const void* qkv, int in_dtype, int n_partials, 
 // ------------------------------------------------------------------ SiLU gate
 // gate_up[t] = [gate (I values) | up (I values)];  out[t, i] = silu(gate_i) * up_i
 // grid: (chunks of the row, tokens); a thread handles 4 consecutive i when I % 4 == 0.
-// interleave > 0: the row holds blocks of `interleave` gate values followed by the `interleave` up
-// values of the same outputs (the layout the gated product kernel wants of its weight rows).
 template <typename TI, typename TO, int VEC>
 __global__ void silu_mul_kernel(const TI* __restrict__ gate_up, int n_partials, long long partial_stride,
-                                TO* __restrict__ out, int inter, int interleave) {
+                                TO* __restrict__ out, int inter) {
   LSE_TL_BEGIN(4)
   pdl_launch_dependents();
   pdl_wait();
@@ -587,8 +573,7 @@ __global__ void silu_mul_kernel(const TI* __restrict__ gate_up, int n_partials, 
   const int i = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
   if (i >= inter) return;
   const TI* row = gate_up + (size_t)t * 2 * inter;
-  const int gi = interleave > 0 ? (i / interleave) * 2 * interleave + i % interleave : i;
-  const int ui = interleave > 0 ? gi + interleave : inter + i;
+  const int gi = i, ui = inter + i;
   float g[4] = {0.f, 0.f, 0.f, 0.f}, u[4] = {0.f, 0.f, 0.f, 0.f};
   for (int p = 0; p < n_partials; ++p) {
     if (VEC == 4) {
@@ -620,7 +605,7 @@ __global__ void silu_mul_kernel(const TI* __restrict__ gate_up, int n_partials, 
 // numbered flat so that no block is half empty
 constexpr int SILU_UNROLL = 1;
 __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out,
-                                       int inter, long long total_chunks, int interleave) {
+                                       int inter, long long total_chunks) {
   LSE_TL_BEGIN(4)
   pdl_launch_dependents();
   pdl_wait();
@@ -637,10 +622,8 @@ __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up
       const long long t = id / per_row;
       const int i = (int)(id - t * per_row) * 8;
       const __nv_bfloat16* row = gate_up + t * 2 * inter;
-      const int gi = interleave > 0 ? (i / interleave) * 2 * interleave + i % interleave : i;
-      const int ui = interleave > 0 ? gi + interleave : inter + i;
-      g[k] = *reinterpret_cast<const uint4*>(row + gi);
-      u[k] = *reinterpret_cast<const uint4*>(row + ui);
+      g[k] = *reinterpret_cast<const uint4*>(row + i);
+      u[k] = *reinterpret_cast<const uint4*>(row + inter + i);
       where[k] = t * inter + i;
     }
   }
@@ -665,26 +648,25 @@ __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up
 }
 
 extern "C" int lse_silu_mul(const void* gate_up, int in_dtype, int n_partials, long long partial_stride, void* out,
-                            int out_dtype, int tokens, int inter, int interleave, cudaStream_t stream) {
+                            int out_dtype, int tokens, int inter, cudaStream_t stream) {
   if (tokens <= 0 || inter <= 0) return 0;
-  if (n_partials < 1 || interleave < 0 || (interleave > 0 && (interleave % 8 || inter % interleave)))
-    return LSE_ERR_BAD_ARGUMENT;
+  if (n_partials < 1) return LSE_ERR_BAD_ARGUMENT;
   const bool vec = inter % 4 == 0 && partial_stride % 4 == 0 && (((uintptr_t)gate_up | (uintptr_t)out) & 15) == 0;
   const int threads = 256;
   if (vec && inter % 8 == 0 && n_partials == 1 && in_dtype == LSE_DTYPE_BF16 && out_dtype == LSE_DTYPE_BF16) {
     const long long total_chunks = (long long)tokens * (inter / 8);
     const unsigned blocks = (unsigned)((total_chunks + threads * SILU_UNROLL - 1) / (threads * SILU_UNROLL));
     lse_launch(silu_mul_bf16x8_kernel, blocks, threads, 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out,
-               inter, total_chunks, interleave);
+               inter, total_chunks);
     LSE_LAUNCH_CHECK();
   }
   const int per_row = vec ? inter / 4 : inter;
   dim3 grid((per_row + threads - 1) / threads, tokens);
 #define LSE_SILU_CASE(TI, TO)                                                                                      \
   if (vec) lse_launch(silu_mul_kernel<TI, TO, 4>, grid, threads, 0, stream, (const TI*)gate_up, n_partials,         \
-                      partial_stride, (TO*)out, inter, interleave);                                                \
+                      partial_stride, (TO*)out, inter);                                                            \
   else lse_launch(silu_mul_kernel<TI, TO, 1>, grid, threads, 0, stream, (const TI*)gate_up, n_partials,             \
-                  partial_stride, (TO*)out, inter, interleave)
+                  partial_stride, (TO*)out, inter)
   if (in_dtype == LSE_DTYPE_F32 && out_dtype == LSE_DTYPE_F32) { LSE_SILU_CASE(float, float); }
   else if (in_dtype == LSE_DTYPE_BF16 && out_dtype == LSE_DTYPE_BF16) { LSE_SILU_CASE(__nv_bfloat16, __nv_bfloat16); }
   else if (in_dtype == LSE_DTYPE_F32 && out_dtype == LSE_DTYPE_BF16) { LSE_SILU_CASE(float, __nv_bfloat16); }

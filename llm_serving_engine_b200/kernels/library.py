@@ -13,18 +13,15 @@ from ..csrc import build
 _lib = None
 
 _SIGNATURES = {
-    "lse_embedding": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "lse_embedding": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "lse_add_rmsnorm": [c_void_p, c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_int,
                         c_int, c_float, c_int, c_void_p],
     "lse_rope_kv_write": [c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                           c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_longlong, c_void_p],
-    "lse_silu_mul": [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
-    "lse_gemm_bf16_skinny": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
-                             c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_float,
-                             c_void_p],
+    "lse_silu_mul": [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p],
+    "lse_gemm_bf16_skinny": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "lse_gemm_bf16_skinny_pad": [c_int],
     "lse_gemm_bf16_skinny_splits": [c_int, c_int],
-    "lse_gemm_bf16_skinny_cluster": [c_int, c_int],
     "lse_gemm_bf16_skinny_test_hooks": [c_uint, c_int],
     "lse_gemm_bf16_skinny_status": [],
     "lse_gemm_bf16_skinny_status_async": [c_void_p, c_void_p],

@@ -45,17 +45,14 @@ def sm_count(device=None) -> int:
     return count
 
 
-def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, sumsq: torch.Tensor | None = None) -> torch.Tensor:
-    """out[t] = float32(table[ids[t]]); ids int32 [T], out float32 [T, H].  ``sumsq`` (float32 [T]), when given,
-    receives the sum of squares of every row (what a ``NormedRows`` of these rows needs)."""
-    _need_cuda(table, ids, out, sumsq)
+def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t] = float32(table[ids[t]]); ids int32 [T], out float32 [T, H]."""
+    _need_cuda(table, ids, out)
     vocab, hidden = table.shape
     assert ids.dtype == torch.int32 and out.dtype == torch.float32 and table.is_contiguous()
     assert out.shape == (ids.shape[0], hidden) and out.is_contiguous()
-    if sumsq is not None:
-        assert sumsq.dtype == torch.float32 and sumsq.numel() >= ids.shape[0] and sumsq.is_contiguous()
     lib = library.load()
-    check(lib.lse_embedding(table.data_ptr(), dtype_code(table.dtype), ids.data_ptr(), out.data_ptr(), _ptr(sumsq),
+    check(lib.lse_embedding(table.data_ptr(), dtype_code(table.dtype), ids.data_ptr(), out.data_ptr(),
                             ids.shape[0], hidden, vocab, _stream()), "embedding")
     return out
 
@@ -304,26 +301,22 @@ def attention_tc_status() -> int:
     return int(library.load().lse_attention_tc_status())
 
 
-def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, interleave: int = 0) -> torch.Tensor:
-    """out[t, i] = silu(gate_i) * up_i; ``gate_up`` is [T, 2I] or a float32 stack of partial sums
-    [P, T, 2I].  ``interleave`` 0: the row is [gate (I) | up (I)]; n > 0: blocks of n gate values
-    followed by the n up values of the same outputs."""
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t, i] = silu(gate_i) * up_i; ``gate_up`` is [T, 2I] (the row is [gate (I) | up (I)]) or a
+    float32 stack of partial sums [P, T, 2I]."""
     _need_cuda(gate_up, out)
     tokens, two_i = gate_up.shape[-2], gate_up.shape[-1]
     assert two_i % 2 == 0 and out.shape == (tokens, two_i // 2) and out.is_contiguous()
     gate_up, n_partials, stride = _partials(gate_up, tokens, two_i)
     lib = library.load()
     check(lib.lse_silu_mul(gate_up.data_ptr(), dtype_code(gate_up.dtype), n_partials, stride, out.data_ptr(),
-                           dtype_code(out.dtype), tokens, two_i // 2, int(interleave), _stream()), "silu_mul")
+                           dtype_code(out.dtype), tokens, two_i // 2, _stream()), "silu_mul")
     return out
 
 
-GEMM_SKINNY_MAX_ROWS = 256      # rows of x the few-rows product takes when it writes partial sums
-GEMM_FUSED_MAX_ROWS = 32        # ... when its splits add themselves up (a cluster) or it makes x from the residual
+GEMM_SKINNY_MAX_ROWS = 256      # rows of x the few-rows product takes
 _GEMM_BLOCKS_PER_SM = 2     # two blocks of the few-rows product fit on an SM; LSE_GEMM_BLOCKS overrides the total
 _GEMM_MAX_SPLITS = int(__import__("os").environ.get("LSE_GEMM_MAX_SPLITS", "16"))
-PARTIALS, PLAIN, RESIDUAL, GATE = 0, 1, 2, 3
-GATE_INTERLEAVE = 64            # gate and up rows alternate in blocks of 64: 128 weight rows per thread block
 
 
 def _gemm_target_blocks() -> int:
@@ -338,53 +331,6 @@ def gemm_bf16_skinny_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
             and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
 
 
-def _wished_splits(m: int, n: int, k: int, block_n: int, max_splits: int | None) -> int:
-    """About two blocks per SM (more of the weights are fetched ahead while earlier kernels run), but no more
-    splits than keep the partial sums (4 bytes per row, column and split) well below the weight bytes."""
-    n_tiles = -(-n // block_n)
-    if n_tiles >= sm_count():
-        return 1
-    return max(1, min(-(-k // 128), _gemm_target_blocks() // n_tiles, max(1, k // (4 * m)), max_splits or _GEMM_MAX_SPLITS))
-
-
-class NormedRows:
-    """Rows that are not normalised yet: ``(residual[m] * inv[m]) * weight`` with ``inv[m] = rsqrt(sum_p sumsq[p][m] /
-    hidden + eps)``.  ``residual`` float32 [M, H] (everything already added), ``sumsq`` float32 [parts, M] partial sums
-    of squares of its rows (left by the kernel that wrote the residual), ``weight`` float32 [H].  The few-rows
-    product takes this in place of x and normalises on the way."""
-
-    __slots__ = ("residual", "sumsq", "weight", "eps")
-
-    def __init__(self, residual: torch.Tensor, sumsq: torch.Tensor, weight: torch.Tensor, eps: float) -> None:
-        self.residual, self.sumsq, self.weight, self.eps = residual, sumsq, weight, float(eps)
-
-    @property
-    def shape(self):
-        return self.residual.shape
-
-    def materialise(self, dtype: torch.dtype) -> torch.Tensor:
-        """The normalised rows as a tensor (the norm kernel; for consumers that need one)."""
-        out = torch.empty(self.residual.shape, dtype=dtype, device=self.residual.device)
-        return add_rmsnorm(self.residual, None, self.weight, self.eps, out, write_residual=False)
-
-
-def _launch_skinny(x, weight: torch.Tensor, m: int, n: int, k: int, splits: int, stages: int, block_n: int, epilogue: int,
-                   out=None, bias=None, residual=None, sumsq_out=None, act_out=None, name="gemm_bf16_skinny") -> None:
-    lib = library.load()
-    if isinstance(x, NormedRows):
-        assert x.residual.dtype == torch.float32 and x.residual.is_contiguous() and x.residual.shape == (m, k)
-        assert x.sumsq.dtype == torch.float32 and x.sumsq.dim() == 2 and x.sumsq.shape[1] >= m and x.sumsq.stride(1) == 1
-        assert x.weight.dtype == torch.float32 and x.weight.shape == (k,)
-        x_args = (None, x.residual.data_ptr(), x.sumsq.data_ptr(), x.sumsq.shape[0], x.sumsq.stride(0),
-                  x.weight.data_ptr(), x.eps)
-    else:
-        x_args = (x.data_ptr(), None, None, 0, 0, None, 0.0)
-    check(lib.lse_gemm_bf16_skinny(x_args[0], weight.data_ptr(), m, n, k, int(splits), int(stages), int(block_n), epilogue,
-                                   _ptr(out), _ptr(bias), _ptr(residual), _ptr(sumsq_out),
-                                   sumsq_out.stride(0) if sumsq_out is not None else 0, _ptr(act_out),
-                                   x_args[1], x_args[2], x_args[3], x_args[4], x_args[5], x_args[6], _stream()), name)
-
-
 def gemm_bf16_skinny(x: torch.Tensor, weight: torch.Tensor, splits: int | None = None, stages: int = 6,
                      max_splits: int | None = None, block_n: int = 128) -> torch.Tensor:
     """Partial sums [P, M, N] (float32) of x[M, K] @ weight[N, K]^T for M <= 256, bfloat16 operands;
@@ -396,76 +342,16 @@ def gemm_bf16_skinny(x: torch.Tensor, weight: torch.Tensor, splits: int | None =
         raise KernelError("gemm_bf16_skinny: operands must be contiguous bfloat16, K a multiple of 8, at most 256 rows")
     lib = library.load()
     if splits is None:
-        splits = _wished_splits(m, n, k, block_n, max_splits)
+        # about two blocks per SM (more of the weights are fetched ahead while earlier kernels run), but no
+        # more splits than keep the partial sums (4 bytes per row, column and split) well below the weight bytes
+        n_tiles = -(-n // block_n)
+        splits = 1 if n_tiles >= sm_count() else max(1, min(-(-k // 128), _gemm_target_blocks() // n_tiles,
+                                                             max(1, k // (4 * m)), max_splits or _GEMM_MAX_SPLITS))
     splits = lib.lse_gemm_bf16_skinny_splits(k, int(splits))
     out = torch.empty((splits, m, n), dtype=torch.float32, device=x.device)
-    _launch_skinny(x, weight, m, n, k, splits, stages, block_n, PARTIALS, out=out)
+    check(lib.lse_gemm_bf16_skinny(x.data_ptr(), weight.data_ptr(), out.data_ptr(), m, n, k, splits, int(stages),
+                                   int(block_n), _stream()), "gemm_bf16_skinny")
     return out
-
-
-def gemm_fused_ok(x, weight: torch.Tensor) -> bool:
-    """Whether the few-rows product with a cluster epilogue (or with x made from the residual) takes these."""
-    if weight.dtype != torch.bfloat16 or not weight.is_contiguous() or weight.data_ptr() % 16 or weight.shape[1] % 8:
-        return False
-    if isinstance(x, NormedRows):
-        return x.residual.shape[0] <= GEMM_FUSED_MAX_ROWS and x.residual.shape[1] == weight.shape[1]
-    return x.shape[0] <= GEMM_FUSED_MAX_ROWS and gemm_bf16_skinny_ok(x, weight) and x.shape[1] == weight.shape[1]
-
-
-def _fused_shape(x, weight, block_n, splits, max_splits):
-    m, k = x.shape
-    n = weight.shape[0]
-    if not gemm_fused_ok(x, weight):
-        raise KernelError("few-rows product: contiguous bfloat16 weight [N, K], K a multiple of 8, at most 32 rows")
-    if splits is None:
-        splits = _wished_splits(m, n, k, block_n, max_splits or 8)
-    return m, n, k, library.load().lse_gemm_bf16_skinny_cluster(k, int(splits))
-
-
-def gemm_bf16_plain(x, weight: torch.Tensor, bias: torch.Tensor | None = None, splits: int | None = None, stages: int = 6,
-                    block_n: int = 128) -> torch.Tensor:
-    """x @ weight^T (+ bias) as float32 [M, N], finished inside the kernel (the splits of a block column add
-    themselves up through distributed shared memory).  ``x``: bfloat16 [M, K] or ``NormedRows``."""
-    m, n, k, cluster = _fused_shape(x, weight, block_n, splits, None)
-    out = torch.empty((m, n), dtype=torch.float32, device=weight.device)
-    if bias is not None:
-        assert bias.dtype == torch.float32 and bias.shape == (n,)
-    _launch_skinny(x, weight, m, n, k, cluster, stages, block_n, PLAIN, out=out, bias=bias, name="gemm_bf16_plain")
-    return out
-
-
-def gemm_bf16_into_residual(x, weight: torch.Tensor, residual: torch.Tensor, splits: int | None = None, stages: int = 6,
-                            block_n: int = 128) -> torch.Tensor:
-    """residual[M, N] += x @ weight^T in place (float32); returns partial sums of squares of the new rows
-    [parts, M] for the ``NormedRows`` of the next product."""
-    m, n, k, cluster = _fused_shape(x, weight, block_n, splits, None)
-    assert residual.dtype == torch.float32 and residual.shape == (m, n) and residual.is_contiguous()
-    sumsq = torch.empty((-(-n // block_n) * cluster, m), dtype=torch.float32, device=weight.device)
-    _launch_skinny(x, weight, m, n, k, cluster, stages, block_n, RESIDUAL, residual=residual, sumsq_out=sumsq,
-                   name="gemm_bf16_into_residual")
-    return sumsq
-
-
-def gemm_bf16_gate(x, weight: torch.Tensor, splits: int | None = None, stages: int = 6,
-                   block_n: int = 2 * GATE_INTERLEAVE) -> torch.Tensor:
-    """silu(x @ gate^T) * (x @ up^T) as bfloat16 [M, I]; ``weight`` is the [2I, K] matrix of
-    ``interleave_gate_up(gate, up, block_n // 2)``."""
-    m, n, k, cluster = _fused_shape(x, weight, block_n, splits, None)
-    if n % block_n:
-        raise KernelError("gemm_bf16_gate: the interleaved weight must have a multiple of block_n rows")
-    act = torch.empty((m, n // 2), dtype=torch.bfloat16, device=weight.device)
-    _launch_skinny(x, weight, m, n, k, cluster, stages, block_n, GATE, act_out=act, name="gemm_bf16_gate")
-    return act
-
-
-def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, interleave: int = GATE_INTERLEAVE) -> torch.Tensor:
-    """[2I, K] weight whose rows alternate ``interleave`` gate rows and the ``interleave`` up rows of the same
-    outputs (I a multiple of ``interleave``)."""
-    inter, k = gate.shape
-    assert inter % interleave == 0 and up.shape == gate.shape
-    blocks = inter // interleave
-    stacked = torch.stack([gate.view(blocks, interleave, k), up.view(blocks, interleave, k)], dim=1)
-    return stacked.reshape(2 * inter, k).contiguous()
 
 
 def gemm_bf16_skinny_test_hooks(spin_limit: int = 0, withhold: bool = False) -> None:

@@ -125,11 +125,8 @@ class DecoderModel:
         [number of wanted rows, vocab] (an empty tensor when nothing is wanted)."""
         tokens = step.num_tokens
         residual = torch.empty((tokens, self.spec.hidden_size), dtype=torch.float32, device=self.device)
-        # few rows: the sums of squares of the rows go with them, for a first product that normalises by itself
-        sumsq = (torch.empty((1, tokens), dtype=torch.float32, device=self.device)
-                 if self.dtype == torch.bfloat16 and tokens <= ops.GEMM_FUSED_MAX_ROWS else None)
-        ops.embedding(self.embedding, step.token_ids, residual, sumsq)
-        stream = ResidualStream(residual, sumsq=sumsq)
+        ops.embedding(self.embedding, step.token_ids, residual)
+        stream = ResidualStream(residual)
         for position, index in enumerate(self.spec.order):   # caches run along the order
             self.blocks[index].forward(stream, step, caches[position])
         if step.num_wanted == 0:

@@ -10,17 +10,18 @@ import torch
 from ..kernels import ops
 from ..weights.tensor_spec import TensorSpec
 from .base import POSITION_ENCODINGS, Mixer, PagedKV, register_mixer
-from .linear import as_tensor, fused_rows, linear_partials
+from .linear import linear_partials
 
 # Which kernel a step with prompt portions takes.  The tcgen05 kernel's block is 128 rows of one request
 # and one head; the mma.sync kernel's about ten rows of all heads of a group.  A step goes to the former
 # when its longest portion has at least TCGEN05_MIN_ROWS rows and either its blocks fit the GPU at once
-# (one block per SM; a long portion beside a few decoding requests: 31 against 46 us for 512 rows beside 8 requests) or
+# (a long portion beside a few decoding requests: 31 against 46 us for 512 rows beside 8 requests) or
 # its portions are long on average (at least 64 rows a request); many short portions or many decoding
 # requests beside a portion (90 against 64 us with 32 of them) stay on the mma.sync kernel.
 # LSE_PREFILL_ATTENTION=mma turns the tcgen05 kernel off.
 TCGEN05_MIN_ROWS = int(os.environ.get("LSE_TCGEN05_MIN_ROWS", "128"))
 TCGEN05_MIN_ROWS_PER_REQUEST = 64
+TCGEN05_BLOCKS_AT_ONCE = 148
 TCGEN05_PREFILL = os.environ.get("LSE_PREFILL_ATTENTION", "tcgen05") != "mma"
 
 
@@ -36,7 +37,6 @@ class GroupedQueryAttention(Mixer):
     """
 
     graph_safe = True
-    fuses_with_stream = True
 
     def __init__(self, params, weights, ctx) -> None:
         super().__init__(params, weights, ctx)
@@ -77,30 +77,23 @@ class GroupedQueryAttention(Mixer):
     def cache_requirement(cls, params, hidden_size):
         return PagedKV(int(params["num_kv_heads"]), int(params["head_dim"]), int(params.get("window", 0)))
 
-    def forward(self, x, step, cache, stream=None):
+    def forward(self, x, step, cache):
         tokens = x.shape[0]
-        dtype = self.ctx.dtype
-        if fused_rows(x, self.qkv_weight, "qkv"):
-            # few rows: the product normalises its rows itself (when they come un-normalised), its splits add
-            # themselves up and the bias is added to the finished sums: float32 [T, width] for the rotation
-            qkv, bias = ops.gemm_bf16_plain(x, self.qkv_weight, self.qkv_bias), None
-        else:
-            # bias is added with the rotation, in float32; at most 8 partial sums: the rotary kernel fetches them in one go
-            x = as_tensor(x, dtype)
-            qkv, bias = linear_partials(x, self.qkv_weight, max_splits=8), self.qkv_bias
-        q = torch.empty((tokens, self.n_q, self.head_dim), dtype=dtype, device=qkv.device)
-        self.position.encode_and_store(qkv, bias, step, cache, q, self.n_q, self.n_kv, self.head_dim)
+        # bias is added with the rotation, in float32; at most 8 partial sums: the rotary kernel fetches them in one go
+        qkv = linear_partials(x, self.qkv_weight, max_splits=8)
+        q = torch.empty((tokens, self.n_q, self.head_dim), dtype=x.dtype, device=x.device)
+        self.position.encode_and_store(qkv, self.qkv_bias, step, cache, q, self.n_q, self.n_kv, self.head_dim)
         attended = torch.empty_like(q)
-        if ops.attention_mma_supported(self.head_dim, self.n_q, self.n_kv, dtype, self.window):
+        if ops.attention_mma_supported(self.head_dim, self.n_q, self.n_kv, x.dtype, self.window):
             if step.decode_only:
                 splits = ops.decode_splits(tokens, self.n_q, self.n_kv, step.max_context)
                 ops.paged_attention_decode(q, cache.keys, cache.values, attended, cache.block_tables,
                                            step.segment_of_token, step.positions, self.scale, splits)
             elif (TCGEN05_PREFILL and step.max_segment_tokens >= TCGEN05_MIN_ROWS
                   and (tokens >= TCGEN05_MIN_ROWS_PER_REQUEST * step.num_segments
-                       or sum(-(-segment.count // 128) for segment in step.segments) * self.n_q <= ops.sm_count())
+                       or sum(-(-segment.count // 128) for segment in step.segments) * self.n_q <= TCGEN05_BLOCKS_AT_ONCE)
                   and ops.attention_tc_supported(
-                    self.head_dim, self.n_q, self.n_kv, cache.keys.shape[2], dtype, self.window)):
+                    self.head_dim, self.n_q, self.n_kv, cache.keys.shape[2], x.dtype, self.window)):
                 ops.paged_attention_prefill_tc(q, cache.keys, cache.values, attended, cache.block_tables,
                                                step.segment_start, step.segment_first_position, self.scale)
             else:
@@ -109,9 +102,4 @@ class GroupedQueryAttention(Mixer):
         else:   # float32, other head sizes, windows: the general kernel
             ops.paged_attention_generic(q, cache.keys, cache.values, attended, cache.block_tables,
                                         step.segment_of_token, step.positions, self.scale, self.window)
-        attended = attended.view(tokens, self.n_q * self.head_dim)
-        if stream is not None and fused_rows(attended, self.o_weight, "o"):
-            # few rows: the output projection adds itself to the residual and leaves the sums of squares for the next norm
-            stream.sumsq = ops.gemm_bf16_into_residual(attended, self.o_weight, stream.residual, block_n=64)
-            return None
-        return linear_partials(attended, self.o_weight)
+        return linear_partials(attended.view(tokens, self.n_q * self.head_dim), self.o_weight)

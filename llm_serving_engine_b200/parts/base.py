@@ -61,35 +61,16 @@ class RequestState:
 
 class ResidualStream:
     """The hidden state between parts: the float32 residual [T, H] and the output
-    of the last branch, not yet added (the next norm adds it in float32).
+    of the last branch, not yet added (the next norm adds it in float32)."""
 
-    ``sumsq`` (float32 [parts, T], or None) holds partial sums of squares of the residual's rows
-    when the kernel that last wrote the residual left them (and ``delta`` is None: everything
-    is added): a norm may then hand its consumer the rows un-normalised (``NormedRows``) and
-    the consumer's product normalises them on the way."""
+    __slots__ = ("residual", "delta")
 
-    __slots__ = ("residual", "delta", "sumsq")
-
-    def __init__(self, residual: torch.Tensor, delta: torch.Tensor | None = None, sumsq: torch.Tensor | None = None) -> None:
+    def __init__(self, residual: torch.Tensor, delta: torch.Tensor | None = None) -> None:
         self.residual = residual
         self.delta = delta
-        self.sumsq = sumsq
-
-    def pend(self, delta: torch.Tensor | None) -> None:
-        """A branch has ended.  ``delta``: its output, to be added by the next norm; None: the branch
-        has added its output to the residual itself (and has left ``sumsq`` or cleared it)."""
-        if delta is not None:
-            self.delta = delta
-            self.sumsq = None
 
 
 class Part:
-    # A mixer or feed-forward that sets this takes ``stream=`` in ``forward``: its input may then be a
-    # ``NormedRows`` (rows that its first product normalises itself), and it may add its output to
-    # ``stream.residual`` itself and return None (see ``ResidualStream.pend``).  Parts without it get a
-    # normalised tensor and return their output, as the interface at the top of this file says.
-    fuses_with_stream = False
-
     # True when the part only launches work whose shape depends on the number of rows and reads
     # everything else (positions, segments, tables, routing decisions) from device memory, without
     # waiting for the device: a step made of such parts can be captured in a CUDA graph and
@@ -106,9 +87,7 @@ class Part:
 
 
 class Norm(Part):
-    def forward(self, stream: ResidualStream, rows: torch.Tensor | None = None, lazy: bool = False) -> torch.Tensor:
-        """Add the pending branch output to the residual and return the normalised rows.  ``lazy``: the
-        consumer takes ``NormedRows``; a norm that cannot give them returns a tensor all the same."""
+    def forward(self, stream: ResidualStream, rows: torch.Tensor | None = None) -> torch.Tensor:
         raise NotImplementedError
 
 

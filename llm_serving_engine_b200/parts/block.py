@@ -13,11 +13,7 @@ class PreNormResidualBlock(Block):
     graph_safe = True
 
     def forward(self, stream: ResidualStream, step, cache) -> None:
-        if self.mixer.fuses_with_stream:
-            stream.pend(self.mixer.forward(self.mixer_norm.forward(stream, lazy=True), step, cache, stream=stream))
-        else:
-            stream.pend(self.mixer.forward(self.mixer_norm.forward(stream), step, cache))
-        if self.feed_forward.fuses_with_stream:
-            stream.pend(self.feed_forward.forward(self.feed_forward_norm.forward(stream, lazy=True), stream=stream))
-        else:
-            stream.pend(self.feed_forward.forward(self.feed_forward_norm.forward(stream)))
+        x = self.mixer_norm.forward(stream)
+        stream.delta = self.mixer.forward(x, step, cache)
+        x = self.feed_forward_norm.forward(stream)
+        stream.delta = self.feed_forward.forward(x)

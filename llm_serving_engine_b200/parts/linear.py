@@ -17,11 +17,6 @@ import os
 
 # above this many rows the library product is faster (LSE_SKINNY_MAX_ROWS overrides, for comparisons)
 SKINNY_MAX_ROWS = int(os.environ.get("LSE_SKINNY_MAX_ROWS", "32"))
-# few rows: the products take the norm before them, the residual sum and the SiLU gate after them into
-# themselves (LSE_FUSE_FEW_ROWS=0: every small kernel runs by itself, for comparisons)
-_FUSE = os.environ.get("LSE_FUSE_FEW_ROWS", "1")
-FUSE_FEW_ROWS = _FUSE != "0"
-FUSE_WHICH = {"qkv", "o", "gate", "down"} if _FUSE in ("0", "1") else set(_FUSE.split(","))
 
 
 def reduce_partials(y: torch.Tensor) -> torch.Tensor:
@@ -29,18 +24,6 @@ def reduce_partials(y: torch.Tensor) -> torch.Tensor:
     if y.dim() == 3:
         return y[0] if y.shape[0] == 1 else y.sum(0)
     return y
-
-
-def fused_rows(x, weight: torch.Tensor, which: str = "") -> bool:
-    """Whether the products of these rows may finish themselves (few bfloat16 rows): see ``ops.gemm_fused_ok``."""
-    rows = x.shape[0]
-    return (FUSE_FEW_ROWS and (not which or which in FUSE_WHICH) and rows <= min(SKINNY_MAX_ROWS, ops.GEMM_FUSED_MAX_ROWS)
-            and ops.gemm_fused_ok(x, weight))
-
-
-def as_tensor(x, dtype: torch.dtype) -> torch.Tensor:
-    """Normalised rows as a tensor, whatever form they came in."""
-    return x.materialise(dtype) if isinstance(x, ops.NormedRows) else x
 
 
 def linear_partials(x: torch.Tensor, weight: torch.Tensor, max_splits: int | None = None) -> torch.Tensor:

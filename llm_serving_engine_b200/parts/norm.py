@@ -24,17 +24,11 @@ class RMSNorm(Norm):
     def expected_tensors(cls, params, hidden_size):
         return {"weight": TensorSpec((hidden_size,), "norm")}
 
-    def forward(self, stream: ResidualStream, rows: torch.Tensor | None = None, lazy: bool = False):
-        if (lazy and rows is None and stream.delta is None and stream.sumsq is not None
-                and self.ctx.dtype == torch.bfloat16 and stream.residual.shape[0] <= ops.GEMM_FUSED_MAX_ROWS):
-            # nothing to add, and the sums of squares are there: the consumer's product normalises on the way
-            return ops.NormedRows(stream.residual, stream.sumsq, self.weight, self.eps)
+    def forward(self, stream: ResidualStream, rows: torch.Tensor | None = None) -> torch.Tensor:
         n_rows = stream.residual.shape[0] if rows is None else rows.shape[0]
         out = torch.empty((n_rows, stream.residual.shape[1]), dtype=self.ctx.dtype, device=stream.residual.device)
-        write_back = rows is None and stream.delta is not None     # the residual changes: old sums of squares are void
         ops.add_rmsnorm(stream.residual, stream.delta, self.weight, self.eps, out, rows=rows,
                         write_residual=rows is None)
         if rows is None:
             stream.delta = None
-            stream.sumsq = None if write_back else stream.sumsq
         return out

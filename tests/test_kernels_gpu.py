@@ -722,93 +722,6 @@ def product_bound(x, w, k):
     return (x.abs().double() @ w.abs().double().t()) * (k * 2.0 ** -24) + 1e-6
 
 
-@pytest.mark.parametrize("m, n, k, splits", [(1, 128, 64, 1), (8, 2048, 1536, 8), (3, 1536, 8960, 8), (16, 1000, 776, 3),
-                                             (32, 1536, 1536, None), (7, 200, 320, 4), (8, 96, 8, 2), (5, 130, 328, 8)])
-@pytest.mark.parametrize("block_n", [128, 64])
-def test_product_whose_splits_add_themselves_up(m, n, k, splits, block_n):
-    """The splits of a block column as a thread-block cluster: finished float32 sums with a bias; the same added to a
-    float32 residual in place, with the partial sums of squares of the new rows; launch after launch."""
-    torch.manual_seed(m + n + k)
-    x = torch.randn(m, k, device=DEV).bfloat16()
-    w = (torch.randn(n, k, device=DEV) * 0.05).bfloat16()
-    bias = torch.randn(n, device=DEV)
-    want = x.double() @ w.double().t()
-    bound = product_bound(x, w, k)
-    for _ in range(2):
-        got = ops().gemm_bf16_plain(x, w, bias, splits, block_n=block_n)
-        assert got.dtype == torch.float32 and got.shape == (m, n)
-        assert bool(((got.double() - (want + bias.double())).abs() <= bound + 1e-6 * bias.abs().double()).all())
-        assert torch.equal(ops().gemm_bf16_plain(x, w, None, splits, block_n=block_n) + bias, got)
-        residual = torch.randn(m, n, device=DEV)
-        before = residual.clone()
-        sumsq = ops().gemm_bf16_into_residual(x, w, residual, splits, block_n=block_n)
-        assert bool(((residual.double() - (before.double() + want)).abs() <= bound + 1e-6).all())
-        assert sumsq.shape[1] == m and rel_err(sumsq.double().sum(0), residual.double().pow(2).sum(1)) < 1e-5
-    assert ops().gemm_bf16_skinny_status() == 0
-
-
-@pytest.mark.parametrize("m, inter, k, splits", [(8, 8960, 1536, None), (1, 64, 64, 1), (5, 192, 520, 3), (16, 1024, 776, 8),
-                                                 (32, 8960, 1536, None), (3, 128, 72, 2)])
-@pytest.mark.parametrize("block_n", [128, 64])
-def test_product_that_applies_the_gate(m, inter, k, splits, block_n):
-    """silu(x gate^T) * (x up^T) from the interleaved weight in one kernel, for any number of splits; and through the
-    separate SiLU kernel reading the interleaved columns of a library product (the many-rows path)."""
-    torch.manual_seed(m + inter)
-    x = torch.randn(m, k, device=DEV).bfloat16()
-    gate = (torch.randn(inter, k, device=DEV) * 0.05).bfloat16()
-    up = (torch.randn(inter, k, device=DEV) * 0.05).bfloat16()
-    half = block_n // 2
-    w = ops().interleave_gate_up(gate, up, half)
-    assert torch.equal(w[:half], gate[:half]) and torch.equal(w[half:2 * half], up[:half])
-    g, u = x.double() @ gate.double().t(), x.double() @ up.double().t()
-    exact = torch.nn.functional.silu(g) * u
-    for _ in range(2):
-        act = ops().gemm_bf16_gate(x, w, splits, block_n=block_n)
-        assert act.dtype == torch.bfloat16 and act.shape == (m, inter)
-        assert float((act.double() - exact).abs().max()) <= 2.0 ** -7 * float(exact.abs().max()) + 1e-6
-    columns = torch.mm(x, w.t())                       # library product, interleaved columns
-    out = torch.empty(m, inter, device=DEV, dtype=torch.bfloat16)
-    ops().silu_mul(columns, out, interleave=half)
-    assert rel_err(out, exact) < TOL[torch.bfloat16] * 4     # its input was rounded to bfloat16 once more
-    assert ops().gemm_bf16_skinny_status() == 0
-
-
-@pytest.mark.parametrize("m, hidden, n, parts", [(8, 1536, 2048, 1), (8, 1536, 17920, 96), (1, 64, 128, 1), (5, 328, 130, 7),
-                                                 (32, 3584, 256, 224), (17, 8, 64, 2)])
-def test_product_that_normalises_its_rows_itself(m, hidden, n, parts):
-    """x = RMSNorm(residual) made inside the product from the residual rows and partial sums of squares: against
-    the norm kernel followed by the product (the same bfloat16 rows but for the last bit of 1/rms), and against float64;
-    in all three ways of finishing."""
-    torch.manual_seed(m + hidden)
-    residual = torch.randn(m, hidden, device=DEV) * 3
-    weight = 1 + 0.1 * torch.randn(hidden, device=DEV)
-    eps = 1e-5
-    exact_sq = residual.double().pow(2).sum(1)
-    shares = torch.rand(parts, m, device=DEV).double() + 0.1
-    sumsq = (shares / shares.sum(0) * exact_sq).float().contiguous()      # any split of the sums into parts
-    rows = ops().NormedRows(residual, sumsq, weight, eps)
-    normed = rows.materialise(torch.bfloat16)
-    want_x = qwen2_plain.rms_norm(residual.double(), weight.double(), eps)
-    assert rel_err(normed, want_x) < TOL[torch.bfloat16] * 2
-    w = (torch.randn(n, hidden, device=DEV) * 0.05).bfloat16()
-    want = want_x @ w.double().t()
-    slack = (want_x.abs() @ w.abs().double().t()) * 2.0 ** -8 + 1e-6      # the rows are rounded to bfloat16
-    got = ops().gemm_bf16_plain(rows, w)
-    assert bool(((got.double() - want).abs() <= slack).all())
-    assert rel_err(got, ops().gemm_bf16_plain(normed, w)) < 2e-3
-    target = torch.randn(m, n, device=DEV)
-    before = target.clone()
-    squares = ops().gemm_bf16_into_residual(rows, w, target)
-    assert bool(((target.double() - before.double() - want).abs() <= slack).all())
-    assert rel_err(squares.double().sum(0), target.double().pow(2).sum(1)) < 1e-5
-    if n % 128 == 0:
-        act = ops().gemm_bf16_gate(rows, w)
-        g, u = want.view(m, n // 128, 2, 64).unbind(2)
-        exact = (torch.nn.functional.silu(g) * u).reshape(m, n // 2)
-        assert float((act.double() - exact).abs().max()) <= 2.0 ** -6 * float(exact.abs().max()) + 1e-6
-    assert ops().gemm_bf16_skinny_status() == 0
-
-
 def test_a_wait_that_runs_out_is_reported_and_the_kernel_returns():
     """Every block leaves out its last weight tile and gives up waiting for it after a few thousand tries: the kernel
     returns, the status word says so (through the synchronous read and through the copy that is queued behind a
@@ -822,7 +735,7 @@ def test_a_wait_that_runs_out_is_reported_and_the_kernel_returns():
         torch.cuda.synchronize()
         assert ops().gemm_bf16_skinny_status() == 1
         ops().kernel_status_reset()
-        ops().gemm_bf16_into_residual(x, w, torch.zeros(8, 256, device=DEV), 4)       # the cluster form gives up and still meets its barriers
+        ops().gemm_bf16_skinny(x, w, 4, block_n=64)
         words = torch.zeros(2, dtype=torch.int32).pin_memory()
         ops().kernel_status_async(words)
         torch.cuda.synchronize()
@@ -830,8 +743,8 @@ def test_a_wait_that_runs_out_is_reported_and_the_kernel_returns():
     finally:
         ops().gemm_bf16_skinny_test_hooks()
         ops().kernel_status_reset()
-    got = ops().gemm_bf16_plain(x, w)
-    assert bool(((got.double() - x.double() @ w.double().t()).abs() <= product_bound(x, w, 512)).all())
+    got = ops().gemm_bf16_skinny(x, w).double().sum(0)
+    assert bool(((got - x.double() @ w.double().t()).abs() <= product_bound(x, w, 512)).all())
     assert ops().gemm_bf16_skinny_status() == 0
 
 

@@ -93,25 +93,3 @@ def test_block_arrangement(name):
     model.blocks[0].forward(stream, step, caches[0])
     got = (stream.residual + reduce_partials(stream.delta).float()).cpu()      # the last branch output is still pending
     assert float((got - want).abs().max()) < 2e-5 * max(1.0, float(want.abs().max()))
-
-
-@pytest.mark.parametrize("fuse_gate", [32, 64])
-def test_feed_forward_with_the_gate_in_the_product_epilogue(fuse_gate):
-    """The optional layout that interleaves gate and up rows: few rows go through the gated product
-    kernel, many rows through the library product and the SiLU kernel that reads interleaved columns."""
-    from llm_serving_engine_b200.parts import FEED_FORWARDS, BuildContext
-    torch.manual_seed(fuse_gate)
-    hidden, inter = 96, 256
-    weights = {"gate_proj.weight": (torch.randn(inter, hidden) * 0.1).bfloat16().cuda(),
-               "up_proj.weight": (torch.randn(inter, hidden) * 0.1).bfloat16().cuda(),
-               "down_proj.weight": (torch.randn(hidden, inter) * 0.1).bfloat16().cuda()}
-    ctx = BuildContext(torch.bfloat16, torch.device("cuda"), hidden, 0, 128)
-    part = FEED_FORWARDS.get("swiglu")({"intermediate_size": inter, "fuse_gate": fuse_gate}, weights, ctx)
-    assert part.interleave == fuse_gate
-    plain_w = {"m.gate_proj.weight": weights["gate_proj.weight"].float().cpu(), "m.up_proj.weight": weights["up_proj.weight"].float().cpu(),
-               "m.down_proj.weight": weights["down_proj.weight"].float().cpu()}
-    for rows in (5, 40):
-        x = torch.randn(rows, hidden).bfloat16()
-        want = qwen2_plain.swiglu(x.float(), plain_w, "m.")
-        got = reduce_partials(part.forward(x.cuda())).float().cpu()
-        assert float((got - want).abs().max()) < 2.0 ** -6 * max(1.0, float(want.abs().max())), rows

@@ -176,7 +176,7 @@ def test_tcgen05_attention_replayed_from_a_portion_graph(folder):
                 assert helpers.rms_ratio(part, want) <= helpers.RMS_RATIO_LARGE_LAYERS
             for entry in entries:
                 cache.free(entry.request_id)
-    assert runner.portion_graph_replays == 2 and ops.attention_tc_status() == 0
+    assert runner.portion_graph_replays >= 2 and ops.attention_tc_status() == 0
 
 
 def test_a_page_of_another_request_is_noticed(folder):
