@@ -40,7 +40,28 @@ argmax_kernel(const float* __restrict__ logits, long long row_stride, int vocab,
   const float* row = logits + (size_t)blockIdx.x * row_stride;
   float bv = -INFINITY;
   int bi = vocab;  // "none yet"
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+  // Sixteen values per thread and round (four 16-byte loads in flight), taken in ascending order of the index, so
+  // that the first maximum wins inside a thread; between threads the smaller index wins a tie (below).
+  const bool vec = (vocab & 3) == 0 && (((uintptr_t)row) & 15) == 0;
+  const int n4 = vec ? vocab >> 2 : 0;
+  for (int c0 = threadIdx.x; c0 < n4; c0 += 4 * blockDim.x) {
+    float4 v[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int c = c0 + k * blockDim.x;
+      v[k] = c < n4 ? reinterpret_cast<const float4*>(row)[c] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int i = (c0 + k * (int)blockDim.x) * 4;
+      if (i >= vocab) continue;
+      if (v[k].x > bv || bi == vocab) { bv = v[k].x; bi = i; }
+      if (v[k].y > bv) { bv = v[k].y; bi = i + 1; }
+      if (v[k].z > bv) { bv = v[k].z; bi = i + 2; }
+      if (v[k].w > bv) { bv = v[k].w; bi = i + 3; }
+    }
+  }
+  for (int i = n4 * 4 + threadIdx.x; i < vocab; i += blockDim.x) {
     const float v = row[i];
     if (v > bv || bi == vocab) { bv = v; bi = i; }  // ascending i per thread: first maximum wins
   }
