@@ -18,6 +18,8 @@
 // Cache layout: [page][kv head][offset in page][D].
 #include "common.cuh"
 
+LSE_CHECK_DEFINE(lse_check_attention_generic)
+
 namespace {
 constexpr int KT = 32;        // keys per tile (one warp lane per key)
 constexpr int GC = 8;         // query heads per block (chunk of a group)
@@ -32,7 +34,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
                                const int* __restrict__ block_tables, int bt_stride,
                                const int* __restrict__ segment_of_token,
                                const int* __restrict__ positions, int n_q, int n_kv, int head_dim,
-                               int page_size, float scale, int window) {
+                               int page_size, float scale, int window, int num_pages, int num_segments) {
   extern __shared__ float smem[];
   pdl_launch_dependents();
   pdl_wait();
@@ -41,7 +43,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
   const int group = n_q / n_kv;
   const int g0 = blockIdx.z * GC;
   const int gcount = min(GC, group - g0);
-  const int seg = segment_of_token[t];
+  const int seg = LSE_CHECKED(segment_of_token[t], -1, num_segments, -1, LSE_CHECK_SEGMENT);
   if (seg < 0) return;
   const int pos = positions[t];
   const int ctx = pos + 1;
@@ -81,7 +83,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
       const int j = base + tid;
       long long off = -1;
       if (j < ctx && j >= kv_begin) {
-        const int page = bt[j / page_size];
+        const int page = LSE_CHECKED(bt[j / page_size], 0, num_pages, 0, LSE_CHECK_TABLE_ENTRY);
         off = (((long long)page * n_kv + kv_head) * page_size + (j % page_size)) * D;
       }
       base_s[tid] = off;
@@ -161,7 +163,7 @@ extern "C" int lse_paged_attention_generic(const void* q, const void* k_cache, c
                                            int bt_stride, const int* segment_of_token,
                                            const int* positions, int tokens, int n_q, int n_kv,
                                            int head_dim, int page_size, float scale, int window,
-                                           cudaStream_t stream) {
+                                           int num_pages, int num_segments, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (head_dim <= 0 || head_dim > MAX_D || head_dim % 16 || n_kv <= 0 || n_q % n_kv || page_size <= 0)
     return LSE_ERR_BAD_ARGUMENT;
@@ -183,12 +185,13 @@ extern "C" int lse_paged_attention_generic(const void* q, const void* k_cache, c
   if (dtype == LSE_DTYPE_F32) {
     lse_launch(paged_attention_generic_kernel<float>, grid, THREADS, smem, stream,
         (const float*)q, (const float*)k_cache, (const float*)v_cache, (float*)out, block_tables,
-        bt_stride, segment_of_token, positions, n_q, n_kv, head_dim, page_size, scale, window);
+        bt_stride, segment_of_token, positions, n_q, n_kv, head_dim, page_size, scale, window, num_pages,
+        num_segments);
   } else if (dtype == LSE_DTYPE_BF16) {
     lse_launch(paged_attention_generic_kernel<__nv_bfloat16>, grid, THREADS, smem, stream,
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
         (__nv_bfloat16*)out, block_tables, bt_stride, segment_of_token, positions, n_q, n_kv,
-        head_dim, page_size, scale, window);
+        head_dim, page_size, scale, window, num_pages, num_segments);
   } else {
     return LSE_ERR_BAD_ARGUMENT;
   }

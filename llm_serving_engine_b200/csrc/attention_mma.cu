@@ -23,6 +23,7 @@
 namespace cg = cooperative_groups;
 
 LSE_TL_DEFINE(lse_timeline_attention)
+LSE_CHECK_DEFINE(lse_check_attention_mma)
 
 namespace {
 
@@ -129,7 +130,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
                    float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ arrivals,
                    const int* __restrict__ block_tables, int bt_stride,
                    const int* __restrict__ segment_of_token, const int* __restrict__ positions,
-                   int n_q, int n_kv, int page_size, float scale_log2e, int num_splits, int dry_run) {
+                   int n_q, int n_kv, int page_size, float scale_log2e, int num_splits, int dry_run, int num_pages,
+                   int num_segments) {
   constexpr int CH = D / 8;                 // 16-byte chunks per row
   constexpr int TILE_BYTES = DEC_TILE * D * 2;
   extern __shared__ __align__(128) unsigned char smem[];
@@ -147,7 +149,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   const int g0 = (blockIdx.y % gchunks) * 16;
   const int gcount = min(16, group - g0);
   const int split = blockIdx.z;
-  const int seg = segment_of_token[t];
+  const int seg = LSE_CHECKED(segment_of_token[t], -1, num_segments, -1, LSE_CHECK_SEGMENT);
   if (seg < 0) return;
   const int ctx = positions[t] + 1;
   const int* bt = block_tables + (size_t)seg * bt_stride;
@@ -165,7 +167,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   const int n_pages = tile_lo < tile_hi ? pm.page(min(ctx, tile_hi * DEC_TILE) - 1) - first_page + 1 : 0;
   const bool staged = n_pages <= BT_STAGE;
   if (staged)
-    for (int i = tid; i < n_pages; i += 128) bt_s[i] = bt[first_page + i];
+    for (int i = tid; i < n_pages; i += 128) bt_s[i] = LSE_CHECKED(bt[first_page + i], 0, num_pages, 0, LSE_CHECK_TABLE_ENTRY);
   __syncthreads();
 
   unsigned char* my_s = kv_s + (size_t)warp * DEC_STAGES * 2 * TILE_BYTES;
@@ -192,7 +194,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
       size_t off = 0;
       if (valid) {
         const int logical = pm.page(j);
-        const int page = staged ? bt_s[logical - first_page] : bt[logical];
+        const int page = staged ? bt_s[logical - first_page] : LSE_CHECKED(bt[logical], 0, num_pages, 0, LSE_CHECK_TABLE_ENTRY);
         off = (((size_t)page * n_kv + kvh) * page_size + pm.offset(j)) * D + c * 8;
       }
       cp_async16(smem_u32(ks_ + tile_off<D>(key, c)), kc + off, valid);
@@ -494,7 +496,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
                     const int* __restrict__ block_tables, int bt_stride,
                     const int* __restrict__ segment_start, const int* __restrict__ segment_first_pos,
                     int num_segments, int n_q, int n_kv, int page_size, float scale_log2e,
-                    int rows_per_tile) {
+                    int rows_per_tile, int num_pages) {
   constexpr int CH = D / 8;
   constexpr int TILE_BYTES = PF_BN * D * 2;
   extern __shared__ __align__(128) unsigned char smem[];
@@ -530,7 +532,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   const int n_pages = pm.page(last_pos) + 1;
   const bool staged = n_pages <= BT_STAGE;
   if (staged)
-    for (int i = tid; i < n_pages; i += 128) bt_s[i] = bt[i];
+    for (int i = tid; i < n_pages; i += 128) bt_s[i] = LSE_CHECKED(bt[i], 0, num_pages, 0, LSE_CHECK_TABLE_ENTRY);
   pdl_wait();
 
   for (int e = tid; e < PF_BM * CH; e += 128) {
@@ -569,7 +571,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
       size_t off = 0;
       if (valid) {
         const int logical = pm.page(j);
-        const int page = staged ? bt_s[logical] : bt[logical];
+        const int page = staged ? bt_s[logical] : LSE_CHECKED(bt[logical], 0, num_pages, 0, LSE_CHECK_TABLE_ENTRY);
         off = (((size_t)page * n_kv + kvh) * page_size + pm.offset(j)) * D + c * 8;
       }
       cp_async16(smem_u32(ks_ + tile_off<D>(key, c)), kc + off, valid);
@@ -694,7 +696,8 @@ template <int D> size_t prefill_smem() { return (size_t)PF_BM * D * 2 + (size_t)
 template <int D, bool CLUSTER>
 int launch_decode_as(const void* q, const void* kc, const void* vc, void* out, float* part_o, float* part_ml,
                      int* arrivals, const int* block_tables, int bt_stride, const int* seg, const int* positions,
-                     int tokens, int n_q, int n_kv, int page_size, float scale, int num_splits, cudaStream_t stream) {
+                     int tokens, int n_q, int n_kv, int page_size, float scale, int num_splits, int num_pages,
+                     int num_segments, cudaStream_t stream) {
   const size_t smem = decode_smem<D>();
   static bool configured = false;   // once per process: not repeated while a stream is captured
   if (!configured) {
@@ -708,7 +711,7 @@ int launch_decode_as(const void* q, const void* kc, const void* vc, void* out, f
       CLUSTER ? (unsigned)num_splits : 1u,
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, (__nv_bfloat16*)out, part_o,
       part_ml, arrivals, block_tables, bt_stride, seg, positions, n_q, n_kv, page_size, scale * LOG2E, num_splits,
-      lse_pdl_enabled ? 1 : 0);
+      lse_pdl_enabled ? 1 : 0, num_pages, num_segments);
   if (err != cudaSuccess) return (int)err;
   return (int)cudaGetLastError();
 }
@@ -717,18 +720,18 @@ template <int D>
 int launch_decode(const void* q, const void* kc, const void* vc, void* out, float* part_o, float* part_ml,
                   int* arrivals, const int* block_tables, int bt_stride, const int* seg, const int* positions,
                   int tokens, int n_q, int n_kv, int page_size, float scale, int num_splits, int cluster,
-                  cudaStream_t stream) {
+                  int num_pages, int num_segments, cudaStream_t stream) {
   if (cluster && num_splits > 1 && num_splits <= 8)
     return launch_decode_as<D, true>(q, kc, vc, out, part_o, part_ml, arrivals, block_tables, bt_stride, seg, positions,
-                                     tokens, n_q, n_kv, page_size, scale, num_splits, stream);
+                                     tokens, n_q, n_kv, page_size, scale, num_splits, num_pages, num_segments, stream);
   return launch_decode_as<D, false>(q, kc, vc, out, part_o, part_ml, arrivals, block_tables, bt_stride, seg, positions,
-                                    tokens, n_q, n_kv, page_size, scale, num_splits, stream);
+                                    tokens, n_q, n_kv, page_size, scale, num_splits, num_pages, num_segments, stream);
 }
 
 template <int D>
 int launch_prefill(const void* q, const void* kc, const void* vc, void* out, const int* block_tables,
                    int bt_stride, const int* segment_start, const int* segment_first_pos, int num_segments,
-                   int tokens, int n_q, int n_kv, int page_size, float scale, cudaStream_t stream) {
+                   int tokens, int n_q, int n_kv, int page_size, float scale, int num_pages, cudaStream_t stream) {
   const size_t smem = prefill_smem<D>();
   static bool configured = false;
   if (!configured) {
@@ -743,7 +746,7 @@ int launch_prefill(const void* q, const void* kc, const void* vc, void* out, con
   lse_launch(attn_prefill_kernel<D>, grid, 128, smem, stream,
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, (__nv_bfloat16*)out,
       block_tables, bt_stride, segment_start, segment_first_pos, num_segments, n_q, n_kv, page_size,
-      scale * LOG2E, rows_per_tile);
+      scale * LOG2E, rows_per_tile, num_pages);
   return (int)cudaGetLastError();
 }
 }  // namespace
@@ -768,7 +771,7 @@ extern "C" int lse_paged_attention_decode(const void* q, const void* k_cache, co
                                           int bt_stride,
                                           const int* segment_of_token, const int* positions, int tokens,
                                           int n_q, int n_kv, int head_dim, int page_size, float scale,
-                                          int num_splits, cudaStream_t stream) {
+                                          int num_splits, int num_pages, int num_segments, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (!lse_attention_mma_supported(head_dim, n_q, n_kv) || page_size <= 0 || num_splits < 1 || num_splits > 32)
     return LSE_ERR_BAD_ARGUMENT;
@@ -778,21 +781,23 @@ extern "C" int lse_paged_attention_decode(const void* q, const void* k_cache, co
   float* part_ml = scratch ? scratch + (size_t)tokens * n_q * num_splits * head_dim : nullptr;
   if (head_dim == 128)
     return launch_decode<128>(q, k_cache, v_cache, out, part_o, part_ml, arrivals, block_tables, bt_stride,
-                              segment_of_token, positions, tokens, n_q, n_kv, page_size, scale, num_splits, cluster, stream);
+                              segment_of_token, positions, tokens, n_q, n_kv, page_size, scale, num_splits, cluster, num_pages,
+                              num_segments, stream);
   return launch_decode<64>(q, k_cache, v_cache, out, part_o, part_ml, arrivals, block_tables, bt_stride,
-                           segment_of_token, positions, tokens, n_q, n_kv, page_size, scale, num_splits, cluster, stream);
+                           segment_of_token, positions, tokens, n_q, n_kv, page_size, scale, num_splits, cluster, num_pages,
+                              num_segments, stream);
 }
 
 extern "C" int lse_paged_attention_prefill(const void* q, const void* k_cache, const void* v_cache, void* out,
                                            const int* block_tables, int bt_stride, const int* segment_start,
                                            const int* segment_first_pos, int num_segments, int tokens, int n_q,
-                                           int n_kv, int head_dim, int page_size, float scale,
+                                           int n_kv, int head_dim, int page_size, float scale, int num_pages,
                                            cudaStream_t stream) {
   if (tokens <= 0 || num_segments <= 0) return 0;
   if (!lse_attention_mma_supported(head_dim, n_q, n_kv) || page_size <= 0) return LSE_ERR_BAD_ARGUMENT;
   if (head_dim == 128)
     return launch_prefill<128>(q, k_cache, v_cache, out, block_tables, bt_stride, segment_start, segment_first_pos,
-                               num_segments, tokens, n_q, n_kv, page_size, scale, stream);
+                               num_segments, tokens, n_q, n_kv, page_size, scale, num_pages, stream);
   return launch_prefill<64>(q, k_cache, v_cache, out, block_tables, bt_stride, segment_start, segment_first_pos,
-                            num_segments, tokens, n_q, n_kv, page_size, scale, stream);
+                            num_segments, tokens, n_q, n_kv, page_size, scale, num_pages, stream);
 }

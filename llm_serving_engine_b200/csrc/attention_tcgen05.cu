@@ -45,6 +45,9 @@ constexpr float REDO_STEP = 64.0f;
 constexpr uint32_t HALF_BYTES = 128 * 128;   // a box of 128 rows x 64 bfloat16
 
 __device__ int lse_attn_tc_error;
+}  // namespace
+LSE_CHECK_DEFINE(lse_check_attention_tc)
+namespace {
 
 // Tuning builds (-DLSE_TRACE): the block of the last tile of the first request, head 0, records clock
 // stamps of the first thread of each softmax group (slots 0-5 of a tile) and of its MMA thread (6, 7).
@@ -56,13 +59,9 @@ __device__ long long lse_attn_tc_stamps[2 * 128 * 8];
 __device__ unsigned long long lse_attn_tc_blocks[4096 * 4];
 __device__ __forceinline__ unsigned long long global_ns() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
 __device__ __forceinline__ unsigned sm_id() { unsigned v; asm volatile("mov.u32 %0, %%smid;" : "=r"(v)); return v; }
-// what-if switches (wrong results): 1 no probability writes, 2 no P V products, 4 no score products, 8 no exponentials, 16 no key and value loads
-__device__ int lse_attn_tc_what_if;
-#define TC_WHAT_IF(bit) ((what_if & (bit)) != 0)
 #else
 #define TC_STAMP(tile, k)
 #define TC_STAMP2(tile, k)
-#define TC_WHAT_IF(bit) false
 #endif
 
 // per group g: index + g
@@ -92,7 +91,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
                        const int* __restrict__ block_tables, int bt_stride, const int* __restrict__ segment_start,
                        const int* __restrict__ segment_first_pos, int num_segments, int n_q, int n_kv, int page_size,
-                       float scale_log2e) {
+                       float scale_log2e, int num_pages) {
   constexpr int HALVES = D / 64;
   constexpr uint32_t Q_BYTES = HALVES * HALF_BYTES, KV_BYTES = HALVES * HALF_BYTES, P_BYTES = 2 * HALF_BYTES;
   constexpr uint32_t GROUP_BYTES = HALVES * 1024;   // 8 keys (or values) in a stage: 8 rows x 128 bytes for every 64 columns
@@ -141,7 +140,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const int n_pages = last_pos / page_size + 1;
   const int* bt = block_tables + (size_t)seg * bt_stride;
 #ifdef LSE_TRACE
-  const int what_if = lse_attn_tc_what_if;
   const bool traced = seg == 0 && head == 0 && r0 + BM >= cnt && (tid == 0 || tid == GROUP_THREADS || tid == MMA_WARP * 32 || tid == PV_WARP * 32);
 #endif
 
@@ -168,7 +166,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       mbar_expect_tx(bar(B_Q), Q_BYTES);
       for (int h = 0; h < HALVES; ++h) tma_load_3d(q_s + h * HALF_BYTES, &map_q, bar(B_Q), h * 64, head, row_base);
     }
-    auto page_of = [&](int j) { return (j < n_tiles && lane < min(ppt, n_pages - j * ppt)) ? bt[j * ppt + lane] : 0; };
+    auto page_of = [&](int j) { return (j < n_tiles && lane < min(ppt, n_pages - j * ppt)) ? LSE_CHECKED(bt[j * ppt + lane], 0, num_pages, 0, LSE_CHECK_TABLE_ENTRY) : 0; };
     auto load = [&](int j, int page, uint32_t dst, const CUtensorMap* map, int full, int empty) -> bool {
       const int g = j & 1;
       const uint32_t parity = (uint32_t)(j >> 1) & 1u;
@@ -176,10 +174,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       int ok = 1;
       if (lane == 0) ok = mbar_wait(bar(empty + g), parity ^ 1u, abort_flag, err) ? 1 : 0;
       if (!__shfl_sync(0xffffffffu, ok, 0)) return false;
-      if (TC_WHAT_IF(16)) {   // no key and value loads
-        if (lane == 0) mbar_arrive(bar(full + g));
-        return true;
-      }
       if (lane == 0) mbar_expect_tx(bar(full + g), (uint32_t)(np * page_size) * 128u * HALVES);
       __syncwarp();
       if (lane < np)   // one copy per page: its groups of 8 keys, the two halves of the head size side by side
@@ -213,7 +207,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         fence_after_sync();
         TC_STAMP2(j, 6)
 #pragma unroll
-        for (int ks = 0; ks < D / 16 && !TC_WHAT_IF(4); ++ks) {
+        for (int ks = 0; ks < D / 16; ++ks) {
           const uint32_t off = (uint32_t)(ks / 4) * HALF_BYTES + (uint32_t)(ks % 4) * 32u;
           const uint32_t k_off = (uint32_t)(ks / 4) * 1024u + (uint32_t)(ks % 4) * 32u;
           umma_bf16(tmem_base + g * S_COLS, smem_desc_k_major(q_s + off),
@@ -242,7 +236,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         fence_after_sync();
         TC_STAMP2(i, 3)
 #pragma unroll
-        for (int ks = 0; ks < BN / 16 && !TC_WHAT_IF(2); ++ks) {
+        for (int ks = 0; ks < BN / 16; ++ks) {
           const uint32_t p_off = (uint32_t)(ks / 4) * HALF_BYTES + (uint32_t)(ks % 4) * 32u;
           umma_bf16(tmem_base + O_COL + g * D, smem_desc_k_major(p_s + g * P_BYTES + p_off),
                     smem_desc_mn_major(v_s + g * KV_BYTES + (uint32_t)ks * 2u * GROUP_BYTES, 1024u, GROUP_BYTES), idesc_o,
@@ -354,14 +348,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             mx = fmaxf(mx, fmaxf(fmaxf(s0, s1), fmaxf(s2, s3)));
             float p0 = fmaf(s0, scale_log2e, neg), p1 = fmaf(s1, scale_log2e, neg);
             float p2 = fmaf(s2, scale_log2e, neg), p3 = fmaf(s3, scale_log2e, neg);
-            if (!TC_WHAT_IF(8)) { p0 = exp2_fast(p0); p1 = exp2_fast(p1); p2 = exp2_fast(p2); p3 = exp2_fast(p3); }
+            p0 = exp2_fast(p0); p1 = exp2_fast(p1); p2 = exp2_fast(p2); p3 = exp2_fast(p3);
             sum += (p0 + p1) + (p2 + p3);
             pk[i] = pack_bf16(p0, p1);
             pk[i + 1] = pack_bf16(p2, p3);
           }
           unsigned char* box = prow + (c / 64) * HALF_BYTES;
 #pragma unroll
-          for (int k = 0; k < 4 && !TC_WHAT_IF(1); ++k) {
+          for (int k = 0; k < 4; ++k) {
             const int chunk = (c % 64) / 8 + k;
             *reinterpret_cast<uint4*>(box + ((chunk ^ (row & 7)) << 4)) = make_uint4(pk[4 * k], pk[4 * k + 1], pk[4 * k + 2], pk[4 * k + 3]);
           }
@@ -485,7 +479,7 @@ int launch_prefill_tc(const void* q, const void* kc, const void* vc, void* out, 
   dim3 grid(tiles * n_q);
   cudaError_t err = lse_launch(attn_prefill_tc_kernel<D>, grid, THREADS, smem, stream, map_q, map_k, map_v,
                                (__nv_bfloat16*)out, block_tables, bt_stride, segment_start, segment_first_pos,
-                               num_segments, n_q, n_kv, page_size, scale * LOG2E);
+                               num_segments, n_q, n_kv, page_size, scale * LOG2E, (int)num_pages);
   if (err != cudaSuccess) return (int)err;
   return (int)cudaGetLastError();
 }
@@ -499,9 +493,6 @@ extern "C" int lse_attention_tc_supported(int head_dim, int n_q, int n_kv, int p
 }
 
 #ifdef LSE_TRACE
-extern "C" int lse_attention_tc_set_what_if(int bits) {
-  return (int)cudaMemcpyToSymbol(lse_attn_tc_what_if, &bits, sizeof(int));
-}
 extern "C" int lse_attention_tc_blocks(unsigned long long* host_out) {
   return (int)cudaMemcpyFromSymbol(host_out, lse_attn_tc_blocks, sizeof(unsigned long long) * 4096 * 4);
 }

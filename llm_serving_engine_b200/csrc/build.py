@@ -75,16 +75,20 @@ def _log(message: str, verbose: bool) -> None:
         print(f"[llm_serving_engine_b200] {message}", file=sys.stderr, flush=True)
 
 
-def library_path(verbose: bool = True, force: bool = False, trace: bool = False) -> Path:
+def library_path(verbose: bool = True, force: bool = False, trace: bool = False, check: bool = False) -> Path:
     """Path of the built library; compiles it first when it is missing or stale.
 
     ``trace``: the tuning variant (``-DLSE_TRACE``), in which block 0 of every kernel records when it
-    started, when its wait for the kernels before returned and when it ended; a library of its own."""
+    started, when its wait for the kernels before returned and when it ended; a library of its own.
+    ``check``: the checked variant (``-DLSE_CHECK``), in which every kernel compares the indices it takes
+    from the step's metadata with their ranges, replaces a bad one by a safe one and records it; a
+    library of its own as well."""
     build_dir = _build_dir()
-    flags = NVCC_FLAGS + (["-DLSE_TRACE"] if trace else [])
+    variant = "_trace" if trace else "_check" if check else ""
+    flags = NVCC_FLAGS + (["-DLSE_TRACE"] if trace else ["-DLSE_CHECK"] if check else [])
     key = _key(flags)
-    lib = build_dir / (LIB_NAME.replace(".so", "_trace.so") if trace else LIB_NAME)
-    stamp = build_dir / ("build_trace.key" if trace else "build.key")
+    lib = build_dir / LIB_NAME.replace(".so", f"{variant}.so")
+    stamp = build_dir / f"build{variant}.key"
     if not force and lib.exists() and stamp.exists() and stamp.read_text().strip() == key:
         return lib
     nvcc = _nvcc()

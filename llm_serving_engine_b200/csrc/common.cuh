@@ -108,6 +108,37 @@ inline cudaError_t lse_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
 }
 
 
+// ------------------------------------------------------------------ checked builds
+// With -DLSE_CHECK every index that a kernel takes from the step's metadata (token ids, cache slots,
+// block-table entries inside the context, segment numbers, gathered rows) is compared with its range
+// before it is used.  An index out of range is replaced by a safe one, so that nothing outside the
+// buffers is touched, and the first violation of each source file is recorded (what kind, the value,
+// the range) for the host to read with the exported reader.  Nothing traps.  Without the flag the
+// macros cost nothing: LSE_CHECKED(value, ...) is `value`.
+#define LSE_CHECK_TOKEN_ID 1
+#define LSE_CHECK_CACHE_SLOT 2
+#define LSE_CHECK_TABLE_ENTRY 3
+#define LSE_CHECK_SEGMENT 4
+#define LSE_CHECK_ROW 5
+#ifdef LSE_CHECK
+#define LSE_CHECK_DEFINE(reader)                                                                           \
+  __device__ int lse_check_word[4];                                                                        \
+  extern "C" int reader(int* host_out, int reset) {                                                        \
+    if (cudaMemcpyFromSymbol(host_out, lse_check_word, sizeof(int) * 4) != cudaSuccess) return -1;          \
+    if (reset) { const int zero[4] = {0, 0, 0, 0}; cudaMemcpyToSymbol(lse_check_word, zero, sizeof(zero)); } \
+    return 0;                                                                                              \
+  }
+__device__ __forceinline__ int lse_checked(int value, int lo, int hi, int safe, int kind, int* word) {
+  if (value >= lo && value < hi) return value;
+  if (atomicCAS(&word[0], 0, kind) == 0) { word[1] = value; word[2] = lo; word[3] = hi; }
+  return safe;
+}
+#define LSE_CHECKED(value, lo, hi, safe, kind) lse_checked((value), (lo), (hi), (safe), (kind), lse_check_word)
+#else
+#define LSE_CHECK_DEFINE(reader)
+#define LSE_CHECKED(value, lo, hi, safe, kind) (value)
+#endif
+
 // ------------------------------------------------------------------ timeline (tuning builds only)
 // With -DLSE_TRACE every kernel's block 0 records when it started, when pdl_wait() returned and
 // when it ended (nanoseconds of %globaltimer) into a per-source-file buffer that a tuning script

@@ -10,6 +10,7 @@
 #include "common.cuh"
 
 LSE_TL_DEFINE(lse_timeline_elementwise)
+LSE_CHECK_DEFINE(lse_check_elementwise)
 
 // ------------------------------------------------------------------ embedding
 // residual[t, :] = float(table[ids[t], :])
@@ -21,7 +22,7 @@ __global__ void embedding_kernel(const T* __restrict__ table, const int* __restr
   pdl_wait();
   LSE_TL_MARK(2)
   const int t = blockIdx.x;
-  const int id = ids[t];
+  const int id = LSE_CHECKED(ids[t], 0, vocab, -1, LSE_CHECK_TOKEN_ID);
   float* dst = out + (size_t)t * hidden;
   if (id < 0 || id >= vocab) {  // padding row of a fixed-shape batch
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = 0.f;
@@ -82,7 +83,7 @@ template <typename TD, typename TO>
 __global__ void __launch_bounds__(NORM_THREADS)
 add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* __restrict__ delta, int n_partials,
                        long long partial_stride, const float* __restrict__ weight, TO* __restrict__ out,
-                       const int* __restrict__ rows, int hidden, float eps, int write_residual) {
+                       const int* __restrict__ rows, int hidden, float eps, int write_residual, int source_rows) {
   LSE_TL_BEGIN(2)
   pdl_launch_dependents();
   __shared__ float scratch[32];
@@ -97,7 +98,7 @@ add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* __restrict__ delt
   pdl_wait();
   LSE_TL_MARK(2)
   const int r = blockIdx.x;
-  const int s = rows ? rows[r] : r;
+  const int s = rows ? LSE_CHECKED(rows[r], -1, source_rows, -1, LSE_CHECK_ROW) : r;
   if (s < 0) return;
   float* res = residual + (size_t)s * hidden;
   const TD* del = delta ? delta + (size_t)s * hidden : nullptr;
@@ -149,12 +150,12 @@ template <typename TD, typename TO>
 __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __restrict__ delta, int n_partials,
                                    long long partial_stride, const float* __restrict__ weight,
                                    TO* __restrict__ out, const int* __restrict__ rows, int hidden, float eps,
-                                   int write_residual) {
+                                   int write_residual, int source_rows) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float scratch[32];
   const int r = blockIdx.x;
-  const int s = rows ? rows[r] : r;
+  const int s = rows ? LSE_CHECKED(rows[r], -1, source_rows, -1, LSE_CHECK_ROW) : r;
   if (s < 0) return;
   float* res = residual + (size_t)s * hidden;
   const TD* del = delta ? delta + (size_t)s * hidden : nullptr;
@@ -235,7 +236,7 @@ add_rmsnorm_rows_kernel(float* __restrict__ residual, const TD* __restrict__ del
 template <typename TD, typename TO>
 static void launch_add_rmsnorm(float* residual, const void* delta, int n_partials, long long partial_stride,
                                const float* weight, void* out, const int* rows, int n_rows, int hidden, float eps,
-                               int write_residual, cudaStream_t stream) {
+                               int write_residual, int source_rows, cudaStream_t stream) {
   const bool aligned = (((uintptr_t)residual | (uintptr_t)delta | (uintptr_t)weight | (uintptr_t)out) & 15) == 0 &&
                        (partial_stride % 4) == 0;
   if (sizeof(TO) == 2 && n_rows >= 256 && n_partials == 1 && delta != nullptr && rows == nullptr && write_residual &&
@@ -256,23 +257,25 @@ static void launch_add_rmsnorm(float* residual, const void* delta, int n_partial
     int threads = (((hidden / 4 + per_thread - 1) / per_thread + 31) / 32) * 32;
     if (threads > NORM_THREADS) threads = NORM_THREADS;
     lse_launch(add_rmsnorm_vec_kernel<TD, TO>, n_rows, threads, 0, stream,
-        residual, (const TD*)delta, n_partials, partial_stride, weight, (TO*)out, rows, hidden, eps, write_residual);
+        residual, (const TD*)delta, n_partials, partial_stride, weight, (TO*)out, rows, hidden, eps, write_residual,
+        source_rows);
   } else {
     const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
     lse_launch(add_rmsnorm_kernel<TD, TO>, n_rows, threads, 0, stream,
-        residual, (const TD*)delta, n_partials, partial_stride, weight, (TO*)out, rows, hidden, eps, write_residual);
+        residual, (const TD*)delta, n_partials, partial_stride, weight, (TO*)out, rows, hidden, eps, write_residual,
+        source_rows);
   }
 }
 
 extern "C" int lse_add_rmsnorm(float* residual, const void* delta, int delta_dtype, int n_partials,
                                long long partial_stride, const float* weight, void* out, int out_dtype,
                                const int* rows, int n_rows, int hidden, float eps, int write_residual,
-                               cudaStream_t stream) {
+                               int source_rows, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (delta && n_partials < 1) return LSE_ERR_BAD_ARGUMENT;
 #define LSE_NORM_CASE(TD, TO)                                                                               \
   launch_add_rmsnorm<TD, TO>(residual, delta, n_partials, partial_stride, weight, out, rows, n_rows, hidden, \
-                             eps, write_residual, stream)
+                             eps, write_residual, source_rows, stream)
   if (delta_dtype == LSE_DTYPE_F32 && out_dtype == LSE_DTYPE_F32) LSE_NORM_CASE(float, float);
   else if (delta_dtype == LSE_DTYPE_BF16 && out_dtype == LSE_DTYPE_BF16) LSE_NORM_CASE(__nv_bfloat16, __nv_bfloat16);
   else if (delta_dtype == LSE_DTYPE_BF16 && out_dtype == LSE_DTYPE_F32) LSE_NORM_CASE(__nv_bfloat16, float);
@@ -311,7 +314,7 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, int n_partials,
                                      const int* __restrict__ slot_mapping, const float* __restrict__ inv_freq,
                                      TO* __restrict__ q_out, TO* __restrict__ k_cache, TO* __restrict__ v_cache,
                                      int n_q, int n_kv, int head_dim, int page_size, int pairing,
-                                     long long qkv_stride) {
+                                     long long qkv_stride, int num_slots) {
   LSE_TL_BEGIN(3)
   pdl_launch_dependents();
   const int t = blockIdx.x;
@@ -334,7 +337,7 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, int n_partials,
   if (in_range) {
     load4<float>(inv_freq + 4 * c, freq);
     if (bias) { load4<float>(bias + col + e0, ba); load4<float>(bias + col + e1, bb); }
-    slot = slot_mapping[t];
+    slot = LSE_CHECKED(slot_mapping[t], -1, num_slots, -1, LSE_CHECK_CACHE_SLOT);
     if (is_q || is_k) {
       const float pos = (float)positions[t];
 #pragma unroll
@@ -434,7 +437,7 @@ __global__ void rope_kv_write_wide_kernel(const TI* __restrict__ qkv, const floa
                                           const float* __restrict__ inv_freq, TO* __restrict__ q_out,
                                           TO* __restrict__ k_cache, TO* __restrict__ v_cache, int tokens, int n_q,
                                           int n_kv, int head_dim, int page_size, int pairing, long long qkv_stride,
-                                          int head_groups) {
+                                          int head_groups, int num_slots) {
   pdl_launch_dependents();
   const int per_head = head_dim >> 4;            // threads per head
   const int per_token = per_head * head_groups;  // threads per token
@@ -452,7 +455,7 @@ __global__ void rope_kv_write_wide_kernel(const TI* __restrict__ qkv, const floa
   if (live) {
     float freq[8];
     load8<float>(inv_freq + 8 * c, freq);
-    slot = slot_mapping[t];
+    slot = LSE_CHECKED(slot_mapping[t], -1, num_slots, -1, LSE_CHECK_CACHE_SLOT);
     const float pos = (float)positions[t];
 #pragma unroll
     for (int j = 0; j < 8; ++j) sincosf(__fmul_rn(pos, freq[j]), &sn[j], &cs[j]);
@@ -513,8 +516,9 @@ extern "C" int lse_rope_kv_write(const void* qkv, int in_dtype, int n_partials, 
                                  const float* bias, const int* positions, const int* slot_mapping,
                                  const float* inv_freq, void* q_out, void* k_cache, void* v_cache, int out_dtype,
                                  int tokens, int n_q, int n_kv, int head_dim, int page_size, int pairing,
-                                 long long qkv_stride, cudaStream_t stream) {
+                                 long long qkv_stride, int num_pages, cudaStream_t stream) {
   if (tokens <= 0) return 0;
+  const int num_slots = num_pages * page_size;   // checked builds compare every cache slot with it
   // eight elements per thread: the head size is a multiple of 8 (16 for the half-split pairing)
   if (head_dim % 8 || (pairing == 1 && head_dim % 16) || head_dim > 2048 || page_size <= 0 ||
       (pairing != 0 && pairing != 1) || n_partials < 1 || qkv_stride % 4 || partial_stride % 4 ||
@@ -532,7 +536,7 @@ extern "C" int lse_rope_kv_write(const void* qkv, int in_dtype, int n_partials, 
 #define LSE_ROPE_WIDE_CASE(TI, TO)                                                                              \
   lse_launch(rope_kv_write_wide_kernel<TI, TO>, blocks, threads, 0, stream, (const TI*)qkv, bias, positions,    \
       slot_mapping, inv_freq, (TO*)q_out, (TO*)k_cache, (TO*)v_cache, tokens, n_q, n_kv, head_dim, page_size,   \
-      pairing, qkv_stride, head_groups)
+      pairing, qkv_stride, head_groups, num_slots)
       if (in_dtype == LSE_DTYPE_F32 && out_dtype == LSE_DTYPE_F32) LSE_ROPE_WIDE_CASE(float, float);
       else if (in_dtype == LSE_DTYPE_BF16 && out_dtype == LSE_DTYPE_BF16) LSE_ROPE_WIDE_CASE(__nv_bfloat16, __nv_bfloat16);
       else if (in_dtype == LSE_DTYPE_F32 && out_dtype == LSE_DTYPE_BF16) LSE_ROPE_WIDE_CASE(float, __nv_bfloat16);
@@ -550,7 +554,7 @@ extern "C" int lse_rope_kv_write(const void* qkv, int in_dtype, int n_partials, 
 #define LSE_ROPE_CASE(TI, TO)                                                                                   \
   lse_launch(rope_kv_write_kernel<TI, TO>, grid, threads, 0, stream,                                            \
       (const TI*)qkv, n_partials, partial_stride, bias, positions, slot_mapping, inv_freq, (TO*)q_out,          \
-      (TO*)k_cache, (TO*)v_cache, n_q, n_kv, head_dim, page_size, pairing, qkv_stride)
+      (TO*)k_cache, (TO*)v_cache, n_q, n_kv, head_dim, page_size, pairing, qkv_stride, num_slots)
   if (in_dtype == LSE_DTYPE_F32 && out_dtype == LSE_DTYPE_F32) LSE_ROPE_CASE(float, float);
   else if (in_dtype == LSE_DTYPE_BF16 && out_dtype == LSE_DTYPE_BF16) LSE_ROPE_CASE(__nv_bfloat16, __nv_bfloat16);
   else if (in_dtype == LSE_DTYPE_F32 && out_dtype == LSE_DTYPE_BF16) LSE_ROPE_CASE(float, __nv_bfloat16);

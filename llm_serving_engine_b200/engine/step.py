@@ -386,9 +386,9 @@ class StepRunner:
         places = 0 if wanted == 0 else (segments if wanted <= segments else tokens)   # none, at most one a request, or any
         if wanted > places:
             return None
-        longest = max(len(entry.tokens) for entry in entries)
-        # (the attention part picks its kernel by the longest portion: steps with and without a long one get graphs of their own)
-        key = ("portions", tokens, segments, places, self._graph_width(self._pages_after(entries)), longest >= 128)
+        # which kernels the parts launch may depend on how the rows are cut into portions: such steps get graphs of their own
+        signature = self.model.launch_signature([len(entry.tokens) for entry in entries]) if hasattr(self.model, "launch_signature") else ()
+        key = ("portions", tokens, segments, places, self._graph_width(self._pages_after(entries)), signature)
         slot = self._portion_graphs.get(key)
         if slot is None:
             seen = self._portion_classes_seen.get(key, 0) + 1

@@ -15,9 +15,9 @@ _lib = None
 _SIGNATURES = {
     "lse_embedding": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "lse_add_rmsnorm": [c_void_p, c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_int,
-                        c_int, c_float, c_int, c_void_p],
+                        c_int, c_float, c_int, c_int, c_void_p],
     "lse_rope_kv_write": [c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                          c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_longlong, c_void_p],
+                          c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_longlong, c_int, c_void_p],
     "lse_silu_mul": [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p],
     "lse_gemm_bf16_skinny": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "lse_gemm_bf16_skinny_pad": [c_int],
@@ -32,11 +32,12 @@ _SIGNATURES = {
                         c_longlong, c_longlong, c_void_p],
     "lse_paged_attention_generic": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
                                     c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
-                                    c_int, c_void_p],
+                                    c_int, c_int, c_int, c_void_p],
     "lse_paged_attention_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
-                                   c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+                                   c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int,
+                                   c_void_p],
     "lse_paged_attention_prefill": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
-                                    c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
+                                    c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "lse_attention_mma_supported": [c_int, c_int, c_int],
     "lse_paged_attention_prefill_tc": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                        c_int, c_int, c_longlong, c_int, c_int, c_int, c_int, c_float, c_void_p],
@@ -58,7 +59,9 @@ def load(verbose: bool = True):
     global _lib
     if _lib is None:
         import os
-        path = build.library_path(verbose=verbose, trace=os.environ.get("LSE_TRACE", "0") == "1")   # 1: the tuning variant
+        # LSE_TRACE=1: the tuning variant; LSE_CHECK=1: the checked variant (indices compared with their ranges)
+        path = build.library_path(verbose=verbose, trace=os.environ.get("LSE_TRACE", "0") == "1",
+                                  check=os.environ.get("LSE_CHECK", "0") == "1")
         lib = ctypes.CDLL(str(path))
         for name, argtypes in _SIGNATURES.items():
             fn = getattr(lib, name)
@@ -78,6 +81,31 @@ def register_signatures(signatures: dict) -> None:
             fn = getattr(_lib, name)
             fn.argtypes = argtypes
             fn.restype = c_int
+
+
+CHECK_READERS = ("lse_check_elementwise", "lse_check_attention_generic", "lse_check_attention_mma", "lse_check_attention_tc")
+CHECK_KINDS = {1: "token id", 2: "cache slot", 3: "block-table entry", 4: "segment number", 5: "row index"}
+
+
+def check_report(reset: bool = True) -> list[str]:
+    """What the checked variant of the library (``LSE_CHECK=1``) has recorded: one line per source file whose
+    kernels met an index outside its range (empty: none).  Synchronises the device.  Raises when the loaded
+    library is not the checked variant."""
+    lib = load()
+    found = []
+    for name in CHECK_READERS:
+        try:
+            reader = getattr(lib, name)
+        except AttributeError:
+            raise KernelError("the loaded kernel library is not the checked variant (set LSE_CHECK=1 before the first use)") from None
+        reader.argtypes = [c_void_p, c_int]
+        reader.restype = c_int
+        words = (c_int * 4)()
+        if reader(words, int(reset)) != 0:
+            raise KernelError(f"{name}: the check words could not be read")
+        if words[0]:
+            found.append(f"{name[len('lse_check_'):]}: {CHECK_KINDS.get(words[0], words[0])} {words[1]} outside [{words[2]}, {words[3]})")
+    return found
 
 
 _launch_count = 0

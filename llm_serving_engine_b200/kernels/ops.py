@@ -92,7 +92,7 @@ def add_rmsnorm(residual: torch.Tensor, delta: torch.Tensor | None, weight: torc
     delta_code = dtype_code(delta.dtype) if delta is not None else dtype_code(out.dtype)
     check(lib.lse_add_rmsnorm(residual.data_ptr(), _ptr(delta), delta_code, n_partials, stride, weight.data_ptr(),
                               out.data_ptr(), dtype_code(out.dtype), _ptr(rows), n_rows, hidden,
-                              float(eps), int(write_residual), _stream()), "add_rmsnorm")
+                              float(eps), int(write_residual), tokens, _stream()), "add_rmsnorm")
     return out
 
 
@@ -142,7 +142,8 @@ def rope_kv_write(qkv: torch.Tensor, bias: torch.Tensor | None, positions: torch
     check(lib.lse_rope_kv_write(qkv.data_ptr(), dtype_code(qkv.dtype), n_partials, stride, _ptr(bias),
                                 positions.data_ptr(), slot_mapping.data_ptr(), inv_freq.data_ptr(),
                                 q_out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), dtype_code(q_out.dtype),
-                                tokens, n_q, n_kv, head_dim, k_cache.shape[2], pairing, row_stride, _stream()),
+                                tokens, n_q, n_kv, head_dim, k_cache.shape[2], pairing, row_stride, k_cache.shape[0],
+                                _stream()),
           "rope_kv_write")
 
 
@@ -172,7 +173,8 @@ def paged_attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
                                           out.data_ptr(), dtype_code(q.dtype), block_tables.data_ptr(),
                                           block_tables.stride(0), segment_of_token.data_ptr(),
                                           positions.data_ptr(), tokens, n_q, n_kv, head_dim, page_size,
-                                          float(scale), int(window), _stream()), "paged_attention_generic")
+                                          float(scale), int(window), k_cache.shape[0], block_tables.shape[0],
+                                          _stream()), "paged_attention_generic")
     return out
 
 
@@ -236,7 +238,8 @@ def paged_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
                                          _ptr(scratch), _ptr(arrivals), int(by_cluster), block_tables.data_ptr(),
                                          block_tables.stride(0),
                                          segment_of_token.data_ptr(), positions.data_ptr(), tokens, n_q, n_kv,
-                                         head_dim, page_size, float(scale), int(num_splits), _stream()),
+                                         head_dim, page_size, float(scale), int(num_splits), k_cache.shape[0],
+                                         block_tables.shape[0], _stream()),
           "paged_attention_decode")
     return out
 
@@ -260,7 +263,7 @@ def paged_attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
     check(lib.lse_paged_attention_prefill(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
                                           block_tables.data_ptr(), block_tables.stride(0), segment_start.data_ptr(),
                                           segment_first_position.data_ptr(), segments, tokens, n_q, n_kv, head_dim,
-                                          page_size, float(scale), _stream()), "paged_attention_prefill")
+                                          page_size, float(scale), k_cache.shape[0], _stream()), "paged_attention_prefill")
     return out
 
 

@@ -104,6 +104,11 @@ class DecoderModel:
                 return False
         return bool(getattr(self.final_norm, "graph_safe", False))
 
+    def launch_signature(self, segment_counts: list[int]) -> tuple:
+        """The mixers' answers to ``Mixer.launch_signature`` for a step of this shape (each distinct answer once)."""
+        answers = {block.mixer.launch_signature(segment_counts) for block in self.blocks}
+        return tuple(sorted(answer for answer in answers if answer))
+
     @property
     def vocab_size(self) -> int:
         return self.spec.vocab_size

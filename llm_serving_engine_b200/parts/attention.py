@@ -77,6 +77,24 @@ class GroupedQueryAttention(Mixer):
     def cache_requirement(cls, params, hidden_size):
         return PagedKV(int(params["num_kv_heads"]), int(params["head_dim"]), int(params.get("window", 0)))
 
+    def prompt_kernel(self, segment_counts: list[int], page_size: int | None = None) -> str:
+        """"tcgen05" or "mma": the kernel a step with prompt portions takes (the rule at the top of this file)."""
+        if not TCGEN05_PREFILL or max(segment_counts) < TCGEN05_MIN_ROWS:
+            return "mma"
+        long_on_average = sum(segment_counts) >= TCGEN05_MIN_ROWS_PER_REQUEST * len(segment_counts)
+        blocks_at_once = sum(-(-count // 128) for count in segment_counts) * self.n_q <= ops.sm_count()
+        if not (long_on_average or blocks_at_once):
+            return "mma"
+        if page_size is not None and not ops.attention_tc_supported(self.head_dim, self.n_q, self.n_kv, page_size,
+                                                                    self.ctx.dtype, self.window):
+            return "mma"
+        return "tcgen05"
+
+    def launch_signature(self, segment_counts):
+        if max(segment_counts) == 1 or not ops.attention_mma_supported(self.head_dim, self.n_q, self.n_kv, self.ctx.dtype, self.window):
+            return ()
+        return (self.prompt_kernel(segment_counts),)
+
     def forward(self, x, step, cache):
         tokens = x.shape[0]
         # bias is added with the rotation, in float32; at most 8 partial sums: the rotary kernel fetches them in one go
@@ -89,11 +107,7 @@ class GroupedQueryAttention(Mixer):
                 splits = ops.decode_splits(tokens, self.n_q, self.n_kv, step.max_context)
                 ops.paged_attention_decode(q, cache.keys, cache.values, attended, cache.block_tables,
                                            step.segment_of_token, step.positions, self.scale, splits)
-            elif (TCGEN05_PREFILL and step.max_segment_tokens >= TCGEN05_MIN_ROWS
-                  and (tokens >= TCGEN05_MIN_ROWS_PER_REQUEST * step.num_segments
-                       or sum(-(-segment.count // 128) for segment in step.segments) * self.n_q <= TCGEN05_BLOCKS_AT_ONCE)
-                  and ops.attention_tc_supported(
-                    self.head_dim, self.n_q, self.n_kv, cache.keys.shape[2], x.dtype, self.window)):
+            elif self.prompt_kernel([segment.count for segment in step.segments], cache.keys.shape[2]) == "tcgen05":
                 ops.paged_attention_prefill_tc(q, cache.keys, cache.values, attended, cache.block_tables,
                                                step.segment_start, step.segment_first_position, self.scale)
             else:

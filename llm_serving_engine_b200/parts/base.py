@@ -105,6 +105,12 @@ class Mixer(Part):
     def forward(self, x: torch.Tensor, step, cache) -> torch.Tensor:
         raise NotImplementedError
 
+    def launch_signature(self, segment_counts: list[int]) -> tuple:
+        """What of a step's shape, beyond its numbers of rows and requests, decides which kernels ``forward``
+        launches (``segment_counts``: tokens of each request in the step).  Steps with different signatures
+        are captured in CUDA graphs of their own; ``forward`` must choose by the same rule."""
+        return ()
+
 
 class FeedForward(Part):
     def forward(self, x: torch.Tensor) -> torch.Tensor:

@@ -19,6 +19,11 @@ import os
 SKINNY_MAX_ROWS = int(os.environ.get("LSE_SKINNY_MAX_ROWS", "32"))
 
 
+# The library product (rows beyond SKINNY_MAX_ROWS) accumulates in float32 all the way: no bfloat16 partial sums
+# when it splits the k range.
+torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+
+
 def reduce_partials(y: torch.Tensor) -> torch.Tensor:
     """[rows, out] from a branch output that may be a stack of partial sums [P, rows, out]."""
     if y.dim() == 3:
