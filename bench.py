@@ -32,9 +32,13 @@ QWEN25_1P5B = {
     "num_attention_heads": 12, "num_key_value_heads": 2, "max_position_embeddings": 4096,
     "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "attention_bias": True, "tie_word_embeddings": True,
 }
-# layer sizes of a larger model of the same architecture, for `--sizes 7b --only decode|prefill` (no bench line)
+# layer sizes of the larger models of the same architecture (the workloads of the `points` beyond the headline, and
+# `--sizes 7b|14b --only decode|prefill`)
 QWEN25_7B_SIZES = {"hidden_size": 3584, "intermediate_size": 18944, "num_attention_heads": 28, "num_key_value_heads": 4,
                    "vocab_size": 152064, "tie_word_embeddings": False}
+QWEN25_14B_SIZES = {"hidden_size": 5120, "intermediate_size": 13824, "num_attention_heads": 40, "num_key_value_heads": 8,
+                    "vocab_size": 152064, "tie_word_embeddings": False, "rms_norm_eps": 1e-5, "max_position_embeddings": 8192}
+LAYERS_7B, LAYERS_14B, LAYERS_14B_RUN = 28, 48, 12
 FULL_LAYERS = QWEN25_1P5B["num_hidden_layers"]
 USE_GRAPHS = True     # --no-graphs: launch by launch (for profilers)
 PROMPT = 2048
@@ -95,14 +99,17 @@ class ClockSampler:
                 "sm_max_mhz": max(maxima) if maxima else None, "reasons": reasons, "samples": len(self.rows)}
 
 
-def build_model(layers: int):
+def build_model(layers: int, sizes: dict | None = None, dtype: str = "bfloat16"):
+    """A model of the architecture with random weights made on the device: N(0, 0.02) matrices and biases,
+    norm weights 1 + U(-0.1, 0.1), seed 0.  ``sizes`` overrides keys of the Qwen2.5-1.5B configuration."""
     import torch
 
     from llm_serving_engine_b200.config import load_config
-    from llm_serving_engine_b200.models import DecoderModel, expected_tensors
+    from llm_serving_engine_b200.models import DecoderModel, expected_tensors, parse_dtype
     from llm_serving_engine_b200.weights.loader import held_dtype
 
-    config = dict(QWEN25_1P5B, num_hidden_layers=layers)
+    compute = parse_dtype(dtype)
+    config = dict(QWEN25_1P5B, **(sizes or {}), num_hidden_layers=layers)
     _, _, spec = load_config(config)
     generator = torch.Generator(device="cuda").manual_seed(0)
     weights = {}
@@ -111,12 +118,15 @@ def build_model(layers: int):
             tensor = 1.0 + (torch.rand(tensor_spec.shape, generator=generator, device="cuda") * 0.2 - 0.1)
         else:
             tensor = torch.randn(tensor_spec.shape, generator=generator, device="cuda") * 0.02
-        weights[name] = tensor.to(held_dtype(tensor_spec, tensor.dtype, torch.bfloat16))
-    return DecoderModel(spec, weights, torch.bfloat16, "cuda"), config
+        weights[name] = tensor.to(held_dtype(tensor_spec, tensor.dtype, compute))
+    return DecoderModel(spec, weights, compute, "cuda"), config
 
 
-def time_decode(model, batch: int, steps: int, warmup: int):
-    """Device time of ``steps`` decode steps at ``batch`` requests that hold PROMPT tokens each."""
+def time_decode(model, batch: int, steps: int, warmup: int, repeats: int = 1, prompt: int = 0):
+    """Device time of decode steps at ``batch`` requests that hold ``prompt`` (default PROMPT) tokens each:
+    ``repeats`` runs of ``steps`` steps, each between a pair of CUDA events.  Returns (median milliseconds a
+    step, the bytes of keys and values a step of the median run reads, launches of one run, every run's
+    milliseconds a step)."""
     import torch
 
     from llm_serving_engine_b200.cache.manager import CacheManager
@@ -125,6 +135,7 @@ def time_decode(model, batch: int, steps: int, warmup: int):
     from llm_serving_engine_b200.kernels import library, ops
     from llm_serving_engine_b200.models import cache_requirements
 
+    prompt = prompt or PROMPT
     context = model.spec.max_position_embeddings
     pages = batch * (context // BLOCK)
     cache = CacheManager(cache_requirements(model.spec), CacheConfig(BLOCK, pages), model.dtype, model.device,
@@ -133,11 +144,13 @@ def time_decode(model, batch: int, steps: int, warmup: int):
                         use_graphs=USE_GRAPHS)
     generator = torch.Generator().manual_seed(1)
     ids = [f"d{index}" for index in range(batch)]
+    runs = []
     with torch.inference_mode():
         for rid in ids:
             cache.create(rid)
-            prompt = torch.randint(0, model.vocab_size, (PROMPT,), generator=generator).tolist()
-            runner.run([StepEntry(rid, prompt, [])])
+            tokens = torch.randint(0, model.vocab_size, (prompt,), generator=generator).tolist()
+            for lo in range(0, prompt, PROMPT):          # a long prompt goes in portions of PROMPT tokens
+                runner.run([StepEntry(rid, tokens[lo:lo + PROMPT], [])])
         tokens = torch.randint(0, model.vocab_size, (batch,), generator=generator).tolist()
         out = torch.empty(batch, dtype=torch.int32, device=model.device)
 
@@ -148,20 +161,24 @@ def time_decode(model, batch: int, steps: int, warmup: int):
         for _ in range(warmup):
             one_step()
         torch.cuda.synchronize()
-        launches = library.launches() + runner.graph_kernel_launches
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        for _ in range(steps):
-            one_step()
-        end.record()
-        torch.cuda.synchronize()
-        launches = library.launches() + runner.graph_kernel_launches - launches
-    ms = start.elapsed_time(end) / steps
-    kv_bytes = batch * (PROMPT + warmup + steps // 2) * cache.kv_bytes_per_token()
+        launches = 0
+        for _ in range(repeats):
+            before = library.launches() + runner.graph_kernel_launches
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            for _ in range(steps):
+                one_step()
+            end.record()
+            torch.cuda.synchronize()
+            launches = library.launches() + runner.graph_kernel_launches - before
+            runs.append(start.elapsed_time(end) / steps)
+    order = sorted(range(repeats), key=lambda index: runs[index])
+    median_run = order[repeats // 2]
+    kv_bytes = batch * (prompt + warmup + median_run * steps + steps // 2) * cache.kv_bytes_per_token()
     cache.free_all()
     del runner, cache
     torch.cuda.empty_cache()
-    return ms, kv_bytes, launches
+    return runs[median_run], kv_bytes, launches, runs
 
 
 def time_prefill(model, repeats: int = 5):
@@ -245,6 +262,144 @@ def time_e2e(model, batch: int, new_tokens: int):
     return decoded / max(seconds, 1e-9), h2d, 4 * batch, decoded // batch
 
 
+REPEATS = 5     # runs of the timed decode region; the median is reported, the spread beside it
+
+
+def time_mixed_traffic(model, requests: int = 32, seed: int = 0):
+    """Continuous batching of ``requests`` requests through the Python entry point: prompt lengths log-normal
+    (median 512, clipped to 64 .. 4,096), 128 to 512 output tokens each, all waiting at the start.  Returns
+    (generated tokens a second over the whole run, generated tokens, prompt tokens, seconds)."""
+    import torch
+
+    from llm_serving_engine_b200 import CacheConfig, GenerationConfig, LLMEngine, SchedulerConfig
+    from llm_serving_engine_b200.workload import ClippedLogNormal, TrafficProfile, make_traffic
+
+    limit = model.spec.max_position_embeddings
+    profile = TrafficProfile(requests=requests, arrival_rate=0.0, prompt=ClippedLogNormal(512, 1.0, 64, 4096),
+                             output=ClippedLogNormal(256, 0.5, 128, 512), seed=seed,
+                             vocabulary_size=model.vocab_size).fitted_to(model.vocab_size, limit)
+    traffic = make_traffic(profile)
+    engine = LLMEngine(model, None, cache_config=CacheConfig(BLOCK, requests * (limit // BLOCK)),
+                       scheduler_config=SchedulerConfig(max_batch_size=requests, max_tokens_per_step=PROMPT),
+                       prefill_chunk_size=PROMPT)
+    engine.warmup()
+    torch.cuda.synchronize()
+    started = time.perf_counter()
+    outputs = engine.generate_many([list(item.prompt_token_ids) for item in traffic],
+                                   [GenerationConfig(max_new_tokens=item.max_new_tokens) for item in traffic])
+    torch.cuda.synchronize()
+    seconds = time.perf_counter() - started
+    generated = sum(len(output) for output in outputs)
+    del engine
+    torch.cuda.empty_cache()
+    return generated / seconds, generated, sum(len(item.prompt_token_ids) for item in traffic), seconds
+
+
+def time_chunks_beside_decoding(model, decoding: int = 8, prompt: int = 8192, chunk: int = 2048):
+    """A ``prompt``-token prompt fed in ``chunk``-token portions beside ``decoding`` requests that decode (each
+    holds ``chunk`` tokens): device milliseconds of each mixed step."""
+    import torch
+
+    from llm_serving_engine_b200.cache.manager import CacheManager
+    from llm_serving_engine_b200.config.runtime_config import CacheConfig
+    from llm_serving_engine_b200.engine.step import StepEntry, StepRunner
+    from llm_serving_engine_b200.models import cache_requirements
+
+    context = model.spec.max_position_embeddings
+    cache = CacheManager(cache_requirements(model.spec), CacheConfig(BLOCK, (decoding + 1) * (context // BLOCK)), model.dtype,
+                         model.device, context, num_state_slots=decoding + 1)
+    runner = StepRunner(model, cache, max_tokens_per_step=chunk + decoding, max_segments=decoding + 1)
+    generator = torch.Generator().manual_seed(4)
+    times = []
+    with torch.inference_mode():
+        for index in range(decoding):
+            cache.create(f"d{index}")
+            runner.run([StepEntry(f"d{index}", torch.randint(0, model.vocab_size, (chunk,), generator=generator).tolist(), [])])
+        for repeat in range(3):          # the first pass launches kernel by kernel, the second captures, the third replays
+            cache.create("long")
+            tokens = torch.randint(0, model.vocab_size, (prompt,), generator=generator).tolist()
+            times = []
+            for lo in range(0, prompt, chunk):
+                entries = [StepEntry("long", tokens[lo:lo + chunk], [chunk - 1] if lo + chunk == prompt else [])]
+                entries += [StepEntry(f"d{index}", [7], [0]) for index in range(decoding)]
+                start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                start.record()
+                runner.run(entries)
+                end.record()
+                torch.cuda.synchronize()
+                times.append(start.elapsed_time(end))
+            cache.free("long")
+    cache.free_all()
+    del runner, cache
+    torch.cuda.empty_cache()
+    return times
+
+
+def kernel_table(batch: int, layers: int) -> dict | None:
+    """Per kind of kernel, what one decode step spends in it: a child process loads the tuning variant of the
+    library (its kernels stamp the device's clock) and prints the sums as JSON.  None when that fails."""
+    try:
+        done = subprocess.run([sys.executable, os.path.abspath(__file__), "--timeline", "1", "--timeline-json", "--batch", str(batch),
+                               "--layers", str(layers)], capture_output=True, text=True, timeout=600)
+        for line in reversed(done.stdout.strip().splitlines()):
+            if line.startswith("{"):
+                return json.loads(line)
+    except Exception:
+        pass
+    return None
+
+
+def other_points(args, peak: dict) -> tuple[dict, dict]:
+    """The workloads beyond the headline: the float32 path, the Qwen2.5-7B sizes under mixed traffic, the Qwen2.5-14B
+    sizes at context 8,192 (fewer layers than the model has: both numbers are in the point's name or note)."""
+    import torch
+
+    points, notes = {}, {}
+    steps = max(args.steps // 4, 8)
+
+    def attempt(name, work):
+        try:
+            work()
+        except Exception as error:    # a point that fails is reported as missing, the headline stands
+            points[name] = None
+            notes[name] = f"{type(error).__name__}: {str(error)[:120]}"
+        torch.cuda.empty_cache()
+
+    def float32():
+        model, _ = build_model(FULL_LAYERS, dtype="float32")
+        ms, kv_bytes, _, _ = time_decode(model, 8, steps, 3)
+        points["fp32_decode_b8"] = round(8 / (ms / 1e3), 1)
+        notes["fp32_decode_b8"] = (f"true float32 path, 28 layers, {ms:.3f} ms a step, "
+                                   f"{(model.weight_bytes_per_step() + kv_bytes) / (ms / 1e3) / 1e9 / peak['hbm_gbs']:.3f} of the copy bandwidth")
+
+    def sizes_7b():
+        model, _ = build_model(LAYERS_7B, QWEN25_7B_SIZES)
+        rate, generated, prompts, seconds = time_mixed_traffic(model)
+        points["7b_mixed32_output_tok_s"] = round(rate, 1)
+        notes["7b_mixed32_output_tok_s"] = (f"Qwen2.5-7B sizes, 28 of 28 layers, 32 requests at once, {prompts} prompt and {generated} "
+                                            f"generated tokens in {seconds:.2f} s through LLMEngine.generate_many")
+        ms, kv_bytes, _, _ = time_decode(model, 8, steps, 3)
+        points["7b_decode_b8"] = round(8 / (ms / 1e3), 1)
+        notes["7b_decode_b8"] = f"{(model.weight_bytes_per_step() + kv_bytes) / (ms / 1e3) / 1e9 / peak['hbm_gbs']:.3f} of the copy bandwidth"
+
+    def sizes_14b():
+        model, _ = build_model(LAYERS_14B_RUN, QWEN25_14B_SIZES)
+        for batch in (1, 8, 64):
+            ms, kv_bytes, _, _ = time_decode(model, batch, steps, 3, prompt=8192 - 64)
+            name = f"14b_{LAYERS_14B_RUN}of{LAYERS_14B}_layers_ctx8192_decode_b{batch}"
+            points[name] = round(batch / (ms / 1e3), 1)
+            notes[name] = f"{(model.weight_bytes_per_step() + kv_bytes) / (ms / 1e3) / 1e9 / peak['hbm_gbs']:.3f} of the copy bandwidth"
+        times = time_chunks_beside_decoding(model)
+        name = f"14b_{LAYERS_14B_RUN}of{LAYERS_14B}_layers_prefill8192_in_2048_chunks_beside_8_decoding_tok_s"
+        points[name] = round(8192 / (sum(times) / 1e3), 1)
+        notes[name] = "ms of the four mixed steps: " + ", ".join(f"{value:.2f}" for value in times)
+
+    attempt("fp32_decode_b8", float32)
+    attempt("7b_mixed32_output_tok_s", sizes_7b)
+    attempt("14b", sizes_14b)
+    return points, notes
+
+
 def run_ours(args) -> dict:
     import torch
 
@@ -252,13 +407,14 @@ def run_ours(args) -> dict:
     __graft_entry__.build()
     torch.cuda.set_device(0)
     layers = args.layers or FULL_LAYERS
-    model, config = build_model(layers)
+    sizes = {"7b": QWEN25_7B_SIZES, "14b": QWEN25_14B_SIZES}.get(args.sizes)
+    model, config = build_model(layers, sizes)
     peak = peaks()
     weight_bytes = model.weight_bytes_per_step()
     batch = args.batch
 
     if args.only == "decode":     # a short run of one part, for profilers; prints no bench line
-        ms, kv_bytes, _ = time_decode(model, batch, args.steps, args.warmup)
+        ms, kv_bytes, _, _ = time_decode(model, batch, args.steps, args.warmup)
         return {"only": "decode", "batch": batch, "layers": layers, "ms_per_step": round(ms, 4),
                 "gb_per_s": round((weight_bytes + kv_bytes) / (ms / 1000) / 1e9, 1)}
     if args.only == "prefill":
@@ -266,17 +422,23 @@ def run_ours(args) -> dict:
         return {"only": "prefill", "layers": layers, "ms": round(ms, 4),
                 "tflops": round(prefill_flops(config, layers, PROMPT) / (ms / 1000) / 1e12, 1)}
     with ClockSampler() as clocks:
-        ms, kv_bytes, launches = time_decode(model, batch, args.steps, args.warmup)
+        ms, kv_bytes, launches, runs = time_decode(model, batch, args.steps, args.warmup, repeats=REPEATS)
     value = batch / (ms / 1e3)
     achieved = (weight_bytes + kv_bytes) / (ms / 1e3) / 1e9
 
     prefill_ms = time_prefill(model)
     flops = prefill_flops(config, layers, PROMPT)
-    points = {}
+    points, fractions = {}, {}
     for point_batch in (1, 64):
-        point_ms, _, _ = time_decode(model, point_batch, max(args.steps // 2, 8), args.warmup)
+        point_ms, point_kv, _, _ = time_decode(model, point_batch, max(args.steps // 2, 8), args.warmup, repeats=3)
         points[f"decode_b{point_batch}"] = round(point_batch / (point_ms / 1e3), 1)
+        fractions[f"decode_b{point_batch}"] = round((weight_bytes + point_kv) / (point_ms / 1e3) / 1e9 / peak["hbm_gbs"], 4)
     e2e_value, h2d, d2h, _ = time_e2e(model, batch, max(args.steps, 16))
+    del model
+    torch.cuda.empty_cache()
+    more, notes = ({}, {}) if args.quick else other_points(args, peak)
+    points.update(more)
+    kernels = None if args.quick else kernel_table(batch, layers)
 
     return {
         "metric": "decode tok/s at batch 8 (Qwen2.5-1.5B shape, 2,048-token prompts)",
@@ -284,11 +446,14 @@ def run_ours(args) -> dict:
         "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic (random weights, uniform random token ids)", "impl": "ours",
         "config": bench_config(config, layers, batch),
+        "repeats": {"count": REPEATS, "ms_per_step": [round(run, 4) for run in runs], "reported": "median",
+                    "spread": round((max(runs) - min(runs)) / ms, 4)},
         "prefill": {"value": round(PROMPT / (prefill_ms / 1e3), 1), "tokens": PROMPT, "ms": round(prefill_ms, 3),
                     "frac": round(flops / (prefill_ms / 1e3) / (peak["bf16_tflops"] * 1e12), 4)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / peak["hbm_gbs"], 4), "peaks": peak["source"]},
-        "points": points,
+        "points": points, "points_roofline_frac": fractions, "points_notes": notes,
+        "kernels": kernels,
         "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "pipeline": "one decode step in flight: every step copies its metadata from pinned host memory and its "
                             "tokens to the host; the tokens feed the next step on the device"},
@@ -532,7 +697,7 @@ def timeline(args) -> int:
 
     torch.cuda.set_device(0)
     lib = library.load()
-    model, _ = build_model(args.layers or FULL_LAYERS)
+    model, _ = build_model(args.layers or FULL_LAYERS, {"7b": QWEN25_7B_SIZES, "14b": QWEN25_14B_SIZES}.get(args.sizes))
     batch = args.batch
     context = model.spec.max_position_embeddings
     cache = CacheManager(cache_requirements(model.spec), CacheConfig(BLOCK, batch * (context // BLOCK)), model.dtype,
@@ -574,12 +739,29 @@ def timeline(args) -> int:
               f"{(ended - origin) / 1000:9.2f} {(ended - waited) / 1000:11.2f} {(waited - before) / 1000:30.2f}")
         before = ended
     totals: dict[str, list] = {}
+    before = origin
     for kind, started, waited, ended in rows:
-        entry = totals.setdefault(names.get(kind, str(kind)), [0, 0.0])
+        entry = totals.setdefault(names.get(kind, str(kind)), [0, 0.0, 0.0])
         entry[0] += 1
         entry[1] += (ended - waited) / 1000
-    for name, (count, active) in totals.items():
-        print(f"{name:10} x{count:4d}: {active:8.1f} us after the wait in total, {active / count:6.2f} us each")
+        entry[2] += max(0.0, (waited - before) / 1000)
+        before = ended
+    for name, (count, active, gaps) in totals.items():
+        print(f"{name:10} x{count:4d}: {active:8.1f} us after the wait in total, {active / count:6.2f} us each; "
+              f"{gaps:8.1f} us between the kernel before and the wait's return")
+    if args.timeline_json:
+        # bytes a kind of kernel has to read in a step over the time its block 0 spends after its wait: a lower
+        # bound of the kind's rate (other blocks end later; the first tiles were fetched before the wait)
+        kv_bytes = batch * (PROMPT + max(args.warmup, 3) + 1) * cache.kv_bytes_per_token()
+        moved = {"product": model.weight_bytes_per_step(), "attention": kv_bytes}
+        table = {"step_us": round((max(row[3] for row in rows) - origin) / 1000, 1), "kernels_in_step": len(rows),
+                 "how": "block 0 of every kernel stamps the global timer at its start, when its wait for the kernels "
+                        "before returns and at its end (tuning variant of the library, one decode step from a CUDA graph)"}
+        for name, (count, active, gaps) in totals.items():
+            table[name] = {"launches": count, "us_after_wait": round(active, 1), "us_handover": round(gaps, 1)}
+            if name in moved:
+                table[name]["gb_per_s_after_wait"] = round(moved[name] / (active * 1e-6) / 1e9, 1)
+        print(json.dumps(table))
     return 0
 
 
@@ -594,19 +776,20 @@ def main() -> int:
     parser.add_argument("--only", choices=("all", "decode", "prefill"), default="all",
                         help="run one part only (a small case for ncu; no bench line)")
     parser.add_argument("--no-graphs", action="store_true", help="decode launch by launch instead of from CUDA graphs")
-    parser.add_argument("--sizes", choices=("1.5b", "7b"), default="1.5b",
-                        help="layer sizes (7b: those of Qwen2.5-7B; only with --only, give --layers to fit the time)")
+    parser.add_argument("--sizes", choices=("1.5b", "7b", "14b"), default="1.5b",
+                        help="layer sizes (7b, 14b: those of Qwen2.5-7B / 14B; only with --only, give --layers to fit the time)")
+    parser.add_argument("--quick", action="store_true", help="the headline, its points and the end-to-end number only "
+                                                             "(no other model sizes, no float32 point, no kernel table)")
+    parser.add_argument("--timeline-json", action="store_true", help="with --timeline: also one JSON line of sums per kind of kernel")
     parser.add_argument("--timeline", type=int, default=0, metavar="LAYERS",
                         help="print the device-side timeline of one decode step (the first LAYERS layers kernel by "
                              "kernel) from the tuning variant of the kernel library; no bench line")
     args = parser.parse_args()
     global USE_GRAPHS
     USE_GRAPHS = not args.no_graphs
-    if args.sizes == "7b":
-        if args.only == "all" and not args.timeline:
-            print("--sizes 7b measures one part only: add --only decode or --only prefill")
-            return 2
-        QWEN25_1P5B.update(QWEN25_7B_SIZES)
+    if args.sizes != "1.5b" and args.only == "all" and not args.timeline:
+        print(f"--sizes {args.sizes} measures one part only: add --only decode or --only prefill")
+        return 2
     if args.timeline:
         return timeline(args)
     if args.gpus != 1:
