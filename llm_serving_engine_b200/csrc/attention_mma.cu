@@ -51,6 +51,12 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
                : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// Transpose of an 8 x 8 matrix of 16-bit values held one 32-bit register a thread (row = lane / 4, columns 2 (lane % 4), +1).
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+  uint32_t d;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(d) : "r"(a));
+  return d;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -104,8 +110,12 @@ struct SubTileCopy {
 // ---------------------------------------------------------------------------------------------
 // decode: one query row per request
 // ---------------------------------------------------------------------------------------------
-constexpr int DEC_STAGES = 3;   // tiles of a warp in flight (more shared memory keeps the next kernel's blocks off the SM: measured slower)
+// Tiles of a warp in flight.  More shared memory keeps the blocks of the next kernel, which fetch their weights early,
+// off the SM (measured slower at few requests); six stages for blocks that walk a whole context (64 requests, one
+// split) were measured no faster either.
+constexpr int DEC_STAGES = 3;
 constexpr int DEC_TILE = 16;
+constexpr int DEC_HEADS = 8;     // query heads of a group that a block takes: the N side of the instruction
 constexpr int BT_STAGE = 1024;   // block-table entries a block keeps in shared memory
 
 // page and offset of key j: by shift and mask when the page size is a power of two
@@ -144,10 +154,10 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   // step's first kernel started: it is read before waiting for the kernels that produce q, k and v.
   const int t = blockIdx.x;
   const int group = n_q / n_kv;
-  const int gchunks = (group + 15) / 16;
+  const int gchunks = (group + DEC_HEADS - 1) / DEC_HEADS;
   const int kvh = blockIdx.y / gchunks;
-  const int g0 = (blockIdx.y % gchunks) * 16;
-  const int gcount = min(16, group - g0);
+  const int g0 = (blockIdx.y % gchunks) * DEC_HEADS;
+  const int gcount = min(DEC_HEADS, group - g0);
   const int split = blockIdx.z;
   const int seg = LSE_CHECKED(segment_of_token[t], -1, num_segments, -1, LSE_CHECK_SEGMENT);
   if (seg < 0) return;
@@ -223,11 +233,14 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   // instructions into the SM's instruction cache, which the other kernels of the step have emptied since
   // this one last ran (a first pass through cold code was measured at about three times a warm one).
   // `dry_run` is a kernel parameter so that the compiler keeps a single copy of the loop.
-  uint32_t qf[D / 16][4];
+  // The keys ride the M side of the instruction (16 keys a tile), the group's heads the N side (8): S^T = K Q^T and
+  // O^T = V^T P^T take half the instructions that heads on the M side (16, mostly padding) would.  A thread holds,
+  // of S^T and of every 16 x 8 block of O^T, rows lane / 4 and lane / 4 + 8 and the heads 2 (lane % 4) and + 1.
+  uint32_t qf[D / 16][2];
 #pragma unroll
-  for (int ks = 0; ks < D / 16; ++ks) qf[ks][0] = qf[ks][1] = qf[ks][2] = qf[ks][3] = 0u;
-  float acc[D / 8][4];
-  float m0, m1, l0, l1;
+  for (int ks = 0; ks < D / 16; ++ks) qf[ks][0] = qf[ks][1] = 0u;
+  float acc[D / 16][4];
+  float m0, m1, l0, l1;    // maximum and sum of this thread's two heads (the sums over this thread's keys only)
 #pragma unroll 1
   for (int pass = dry_run ? 0 : 1; pass < 2; ++pass) {
   if (pass == 1) {
@@ -246,15 +259,18 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
       *reinterpret_cast<uint4*>(q_s + tile_off<D>(r, c)) = v;
     }
     __syncthreads();
-    {
-      const int mi = lane >> 3, r = (lane & 7) + (mi & 1) * 8;
+    {   // B operand: Q as [head][d]; one load brings the fragments of two 16-wide steps of d
 #pragma unroll
-      for (int ks = 0; ks < D / 16; ++ks) ldmatrix_x4(qf[ks], smem_u32(q_s + tile_off<D>(r, ks * 2 + (mi >> 1))));
+      for (int ks = 0; ks < D / 16; ks += 2) {
+        uint32_t r[4];
+        ldmatrix_x4(r, smem_u32(q_s + tile_off<D>(lane & 7, ks * 2 + (lane >> 3))));
+        qf[ks][0] = r[0]; qf[ks][1] = r[1]; qf[ks + 1][0] = r[2]; qf[ks + 1][1] = r[3];
+      }
     }
     LSE_TL_MARK(4)
   }
 #pragma unroll
-  for (int i = 0; i < D / 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+  for (int i = 0; i < D / 16; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
   m0 = m1 = -INFINITY;
   l0 = l1 = 0.f;
   const int n_run = pass == 0 ? min(n_mine, 1) : n_mine;
@@ -265,60 +281,50 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     const uint32_t ks_ = my_u32 + (uint32_t)(it % DEC_STAGES) * 2 * TILE_BYTES;
     const uint32_t vs_ = ks_ + TILE_BYTES;
 
-    float s[2][4], s_odd[2][4];   // even and odd 16-column steps add up apart: two short chains of dependent MMAs instead of a long one
-#pragma unroll
-    for (int i = 0; i < 2; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = s_odd[i][0] = s_odd[i][1] = s_odd[i][2] = s_odd[i][3] = 0.f;
-    {
-      const int mi = lane >> 3, key = (lane & 7) + (mi >> 1) * 8;
-#pragma unroll
-      for (int ks = 0; ks < D / 16; ks += 2) {
-        uint32_t b[4], c[4];
-        ldmatrix_x4(b, ks_ + tile_off<D>(key, ks * 2 + (mi & 1)));
-        ldmatrix_x4(c, ks_ + tile_off<D>(key, (ks + 1) * 2 + (mi & 1)));
-        mma_bf16(s[0], qf[ks], b[0], b[1]);
-        mma_bf16(s[1], qf[ks], b[2], b[3]);
-        mma_bf16(s_odd[0], qf[ks + 1], c[0], c[1]);
-        mma_bf16(s_odd[1], qf[ks + 1], c[2], c[3]);
-      }
-#pragma unroll
-      for (int i = 0; i < 2; ++i) { s[i][0] += s_odd[i][0]; s[i][1] += s_odd[i][1]; s[i][2] += s_odd[i][2]; s[i][3] += s_odd[i][3]; }
-    }
-#pragma unroll
-    for (int nb = 0; nb < 2; ++nb)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int j = tile * DEC_TILE + nb * 8 + (lane & 3) * 2 + (e & 1);
-        s[nb][e] = j < ctx ? s[nb][e] * scale_log2e : -INFINITY;
-      }
-    float mx0 = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
-    float mx1 = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
-    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
-    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
-    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
-    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-    const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
-    const float c0 = fast_exp2(m0 - mn0), c1 = fast_exp2(m1 - mn1);
-    m0 = mn0; m1 = mn1;
-    float p[2][4];
-#pragma unroll
-    for (int nb = 0; nb < 2; ++nb) {
-      p[nb][0] = fast_exp2(s[nb][0] - mn0); p[nb][1] = fast_exp2(s[nb][1] - mn0);
-      p[nb][2] = fast_exp2(s[nb][2] - mn1); p[nb][3] = fast_exp2(s[nb][3] - mn1);
-    }
-    l0 = l0 * c0 + (p[0][0] + p[0][1]) + (p[1][0] + p[1][1]);
-    l1 = l1 * c1 + (p[0][2] + p[0][3]) + (p[1][2] + p[1][3]);
-#pragma unroll
-    for (int i = 0; i < D / 8; ++i) { acc[i][0] *= c0; acc[i][1] *= c0; acc[i][2] *= c1; acc[i][3] *= c1; }
-    uint32_t pa[4] = {pack_bf16(p[0][0], p[0][1]), pack_bf16(p[0][2], p[0][3]),
-                      pack_bf16(p[1][0], p[1][1]), pack_bf16(p[1][2], p[1][3])};
+    float s[4] = {0.f, 0.f, 0.f, 0.f}, s_odd[4] = {0.f, 0.f, 0.f, 0.f};   // even and odd steps of d add up apart: two short chains
     {
       const int mi = lane >> 3, key = (lane & 7) + (mi & 1) * 8;
 #pragma unroll
-      for (int nbp = 0; nbp < D / 16; ++nbp) {
-        uint32_t b[4];
-        ldmatrix_x4_trans(b, vs_ + tile_off<D>(key, nbp * 2 + (mi >> 1)));
-        mma_bf16(acc[2 * nbp], pa, b[0], b[1]);
-        mma_bf16(acc[2 * nbp + 1], pa, b[2], b[3]);
+      for (int ks = 0; ks < D / 16; ks += 2) {
+        uint32_t a[4], b[4];
+        ldmatrix_x4(a, ks_ + tile_off<D>(key, ks * 2 + (mi >> 1)));
+        ldmatrix_x4(b, ks_ + tile_off<D>(key, (ks + 1) * 2 + (mi >> 1)));
+        mma_bf16(s, a, qf[ks][0], qf[ks][1]);
+        mma_bf16(s_odd, b, qf[ks + 1][0], qf[ks + 1][1]);
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s[e] += s_odd[e];
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int j = tile * DEC_TILE + (lane >> 2) + (e >> 1) * 8;
+      s[e] = j < ctx ? s[e] * scale_log2e : -INFINITY;
+    }
+    // maxima of the two heads over the tile's 16 keys: this thread's two, then the lanes that hold the same heads
+    float mx0 = fmaxf(s[0], s[2]), mx1 = fmaxf(s[1], s[3]);
+#pragma unroll
+    for (int o = 4; o < 32; o <<= 1) {
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o));
+    }
+    const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);   // finite: the first key of a tile lies inside the context
+    const float c0 = fast_exp2(m0 - mn0), c1 = fast_exp2(m1 - mn1);
+    m0 = mn0; m1 = mn1;
+    const float p0 = fast_exp2(s[0] - mn0), p1 = fast_exp2(s[1] - mn1), p2 = fast_exp2(s[2] - mn0), p3 = fast_exp2(s[3] - mn1);
+    l0 = l0 * c0 + (p0 + p2);
+    l1 = l1 * c1 + (p1 + p3);
+#pragma unroll
+    for (int i = 0; i < D / 16; ++i) { acc[i][0] *= c0; acc[i][1] *= c1; acc[i][2] *= c0; acc[i][3] *= c1; }
+    // P^T as the B operand: the probabilities lie as [key][head] (keys 0-7, then 8-15); transposed 8 x 8 they are
+    // [head][key], a head a lane group and two neighbouring keys a register, which is what the instruction wants
+    const uint32_t pb0 = movmatrix_trans(pack_bf16(p0, p1)), pb1 = movmatrix_trans(pack_bf16(p2, p3));
+    {
+      const int mi = lane >> 3, key = (lane & 7) + (mi >> 1) * 8;
+#pragma unroll
+      for (int db = 0; db < D / 16; ++db) {
+        uint32_t a[4];   // V^T block [16 d][16 keys]: the tile's [key][d] pieces read transposed
+        ldmatrix_x4_trans(a, vs_ + tile_off<D>(key, db * 2 + (mi & 1)));
+        mma_bf16(acc[db], a, pb0, pb1);
       }
     }
     __syncwarp();
@@ -331,29 +337,31 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   }
   }   // pass
   cp_async_wait<0>();
-  // row sums over the 4 lanes that share a row
-  l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
-  l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  // sums of a head over the lanes that hold it
+#pragma unroll
+  for (int o = 4; o < 32; o <<= 1) {
+    l0 += __shfl_xor_sync(0xffffffffu, l0, o);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, o);
+  }
   __syncthreads();  // every warp is done with its pipeline buffers: reuse them for the merge
 
-  float* mg_acc = reinterpret_cast<float*>(kv_s);                // [4][16][D]
+  float* mg_acc = reinterpret_cast<float*>(kv_s);                // [4][16][D]  (heads 0 .. 7 of the 16 are used)
   float* mg_m = mg_acc + 4 * 16 * D;                             // [4][16]
   float* mg_l = mg_m + 4 * 16;                                   // [4][16]
   float* c_o = mg_l + 4 * 16;                                    // [16][D]  this block's sums, read by the cluster
   float* c_m = c_o + 16 * D;                                     // [16]
   float* c_l = c_m + 16;                                         // [16]
   {
-    const int r0 = lane >> 2, r1 = r0 + 8;
+    const int h0 = 2 * (lane & 3), h1 = h0 + 1, d0 = lane >> 2;
 #pragma unroll
-    for (int i = 0; i < D / 8; ++i) {
-      const int d = i * 8 + (lane & 3) * 2;
-      float* a0 = mg_acc + ((size_t)warp * 16 + r0) * D + d;
-      float* a1 = mg_acc + ((size_t)warp * 16 + r1) * D + d;
-      a0[0] = acc[i][0]; a0[1] = acc[i][1]; a1[0] = acc[i][2]; a1[1] = acc[i][3];
+    for (int i = 0; i < D / 16; ++i) {
+      float* a0 = mg_acc + ((size_t)warp * 16 + h0) * D + i * 16 + d0;
+      float* a1 = mg_acc + ((size_t)warp * 16 + h1) * D + i * 16 + d0;
+      a0[0] = acc[i][0]; a1[0] = acc[i][1]; a0[8] = acc[i][2]; a1[8] = acc[i][3];
     }
-    if ((lane & 3) == 0) {
-      mg_m[warp * 16 + r0] = m0; mg_m[warp * 16 + r1] = m1;
-      mg_l[warp * 16 + r0] = l0; mg_l[warp * 16 + r1] = l1;
+    if (lane < 4) {
+      mg_m[warp * 16 + h0] = m0; mg_m[warp * 16 + h1] = m1;
+      mg_l[warp * 16 + h0] = l0; mg_l[warp * 16 + h1] = l1;
     }
   }
   __syncthreads();
@@ -394,16 +402,26 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     const int items = gcount * D;
     const int per = (items + num_splits - 1) / num_splits;
     const int hi = min(items, (rank + 1) * per);
+    const bool warp_shares_head = per % 32 == 0 && D % 32 == 0 && items % 32 == 0;   // whole warps, inside one head
     for (int e = rank * per + tid; e < hi; e += 128) {
       const int g = e / D, d = e % D;
       float mr[8], lr[8], orr[8];
 #pragma unroll
-      for (int r = 0; r < 8; ++r) {
-        if (r < num_splits) {
-          mr[r] = cluster.map_shared_rank(c_m, r)[g];
-          lr[r] = cluster.map_shared_rank(c_l, r)[g];
-          orr[r] = cluster.map_shared_rank(c_o, r)[g * D + d];
-        } else { mr[r] = -INFINITY; lr[r] = 0.f; orr[r] = 0.f; }
+      for (int r = 0; r < 8; ++r) orr[r] = r < num_splits ? cluster.map_shared_rank(c_o, r)[g * D + d] : 0.f;
+      if (warp_shares_head) {
+        // the 32 outputs of a warp belong to one head: lane r fetches the maximum and the sum of split r, and the
+        // warp passes them round (two remote loads a thread instead of sixteen)
+        const int r = lane & 7;
+        const float mv = r < num_splits ? cluster.map_shared_rank(c_m, r)[g] : -INFINITY;
+        const float lv = r < num_splits ? cluster.map_shared_rank(c_l, r)[g] : 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) { mr[k] = __shfl_sync(0xffffffffu, mv, k); lr[k] = __shfl_sync(0xffffffffu, lv, k); }
+      } else {
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          mr[r] = r < num_splits ? cluster.map_shared_rank(c_m, r)[g] : -INFINITY;
+          lr[r] = r < num_splits ? cluster.map_shared_rank(c_l, r)[g] : 0.f;
+        }
       }
       float M = mr[0];
 #pragma unroll
@@ -706,7 +724,7 @@ int launch_decode_as(const void* q, const void* kc, const void* vc, void* out, f
     configured = true;
   }
   const int group = n_q / n_kv;
-  dim3 grid(tokens, n_kv * ((group + 15) / 16), num_splits);
+  dim3 grid(tokens, n_kv * ((group + DEC_HEADS - 1) / DEC_HEADS), num_splits);
   cudaError_t err = lse_launch_cluster(attn_decode_kernel<D, CLUSTER>, grid, 128, smem, stream,
       CLUSTER ? (unsigned)num_splits : 1u,
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, (__nv_bfloat16*)out, part_o,
@@ -765,7 +783,7 @@ extern "C" long long lse_attention_decode_scratch_floats(int tokens, int n_q, in
 
 // `cluster` != 0 and 2 <= num_splits <= 8: the splits form a thread-block cluster and need neither
 // `scratch` nor `arrivals`.  Else `scratch` holds the partial sums and `arrivals` is tokens * n_kv *
-// ceil(group / 16) ints that are zero before the first launch (the kernel leaves them zero).
+// ceil(group / 8) ints that are zero before the first launch (the kernel leaves them zero).
 extern "C" int lse_paged_attention_decode(const void* q, const void* k_cache, const void* v_cache, void* out,
                                           float* scratch, int* arrivals, int cluster, const int* block_tables,
                                           int bt_stride,

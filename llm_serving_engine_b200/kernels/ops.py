@@ -192,8 +192,8 @@ _DECODE_MAX_SPLITS = int(__import__("os").environ.get("LSE_DECODE_MAX_SPLITS", "
 def decode_splits(tokens: int, n_q: int, n_kv: int, max_context: int | None) -> int:
     """How many splits of the keys a decode launch uses: enough blocks to fill the GPU and a little
     more (a block that ends early makes room for the next kernel's blocks), at least one 16-key
-    tile per warp and split."""
-    base = tokens * n_kv * ((n_q // n_kv + 15) // 16)
+    tile per warp and split.  (A block takes up to 8 query heads of a group.)"""
+    base = tokens * n_kv * ((n_q // n_kv + 7) // 8)
     # about 1.4 blocks per SM (measured best from 12 to 64 rows on 148 SMs: 192 blocks beat 128 and 256); at most
     # 8 splits: one cluster adds them up
     splits = max(1, min(_DECODE_MAX_SPLITS, ((sm_count() * 7 + 4) // 5) // base))
@@ -232,7 +232,7 @@ def paged_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
     by_cluster = cluster and 1 < num_splits <= 8      # the splits add up through distributed shared memory
     if num_splits > 1 and not by_cluster:
         scratch = torch.empty(tokens * n_q * num_splits * (head_dim + 2), dtype=torch.float32, device=q.device)
-        arrivals = _arrival_counters(q.device, tokens * n_kv * ((n_q // n_kv + 15) // 16))
+        arrivals = _arrival_counters(q.device, tokens * n_kv * ((n_q // n_kv + 7) // 8))
     lib = library.load()
     check(lib.lse_paged_attention_decode(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
                                          _ptr(scratch), _ptr(arrivals), int(by_cluster), block_tables.data_ptr(),
