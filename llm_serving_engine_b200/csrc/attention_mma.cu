@@ -348,9 +348,6 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   float* mg_acc = reinterpret_cast<float*>(kv_s);                // [4][16][D]  (heads 0 .. 7 of the 16 are used)
   float* mg_m = mg_acc + 4 * 16 * D;                             // [4][16]
   float* mg_l = mg_m + 4 * 16;                                   // [4][16]
-  float* c_o = mg_l + 4 * 16;                                    // [16][D]  this block's sums, read by the cluster
-  float* c_m = c_o + 16 * D;                                     // [16]
-  float* c_l = c_m + 16;                                         // [16]
   {
     const int h0 = 2 * (lane & 3), h1 = h0 + 1, d0 = lane >> 2;
 #pragma unroll
@@ -365,6 +362,10 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     }
   }
   __syncthreads();
+  // Split-KV through a cluster: block r of the cluster finishes the outputs r * push_per .. of the group's heads x D.
+  __shared__ float recv_o[DEC_HEADS * 128 + 8], recv_m[8 * DEC_HEADS], recv_l[8 * DEC_HEADS];
+  cg::cluster_group cluster = cg::this_cluster();
+  const int push_per = (gcount * D + num_splits - 1) / num_splits;
   for (int e = tid; e < gcount * D; e += 128) {
     const int g = e / D, d = e % D;
     float M = -INFINITY;
@@ -383,8 +384,14 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     if (num_splits == 1) {
       out[((size_t)t * n_q + head) * D + d] = __float2bfloat16_rn(O / L);
     } else if (CLUSTER) {
-      c_o[g * D + d] = O;
-      if (d == 0) { c_m[g] = M; c_l[g] = L; }
+      // pushed to the block of the cluster that finishes this output (its receive buffers are its own: nobody else
+      // writes or reads them before the barrier); maximum and sum of a head go to every block
+      const int owner = e / push_per;
+      cluster.map_shared_rank(recv_o, owner)[split * push_per + e % push_per] = O;
+      if (d < num_splits) {
+        cluster.map_shared_rank(recv_m, d)[split * DEC_HEADS + g] = M;
+        cluster.map_shared_rank(recv_l, d)[split * DEC_HEADS + g] = L;
+      }
     } else {
       const size_t pidx = ((size_t)t * n_q + head) * num_splits + split;
       part_o[pidx * D + d] = O;
@@ -394,49 +401,32 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   LSE_TL_MARK(3)
   if (num_splits == 1) return;
   if (CLUSTER) {
-    // every split of this (row, kv head) has its sums in its own shared memory; block r of the cluster
-    // reads all of them (in split order) for its share of the outputs
-    cg::cluster_group cluster = cg::this_cluster();
+    // every split has pushed its sums; after the barrier (release / acquire: the remote stores are visible) a block
+    // adds up, in split order, what it received, from its own shared memory, and is free to leave
     cluster.sync();
+    LSE_TL_MARK(6)
     const int rank = (int)cluster.block_rank();
     const int items = gcount * D;
-    const int per = (items + num_splits - 1) / num_splits;
-    const int hi = min(items, (rank + 1) * per);
-    const bool warp_shares_head = per % 32 == 0 && D % 32 == 0 && items % 32 == 0;   // whole warps, inside one head
-    for (int e = rank * per + tid; e < hi; e += 128) {
+    const int hi = min(items, (rank + 1) * push_per);
+    for (int e = rank * push_per + tid; e < hi; e += 128) {
       const int g = e / D, d = e % D;
-      float mr[8], lr[8], orr[8];
+      float M = -INFINITY;
 #pragma unroll
-      for (int r = 0; r < 8; ++r) orr[r] = r < num_splits ? cluster.map_shared_rank(c_o, r)[g * D + d] : 0.f;
-      if (warp_shares_head) {
-        // the 32 outputs of a warp belong to one head: lane r fetches the maximum and the sum of split r, and the
-        // warp passes them round (two remote loads a thread instead of sixteen)
-        const int r = lane & 7;
-        const float mv = r < num_splits ? cluster.map_shared_rank(c_m, r)[g] : -INFINITY;
-        const float lv = r < num_splits ? cluster.map_shared_rank(c_l, r)[g] : 0.f;
-#pragma unroll
-        for (int k = 0; k < 8; ++k) { mr[k] = __shfl_sync(0xffffffffu, mv, k); lr[k] = __shfl_sync(0xffffffffu, lv, k); }
-      } else {
-#pragma unroll
-        for (int r = 0; r < 8; ++r) {
-          mr[r] = r < num_splits ? cluster.map_shared_rank(c_m, r)[g] : -INFINITY;
-          lr[r] = r < num_splits ? cluster.map_shared_rank(c_l, r)[g] : 0.f;
-        }
-      }
-      float M = mr[0];
-#pragma unroll
-      for (int r = 1; r < 8; ++r) M = fmaxf(M, mr[r]);
+      for (int r = 0; r < 8; ++r)
+        if (r < num_splits) M = fmaxf(M, recv_m[r * DEC_HEADS + g]);
       float L = 0.f, O = 0.f;
 #pragma unroll
       for (int r = 0; r < 8; ++r) {
-        const float w = mr[r] == -INFINITY ? 0.f : exp2f(mr[r] - M);
-        L += lr[r] * w;
-        O += orr[r] * w;
+        if (r < num_splits) {
+          const float mr = recv_m[r * DEC_HEADS + g];
+          const float w = mr == -INFINITY ? 0.f : exp2f(mr - M);
+          L += recv_l[r * DEC_HEADS + g] * w;
+          O += recv_o[r * push_per + (e - rank * push_per)] * w;
+        }
       }
       out[((size_t)t * n_q + first_head + g) * D + d] = __float2bfloat16_rn(O / L);
     }
     LSE_TL_MARK_ANY(5, tid == 0 && blockIdx.x == 0 && blockIdx.y == 0 && rank == 0)
-    cluster.sync();   // nobody leaves while its shared memory may still be read
     return;
   }
 
