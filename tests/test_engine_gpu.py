@@ -274,3 +274,26 @@ def test_dependent_launch_off_gives_the_same_logits(tmp_path):
         assert run.returncode == 0, run.stderr
         outs[flag] = helpers.collect(steps, out_dir)["a"]
     assert torch.equal(outs["0"], outs["1"])
+
+
+def test_a_wait_that_gave_up_fails_the_requests_and_leaves_the_engine_usable():
+    """The few-rows product is made to give up a wait (a test hook: a tile that never arrives and a small limit; no
+    fault, the kernel returns).  Its status word reaches the host with the step's tokens: the requests fail with a
+    KernelError instead of getting tokens sampled from memory that nobody wrote, every page goes back, the word is
+    cleared, and the same engine generates the right tokens afterwards."""
+    from llm_serving_engine_b200 import GenerationConfig
+    from llm_serving_engine_b200.kernels import ops
+    from llm_serving_engine_b200.kernels.library import KernelError
+
+    engine = engine_for("D", dtype="bfloat16")
+    prompts = prompts_for("D", (9, 21), seed=4)
+    good = engine.generate_many(prompts, GenerationConfig(max_new_tokens=4))
+    ops.gemm_bf16_skinny_test_hooks(spin_limit=2000, withhold=True)
+    try:
+        with pytest.raises(KernelError, match="bounded wait"):
+            engine.generate_many(prompts, GenerationConfig(max_new_tokens=4))
+    finally:
+        ops.gemm_bf16_skinny_test_hooks()
+    assert engine.scheduler.idle and not engine.cache.requests and engine.cache.groups[0].pool.used_pages == 0
+    assert ops.gemm_bf16_skinny_status() == 0
+    assert engine.generate_many(prompts, GenerationConfig(max_new_tokens=4)) == good
