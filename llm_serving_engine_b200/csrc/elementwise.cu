@@ -180,21 +180,17 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __res
 
 // Many rows (portions of prompts), one set of sums, bfloat16 out: a warp owns a row and keeps it in
 // registers (C float4 chunks per lane), so that no block-wide barrier stands between the loads and
-// the stores and eight rows are in flight per block.  hidden % 4 == 0, hidden <= 128 * C.
+// the stores.  The norm's weights are read when they are used (they stay in the L1), which keeps the
+// kernel at two blocks of eight rows an SM: 2,048 rows are all in flight at once on 148 SMs.
+// hidden % 4 == 0, hidden <= 128 * C.
 template <typename TD, int C>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, C <= 12 ? 2 : 1)
 add_rmsnorm_rows_kernel(float* __restrict__ residual, const TD* __restrict__ delta, const float* __restrict__ weight,
                         __nv_bfloat16* __restrict__ out, int n_rows, int hidden, float eps) {
   pdl_launch_dependents();
   const int lane = threadIdx.x & 31;
   const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int chunks = hidden >> 2;
-  float w[C][4];
-#pragma unroll
-  for (int c = 0; c < C; ++c) {
-    const int i = c * 32 + lane;
-    if (i < chunks) load4<float>(weight + 4 * i, w[c]);
-  }
   pdl_wait();
   if (r >= n_rows) return;
   float* res = residual + (size_t)r * hidden;
@@ -225,9 +221,10 @@ add_rmsnorm_rows_kernel(float* __restrict__ residual, const TD* __restrict__ del
   for (int c = 0; c < C; ++c) {
     const int i = c * 32 + lane;
     if (i < chunks) {
-      float y[4];
-      y[0] = (x[c][0] * inv) * w[c][0]; y[1] = (x[c][1] * inv) * w[c][1];
-      y[2] = (x[c][2] * inv) * w[c][2]; y[3] = (x[c][3] * inv) * w[c][3];
+      float w[4], y[4];
+      load4<float>(weight + 4 * i, w);
+      y[0] = (x[c][0] * inv) * w[0]; y[1] = (x[c][1] * inv) * w[1];
+      y[2] = (x[c][2] * inv) * w[2]; y[3] = (x[c][3] * inv) * w[3];
       store4<__nv_bfloat16>(dst + 4 * i, y);
     }
   }
@@ -448,17 +445,16 @@ __global__ void rope_kv_write_wide_kernel(const TI* __restrict__ qkv, const floa
   const bool live = t < tokens && threadIdx.x < (blockDim.x / per_token) * per_token;
   const int e0 = pairing == 0 ? 16 * c : 8 * c;
   const int e1 = pairing == 0 ? 16 * c + 8 : (head_dim >> 1) + 8 * c;
-  // position, cache slot and frequencies are the step's own data: fetched, and the sines and
-  // cosines worked out, before waiting for the kernel that makes the projections
-  float sn[8], cs[8];
+  // position, cache slot and frequencies are the step's own data: fetched before waiting for the
+  // kernel that makes the projections; the sines and cosines are worked out while the loads of the
+  // projections are in flight
+  float freq[8];
   int slot = -1;
+  float pos = 0.f;
   if (live) {
-    float freq[8];
     load8<float>(inv_freq + 8 * c, freq);
     slot = LSE_CHECKED(slot_mapping[t], -1, num_slots, -1, LSE_CHECK_CACHE_SLOT);
-    const float pos = (float)positions[t];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) sincosf(__fmul_rn(pos, freq[j]), &sn[j], &cs[j]);
+    pos = (float)positions[t];
   }
   pdl_wait();
   if (!live) return;
@@ -472,6 +468,9 @@ __global__ void rope_kv_write_wide_kernel(const TI* __restrict__ qkv, const floa
       load8<TI>(row + (size_t)head * head_dim + e1, b[k]);
     }
   }
+  float sn[8], cs[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) sincosf(__fmul_rn(pos, freq[j]), &sn[j], &cs[j]);
 #pragma unroll
   for (int k = 0; k < ROPE_WIDE_HEADS; ++k) {
     const int head = group + k * head_groups;
