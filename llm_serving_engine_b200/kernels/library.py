@@ -32,7 +32,8 @@ _SIGNATURES = {
                         c_longlong, c_longlong, c_void_p],
     "lse_paged_attention_generic": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
                                     c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
-                                    c_int, c_int, c_int, c_void_p],
+                                    c_int, c_int, c_int, c_void_p, c_int, c_void_p],
+    "lse_attention_generic_chunk": [],
     "lse_paged_attention_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
                                    c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int,
                                    c_void_p],

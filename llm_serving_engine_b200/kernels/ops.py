@@ -147,14 +147,20 @@ def rope_kv_write(qkv: torch.Tensor, bias: torch.Tensor | None, positions: torch
           "rope_kv_write")
 
 
+GENERIC_SPLIT_MAX_ROWS = 64   # up to this many rows every chunk of keys of a row gets a block of its own
+
+
 def paged_attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                             out: torch.Tensor, block_tables: torch.Tensor,
                             segment_of_token: torch.Tensor, positions: torch.Tensor, scale: float,
-                            window: int = 0) -> torch.Tensor:
+                            window: int = 0, split: bool | None = None) -> torch.Tensor:
     """Attention of every token of the step over its request's cached keys.
 
     q, out [T, n_q, D]; k_cache, v_cache [pages, n_kv, page_size, D];
     block_tables int32 [S, max_pages]; segment_of_token, positions int32 [T].
+    A row's keys are summed in chunks of fixed size; ``split`` gives every chunk a block of its own
+    (default: with few rows, where one block per row would leave the GPU idle).  The result does not
+    depend on it, bit for bit.
     """
     _need_cuda(q, k_cache, v_cache, out, block_tables, segment_of_token, positions)
     tokens, n_q, head_dim = q.shape
@@ -169,11 +175,17 @@ def paged_attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
     assert block_tables.dtype == torch.int32 and block_tables.dim() == 2 and block_tables.stride(1) == 1
     assert segment_of_token.dtype == torch.int32 and positions.dtype == torch.int32
     lib = library.load()
+    partials, max_chunks = None, 0
+    if split if split is not None else tokens <= GENERIC_SPLIT_MAX_ROWS:
+        chunk = int(lib.lse_attention_generic_chunk())
+        max_chunks = max(1, -(-(block_tables.stride(0) * page_size) // chunk))
+        partials = torch.empty(tokens * n_q * max_chunks * (head_dim + 2), dtype=torch.float32, device=q.device)
     check(lib.lse_paged_attention_generic(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
                                           out.data_ptr(), dtype_code(q.dtype), block_tables.data_ptr(),
                                           block_tables.stride(0), segment_of_token.data_ptr(),
                                           positions.data_ptr(), tokens, n_q, n_kv, head_dim, page_size,
                                           float(scale), int(window), k_cache.shape[0], block_tables.shape[0],
+                                          partials.data_ptr() if partials is not None else None, max_chunks,
                                           _stream()), "paged_attention_generic")
     return out
 

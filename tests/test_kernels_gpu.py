@@ -292,6 +292,39 @@ def test_one_far_key_among_hundreds_is_found(dtype, needle):
         assert float((out[0, g * 3].double() - v[needle, g].double()).abs().max()) < 0.05
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window", [0, 300])
+def test_general_attention_gives_the_same_bits_with_a_block_per_chunk_of_keys(dtype, window):
+    """The general kernel sums a row's keys chunk by chunk (256 keys): one block walks all chunks of its row, or every
+    chunk has a block of its own and a second kernel merges them.  Rows at the edges of chunks (255, 256, 257 keys, ...),
+    a far key that carries a row's weight: both ways against dense attention, and bit for bit against each other."""
+    rng = random.Random(21)
+    torch.manual_seed(21)
+    n_q, n_kv, head_dim, page = 6, 2, 48, 8
+    contexts = [1, 31, 255, 256, 257, 511, 512, 513, 700, 1025]
+    k_cache, v_cache, tables, dense = paged_setup(rng, contexts, n_kv, head_dim, page, dtype)
+    q = torch.randn(len(contexts), n_q, head_dim, device=DEV).to(dtype)
+    needle = 3 if window == 0 else 1025 - 290     # a far key of the longest request: first chunk, or the window's first chunk
+    k, v = dense[-1]
+    k[needle, 1] = (q[-1, 5].float() * 6).to(dtype)
+    k_cache[int(tables[-1, needle // page]), 1, needle % page] = k[needle, 1]
+    poison_unowned(k_cache, v_cache, tables, contexts, page)
+    segs = torch.arange(len(contexts), dtype=torch.int32, device=DEV)
+    positions = torch.tensor([c - 1 for c in contexts], dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(head_dim)
+    outs = []
+    for split in (False, True):
+        out = torch.full_like(q, 9.0)
+        ops().paged_attention_generic(q, k_cache, v_cache, out, tables, segs, positions, scale, window=window, split=split)
+        outs.append(out)
+    assert torch.equal(outs[0], outs[1])
+    bound = 1e-5 if dtype == torch.float32 else 2.0 ** -7
+    for r, ctx in enumerate(contexts):
+        want = dense_attention(q[r], dense[r][0][:ctx], dense[r][1][:ctx], scale, window=window)
+        assert float((outs[0][r].double() - want).abs().max()) < bound * max(1.0, float(want.abs().max())), (r, ctx)
+    assert float((outs[0][-1, 5].double() - v[needle, 1].double()).abs().max()) < 0.05
+
+
 @pytest.mark.parametrize("window", [1, 5, 16, 33, 100])
 def test_window_edge(window):
     rng = random.Random(window)
