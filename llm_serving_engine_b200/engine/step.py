@@ -407,7 +407,7 @@ class StepRunner:
         self._copied.record()
         self._copy_pending = True
         if slot.graph is None:
-            self._capture(slot, step)
+            self._capture(slot, step, first_use=False)   # the class ran launch by launch at its first sighting
         slot.graph.replay()
         self.graph_replays += 1
         self.portion_graph_replays += 1
@@ -547,13 +547,15 @@ class StepRunner:
             width *= 2
         return width
 
-    def _capture(self, slot: _Graph, step: StepContext) -> None:
-        """Run the step once launch by launch (first-use set-up happens here), then capture the same
-        launches into a graph.  The captured step is this very step, so replaying it is harmless."""
+    def _capture(self, slot: _Graph, step: StepContext, first_use: bool = True) -> None:
+        """Run the step once launch by launch (first-use set-up happens here; left out when a step of the
+        same class has run launch by launch before), then capture the same launches into a graph.  The
+        captured step is this very step, so replaying it is harmless."""
         from ..kernels import library
 
         step, caches = self._views(step, slot.device, slot.layout)
-        self.model.forward(step, caches)
+        if first_use:
+            self.model.forward(step, caches)
         current = torch.cuda.current_stream()
         current.synchronize()
         if self._capture_stream is None:
@@ -566,7 +568,6 @@ class StepRunner:
         # engines that are no longer used (their graphs, their events), and such a call from this thread
         # would invalidate the capture.
         collecting = gc.isenabled()
-        gc.collect()
         gc.disable()
         try:
             with torch.cuda.stream(self._capture_stream):
@@ -584,7 +585,11 @@ class StepRunner:
 
     def warmup(self, batch_sizes=None) -> None:
         """Capture the decode graphs of the given batch sizes (default: every bucket up to
-        ``max_segments``) with temporary one-token requests, then give their pages back."""
+        ``max_segments``) with temporary one-token requests, then give their pages back.  Before that, one
+        step with a prompt portion as long as a step may be, beside a single token of another request: the
+        library's products and the prompt kernels load and configure themselves at their first use, which
+        would otherwise cost the first request a tenth of a second."""
+        self._warm_prompt_path()
         if not self.use_graphs:
             return
         sizes = batch_sizes or [b for b in self.GRAPH_BUCKETS if b <= self.max_segments]
@@ -601,6 +606,23 @@ class StepRunner:
                 for name in names:
                     if name in self.cache.requests:
                         self.cache.free(name)
+
+    def _warm_prompt_path(self) -> None:
+        cache = self.cache
+        room = min(group.pool.free_pages for group in cache.groups) * cache.page_size if cache.groups else self.max_tokens
+        tokens = min(self.max_tokens - 1, self.model.spec.max_position_embeddings - 1, room - cache.page_size)
+        if tokens < 2 or self.max_segments < 2:
+            return
+        names = ["__warmup_portion", "__warmup_token"]
+        try:
+            for name in names:
+                cache.create(name)
+            self.run([StepEntry(names[0], [0] * tokens, [tokens - 1]), StepEntry(names[1], [0], [0])])
+            torch.cuda.current_stream().synchronize()
+        finally:
+            for name in names:
+                if name in cache.requests:
+                    cache.free(name)
 
     def finish(self, entries: list[StepEntry]) -> None:
         """After the step: give back pages that a window has passed."""
