@@ -350,8 +350,9 @@ def kernel_table(batch: int, layers: int) -> dict | None:
 
 
 def other_points(args, peak: dict) -> tuple[dict, dict]:
-    """The workloads beyond the headline: the float32 path, the Qwen2.5-7B sizes under mixed traffic, the Qwen2.5-14B
-    sizes at context 8,192 (fewer layers than the model has: both numbers are in the point's name or note)."""
+    """The workloads beyond the headline: the float32 path, contexts of 30,000 keys, the Qwen2.5-7B sizes under mixed
+    traffic, the Qwen2.5-14B sizes at context 8,192 (fewer layers than the model has: both numbers are in the point's
+    name or note)."""
     import torch
 
     points, notes = {}, {}
@@ -394,7 +395,17 @@ def other_points(args, peak: dict) -> tuple[dict, dict]:
         points[name] = round(8192 / (sum(times) / 1e3), 1)
         notes[name] = "ms of the four mixed steps: " + ", ".join(f"{value:.2f}" for value in times)
 
+    def long_contexts():
+        model, _ = build_model(FULL_LAYERS, {"max_position_embeddings": 32768})
+        for batch in (1, 8):
+            ms, kv_bytes, _, _ = time_decode(model, batch, steps, 3, prompt=30000)
+            name = f"ctx30000_decode_b{batch}"
+            points[name] = round(batch / (ms / 1e3), 1)
+            notes[name] = (f"the headline's model, {ms:.3f} ms a step, "
+                           f"{(model.weight_bytes_per_step() + kv_bytes) / (ms / 1e3) / 1e9 / peak['hbm_gbs']:.3f} of the copy bandwidth")
+
     attempt("fp32_decode_b8", float32)
+    attempt("ctx30000_decode", long_contexts)
     attempt("7b_mixed32_output_tok_s", sizes_7b)
     attempt("14b", sizes_14b)
     return points, notes

@@ -68,10 +68,15 @@ class StepContext:
         self.max_segment_tokens = 0
         self.max_context = 0                         # None: not known on the host (a replayed graph)
         self.decode_only = False                     # every segment brings exactly one token
+        self.long_context = False                    # some request holds more than LONG_CONTEXT keys (known on the host always:
+                                                     # graphs of decode steps are captured for either case)
 
 
 def _round4(n: int) -> int:
     return (n + 3) & ~3
+
+
+LONG_CONTEXT = 8192   # keys of a request beyond which a decode step counts as one over long contexts
 
 
 class _Layout:
@@ -144,7 +149,7 @@ class StepRunner:
         self._copied = torch.cuda.Event() if pinned else None
         self._copy_pending = False
         self.use_graphs = bool(use_graphs) and pinned and getattr(model, "graph_safe", False)
-        self._graphs: dict[tuple[int, int], _Graph] = {}
+        self._graphs: dict[tuple[int, int, bool], _Graph] = {}   # (batch bucket, block-table width, long contexts)
         self._graph_pool = None          # one memory pool for all graphs: only one of them runs at a time
         self._capture_stream = None
         self._arange = np.arange(max(self.GRAPH_BUCKETS), dtype=np.int32)
@@ -248,6 +253,7 @@ class StepRunner:
             step.max_context = max(step.max_context, first + count)
             row += count
         host[lay.start[0] + len(entries): lay.start[1]] = row      # padding segments are empty
+        step.long_context = step.max_context > LONG_CONTEXT
         if wanted_all_rows:
             host[lay.want[0]:lay.want[1]] = np.arange(lay.wanted, dtype=np.int32)
         step.decode_only = step.max_segment_tokens == 1
@@ -291,6 +297,7 @@ class StepRunner:
             host[lay.maps[g][0]:lay.maps[g][1]] = group_slots[g] + [-1] * pad
         step.max_segment_tokens = 1
         step.max_context = max(firsts) + 1
+        step.long_context = step.max_context > LONG_CONTEXT
         step.decode_only = True
         return step
 
@@ -342,7 +349,8 @@ class StepRunner:
         if bucket is None:
             step, caches = self.prepare(entries, validated=True)
             return self.model.forward(step, caches)
-        key = (bucket, self._graph_width(self._pages_after(entries)))
+        pages = self._pages_after(entries)
+        key = (bucket, self._graph_width(pages), pages * self.cache.page_size > LONG_CONTEXT)
         slot = self._graphs.get(key)
         if slot is None:
             slot = _Graph(_Layout(bucket, bucket, bucket, key[1], self._groups), self.device, True)
@@ -352,6 +360,7 @@ class StepRunner:
             self._copy_pending = False
         step = self._pack_decode(entries, slot.host_np, slot.layout)
         step.max_context = None
+        step.long_context = key[2]   # what the graph was, or is now, captured for
         slot.device.copy_(slot.host, non_blocking=True)
         self.last_h2d_bytes = slot.layout.size * 4
         self._copied.record()
@@ -440,7 +449,7 @@ class StepRunner:
                 return None          # the token opens a page and none is free: the ordinary path decides
             firsts.append(first)
         pages = max(1, max(first // page_size + 1 for first in firsts))
-        key = (bucket, self._graph_width(pages))
+        key = (bucket, self._graph_width(pages), pages * page_size > LONG_CONTEXT)
         slot = self._graphs.get(key)
         if slot is None or slot.graph is None:
             return None

@@ -201,14 +201,22 @@ def attention_mma_supported(head_dim: int, n_q: int, n_kv: int, dtype: torch.dty
 _DECODE_MAX_SPLITS = int(__import__("os").environ.get("LSE_DECODE_MAX_SPLITS", "8"))
 
 
-def decode_splits(tokens: int, n_q: int, n_kv: int, max_context: int | None) -> int:
+_DECODE_MAX_SPLITS_LONG = 32    # the kernel's own limit
+
+
+def decode_splits(tokens: int, n_q: int, n_kv: int, max_context: int | None, long_context: bool = False) -> int:
     """How many splits of the keys a decode launch uses: enough blocks to fill the GPU and a little
     more (a block that ends early makes room for the next kernel's blocks), at least one 16-key
     tile per warp and split.  (A block takes up to 8 query heads of a group.)"""
     base = tokens * n_kv * ((n_q // n_kv + 7) // 8)
     # about 1.4 blocks per SM (measured best from 12 to 64 rows on 148 SMs: 192 blocks beat 128 and 256); at most
-    # 8 splits: one cluster adds them up
-    splits = max(1, min(_DECODE_MAX_SPLITS, ((sm_count() * 7 + 4) // 5) // base))
+    # 8 splits: one cluster adds them up.  Over long contexts (more than 8,192 keys) with so few rows that 8 splits
+    # leave SMs without a block, more splits pay although the last-arriving block then adds them up through global
+    # memory (one request of 30,000 keys: 1.60 against 2.05 ms a step; four: 1.87 against 2.13; at 8,192 keys: no gain).
+    cap = _DECODE_MAX_SPLITS
+    if long_context and 10 * base * cap < 7 * sm_count():
+        cap = max(cap, _DECODE_MAX_SPLITS_LONG)
+    splits = max(1, min(cap, ((sm_count() * 7 + 4) // 5) // base))
     if max_context is not None:
         splits = min(splits, max(1, -(-max_context // 64)))
     return splits

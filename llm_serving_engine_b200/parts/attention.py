@@ -104,7 +104,7 @@ class GroupedQueryAttention(Mixer):
         attended = torch.empty_like(q)
         if ops.attention_mma_supported(self.head_dim, self.n_q, self.n_kv, x.dtype, self.window):
             if step.decode_only:
-                splits = ops.decode_splits(tokens, self.n_q, self.n_kv, step.max_context)
+                splits = ops.decode_splits(tokens, self.n_q, self.n_kv, step.max_context, getattr(step, "long_context", False))
                 ops.paged_attention_decode(q, cache.keys, cache.values, attended, cache.block_tables,
                                            step.segment_of_token, step.positions, self.scale, splits)
             elif self.prompt_kernel([segment.count for segment in step.segments], cache.keys.shape[2]) == "tcgen05":

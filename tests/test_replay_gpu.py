@@ -159,3 +159,43 @@ def test_long_context_in_chunks_then_a_portion_then_decoding(dtype):
     limit = helpers.tolerance(dtype, reference)
     assert float(error.max()) <= limit, f"max error {float(error.max()):.3e} > {limit:.3e} at position {wanted[int(error.argmax())]}"
     assert helpers.rms_ratio(got, reference) <= helpers.RMS_RATIO[dtype]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decoding_across_the_line_where_a_context_counts_as_long(dtype):
+    """Decode steps over more than 8,192 keys are replayed from graphs of their own, in which a single request's keys
+    are cut into more splits than one thread-block cluster adds up (the last-arriving block adds them).  One request
+    decodes from 8,170 to 8,230 keys, a second one joins for a few steps at a short context."""
+    from tiny_configs import EXTRA
+
+    config, page, _ = EXTRA["L2"]
+    rng = random.Random(43)
+    long_tokens = helpers.random_tokens(rng, config["vocab_size"], 8230)
+    short_tokens = helpers.random_tokens(rng, config["vocab_size"], 40)
+    steps, wanted = [], {"long": [], "short": []}
+    cuts = [(0, 2048), (2048, 4096), (4096, 6144), (6144, 8170)]
+    for number, (lo, hi) in enumerate(cuts):
+        steps.append({"step": number, "entries": [{"id": "long", "tokens": long_tokens[lo:hi], "want": [hi - lo - 1]}], "end": []})
+        wanted["long"].append(hi - 1)
+    for position in range(8170, 8230):
+        entries = [{"id": "long", "tokens": [long_tokens[position]], "want": [0]}]
+        wanted["long"].append(position)
+        ends = ["long"] if position == 8229 else []
+        if 8185 <= position < 8205:     # beside it, for twenty steps, a request at a short context
+            index = position - 8185
+            portion = short_tokens[:21] if index == 0 else [short_tokens[20 + index]]
+            entries.append({"id": "short", "tokens": portion, "want": [len(portion) - 1]})
+            wanted["short"].append(20 + index)
+            if position == 8204:
+                ends.append("short")
+        steps.append({"step": len(steps), "entries": entries, "end": ends})
+    got = helpers.run_trace("L2", dtype, steps, 8448, page)
+    for name, tokens in (("long", long_tokens), ("short", short_tokens[:40])):
+        reference = helpers.plain_logits("L2", dtype, tokens)[wanted[name]]
+        rows = got[name]
+        assert rows.shape[0] == len(wanted[name])
+        error = (rows - reference).abs().max(dim=1).values
+        limit = helpers.tolerance(dtype, reference)
+        assert float(error.max()) <= limit, f"{name}: max error {float(error.max()):.3e} > {limit:.3e} at position {wanted[name][int(error.argmax())]}"
+        assert helpers.rms_ratio(rows, reference) <= helpers.RMS_RATIO[dtype], name
+

@@ -60,4 +60,4 @@ TINY_LONG = {
     "num_attention_heads": 5, "num_key_value_heads": 1, "head_dim": 128, "max_position_embeddings": 8192,
     "rope_theta": 1000000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": False,
 }
-EXTRA = {"L": (TINY_LONG, 16, 6)}
+EXTRA = {"L": (TINY_LONG, 16, 6), "L2": (dict(TINY_LONG, max_position_embeddings=8448), 16, 6)}
