@@ -141,7 +141,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
                    const int* __restrict__ block_tables, int bt_stride,
                    const int* __restrict__ segment_of_token, const int* __restrict__ positions,
                    int n_q, int n_kv, int page_size, float scale_log2e, int num_splits, int dry_run, int num_pages,
-                   int num_segments) {
+                   int num_segments, const int* __restrict__ segment_start) {
   constexpr int CH = D / 8;                 // 16-byte chunks per row
   constexpr int TILE_BYTES = DEC_TILE * D * 2;
   extern __shared__ __align__(128) unsigned char smem[];
@@ -152,7 +152,14 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   pdl_launch_dependents();
   // The step's metadata (segments, positions, block tables) was copied to the device before the
   // step's first kernel started: it is read before waiting for the kernels that produce q, k and v.
-  const int t = blockIdx.x;
+  // blockIdx.x numbers the rows of the step, or (segment_start given: a step that also holds prompt portions) its
+  // requests, of which only those that bring exactly one token are this kernel's
+  const int slot = blockIdx.x;
+  int t = slot;
+  if (segment_start != nullptr) {
+    t = segment_start[slot];
+    if (segment_start[slot + 1] - t != 1) return;   // all blocks of a cluster share the request: they leave together
+  }
   const int group = n_q / n_kv;
   const int gchunks = (group + DEC_HEADS - 1) / DEC_HEADS;
   const int kvh = blockIdx.y / gchunks;
@@ -393,7 +400,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
         cluster.map_shared_rank(recv_l, d)[split * DEC_HEADS + g] = L;
       }
     } else {
-      const size_t pidx = ((size_t)t * n_q + head) * num_splits + split;
+      const size_t pidx = ((size_t)slot * n_q + head) * num_splits + split;
       part_o[pidx * D + d] = O;
       if (d == 0) { part_ml[pidx * 2] = M; part_ml[pidx * 2 + 1] = L; }
     }
@@ -437,7 +444,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   __threadfence();
   __syncthreads();
   if (tid == 0) {
-    const int seen = atomicAdd(&arrivals[t * gridDim.y + blockIdx.y], 1);
+    const int seen = atomicAdd(&arrivals[slot * gridDim.y + blockIdx.y], 1);
     last_flag = seen == num_splits - 1;
   }
   __syncthreads();
@@ -449,7 +456,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   __syncthreads();
   for (int e = tid; e < gcount * 32; e += 128) {
     const int g = e >> 5, sp = e & 31;
-    const size_t pbase = ((size_t)t * n_q + first_head + g) * num_splits;
+    const size_t pbase = ((size_t)slot * n_q + first_head + g) * num_splits;
     const float m = sp < num_splits ? __ldcg(part_ml + (pbase + sp) * 2) : -INFINITY;
     const float l = sp < num_splits ? __ldcg(part_ml + (pbase + sp) * 2 + 1) : 0.f;
     // the 32 lanes of a warp hold the 32 splits of one head
@@ -467,7 +474,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   // eight splits issued together (splits are added in index order)
   for (int item = tid; item < gcount * (D / 4); item += 128) {
     const int g = item / (D / 4), d = (item % (D / 4)) * 4;
-    const float* src = part_o + ((size_t)t * n_q + first_head + g) * num_splits * D + d;
+    const float* src = part_o + ((size_t)slot * n_q + first_head + g) * num_splits * D + d;
     float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int sp0 = 0; sp0 < num_splits; sp0 += 8) {
       float4 v[8];
@@ -487,7 +494,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     packed.y = *reinterpret_cast<uint32_t*>(&hi);
     *reinterpret_cast<uint2*>(out + ((size_t)t * n_q + first_head + g) * D + d) = packed;
   }
-  if (tid == 0) arrivals[t * gridDim.y + blockIdx.y] = 0;
+  if (tid == 0) arrivals[slot * gridDim.y + blockIdx.y] = 0;
   LSE_TL_MARK_ANY(5, tid == 0 && blockIdx.x == 0 && blockIdx.y == 0)
 }
 
@@ -504,7 +511,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
                     const int* __restrict__ block_tables, int bt_stride,
                     const int* __restrict__ segment_start, const int* __restrict__ segment_first_pos,
                     int num_segments, int n_q, int n_kv, int page_size, float scale_log2e,
-                    int rows_per_tile, int num_pages) {
+                    int rows_per_tile, int num_pages, int skip_single) {
   constexpr int CH = D / 8;
   constexpr int TILE_BYTES = PF_BN * D * 2;
   extern __shared__ __align__(128) unsigned char smem[];
@@ -524,7 +531,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     const int tile = gridDim.x - 1 - blockIdx.x;   // late tiles (longest walks) are launched first
     for (int s = 0; s < num_segments; ++s) {
       const int c = segment_start[s + 1] - segment_start[s];
-      const int nt = (c + rows_per_tile - 1) / rows_per_tile;
+      const int nt = (skip_single && c == 1) ? 0 : (c + rows_per_tile - 1) / rows_per_tile;   // single tokens: the decode kernel's
       if (tile < before + nt) { seg = s; r0 = (tile - before) * rows_per_tile; cnt = c; break; }
       before += nt;
     }
@@ -705,7 +712,7 @@ template <int D, bool CLUSTER>
 int launch_decode_as(const void* q, const void* kc, const void* vc, void* out, float* part_o, float* part_ml,
                      int* arrivals, const int* block_tables, int bt_stride, const int* seg, const int* positions,
                      int tokens, int n_q, int n_kv, int page_size, float scale, int num_splits, int num_pages,
-                     int num_segments, cudaStream_t stream) {
+                     int num_segments, const int* segment_start, cudaStream_t stream) {
   const size_t smem = decode_smem<D>();
   static bool configured = false;   // once per process: not repeated while a stream is captured
   if (!configured) {
@@ -719,7 +726,7 @@ int launch_decode_as(const void* q, const void* kc, const void* vc, void* out, f
       CLUSTER ? (unsigned)num_splits : 1u,
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, (__nv_bfloat16*)out, part_o,
       part_ml, arrivals, block_tables, bt_stride, seg, positions, n_q, n_kv, page_size, scale * LOG2E, num_splits,
-      lse_pdl_enabled ? 1 : 0, num_pages, num_segments);
+      lse_pdl_enabled ? 1 : 0, num_pages, num_segments, segment_start);
   if (err != cudaSuccess) return (int)err;
   return (int)cudaGetLastError();
 }
@@ -728,18 +735,19 @@ template <int D>
 int launch_decode(const void* q, const void* kc, const void* vc, void* out, float* part_o, float* part_ml,
                   int* arrivals, const int* block_tables, int bt_stride, const int* seg, const int* positions,
                   int tokens, int n_q, int n_kv, int page_size, float scale, int num_splits, int cluster,
-                  int num_pages, int num_segments, cudaStream_t stream) {
+                  int num_pages, int num_segments, const int* segment_start, cudaStream_t stream) {
   if (cluster && num_splits > 1 && num_splits <= 8)
     return launch_decode_as<D, true>(q, kc, vc, out, part_o, part_ml, arrivals, block_tables, bt_stride, seg, positions,
-                                     tokens, n_q, n_kv, page_size, scale, num_splits, num_pages, num_segments, stream);
+                                     tokens, n_q, n_kv, page_size, scale, num_splits, num_pages, num_segments, segment_start, stream);
   return launch_decode_as<D, false>(q, kc, vc, out, part_o, part_ml, arrivals, block_tables, bt_stride, seg, positions,
-                                    tokens, n_q, n_kv, page_size, scale, num_splits, num_pages, num_segments, stream);
+                                    tokens, n_q, n_kv, page_size, scale, num_splits, num_pages, num_segments, segment_start, stream);
 }
 
 template <int D>
 int launch_prefill(const void* q, const void* kc, const void* vc, void* out, const int* block_tables,
                    int bt_stride, const int* segment_start, const int* segment_first_pos, int num_segments,
-                   int tokens, int n_q, int n_kv, int page_size, float scale, int num_pages, cudaStream_t stream) {
+                   int tokens, int n_q, int n_kv, int page_size, float scale, int num_pages, int skip_single,
+                   cudaStream_t stream) {
   const size_t smem = prefill_smem<D>();
   static bool configured = false;
   if (!configured) {
@@ -754,7 +762,7 @@ int launch_prefill(const void* q, const void* kc, const void* vc, void* out, con
   lse_launch(attn_prefill_kernel<D>, grid, 128, smem, stream,
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, (__nv_bfloat16*)out,
       block_tables, bt_stride, segment_start, segment_first_pos, num_segments, n_q, n_kv, page_size,
-      scale * LOG2E, rows_per_tile, num_pages);
+      scale * LOG2E, rows_per_tile, num_pages, skip_single);
   return (int)cudaGetLastError();
 }
 }  // namespace
@@ -774,12 +782,16 @@ extern "C" long long lse_attention_decode_scratch_floats(int tokens, int n_q, in
 // `cluster` != 0 and 2 <= num_splits <= 8: the splits form a thread-block cluster and need neither
 // `scratch` nor `arrivals`.  Else `scratch` holds the partial sums and `arrivals` is tokens * n_kv *
 // ceil(group / 8) ints that are zero before the first launch (the kernel leaves them zero).
+// segment_start != null (a step that also holds prompt portions): `tokens` counts the step's requests, block x
+// of the grid is request x, and only requests that bring exactly one token are worked on (its row is
+// segment_start[x]); scratch and arrivals are then sized by the number of requests.
 extern "C" int lse_paged_attention_decode(const void* q, const void* k_cache, const void* v_cache, void* out,
                                           float* scratch, int* arrivals, int cluster, const int* block_tables,
                                           int bt_stride,
                                           const int* segment_of_token, const int* positions, int tokens,
                                           int n_q, int n_kv, int head_dim, int page_size, float scale,
-                                          int num_splits, int num_pages, int num_segments, cudaStream_t stream) {
+                                          int num_splits, int num_pages, int num_segments, const int* segment_start,
+                                          cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (!lse_attention_mma_supported(head_dim, n_q, n_kv) || page_size <= 0 || num_splits < 1 || num_splits > 32)
     return LSE_ERR_BAD_ARGUMENT;
@@ -790,22 +802,22 @@ extern "C" int lse_paged_attention_decode(const void* q, const void* k_cache, co
   if (head_dim == 128)
     return launch_decode<128>(q, k_cache, v_cache, out, part_o, part_ml, arrivals, block_tables, bt_stride,
                               segment_of_token, positions, tokens, n_q, n_kv, page_size, scale, num_splits, cluster, num_pages,
-                              num_segments, stream);
+                              num_segments, segment_start, stream);
   return launch_decode<64>(q, k_cache, v_cache, out, part_o, part_ml, arrivals, block_tables, bt_stride,
                            segment_of_token, positions, tokens, n_q, n_kv, page_size, scale, num_splits, cluster, num_pages,
-                              num_segments, stream);
+                           num_segments, segment_start, stream);
 }
 
 extern "C" int lse_paged_attention_prefill(const void* q, const void* k_cache, const void* v_cache, void* out,
                                            const int* block_tables, int bt_stride, const int* segment_start,
                                            const int* segment_first_pos, int num_segments, int tokens, int n_q,
                                            int n_kv, int head_dim, int page_size, float scale, int num_pages,
-                                           cudaStream_t stream) {
+                                           int skip_single, cudaStream_t stream) {
   if (tokens <= 0 || num_segments <= 0) return 0;
   if (!lse_attention_mma_supported(head_dim, n_q, n_kv) || page_size <= 0) return LSE_ERR_BAD_ARGUMENT;
   if (head_dim == 128)
     return launch_prefill<128>(q, k_cache, v_cache, out, block_tables, bt_stride, segment_start, segment_first_pos,
-                               num_segments, tokens, n_q, n_kv, page_size, scale, num_pages, stream);
+                               num_segments, tokens, n_q, n_kv, page_size, scale, num_pages, skip_single, stream);
   return launch_prefill<64>(q, k_cache, v_cache, out, block_tables, bt_stride, segment_start, segment_first_pos,
-                            num_segments, tokens, n_q, n_kv, page_size, scale, num_pages, stream);
+                            num_segments, tokens, n_q, n_kv, page_size, scale, num_pages, skip_single, stream);
 }

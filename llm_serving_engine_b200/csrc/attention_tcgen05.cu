@@ -91,7 +91,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
                        const int* __restrict__ block_tables, int bt_stride, const int* __restrict__ segment_start,
                        const int* __restrict__ segment_first_pos, int num_segments, int n_q, int n_kv, int page_size,
-                       float scale_log2e, int num_pages) {
+                       float scale_log2e, int num_pages, int skip_single) {
   constexpr int HALVES = D / 64;
   constexpr uint32_t Q_BYTES = HALVES * HALF_BYTES, KV_BYTES = HALVES * HALF_BYTES, P_BYTES = 2 * HALF_BYTES;
   constexpr uint32_t GROUP_BYTES = HALVES * 1024;   // 8 keys (or values) in a stage: 8 rows x 128 bytes for every 64 columns
@@ -122,7 +122,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int tile = (int)(gridDim.x / n_q) - 1 - (int)(blockIdx.x / n_q);
     for (int s = 0; s < num_segments; ++s) {
       const int c = segment_start[s + 1] - segment_start[s];
-      const int nt = (c + BM - 1) / BM;
+      const int nt = (skip_single && c == 1) ? 0 : (c + BM - 1) / BM;   // single tokens are the decode kernel's
       if (tile < before + nt) { seg = s; r0 = (tile - before) * BM; cnt = c; break; }
       before += nt;
     }
@@ -462,7 +462,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 template <int D>
 int launch_prefill_tc(const void* q, const void* kc, const void* vc, void* out, const int* block_tables, int bt_stride,
                       const int* segment_start, const int* segment_first_pos, int num_segments, int tokens,
-                      long long num_pages, int n_q, int n_kv, int page_size, float scale, cudaStream_t stream) {
+                      long long num_pages, int n_q, int n_kv, int page_size, float scale, int skip_single,
+                      cudaStream_t stream) {
   const size_t smem = attn_tc_smem<D>();
   static bool configured = false;
   if (!configured) {
@@ -479,7 +480,7 @@ int launch_prefill_tc(const void* q, const void* kc, const void* vc, void* out, 
   dim3 grid(tiles * n_q);
   cudaError_t err = lse_launch(attn_prefill_tc_kernel<D>, grid, THREADS, smem, stream, map_q, map_k, map_v,
                                (__nv_bfloat16*)out, block_tables, bt_stride, segment_start, segment_first_pos,
-                               num_segments, n_q, n_kv, page_size, scale * LOG2E, (int)num_pages);
+                               num_segments, n_q, n_kv, page_size, scale * LOG2E, (int)num_pages, skip_single);
   if (err != cudaSuccess) return (int)err;
   return (int)cudaGetLastError();
 }
@@ -525,14 +526,14 @@ extern "C" int lse_paged_attention_prefill_tc(const void* q, const void* k_cache
                                               const int* block_tables, int bt_stride, const int* segment_start,
                                               const int* segment_first_pos, int num_segments, int tokens,
                                               long long num_pages, int n_q, int n_kv, int head_dim, int page_size,
-                                              float scale, cudaStream_t stream) {
+                                              float scale, int skip_single, cudaStream_t stream) {
   if (tokens <= 0 || num_segments <= 0) return 0;
   if (!lse_attention_tc_supported(head_dim, n_q, n_kv, page_size) || num_pages <= 0 || !(scale > 0.f) ||
       (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15))
     return LSE_ERR_BAD_ARGUMENT;
   if (head_dim == 128)
     return launch_prefill_tc<128>(q, k_cache, v_cache, out, block_tables, bt_stride, segment_start, segment_first_pos,
-                                  num_segments, tokens, num_pages, n_q, n_kv, page_size, scale, stream);
+                                  num_segments, tokens, num_pages, n_q, n_kv, page_size, scale, skip_single, stream);
   return launch_prefill_tc<64>(q, k_cache, v_cache, out, block_tables, bt_stride, segment_start, segment_first_pos,
-                               num_segments, tokens, num_pages, n_q, n_kv, page_size, scale, stream);
+                               num_segments, tokens, num_pages, n_q, n_kv, page_size, scale, skip_single, stream);
 }

@@ -239,15 +239,22 @@ def _arrival_counters(device, count: int) -> torch.Tensor:
 
 def paged_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
                            block_tables: torch.Tensor, segment_of_token: torch.Tensor, positions: torch.Tensor,
-                           scale: float, num_splits: int, cluster: bool = True) -> torch.Tensor:
+                           scale: float, num_splits: int, cluster: bool = True,
+                           segment_start: torch.Tensor | None = None) -> torch.Tensor:
     """Attention of single decoded tokens (one row per request) with the keys split over
-    ``num_splits`` blocks; bfloat16, head size 64 or 128."""
+    ``num_splits`` blocks; bfloat16, head size 64 or 128.  With ``segment_start`` (int32 [S + 1], a step that
+    also holds prompt portions) the rows are those of the requests that bring exactly one token, wherever they
+    lie among q's rows; the other rows of ``out`` are left alone."""
     _need_cuda(q, k_cache, v_cache, out, block_tables, segment_of_token, positions)
     tokens, n_q, head_dim = q.shape
     n_kv, page_size = k_cache.shape[1], k_cache.shape[2]
     assert q.dtype == out.dtype == k_cache.dtype == v_cache.dtype == torch.bfloat16
     assert q.is_contiguous() and out.is_contiguous() and k_cache.is_contiguous() and v_cache.is_contiguous()
     assert block_tables.dtype == torch.int32 and block_tables.stride(1) == 1
+    if segment_start is not None:
+        _need_cuda(segment_start)
+        assert segment_start.dtype == torch.int32 and segment_start.shape[0] == block_tables.shape[0] + 1
+        tokens = block_tables.shape[0]      # one block row per request of the step
     scratch = arrivals = None
     by_cluster = cluster and 1 < num_splits <= 8      # the splits add up through distributed shared memory
     if num_splits > 1 and not by_cluster:
@@ -259,18 +266,19 @@ def paged_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
                                          block_tables.stride(0),
                                          segment_of_token.data_ptr(), positions.data_ptr(), tokens, n_q, n_kv,
                                          head_dim, page_size, float(scale), int(num_splits), k_cache.shape[0],
-                                         block_tables.shape[0], _stream()),
+                                         block_tables.shape[0], _ptr(segment_start), _stream()),
           "paged_attention_decode")
     return out
 
 
 def paged_attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
                             block_tables: torch.Tensor, segment_start: torch.Tensor,
-                            segment_first_position: torch.Tensor, scale: float) -> torch.Tensor:
+                            segment_first_position: torch.Tensor, scale: float, skip_single: bool = False) -> torch.Tensor:
     """Attention of prompt portions (any mix of segment lengths): causal inside the portion,
     all earlier keys of the request before it; bfloat16, head size 64 or 128.
 
     segment_start int32 [S + 1]: first row of each segment; segment_first_position int32 [S].
+    ``skip_single``: requests that bring exactly one token are left to :func:`paged_attention_decode`.
     """
     _need_cuda(q, k_cache, v_cache, out, block_tables, segment_start, segment_first_position)
     tokens, n_q, head_dim = q.shape
@@ -283,7 +291,8 @@ def paged_attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
     check(lib.lse_paged_attention_prefill(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
                                           block_tables.data_ptr(), block_tables.stride(0), segment_start.data_ptr(),
                                           segment_first_position.data_ptr(), segments, tokens, n_q, n_kv, head_dim,
-                                          page_size, float(scale), k_cache.shape[0], _stream()), "paged_attention_prefill")
+                                          page_size, float(scale), k_cache.shape[0], int(skip_single), _stream()),
+          "paged_attention_prefill")
     return out
 
 
@@ -298,7 +307,7 @@ def attention_tc_supported(head_dim: int, n_q: int, n_kv: int, page_size: int, d
 
 def paged_attention_prefill_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
                                block_tables: torch.Tensor, segment_start: torch.Tensor,
-                               segment_first_position: torch.Tensor, scale: float) -> torch.Tensor:
+                               segment_first_position: torch.Tensor, scale: float, skip_single: bool = False) -> torch.Tensor:
     """Attention of prompt portions on the 5th-generation tensor cores: the arguments and the
     result of :func:`paged_attention_prefill`; blocks of 128 rows of one head, keys in tiles of 128
     brought in by TMA page by page, scores and outputs accumulated in tensor memory."""
@@ -314,7 +323,7 @@ def paged_attention_prefill_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: 
     check(lib.lse_paged_attention_prefill_tc(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
                                              block_tables.data_ptr(), block_tables.stride(0), segment_start.data_ptr(),
                                              segment_first_position.data_ptr(), segments, tokens, pages, n_q, n_kv,
-                                             head_dim, page_size, float(scale), _stream()),
+                                             head_dim, page_size, float(scale), int(skip_single), _stream()),
           "paged_attention_prefill_tc")
     return out
 

@@ -12,17 +12,18 @@ from ..weights.tensor_spec import TensorSpec
 from .base import POSITION_ENCODINGS, Mixer, PagedKV, register_mixer
 from .linear import linear_partials
 
-# Which kernel a step with prompt portions takes.  The tcgen05 kernel's block is 128 rows of one request
-# and one head; the mma.sync kernel's about ten rows of all heads of a group.  A step goes to the former
-# when its longest portion has at least TCGEN05_MIN_ROWS rows and either its blocks fit the GPU at once
-# (a long portion beside a few decoding requests: 31 against 46 us for 512 rows beside 8 requests) or
-# its portions are long on average (at least 64 rows a request); many short portions or many decoding
-# requests beside a portion (90 against 64 us with 32 of them) stay on the mma.sync kernel.
-# LSE_PREFILL_ATTENTION=mma turns the tcgen05 kernel off.
+# Which kernels a step with prompt portions takes.  Requests that bring a single token (decoding requests beside
+# the portions, a prompt's last token) go to the decode kernel, which splits their keys over blocks; the portions
+# go to one of the two prompt kernels.  The tcgen05 kernel's block is 128 rows of one request and one head; the
+# mma.sync kernel's about ten rows of all heads of a group.  The portions go to the former when the longest has at
+# least TCGEN05_MIN_ROWS rows and either their blocks fit the GPU at once or they are long on average (at least 64
+# rows each); many short portions stay on the mma.sync kernel.  LSE_PREFILL_ATTENTION=mma turns the tcgen05
+# kernel off, LSE_MIXED_DECODE_KERNEL=0 sends single tokens through the prompt kernels as well.
 TCGEN05_MIN_ROWS = int(os.environ.get("LSE_TCGEN05_MIN_ROWS", "128"))
 TCGEN05_MIN_ROWS_PER_REQUEST = 64
 TCGEN05_BLOCKS_AT_ONCE = 148
 TCGEN05_PREFILL = os.environ.get("LSE_PREFILL_ATTENTION", "tcgen05") != "mma"
+MIXED_DECODE_KERNEL = os.environ.get("LSE_MIXED_DECODE_KERNEL", "1") != "0"
 
 
 @register_mixer("gqa_attention")
@@ -90,10 +91,17 @@ class GroupedQueryAttention(Mixer):
             return "mma"
         return "tcgen05"
 
+    @staticmethod
+    def _portions(segment_counts: list[int]) -> tuple[list[int], bool]:
+        """The portions that the prompt kernel takes, and whether the decode kernel takes the single tokens."""
+        singles = MIXED_DECODE_KERNEL and any(count == 1 for count in segment_counts) and max(segment_counts) > 1
+        return ([count for count in segment_counts if count > 1] if singles else list(segment_counts)), singles
+
     def launch_signature(self, segment_counts):
         if max(segment_counts) == 1 or not ops.attention_mma_supported(self.head_dim, self.n_q, self.n_kv, self.ctx.dtype, self.window):
             return ()
-        return (self.prompt_kernel(segment_counts),)
+        portions, singles = self._portions(segment_counts)
+        return (self.prompt_kernel(portions), singles)
 
     def forward(self, x, step, cache):
         tokens = x.shape[0]
@@ -107,12 +115,18 @@ class GroupedQueryAttention(Mixer):
                 splits = ops.decode_splits(tokens, self.n_q, self.n_kv, step.max_context, getattr(step, "long_context", False))
                 ops.paged_attention_decode(q, cache.keys, cache.values, attended, cache.block_tables,
                                            step.segment_of_token, step.positions, self.scale, splits)
-            elif self.prompt_kernel([segment.count for segment in step.segments], cache.keys.shape[2]) == "tcgen05":
-                ops.paged_attention_prefill_tc(q, cache.keys, cache.values, attended, cache.block_tables,
-                                               step.segment_start, step.segment_first_position, self.scale)
             else:
-                ops.paged_attention_prefill(q, cache.keys, cache.values, attended, cache.block_tables,
-                                            step.segment_start, step.segment_first_position, self.scale)
+                portions, singles = self._portions([segment.count for segment in step.segments])
+                if singles:   # one block row per request of the step; requests with portions leave at once
+                    requests = cache.block_tables.shape[0]
+                    splits = ops.decode_splits(requests, self.n_q, self.n_kv, None)
+                    ops.paged_attention_decode(q, cache.keys, cache.values, attended, cache.block_tables,
+                                               step.segment_of_token, step.positions, self.scale, splits,
+                                               segment_start=step.segment_start)
+                prompt = (ops.paged_attention_prefill_tc if self.prompt_kernel(portions, cache.keys.shape[2]) == "tcgen05"
+                          else ops.paged_attention_prefill)
+                prompt(q, cache.keys, cache.values, attended, cache.block_tables, step.segment_start,
+                       step.segment_first_position, self.scale, skip_single=singles)
         else:   # float32, other head sizes, windows: the general kernel
             ops.paged_attention_generic(q, cache.keys, cache.values, attended, cache.block_tables,
                                         step.segment_of_token, step.positions, self.scale, self.window)

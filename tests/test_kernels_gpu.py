@@ -664,6 +664,47 @@ def test_tcgen05_prefill_attention(head_dim, n_q, n_kv, page):
         assert float(err.max()) < 2.0 ** -7 * max(1.0, float(want.abs().max())), (s, before, rows, float(err.max()))
 
 
+@pytest.mark.parametrize("prompt_kernel", ["tcgen05", "mma"])
+@pytest.mark.parametrize("head_dim, n_q, n_kv, page, splits", [(128, 12, 2, 16, 8), (64, 6, 2, 8, 3), (128, 7, 1, 32, 1), (64, 16, 2, 16, 20)])
+def test_single_tokens_beside_portions_go_to_the_decode_kernel(prompt_kernel, head_dim, n_q, n_kv, page, splits):
+    """A step with prompt portions and single tokens in any order: the decode kernel, given the step's segment starts,
+    works on the requests that bring one token and leaves the others alone; the prompt kernel skips exactly those.
+    Every row is written once and equals dense attention; unowned pages hold NaN."""
+    rng = random.Random(head_dim + n_q + splits)
+    torch.manual_seed(n_q + page)
+    portions = [(700, 1), (0, 130), (40, 1), (0, 1), (5, 2), (1999, 1), (300, 200), (63, 1), (0, 64)]   # (keys before, rows)
+    contexts = [before + rows for before, rows in portions]
+    k_cache, v_cache, tables, dense = paged_setup(rng, contexts, n_kv, head_dim, page, torch.bfloat16)
+    poison_unowned(k_cache, v_cache, tables, contexts, page)
+    starts = [0]
+    for _, rows in portions:
+        starts.append(starts[-1] + rows)
+    total = starts[-1]
+    q = torch.randn(total, n_q, head_dim, device=DEV).bfloat16()
+    segs = torch.cat([torch.full((rows,), s, dtype=torch.int32) for s, (_, rows) in enumerate(portions)]).to(DEV)
+    positions = torch.cat([torch.arange(before, before + rows, dtype=torch.int32) for before, rows in portions]).to(DEV)
+    start_t = torch.tensor(starts, dtype=torch.int32, device=DEV)
+    first_t = torch.tensor([before for before, _ in portions], dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(head_dim)
+    out = torch.full_like(q, 9.0)
+    ops().paged_attention_decode(q, k_cache, v_cache, out, tables, segs, positions, scale, splits, segment_start=start_t)
+    single_rows = [starts[s] for s, (_, rows) in enumerate(portions) if rows == 1]
+    untouched = torch.ones(total, dtype=torch.bool)
+    untouched[single_rows] = False
+    assert bool((out[untouched.to(DEV)] == 9.0).all()) and not bool((out[~untouched.to(DEV)] == 9.0).any())
+    prompt = ops().paged_attention_prefill_tc if prompt_kernel == "tcgen05" else ops().paged_attention_prefill
+    marked = out.clone()
+    marked[~untouched.to(DEV)] = 7.0      # the prompt kernel must not write these rows again
+    prompt(q, k_cache, v_cache, marked, tables, start_t, first_t, scale, skip_single=True)
+    assert bool((marked[~untouched.to(DEV)] == 7.0).all()) and not bool((marked[untouched.to(DEV)] == 9.0).any())
+    out[untouched.to(DEV)] = marked[untouched.to(DEV)]
+    assert ops().attention_tc_status() == 0
+    for s, (before, rows) in enumerate(portions):
+        want = dense_causal(q[starts[s]:starts[s + 1]], dense[s][0], dense[s][1], before, scale)
+        err = float((out[starts[s]:starts[s + 1]].double() - want).abs().max())
+        assert err < 2.0 ** -7 * max(1.0, float(want.abs().max())), (s, before, rows, err)
+
+
 @pytest.mark.parametrize("slope", [40.0, 8.0])
 def test_tcgen05_prefill_attention_when_the_maximum_grows(slope):
     """Scores that grow by far more than 2^8 from tile to tile (keys scaled up along the sequence):
