@@ -110,7 +110,9 @@ add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* __restrict__ delt
     if (i < chunks) {
       load4<float>(res + 4 * i, x[c]);
       if (del) {
-        // sixteen partial sums are fetched together (one round trip), then added in index order
+        // sixteen partial sums are fetched together (one round trip), then added in index order, starting from
+        // zero: the branch's output first, as a product that adds its own ranges up makes it; then the residual
+        float sum[4] = {0.f, 0.f, 0.f, 0.f};
         for (int p0 = 0; p0 < n_partials; p0 += 16) {
           float d[16][4];
 #pragma unroll
@@ -120,9 +122,10 @@ add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* __restrict__ delt
           }
 #pragma unroll
           for (int p = 0; p < 16; ++p) {
-            if (p0 + p < n_partials) { x[c][0] += d[p][0]; x[c][1] += d[p][1]; x[c][2] += d[p][2]; x[c][3] += d[p][3]; }
+            if (p0 + p < n_partials) { sum[0] += d[p][0]; sum[1] += d[p][1]; sum[2] += d[p][2]; sum[3] += d[p][3]; }
           }
         }
+        x[c][0] += sum[0]; x[c][1] += sum[1]; x[c][2] += sum[2]; x[c][3] += sum[3];
         if (write_residual) store4<float>(res + 4 * i, x[c]);
       }
       sq = fmaf(x[c][0], x[c][0], sq); sq = fmaf(x[c][1], x[c][1], sq);
@@ -163,8 +166,11 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __res
   float sq = 0.f;
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
     float x = res[i];
-    if (del)
-      for (int p = 0; p < n_partials; ++p) x += to_f32<TD>(del[(size_t)p * partial_stride + i]);
+    if (del) {   // the branch's output first (its partial sums in index order, starting from zero), then the residual
+      float sum = 0.f;
+      for (int p = 0; p < n_partials; ++p) sum += to_f32<TD>(del[(size_t)p * partial_stride + i]);
+      x += sum;
+    }
     if (del && write_residual) res[i] = x;
     sq = fmaf(x, x, sq);
   }
@@ -172,8 +178,11 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __res
   const float inv = 1.0f / sqrtf(total / (float)hidden + eps);
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
     float x = res[i];
-    if (del && !write_residual)
-      for (int p = 0; p < n_partials; ++p) x += to_f32<TD>(del[(size_t)p * partial_stride + i]);
+    if (del && !write_residual) {
+      float sum = 0.f;
+      for (int p = 0; p < n_partials; ++p) sum += to_f32<TD>(del[(size_t)p * partial_stride + i]);
+      x += sum;
+    }
     dst[i] = from_f32<TO>((x * inv) * weight[i]);
   }
 }

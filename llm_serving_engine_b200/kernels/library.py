@@ -29,7 +29,9 @@ _SIGNATURES = {
     "lse_attention_tc_status_async": [c_void_p, c_void_p],
     "lse_attention_tc_status_reset": [],
     "lse_gemm_f32_nt": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong,
-                        c_longlong, c_longlong, c_void_p],
+                        c_longlong, c_longlong, c_int, c_longlong, c_void_p],
+    "lse_gemm_f32_ranges": [c_int],
+    "lse_gemm_f32_stack_ok": [c_void_p, c_void_p, c_int, c_int, c_longlong, c_longlong],
     "lse_paged_attention_generic": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
                                     c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
                                     c_int, c_int, c_int, c_void_p, c_int, c_void_p],

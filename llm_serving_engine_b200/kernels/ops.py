@@ -108,7 +108,30 @@ def gemm_f32_nt(a: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None
         assert bias.dtype == torch.float32 and bias.shape == (n,)
     lib = library.load()
     check(lib.lse_gemm_f32_nt(a.data_ptr(), weight.data_ptr(), _ptr(bias), out.data_ptr(), m, n, k,
-                              a.stride(0), weight.stride(0), out.stride(0), _stream()), "gemm_f32_nt")
+                              a.stride(0), weight.stride(0), out.stride(0), 0, 0, _stream()), "gemm_f32_nt")
+    return out
+
+
+def gemm_f32_stack_ok(a: torch.Tensor, weight: torch.Tensor) -> bool:
+    """Whether :func:`gemm_f32_stack` takes this product (few rows, k a multiple of 4, aligned rows)."""
+    return bool(library.load().lse_gemm_f32_stack_ok(a.data_ptr(), weight.data_ptr(), a.shape[0], a.shape[1],
+                                                     a.stride(0), weight.stride(0)))
+
+
+def gemm_f32_stack(a: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """a @ weight^T in true float32 as a stack [P, M, N] of the sums over the k ranges that the product is
+    always cut into: a block per range, so that a product of few rows has enough blocks to stream the weights.
+    Added up in index order, starting from zero, the stack gives :func:`gemm_f32_nt`'s result bit for bit."""
+    _need_cuda(a, weight)
+    m, k = a.shape
+    n = weight.shape[0]
+    assert a.dtype == weight.dtype == torch.float32 and weight.shape[1] == k
+    assert a.stride(1) == 1 and weight.stride(1) == 1
+    lib = library.load()
+    ranges = int(lib.lse_gemm_f32_ranges(k))
+    out = torch.empty((ranges, m, n), dtype=torch.float32, device=a.device)
+    check(lib.lse_gemm_f32_nt(a.data_ptr(), weight.data_ptr(), None, out.data_ptr(), m, n, k,
+                              a.stride(0), weight.stride(0), out.stride(1), 1, out.stride(0), _stream()), "gemm_f32_stack")
     return out
 
 

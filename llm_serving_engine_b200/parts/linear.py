@@ -1,6 +1,7 @@
 """Matrix products of the layers: y = x W^T (+ b), W kept [out, in].
 
-float32: the engine's own FMA kernel (true 32-bit, fixed summation order).
+float32: the engine's own FMA kernel (true 32-bit, fixed summation order: a few rows give the same bits as a
+stack of partial sums that the next kernel adds up as they do from the kernel that adds them up itself).
 bfloat16, few rows (decoding): the engine's tcgen05 kernel, which streams the
 weights with TMA and may cut the k range into splits; it returns a float32 stack
 of partial sums [P, rows, out] that the next kernel (norm, rotary, SiLU) adds up.
@@ -25,9 +26,13 @@ torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
 
 
 def reduce_partials(y: torch.Tensor) -> torch.Tensor:
-    """[rows, out] from a branch output that may be a stack of partial sums [P, rows, out]."""
+    """[rows, out] from a branch output that may be a stack of partial sums [P, rows, out]: added in index
+    order, starting from zero, as the kernels that consume such stacks add them."""
     if y.dim() == 3:
-        return y[0] if y.shape[0] == 1 else y.sum(0)
+        total = torch.zeros_like(y[0])
+        for part in y:
+            total += part
+        return total
     return y
 
 
@@ -37,6 +42,8 @@ def linear_partials(x: torch.Tensor, weight: torch.Tensor, max_splits: int | Non
     if (x.is_cuda and weight.dtype == torch.bfloat16 and x.shape[0] <= SKINNY_MAX_ROWS
             and ops.gemm_bf16_skinny_ok(x, weight)):
         return ops.gemm_bf16_skinny(x, weight, max_splits=max_splits)
+    if x.is_cuda and weight.dtype == torch.float32 and x.dtype == torch.float32 and ops.gemm_f32_stack_ok(x, weight):
+        return ops.gemm_f32_stack(x, weight)   # at most eight partial sums: what every consumer fetches in one go
     return linear(x, weight)
 
 

@@ -108,6 +108,33 @@ def test_gemm_f32_is_true_float32_and_row_invariant(m, n, k):
     assert rel_err(no_bias, a.double() @ w.double().t()) < 1e-5
 
 
+@pytest.mark.parametrize("m, n, k", [(1, 64, 64), (8, 1536, 8960), (3, 100, 1536), (16, 257, 520), (5, 96, 4100)])
+def test_gemm_f32_as_a_stack_of_range_sums(m, n, k):
+    """Few rows as a stack of partial sums (a block per k range): added up in index order from zero, the stack gives
+    the bits of the product that adds its ranges up itself, with few rows and as rows of a large batch."""
+    torch.manual_seed(n + k)
+    a = torch.randn(m, k, device=DEV)
+    w = torch.randn(n, k, device=DEV)
+    assert ops().gemm_f32_stack_ok(a, w)
+    stack = ops().gemm_f32_stack(a, w)
+    assert stack.dim() == 3 and stack.shape[1:] == (m, n) and 1 <= stack.shape[0] <= 8
+    total = torch.zeros(m, n, device=DEV)
+    for part in stack:
+        total += part
+    whole = torch.empty(m, n, device=DEV)
+    ops().gemm_f32_nt(a, w, None, whole)
+    assert torch.equal(total, whole)
+    many = torch.randn(70, k, device=DEV)
+    many[11:11 + m] = a
+    large = torch.empty(70, n, device=DEV)
+    ops().gemm_f32_nt(many, w, None, large)       # the many-rows kernel
+    assert torch.equal(large[11:11 + m], whole)
+    want = a.double() @ w.double().t()
+    assert float((whole.double() - want).abs().max()) < 2.0 ** -15 * float((a.abs().double() @ w.abs().double().t()).max())
+    assert not ops().gemm_f32_stack_ok(torch.randn(17, k, device=DEV), w)
+    assert not ops().gemm_f32_stack_ok(torch.randn(2, 6, device=DEV), torch.randn(4, 6, device=DEV))
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("head_dim, n_q, n_kv, page, pairing", [(16, 4, 2, 16, "interleaved"), (48, 10, 2, 8, "half"),
                                                              (128, 12, 2, 16, "interleaved"), (256, 3, 1, 4, "half")])
