@@ -525,17 +525,9 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
 
   // (the step's metadata is read before waiting for the kernels that produce q, k and v)
   // which tile of which request is this block's (blocks beyond the last tile leave)
-  int seg = -1, r0 = 0, cnt = 0;
-  {
-    int before = 0;
-    const int tile = gridDim.x - 1 - blockIdx.x;   // late tiles (longest walks) are launched first
-    for (int s = 0; s < num_segments; ++s) {
-      const int c = segment_start[s + 1] - segment_start[s];
-      const int nt = (skip_single && c == 1) ? 0 : (c + rows_per_tile - 1) / rows_per_tile;   // single tokens: the decode kernel's
-      if (tile < before + nt) { seg = s; r0 = (tile - before) * rows_per_tile; cnt = c; break; }
-      before += nt;
-    }
-  }
+  int seg, r0, cnt;
+  __shared__ int tile_slot[3];
+  lse_find_tile(segment_start, num_segments, rows_per_tile, skip_single, gridDim.x - 1 - blockIdx.x, tile_slot, seg, r0, cnt);   // late tiles (longest walks) are launched first
   if (seg < 0) return;
   const int nrows = min(rows_per_tile, cnt - r0);
   const int row_base = segment_start[seg] + r0;

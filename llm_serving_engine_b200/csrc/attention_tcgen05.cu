@@ -116,17 +116,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
   // which tile of which request (the step's own data: read before waiting for the kernels before);
   // blocks beyond the last tile leave.  Late tiles walk the most keys and are launched first.
-  int seg = -1, r0 = 0, cnt = 0;
-  {
-    int before = 0;
-    const int tile = (int)(gridDim.x / n_q) - 1 - (int)(blockIdx.x / n_q);
-    for (int s = 0; s < num_segments; ++s) {
-      const int c = segment_start[s + 1] - segment_start[s];
-      const int nt = (skip_single && c == 1) ? 0 : (c + BM - 1) / BM;   // single tokens are the decode kernel's
-      if (tile < before + nt) { seg = s; r0 = (tile - before) * BM; cnt = c; break; }
-      before += nt;
-    }
-  }
+  int seg, r0, cnt;
+  __shared__ int tile_slot[3];
+  lse_find_tile(segment_start, num_segments, BM, skip_single, (int)(gridDim.x / n_q) - 1 - (int)(blockIdx.x / n_q), tile_slot, seg, r0, cnt);
 #ifdef LSE_TRACE
   const int block_linear = blockIdx.x;
   if (tid == 0 && block_linear < 4096) { lse_attn_tc_blocks[block_linear * 4] = global_ns(); lse_attn_tc_blocks[block_linear * 4 + 2] = sm_id(); lse_attn_tc_blocks[block_linear * 4 + 3] = 0; }

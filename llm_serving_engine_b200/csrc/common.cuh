@@ -77,6 +77,45 @@ inline int lse_pdl_enabled = 1;
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 
+// Which request's which rows tile number `tile` of a launch covers, when every request's rows (segment_start[s] ..
+// segment_start[s + 1]) are cut into tiles of rows_per_tile rows and the tiles are numbered request by request
+// (requests of one row take none when skip_single).  The block's first warp works it out, 32 requests at a time (a
+// step may hold hundreds), and hands it to the other warps through `slot` (three ints of shared memory).  Every
+// thread of the block calls it; it ends with a __syncthreads().  seg = -1: there is no such tile.
+__device__ __forceinline__ void lse_find_tile(const int* __restrict__ segment_start, int num_segments, int rows_per_tile,
+                                              int skip_single, int tile, int* slot, int& seg, int& r0, int& cnt) {
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    int before = 0, found_seg = -1, found_r0 = 0, found_cnt = 0;   // the same in every lane
+    for (int base = 0; base < num_segments && found_seg < 0; base += 32) {
+      const int s = base + lane;
+      int c = 0, nt = 0;
+      if (s < num_segments) {
+        c = segment_start[s + 1] - segment_start[s];
+        nt = (skip_single && c == 1) ? 0 : (c + rows_per_tile - 1) / rows_per_tile;
+      }
+      int incl = nt;   // tiles of the requests base .. s
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+      }
+      const int excl = incl - nt;
+      const unsigned vote = __ballot_sync(0xffffffffu, nt > 0 && tile >= before + excl && tile < before + incl);
+      if (vote) {
+        const int src = __ffs(vote) - 1;
+        found_seg = base + src;
+        found_r0 = (tile - before - __shfl_sync(0xffffffffu, excl, src)) * rows_per_tile;
+        found_cnt = __shfl_sync(0xffffffffu, c, src);
+      }
+      before += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) { slot[0] = found_seg; slot[1] = found_r0; slot[2] = found_cnt; }
+  }
+  __syncthreads();
+  seg = slot[0]; r0 = slot[1]; cnt = slot[2];
+}
+
 // cluster_z > 1: the blocks (x, y, 0 .. cluster_z-1) form a thread-block cluster (distributed shared memory).
 template <typename... KArgs, typename... Args>
 inline cudaError_t lse_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
