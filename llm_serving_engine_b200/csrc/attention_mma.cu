@@ -527,7 +527,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   // which tile of which request is this block's (blocks beyond the last tile leave)
   int seg, r0, cnt;
   __shared__ int tile_slot[3];
-  lse_find_tile(segment_start, num_segments, rows_per_tile, skip_single, gridDim.x - 1 - blockIdx.x, tile_slot, seg, r0, cnt);   // late tiles (longest walks) are launched first
+  lse_find_tile(segment_start, num_segments, rows_per_tile, skip_single, blockIdx.x, tile_slot, seg, r0, cnt);
   if (seg < 0) return;
   const int nrows = min(rows_per_tile, cnt - r0);
   const int row_base = segment_start[seg] + r0;
@@ -739,7 +739,7 @@ template <int D>
 int launch_prefill(const void* q, const void* kc, const void* vc, void* out, const int* block_tables,
                    int bt_stride, const int* segment_start, const int* segment_first_pos, int num_segments,
                    int tokens, int n_q, int n_kv, int page_size, float scale, int num_pages, int skip_single,
-                   cudaStream_t stream) {
+                   int max_portions, cudaStream_t stream) {
   const size_t smem = prefill_smem<D>();
   static bool configured = false;
   if (!configured) {
@@ -749,7 +749,10 @@ int launch_prefill(const void* q, const void* kc, const void* vc, void* out, con
   }
   const int group = n_q / n_kv;
   const int rows_per_tile = PF_BM / group;
-  const int tiles = (tokens + rows_per_tile - 1) / rows_per_tile + num_segments;   // upper bound
+  // upper bound: every request that has tiles may end with a partial one (max_portions > 0: the caller knows that
+  // at most so many requests have tiles, the others bringing single tokens that are skipped)
+  const int with_tiles = (max_portions > 0 && max_portions < num_segments) ? max_portions : num_segments;
+  const int tiles = (tokens + rows_per_tile - 1) / rows_per_tile + with_tiles;
   dim3 grid(tiles, n_kv);
   lse_launch(attn_prefill_kernel<D>, grid, 128, smem, stream,
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, (__nv_bfloat16*)out,
@@ -804,12 +807,12 @@ extern "C" int lse_paged_attention_prefill(const void* q, const void* k_cache, c
                                            const int* block_tables, int bt_stride, const int* segment_start,
                                            const int* segment_first_pos, int num_segments, int tokens, int n_q,
                                            int n_kv, int head_dim, int page_size, float scale, int num_pages,
-                                           int skip_single, cudaStream_t stream) {
+                                           int skip_single, int max_portions, cudaStream_t stream) {
   if (tokens <= 0 || num_segments <= 0) return 0;
   if (!lse_attention_mma_supported(head_dim, n_q, n_kv) || page_size <= 0) return LSE_ERR_BAD_ARGUMENT;
   if (head_dim == 128)
     return launch_prefill<128>(q, k_cache, v_cache, out, block_tables, bt_stride, segment_start, segment_first_pos,
-                               num_segments, tokens, n_q, n_kv, page_size, scale, num_pages, skip_single, stream);
+                               num_segments, tokens, n_q, n_kv, page_size, scale, num_pages, skip_single, max_portions, stream);
   return launch_prefill<64>(q, k_cache, v_cache, out, block_tables, bt_stride, segment_start, segment_first_pos,
-                            num_segments, tokens, n_q, n_kv, page_size, scale, num_pages, skip_single, stream);
+                            num_segments, tokens, n_q, n_kv, page_size, scale, num_pages, skip_single, max_portions, stream);
 }

@@ -118,7 +118,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   // blocks beyond the last tile leave.  Late tiles walk the most keys and are launched first.
   int seg, r0, cnt;
   __shared__ int tile_slot[3];
-  lse_find_tile(segment_start, num_segments, BM, skip_single, (int)(gridDim.x / n_q) - 1 - (int)(blockIdx.x / n_q), tile_slot, seg, r0, cnt);
+  lse_find_tile(segment_start, num_segments, BM, skip_single, (int)(blockIdx.x / n_q), tile_slot, seg, r0, cnt);
 #ifdef LSE_TRACE
   const int block_linear = blockIdx.x;
   if (tid == 0 && block_linear < 4096) { lse_attn_tc_blocks[block_linear * 4] = global_ns(); lse_attn_tc_blocks[block_linear * 4 + 2] = sm_id(); lse_attn_tc_blocks[block_linear * 4 + 3] = 0; }
@@ -455,7 +455,7 @@ template <int D>
 int launch_prefill_tc(const void* q, const void* kc, const void* vc, void* out, const int* block_tables, int bt_stride,
                       const int* segment_start, const int* segment_first_pos, int num_segments, int tokens,
                       long long num_pages, int n_q, int n_kv, int page_size, float scale, int skip_single,
-                      cudaStream_t stream) {
+                      int max_portions, cudaStream_t stream) {
   const size_t smem = attn_tc_smem<D>();
   static bool configured = false;
   if (!configured) {
@@ -468,7 +468,10 @@ int launch_prefill_tc(const void* q, const void* kc, const void* vc, void* out, 
       !make_map_row_groups(&map_k, kc, num_pages * n_kv * page_size, D, page_size) ||
       !make_map_row_groups(&map_v, vc, num_pages * n_kv * page_size, D, page_size))
     return LSE_ERR_BAD_ARGUMENT;
-  const int tiles = (tokens + BM - 1) / BM + num_segments;   // upper bound
+  // upper bound: every request that has tiles may end with a partial one (max_portions > 0: the caller knows that
+  // at most so many requests have tiles, the others bringing single tokens that are skipped)
+  const int with_tiles = (max_portions > 0 && max_portions < num_segments) ? max_portions : num_segments;
+  const int tiles = (tokens + BM - 1) / BM + with_tiles;
   dim3 grid(tiles * n_q);
   cudaError_t err = lse_launch(attn_prefill_tc_kernel<D>, grid, THREADS, smem, stream, map_q, map_k, map_v,
                                (__nv_bfloat16*)out, block_tables, bt_stride, segment_start, segment_first_pos,
@@ -518,14 +521,14 @@ extern "C" int lse_paged_attention_prefill_tc(const void* q, const void* k_cache
                                               const int* block_tables, int bt_stride, const int* segment_start,
                                               const int* segment_first_pos, int num_segments, int tokens,
                                               long long num_pages, int n_q, int n_kv, int head_dim, int page_size,
-                                              float scale, int skip_single, cudaStream_t stream) {
+                                              float scale, int skip_single, int max_portions, cudaStream_t stream) {
   if (tokens <= 0 || num_segments <= 0) return 0;
   if (!lse_attention_tc_supported(head_dim, n_q, n_kv, page_size) || num_pages <= 0 || !(scale > 0.f) ||
       (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15))
     return LSE_ERR_BAD_ARGUMENT;
   if (head_dim == 128)
     return launch_prefill_tc<128>(q, k_cache, v_cache, out, block_tables, bt_stride, segment_start, segment_first_pos,
-                                  num_segments, tokens, num_pages, n_q, n_kv, page_size, scale, skip_single, stream);
+                                  num_segments, tokens, num_pages, n_q, n_kv, page_size, scale, skip_single, max_portions, stream);
   return launch_prefill_tc<64>(q, k_cache, v_cache, out, block_tables, bt_stride, segment_start, segment_first_pos,
-                               num_segments, tokens, num_pages, n_q, n_kv, page_size, scale, skip_single, stream);
+                               num_segments, tokens, num_pages, n_q, n_kv, page_size, scale, skip_single, max_portions, stream);
 }

@@ -77,24 +77,37 @@ inline int lse_pdl_enabled = 1;
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 
-// Which request's which rows tile number `tile` of a launch covers, when every request's rows (segment_start[s] ..
-// segment_start[s + 1]) are cut into tiles of rows_per_tile rows and the tiles are numbered request by request
-// (requests of one row take none when skip_single).  The block's first warp works it out, 32 requests at a time (a
-// step may hold hundreds), and hands it to the other warps through `slot` (three ints of shared memory).  Every
-// thread of the block calls it; it ends with a __syncthreads().  seg = -1: there is no such tile.
+// Which request's which rows the block of rank `rank` covers, when every request's rows (segment_start[s] ..
+// segment_start[s + 1]) are cut into tiles of rows_per_tile rows (requests of one row take none when skip_single).
+// Tiles are numbered request by request and handed out from the last one backwards: rank 0 takes the last tile (late
+// tiles walk the most keys and should start first), and the ranks beyond the number of tiles (a grid is sized by an
+// upper bound) come last and leave at once.  The block's first warp works it out, 32 requests at a time (a step may
+// hold hundreds), and hands it to the other warps through `slot` (three ints of shared memory).  Every thread of
+// the block calls it; it ends with a __syncthreads().  seg = -1: the rank has no tile.
 __device__ __forceinline__ void lse_find_tile(const int* __restrict__ segment_start, int num_segments, int rows_per_tile,
-                                              int skip_single, int tile, int* slot, int& seg, int& r0, int& cnt) {
+                                              int skip_single, int rank, int* slot, int& seg, int& r0, int& cnt) {
   if (threadIdx.x < 32) {
     const int lane = threadIdx.x;
+    auto tiles_of = [&](int s, int& c) {
+      c = 0;
+      if (s >= num_segments) return 0;
+      c = segment_start[s + 1] - segment_start[s];
+      return (skip_single && c == 1) ? 0 : (c + rows_per_tile - 1) / rows_per_tile;
+    };
+    int total = 0;
+    for (int base = 0; base < num_segments; base += 32) {
+      int c;
+      int nt = tiles_of(base + lane, c);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) nt += __shfl_xor_sync(0xffffffffu, nt, o);
+      total += nt;
+    }
+    const int tile = total - 1 - rank;
     int before = 0, found_seg = -1, found_r0 = 0, found_cnt = 0;   // the same in every lane
-    for (int base = 0; base < num_segments && found_seg < 0; base += 32) {
-      const int s = base + lane;
-      int c = 0, nt = 0;
-      if (s < num_segments) {
-        c = segment_start[s + 1] - segment_start[s];
-        nt = (skip_single && c == 1) ? 0 : (c + rows_per_tile - 1) / rows_per_tile;
-      }
-      int incl = nt;   // tiles of the requests base .. s
+    for (int base = 0; base < num_segments && found_seg < 0 && tile >= 0; base += 32) {
+      int c;
+      const int nt = tiles_of(base + lane, c);
+      int incl = nt;   // tiles of the requests base .. base + lane
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
         const int v = __shfl_up_sync(0xffffffffu, incl, o);

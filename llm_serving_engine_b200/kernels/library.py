@@ -40,10 +40,10 @@ _SIGNATURES = {
                                    c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int,
                                    c_void_p, c_void_p],
     "lse_paged_attention_prefill": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
-                                    c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p],
+                                    c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p],
     "lse_attention_mma_supported": [c_int, c_int, c_int],
     "lse_paged_attention_prefill_tc": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
-                                       c_int, c_int, c_longlong, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+                                       c_int, c_int, c_longlong, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p],
     "lse_attention_tc_supported": [c_int, c_int, c_int, c_int],
     "lse_attention_tc_status": [],
     "lse_set_pdl": [c_int],

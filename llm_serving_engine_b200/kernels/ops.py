@@ -296,12 +296,14 @@ def paged_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
 
 def paged_attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
                             block_tables: torch.Tensor, segment_start: torch.Tensor,
-                            segment_first_position: torch.Tensor, scale: float, skip_single: bool = False) -> torch.Tensor:
+                            segment_first_position: torch.Tensor, scale: float, skip_single: bool = False,
+                            max_portions: int = 0) -> torch.Tensor:
     """Attention of prompt portions (any mix of segment lengths): causal inside the portion,
     all earlier keys of the request before it; bfloat16, head size 64 or 128.
 
     segment_start int32 [S + 1]: first row of each segment; segment_first_position int32 [S].
-    ``skip_single``: requests that bring exactly one token are left to :func:`paged_attention_decode`.
+    ``skip_single``: requests that bring exactly one token are left to :func:`paged_attention_decode`;
+    ``max_portions`` (with it): at most so many requests bring more than one token (it sizes the grid).
     """
     _need_cuda(q, k_cache, v_cache, out, block_tables, segment_start, segment_first_position)
     tokens, n_q, head_dim = q.shape
@@ -314,7 +316,8 @@ def paged_attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
     check(lib.lse_paged_attention_prefill(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
                                           block_tables.data_ptr(), block_tables.stride(0), segment_start.data_ptr(),
                                           segment_first_position.data_ptr(), segments, tokens, n_q, n_kv, head_dim,
-                                          page_size, float(scale), k_cache.shape[0], int(skip_single), _stream()),
+                                          page_size, float(scale), k_cache.shape[0], int(skip_single),
+                                          int(max_portions) if skip_single else 0, _stream()),
           "paged_attention_prefill")
     return out
 
@@ -330,7 +333,8 @@ def attention_tc_supported(head_dim: int, n_q: int, n_kv: int, page_size: int, d
 
 def paged_attention_prefill_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
                                block_tables: torch.Tensor, segment_start: torch.Tensor,
-                               segment_first_position: torch.Tensor, scale: float, skip_single: bool = False) -> torch.Tensor:
+                               segment_first_position: torch.Tensor, scale: float, skip_single: bool = False,
+                               max_portions: int = 0) -> torch.Tensor:
     """Attention of prompt portions on the 5th-generation tensor cores: the arguments and the
     result of :func:`paged_attention_prefill`; blocks of 128 rows of one head, keys in tiles of 128
     brought in by TMA page by page, scores and outputs accumulated in tensor memory."""
@@ -346,7 +350,8 @@ def paged_attention_prefill_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: 
     check(lib.lse_paged_attention_prefill_tc(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
                                              block_tables.data_ptr(), block_tables.stride(0), segment_start.data_ptr(),
                                              segment_first_position.data_ptr(), segments, tokens, pages, n_q, n_kv,
-                                             head_dim, page_size, float(scale), int(skip_single), _stream()),
+                                             head_dim, page_size, float(scale), int(skip_single),
+                                             int(max_portions) if skip_single else 0, _stream()),
           "paged_attention_prefill_tc")
     return out
 

@@ -97,11 +97,19 @@ class GroupedQueryAttention(Mixer):
         singles = MIXED_DECODE_KERNEL and any(count == 1 for count in segment_counts) and max(segment_counts) > 1
         return ([count for count in segment_counts if count > 1] if singles else list(segment_counts)), singles
 
+    PORTION_CLASSES = (2, 16)   # beside single tokens: at most so many portions (it sizes the prompt kernel's grid)
+
+    def _portion_class(self, portions: list[int], singles: bool) -> int:
+        """An upper bound on the number of portions that a step of this kind holds beside its single tokens (0: no bound)."""
+        if not singles:
+            return 0
+        return next((bound for bound in self.PORTION_CLASSES if bound >= len(portions)), 0)
+
     def launch_signature(self, segment_counts):
         if max(segment_counts) == 1 or not ops.attention_mma_supported(self.head_dim, self.n_q, self.n_kv, self.ctx.dtype, self.window):
             return ()
         portions, singles = self._portions(segment_counts)
-        return (self.prompt_kernel(portions), singles)
+        return (self.prompt_kernel(portions), singles, self._portion_class(portions, singles))
 
     def forward(self, x, step, cache):
         tokens = x.shape[0]
@@ -126,7 +134,8 @@ class GroupedQueryAttention(Mixer):
                 prompt = (ops.paged_attention_prefill_tc if self.prompt_kernel(portions, cache.keys.shape[2]) == "tcgen05"
                           else ops.paged_attention_prefill)
                 prompt(q, cache.keys, cache.values, attended, cache.block_tables, step.segment_start,
-                       step.segment_first_position, self.scale, skip_single=singles)
+                       step.segment_first_position, self.scale, skip_single=singles,
+                       max_portions=self._portion_class(portions, singles))
         else:   # float32, other head sizes, windows: the general kernel
             ops.paged_attention_generic(q, cache.keys, cache.values, attended, cache.block_tables,
                                         step.segment_of_token, step.positions, self.scale, self.window)

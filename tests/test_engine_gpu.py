@@ -246,7 +246,7 @@ def test_steps_with_prompt_portions_replayed_from_graphs_give_the_same_tokens():
     assert plain.runner.portion_graph_replays == 0
     graphs = engine_for("D", dtype="bfloat16", batch=4, pages=160, budget=24, chunk=16)
     assert graphs.generate_many(prompts, config) == want
-    assert graphs.runner.portion_graph_replays > 10 and len(graphs.runner._portion_graphs) >= 2
+    assert graphs.runner.portion_graph_replays >= 8 and len(graphs.runner._portion_graphs) >= 2
     assert not graphs.cache.requests and graphs.cache.groups[0].pool.used_pages == 0
     # float32 too (the general attention kernel): bit for bit the same logits with and without padding rows
     one = engine_for("B", dtype="float32", batch=3, budget=20, chunk=8)
