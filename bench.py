@@ -419,7 +419,7 @@ def run_ours(args) -> dict:
     torch.cuda.set_device(0)
     layers = args.layers or FULL_LAYERS
     sizes = {"7b": QWEN25_7B_SIZES, "14b": QWEN25_14B_SIZES}.get(args.sizes)
-    model, config = build_model(layers, sizes)
+    model, config = build_model(layers, sizes, dtype=args.dtype if args.only != "all" else "bfloat16")
     peak = peaks()
     weight_bytes = model.weight_bytes_per_step()
     batch = args.batch
@@ -789,6 +789,8 @@ def main() -> int:
     parser.add_argument("--no-graphs", action="store_true", help="decode launch by launch instead of from CUDA graphs")
     parser.add_argument("--sizes", choices=("1.5b", "7b", "14b"), default="1.5b",
                         help="layer sizes (7b, 14b: those of Qwen2.5-7B / 14B; only with --only, give --layers to fit the time)")
+    parser.add_argument("--dtype", choices=("bfloat16", "float32"), default="bfloat16",
+                        help="with --only: the true float32 path instead of the serving precision")
     parser.add_argument("--quick", action="store_true", help="the headline, its points and the end-to-end number only "
                                                              "(no other model sizes, no float32 point, no kernel table)")
     parser.add_argument("--timeline-json", action="store_true", help="with --timeline: also one JSON line of sums per kind of kernel")
