@@ -295,6 +295,32 @@ def time_mixed_traffic(model, requests: int = 32, seed: int = 0):
     return generated / seconds, generated, sum(len(item.prompt_token_ids) for item in traffic), seconds
 
 
+def time_short_requests(model, batch: int, prompt: int = 128, new_tokens: int = 32, chunk: int = 32, repeats: int = 3):
+    """The workload of the reference's committed T4 results (``artifacts/checkpoint3-t4.json``): ``batch`` prompts of
+    ``prompt`` tokens, ``new_tokens`` generated tokens each, prompts fed in portions of ``chunk`` tokens, through the
+    Python entry point.  Returns generated tokens a second over the whole run (the median of ``repeats`` runs)."""
+    import torch
+
+    from llm_serving_engine_b200 import CacheConfig, GenerationConfig, LLMEngine, SchedulerConfig
+
+    engine = LLMEngine(model, None, cache_config=CacheConfig(BLOCK, batch * 16 + 16),
+                       scheduler_config=SchedulerConfig(max_batch_size=batch, max_tokens_per_step=max(chunk, batch)),
+                       prefill_chunk_size=chunk)
+    engine.warmup()
+    generator = torch.Generator().manual_seed(5)
+    rates = []
+    for _ in range(repeats + 1):     # the first run meets every size class for the first time
+        prompts = [torch.randint(0, model.vocab_size, (prompt,), generator=generator).tolist() for _ in range(batch)]
+        torch.cuda.synchronize()
+        started = time.perf_counter()
+        outputs = engine.generate_many(prompts, GenerationConfig(max_new_tokens=new_tokens))
+        torch.cuda.synchronize()
+        rates.append(sum(len(output) for output in outputs) / (time.perf_counter() - started))
+    del engine
+    torch.cuda.empty_cache()
+    return sorted(rates[1:])[repeats // 2]
+
+
 def time_chunks_beside_decoding(model, decoding: int = 8, prompt: int = 8192, chunk: int = 2048):
     """A ``prompt``-token prompt fed in ``chunk``-token portions beside ``decoding`` requests that decode (each
     holds ``chunk`` tokens): device milliseconds of each mixed step."""
@@ -404,7 +430,18 @@ def other_points(args, peak: dict) -> tuple[dict, dict]:
             notes[name] = (f"the headline's model, {ms:.3f} ms a step, "
                            f"{(model.weight_bytes_per_step() + kv_bytes) / (ms / 1e3) / 1e9 / peak['hbm_gbs']:.3f} of the copy bandwidth")
 
+    def short_requests():
+        model, _ = build_model(FULL_LAYERS)
+        published = {1: 18.84, 8: 128.61}    # the reference's own Tesla T4 results for this workload (the real Qwen2.5-1.5B, float16)
+        for batch in (1, 8):
+            rate = time_short_requests(model, batch)
+            name = f"128x32_chunk32_b{batch}_output_tok_s"
+            points[name] = round(rate, 1)
+            notes[name] = (f"{batch} prompts of 128 tokens, 32 generated tokens each, portions of 32, through generate_many; the "
+                           f"reference publishes {published[batch]} on a Tesla T4 for this workload (no B200 figure exists)")
+
     attempt("fp32_decode_b8", float32)
+    attempt("128x32_chunk32", short_requests)
     attempt("ctx30000_decode", long_contexts)
     attempt("7b_mixed32_output_tok_s", sizes_7b)
     attempt("14b", sizes_14b)
