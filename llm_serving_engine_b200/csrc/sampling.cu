@@ -81,14 +81,96 @@ argmax_kernel(const float* __restrict__ logits, long long row_stride, int vocab,
   }
 }
 
-// Sum of the values of `e` that are greater than `threshold`, in a fixed order.
-__device__ float mass_above(const float* e, int vocab, float threshold, float* red) {
-  float s = 0.f;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-    const float v = e[i];
-    if (v > threshold) s += v;
+constexpr int RADIX_BITS = 11;   // the bits of a value are decided 11, 11 and 10 at a time: a histogram of 2,048 bins
+
+// top-p: the smallest threshold t (as the bits of a float in [0, 1]) such that the mass of the values strictly greater
+// than t is below top_p times the whole mass; tokens with e >= t are kept.  Found by three passes over the row, each a
+// histogram of mass by the next bits of the values that share the bits decided so far (what thirty passes of a
+// bisection over the float's bits gave before).  Mass is counted in integers, 2^-31 of the whole mass `total` each
+// (32-bit sums, which do not depend on the order in which threads add: the threshold is the same in every run).
+// top_p = 0 keeps the largest values only.
+__device__ float top_p_threshold(const float* __restrict__ e, int vocab, float top_p, float total, unsigned* hist, int* chosen) {
+  const float unit = 2147483648.0f / total;
+  unsigned prefix = 0;              // the bits decided so far
+  int done = 0;
+  unsigned long long above = 0;     // mass of the values greater than every value with this prefix
+  unsigned long long limit = 0;
+  __shared__ unsigned long long above_s, limit_s;
+  for (int level = 0; level < 3; ++level) {
+    const int bits = level < 2 ? RADIX_BITS : 32 - 2 * RADIX_BITS;
+    const int shift = 32 - done - bits;
+    for (int b = threadIdx.x; b < (1 << bits); b += blockDim.x) hist[b] = 0;
+    __syncthreads();
+    // A thread adds up the values that fall into the same bin one after the other before it touches the histogram: a
+    // narrow distribution (all values in a few bins) then costs an addition a thread, not one a value.  Values are
+    // fetched eight at a time (two 16-byte loads in flight), neighbours in the vocabulary.
+    {
+      unsigned held_bin = 0xffffffffu, held = 0;
+      auto take = [&](float v) {
+        const unsigned u = __float_as_uint(v);
+        if (done != 0 && (u >> (32 - done)) != prefix) return;
+        const unsigned bin = (u >> shift) & ((1u << bits) - 1u);
+        if (bin != held_bin) {
+          if (held_bin != 0xffffffffu) atomicAdd(&hist[held_bin], held);
+          held_bin = bin;
+          held = 0;
+        }
+        held += __float2uint_rz(v * unit);
+      };
+      const int quads = (((uintptr_t)e & 15) == 0) ? vocab / 4 : 0;
+      const float4* e4 = reinterpret_cast<const float4*>(e);
+      for (int j = threadIdx.x; j < quads; j += 2 * blockDim.x) {
+        const bool two = j + (int)blockDim.x < quads;
+        const float4 a = e4[j];
+        const float4 b = two ? e4[j + blockDim.x] : a;
+        take(a.x); take(a.y); take(a.z); take(a.w);
+        if (two) { take(b.x); take(b.y); take(b.z); take(b.w); }
+      }
+      for (int i = 4 * quads + threadIdx.x; i < vocab; i += blockDim.x) take(e[i]);
+      if (held_bin != 0xffffffffu) atomicAdd(&hist[held_bin], held);
+    }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      // The lowest bin whose values all leave less than `limit` above them.  A lane owns a run of bins; the mass above
+      // a lane's top bin is a suffix sum over the lanes; the lowest lane whose top bin qualifies holds the bin.
+      const int lane = threadIdx.x, per = (1 << bits) / 32;
+      unsigned long long mine = 0;
+      for (int k = 0; k < per; ++k) mine += hist[lane * per + k];
+      auto shuffle_down = [](unsigned long long v, int o) {
+        const unsigned lo = __shfl_down_sync(0xffffffffu, (unsigned)v, o), hi = __shfl_down_sync(0xffffffffu, (unsigned)(v >> 32), o);
+        return ((unsigned long long)hi << 32) | lo;
+      };
+      unsigned long long suffix = mine;   // mass of this lane's bins and of all lanes above
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const unsigned long long v = shuffle_down(suffix, o);
+        if (lane + o < 32) suffix += v;
+      }
+      if (level == 0) {
+        const unsigned lo = __shfl_sync(0xffffffffu, (unsigned)suffix, 0), hi = __shfl_sync(0xffffffffu, (unsigned)(suffix >> 32), 0);
+        limit = (unsigned long long)((double)top_p * (double)(((unsigned long long)hi << 32) | lo));
+      }
+      const unsigned long long over_top = above + suffix - mine;   // mass above this lane's top bin
+      const unsigned qualifies = __ballot_sync(0xffffffffu, over_top < limit);
+      const int holder = qualifies ? __ffs(qualifies) - 1 : 31;
+      if (lane == holder) {
+        unsigned long long c = over_top;
+        int b = lane * per + per - 1;
+        const int bottom = lane * per;
+        while (b > bottom && c + hist[b] < limit) { c += hist[b]; --b; }
+        *chosen = b;
+        above_s = c;
+        limit_s = limit;
+      }
+    }
+    __syncthreads();
+    prefix = (prefix << bits) | (unsigned)*chosen;
+    above = above_s;
+    limit = limit_s;
+    done += bits;
+    __syncthreads();
   }
-  return block_sum(s, red);
+  return limit == 0 ? 1.0f : __uint_as_float(prefix);   // nothing may lie above: only the largest values (e = 1) stay
 }
 
 __global__ void __launch_bounds__(THREADS)
@@ -98,6 +180,7 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int vocab,
               float* __restrict__ scratch, int* __restrict__ out) {
   __shared__ float red[32];
   __shared__ float chunk_sum[THREADS];
+  __shared__ unsigned hist[1 << RADIX_BITS];
   __shared__ int chosen;
   pdl_launch_dependents();
   pdl_wait();
@@ -123,26 +206,43 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int vocab,
     return;
   }
   const float inv_t = 1.0f / temp;
+  // sixteen-byte loads, two of them in flight a thread, where the row allows it; the rest one value at a time
+  const int quads = ((((uintptr_t)row | (uintptr_t)e) & 15) == 0) ? vocab / 4 : 0;
+  const float4* row4 = reinterpret_cast<const float4*>(row);
+  float4* e4 = reinterpret_cast<float4*>(e);
   float mx = -INFINITY;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) mx = fmaxf(mx, row[i] * inv_t);
+  for (int j = threadIdx.x; j < quads; j += 2 * blockDim.x) {
+    const float4 a = row4[j];
+    const float4 b = j + (int)blockDim.x < quads ? row4[j + blockDim.x] : a;
+    mx = fmaxf(mx, fmaxf(fmaxf(a.x, a.y), fmaxf(a.z, a.w)) * inv_t);
+    mx = fmaxf(mx, fmaxf(fmaxf(b.x, b.y), fmaxf(b.z, b.w)) * inv_t);
+  }
+  for (int i = 4 * quads + threadIdx.x; i < vocab; i += blockDim.x) mx = fmaxf(mx, row[i] * inv_t);
   mx = block_max(mx, red);
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) e[i] = expf(row[i] * inv_t - mx);
+  float mass = 0.f;
+  for (int j = threadIdx.x; j < quads; j += 2 * blockDim.x) {
+    const bool two = j + (int)blockDim.x < quads;
+    const float4 a = row4[j];
+    const float4 b = two ? row4[j + blockDim.x] : a;
+    const float4 ea = make_float4(expf(a.x * inv_t - mx), expf(a.y * inv_t - mx), expf(a.z * inv_t - mx), expf(a.w * inv_t - mx));
+    e4[j] = ea;
+    mass += (ea.x + ea.y) + (ea.z + ea.w);
+    if (two) {
+      const float4 eb = make_float4(expf(b.x * inv_t - mx), expf(b.y * inv_t - mx), expf(b.z * inv_t - mx), expf(b.w * inv_t - mx));
+      e4[j + blockDim.x] = eb;
+      mass += (eb.x + eb.y) + (eb.z + eb.w);
+    }
+  }
+  for (int i = 4 * quads + threadIdx.x; i < vocab; i += blockDim.x) {
+    const float v = expf(row[i] * inv_t - mx);
+    e[i] = v;
+    mass += v;
+  }
   __syncthreads();
 
-  // top-p: smallest threshold (as float bits) whose strictly-greater mass is below top_p * Z
   float keep_from = 0.f;  // keep e_i >= keep_from
   const float p = top_p[r];
-  if (p < 1.0f) {
-    const float total = mass_above(e, vocab, -1.f, red);
-    const float limit = p * total;
-    unsigned lo = 0u, hi = 0x3F800000u;  // bits of 0.0f .. 1.0f; e_i <= 1 so mass_above(1.0) = 0 < limit
-    while (lo < hi) {
-      const unsigned mid = lo + ((hi - lo) >> 1);
-      const float m = mass_above(e, vocab, __uint_as_float(mid), red);
-      if (m < limit) hi = mid; else lo = mid + 1;
-    }
-    keep_from = __uint_as_float(lo);
-  }
+  if (p < 1.0f) keep_from = top_p_threshold(e, vocab, p, block_sum(mass, red), hist, &chosen);
 
   // inverse CDF over the kept tokens, vocabulary order: thread c owns the chunk [c*per, (c+1)*per)
   const int per = (vocab + THREADS - 1) / THREADS;
@@ -152,12 +252,25 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int vocab,
   chunk_sum[threadIdx.x] = mine;
   if (threadIdx.x == 0) chosen = -1;
   __syncthreads();
-  if (threadIdx.x == 0) {
-    float total = 0.f;
-    for (int c = 0; c < THREADS; ++c) total += chunk_sum[c];
+  if (threadIdx.x < 32) {
+    // which chunk holds the draw: a lane adds up 32 chunks, the lanes' sums are scanned, and the first lane whose
+    // chunks reach the target walks them (one thread walking all 1,024 sums took 15 us)
+    const int lane = threadIdx.x;
+    float lane_sum = 0.f;
+    for (int k = 0; k < THREADS / 32; ++k) lane_sum += chunk_sum[lane * (THREADS / 32) + k];
+    float incl = lane_sum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    const float total = __shfl_sync(0xffffffffu, incl, 31);
     const float target = uniform01(seed[r], counter[r]) * total;
-    float run = 0.f;
-    int c = 0;
+    const unsigned reaches = __ballot_sync(0xffffffffu, incl > target);
+    const int holder = reaches ? __ffs(reaches) - 1 : 31;
+    if (lane != holder) return;
+    float run = incl - lane_sum;     // the kept mass of the chunks before this lane's
+    int c = lane * (THREADS / 32);
     for (; c < THREADS - 1; ++c) {
       if (run + chunk_sum[c] > target) break;
       run += chunk_sum[c];
