@@ -141,7 +141,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
                    const int* __restrict__ block_tables, int bt_stride,
                    const int* __restrict__ segment_of_token, const int* __restrict__ positions,
                    int n_q, int n_kv, int page_size, float scale_log2e, int num_splits, int dry_run, int num_pages,
-                   int num_segments, const int* __restrict__ segment_start) {
+                   int num_segments, const int* __restrict__ segment_start,
+                   const int* __restrict__ segment_first_pos) {
   constexpr int CH = D / 8;                 // 16-byte chunks per row
   constexpr int TILE_BYTES = DEC_TILE * D * 2;
   extern __shared__ __align__(128) unsigned char smem[];
@@ -225,12 +226,14 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   // Keys and values of earlier steps do not depend on the kernels before this one: the first tiles are
   // fetched at once, while those kernels may still run.  Only the tile that holds the row's own position
   // (its key and value were written just before this kernel) has to wait.
-  const int newest_tile = (ctx - 1) / DEC_TILE;
-  int deferred = -1;
+  // Keys that this very step writes are not fetched before the wait: the row's own position, or (a row of a prompt
+  // portion: segment_first_pos given) everything from the portion's first position on.
+  const int newest_tile = (segment_first_pos ? segment_first_pos[seg] : ctx - 1) / DEC_TILE;
+  unsigned deferred = 0;   // stages whose tile waits
 #pragma unroll
   for (int s = 0; s < DEC_STAGES; ++s) {
     if (s < n_mine) {
-      if (first + 4 * s == newest_tile) deferred = s;
+      if (first + 4 * s >= newest_tile) deferred |= 1u << s;
       else load_tile(first + 4 * s, s);
     }
     cp_async_commit();
@@ -253,8 +256,10 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   if (pass == 1) {
     pdl_wait();
     LSE_TL_MARK(2)
-    if (deferred >= 0) {   // one warp of one split: the tile comes from the L2, and the warp waits for it here
-      load_tile(newest_tile, deferred);
+    if (deferred) {   // (decoding: one warp of one split) the tiles come from the L2, and the warp waits for them here
+#pragma unroll
+      for (int s = 0; s < DEC_STAGES; ++s)
+        if (deferred & (1u << s)) load_tile(first + 4 * s, s);
       cp_async_commit();
       cp_async_wait<0>();
     }
@@ -704,7 +709,7 @@ template <int D, bool CLUSTER>
 int launch_decode_as(const void* q, const void* kc, const void* vc, void* out, float* part_o, float* part_ml,
                      int* arrivals, const int* block_tables, int bt_stride, const int* seg, const int* positions,
                      int tokens, int n_q, int n_kv, int page_size, float scale, int num_splits, int num_pages,
-                     int num_segments, const int* segment_start, cudaStream_t stream) {
+                     int num_segments, const int* segment_start, const int* segment_first_pos, cudaStream_t stream) {
   const size_t smem = decode_smem<D>();
   static bool configured = false;   // once per process: not repeated while a stream is captured
   if (!configured) {
@@ -718,7 +723,7 @@ int launch_decode_as(const void* q, const void* kc, const void* vc, void* out, f
       CLUSTER ? (unsigned)num_splits : 1u,
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, (__nv_bfloat16*)out, part_o,
       part_ml, arrivals, block_tables, bt_stride, seg, positions, n_q, n_kv, page_size, scale * LOG2E, num_splits,
-      lse_pdl_enabled ? 1 : 0, num_pages, num_segments, segment_start);
+      lse_pdl_enabled ? 1 : 0, num_pages, num_segments, segment_start, segment_first_pos);
   if (err != cudaSuccess) return (int)err;
   return (int)cudaGetLastError();
 }
@@ -727,12 +732,15 @@ template <int D>
 int launch_decode(const void* q, const void* kc, const void* vc, void* out, float* part_o, float* part_ml,
                   int* arrivals, const int* block_tables, int bt_stride, const int* seg, const int* positions,
                   int tokens, int n_q, int n_kv, int page_size, float scale, int num_splits, int cluster,
-                  int num_pages, int num_segments, const int* segment_start, cudaStream_t stream) {
+                  int num_pages, int num_segments, const int* segment_start, const int* segment_first_pos,
+                  cudaStream_t stream) {
   if (cluster && num_splits > 1 && num_splits <= 8)
     return launch_decode_as<D, true>(q, kc, vc, out, part_o, part_ml, arrivals, block_tables, bt_stride, seg, positions,
-                                     tokens, n_q, n_kv, page_size, scale, num_splits, num_pages, num_segments, segment_start, stream);
+                                     tokens, n_q, n_kv, page_size, scale, num_splits, num_pages, num_segments, segment_start,
+                                     segment_first_pos, stream);
   return launch_decode_as<D, false>(q, kc, vc, out, part_o, part_ml, arrivals, block_tables, bt_stride, seg, positions,
-                                    tokens, n_q, n_kv, page_size, scale, num_splits, num_pages, num_segments, segment_start, stream);
+                                    tokens, n_q, n_kv, page_size, scale, num_splits, num_pages, num_segments, segment_start,
+                                     segment_first_pos, stream);
 }
 
 template <int D>
@@ -777,6 +785,8 @@ extern "C" long long lse_attention_decode_scratch_floats(int tokens, int n_q, in
 // `cluster` != 0 and 2 <= num_splits <= 8: the splits form a thread-block cluster and need neither
 // `scratch` nor `arrivals`.  Else `scratch` holds the partial sums and `arrivals` is tokens * n_kv *
 // ceil(group / 8) ints that are zero before the first launch (the kernel leaves them zero).
+// segment_first_pos != null: the rows may be rows of prompt portions (several rows of a request in one step); a row
+// then fetches nothing from its request's first position of this step on before the kernels before have finished.
 // segment_start != null (a step that also holds prompt portions): `tokens` counts the step's requests, block x
 // of the grid is request x, and only requests that bring exactly one token are worked on (its row is
 // segment_start[x]); scratch and arrivals are then sized by the number of requests.
@@ -786,7 +796,7 @@ extern "C" int lse_paged_attention_decode(const void* q, const void* k_cache, co
                                           const int* segment_of_token, const int* positions, int tokens,
                                           int n_q, int n_kv, int head_dim, int page_size, float scale,
                                           int num_splits, int num_pages, int num_segments, const int* segment_start,
-                                          cudaStream_t stream) {
+                                          const int* segment_first_pos, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (!lse_attention_mma_supported(head_dim, n_q, n_kv) || page_size <= 0 || num_splits < 1 || num_splits > 32)
     return LSE_ERR_BAD_ARGUMENT;
@@ -797,10 +807,10 @@ extern "C" int lse_paged_attention_decode(const void* q, const void* k_cache, co
   if (head_dim == 128)
     return launch_decode<128>(q, k_cache, v_cache, out, part_o, part_ml, arrivals, block_tables, bt_stride,
                               segment_of_token, positions, tokens, n_q, n_kv, page_size, scale, num_splits, cluster, num_pages,
-                              num_segments, segment_start, stream);
+                              num_segments, segment_start, segment_first_pos, stream);
   return launch_decode<64>(q, k_cache, v_cache, out, part_o, part_ml, arrivals, block_tables, bt_stride,
                            segment_of_token, positions, tokens, n_q, n_kv, page_size, scale, num_splits, cluster, num_pages,
-                           num_segments, segment_start, stream);
+                           num_segments, segment_start, segment_first_pos, stream);
 }
 
 extern "C" int lse_paged_attention_prefill(const void* q, const void* k_cache, const void* v_cache, void* out,

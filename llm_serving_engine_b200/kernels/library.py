@@ -38,7 +38,7 @@ _SIGNATURES = {
     "lse_attention_generic_chunk": [],
     "lse_paged_attention_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
                                    c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int,
-                                   c_void_p, c_void_p],
+                                   c_void_p, c_void_p, c_void_p],
     "lse_paged_attention_prefill": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                     c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p],
     "lse_attention_mma_supported": [c_int, c_int, c_int],

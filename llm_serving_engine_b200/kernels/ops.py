@@ -263,11 +263,14 @@ def _arrival_counters(device, count: int) -> torch.Tensor:
 def paged_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
                            block_tables: torch.Tensor, segment_of_token: torch.Tensor, positions: torch.Tensor,
                            scale: float, num_splits: int, cluster: bool = True,
-                           segment_start: torch.Tensor | None = None) -> torch.Tensor:
+                           segment_start: torch.Tensor | None = None,
+                           segment_first_position: torch.Tensor | None = None) -> torch.Tensor:
     """Attention of single decoded tokens (one row per request) with the keys split over
     ``num_splits`` blocks; bfloat16, head size 64 or 128.  With ``segment_start`` (int32 [S + 1], a step that
     also holds prompt portions) the rows are those of the requests that bring exactly one token, wherever they
-    lie among q's rows; the other rows of ``out`` are left alone."""
+    lie among q's rows; the other rows of ``out`` are left alone.  With ``segment_first_position`` (int32 [S])
+    the rows may be rows of prompt portions, several of a request: every row walks its keys on its own (for
+    steps of few rows, where the prompt kernels would leave most of the GPU idle)."""
     _need_cuda(q, k_cache, v_cache, out, block_tables, segment_of_token, positions)
     tokens, n_q, head_dim = q.shape
     n_kv, page_size = k_cache.shape[1], k_cache.shape[2]
@@ -289,7 +292,7 @@ def paged_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
                                          block_tables.stride(0),
                                          segment_of_token.data_ptr(), positions.data_ptr(), tokens, n_q, n_kv,
                                          head_dim, page_size, float(scale), int(num_splits), k_cache.shape[0],
-                                         block_tables.shape[0], _ptr(segment_start), _stream()),
+                                         block_tables.shape[0], _ptr(segment_start), _ptr(segment_first_position), _stream()),
           "paged_attention_decode")
     return out
 

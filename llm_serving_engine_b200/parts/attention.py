@@ -24,6 +24,11 @@ TCGEN05_MIN_ROWS_PER_REQUEST = 64
 TCGEN05_BLOCKS_AT_ONCE = 148
 TCGEN05_PREFILL = os.environ.get("LSE_PREFILL_ATTENTION", "tcgen05") != "mma"
 MIXED_DECODE_KERNEL = os.environ.get("LSE_MIXED_DECODE_KERNEL", "1") != "0"
+# A step of fewer rows than this (portions and single tokens together) goes to the decode kernel row by row: a prompt
+# kernel would have a handful of blocks, each walking all keys of its request (64 rows on 8,000 earlier keys: 51 against
+# 151 us; 16 rows: 21 against 150 us; on 200 keys no difference).  LSE_ROWS_KERNEL_BELOW=0 turns it off.
+ROWS_KERNEL_BELOW = int(os.environ.get("LSE_ROWS_KERNEL_BELOW", "128"))
+ROWS_KERNEL_BLOCKS = 256
 
 
 @register_mixer("gqa_attention")
@@ -108,6 +113,8 @@ class GroupedQueryAttention(Mixer):
     def launch_signature(self, segment_counts):
         if max(segment_counts) == 1 or not ops.attention_mma_supported(self.head_dim, self.n_q, self.n_kv, self.ctx.dtype, self.window):
             return ()
+        if sum(segment_counts) < ROWS_KERNEL_BELOW:
+            return ("rows",)
         portions, singles = self._portions(segment_counts)
         return (self.prompt_kernel(portions), singles, self._portion_class(portions, singles))
 
@@ -123,6 +130,13 @@ class GroupedQueryAttention(Mixer):
                 splits = ops.decode_splits(tokens, self.n_q, self.n_kv, step.max_context, getattr(step, "long_context", False))
                 ops.paged_attention_decode(q, cache.keys, cache.values, attended, cache.block_tables,
                                            step.segment_of_token, step.positions, self.scale, splits)
+            elif sum(segment.count for segment in step.segments) < ROWS_KERNEL_BELOW:
+                # few rows: every row walks its keys on its own, split over blocks (256 blocks or so), as in a decode step
+                blocks_a_split = tokens * self.n_kv * ((self.n_q // self.n_kv + 7) // 8)
+                ops.paged_attention_decode(q, cache.keys, cache.values, attended, cache.block_tables,
+                                           step.segment_of_token, step.positions, self.scale,
+                                           max(1, min(8, ROWS_KERNEL_BLOCKS // blocks_a_split)),
+                                           segment_first_position=step.segment_first_position)
             else:
                 portions, singles = self._portions([segment.count for segment in step.segments])
                 if singles:   # one block row per request of the step; requests with portions leave at once

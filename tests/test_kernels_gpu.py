@@ -691,6 +691,40 @@ def test_tcgen05_prefill_attention(head_dim, n_q, n_kv, page):
         assert float(err.max()) < 2.0 ** -7 * max(1.0, float(want.abs().max())), (s, before, rows, float(err.max()))
 
 
+@pytest.mark.parametrize("head_dim, n_q, n_kv, page, splits", [(128, 12, 2, 16, 2), (64, 6, 2, 8, 8), (128, 7, 1, 32, 1), (64, 16, 2, 16, 20)])
+def test_decode_kernel_takes_the_rows_of_prompt_portions(head_dim, n_q, n_kv, page, splits):
+    """Rows of prompt portions through the decode kernel, every row on its own: several rows of a request in one
+    launch, each seeing the keys up to its own position, those of the earlier rows of its portion included (which
+    the same step wrote: with the portions' first positions the kernel fetches none of them ahead of its wait).
+    Every row against dense attention; a key right after a row's position looks like its query and must not be read."""
+    rng = random.Random(head_dim + splits)
+    torch.manual_seed(n_q + splits)
+    portions = [(700, 40), (0, 33), (40, 1), (0, 1), (1999, 17), (15, 2), (3000, 30)]   # (keys before, rows)
+    contexts = [before + rows for before, rows in portions]
+    k_cache, v_cache, tables, dense = paged_setup(rng, contexts, n_kv, head_dim, page, torch.bfloat16)
+    starts = [0]
+    for _, rows in portions:
+        starts.append(starts[-1] + rows)
+    q = torch.randn(starts[-1], n_q, head_dim, device=DEV).bfloat16()
+    for s, (before, rows) in enumerate(portions):   # the key after row `local` of a portion matches that row's query
+        k, _ = dense[s]
+        for local in range(rows - 1):
+            position = before + local + 1
+            k[position, :] = (q[starts[s] + local, 0].float() * 4).bfloat16()
+            k_cache[int(tables[s, position // page]), :, position % page] = k[position]
+    poison_unowned(k_cache, v_cache, tables, contexts, page)
+    segs = torch.cat([torch.full((rows,), s, dtype=torch.int32) for s, (_, rows) in enumerate(portions)]).to(DEV)
+    positions = torch.cat([torch.arange(before, before + rows, dtype=torch.int32) for before, rows in portions]).to(DEV)
+    first_t = torch.tensor([before for before, _ in portions], dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(head_dim)
+    out = torch.full_like(q, 9.0)
+    ops().paged_attention_decode(q, k_cache, v_cache, out, tables, segs, positions, scale, splits, segment_first_position=first_t)
+    for s, (before, rows) in enumerate(portions):
+        want = dense_causal(q[starts[s]:starts[s + 1]], dense[s][0], dense[s][1], before, scale)
+        err = float((out[starts[s]:starts[s + 1]].double() - want).abs().max())
+        assert err < 2.0 ** -7 * max(1.0, float(want.abs().max())), (s, before, rows, err)
+
+
 @pytest.mark.parametrize("prompt_kernel", ["tcgen05", "mma"])
 @pytest.mark.parametrize("head_dim, n_q, n_kv, page, splits", [(128, 12, 2, 16, 8), (64, 6, 2, 8, 3), (128, 7, 1, 32, 1), (64, 16, 2, 16, 20)])
 def test_single_tokens_beside_portions_go_to_the_decode_kernel(prompt_kernel, head_dim, n_q, n_kv, page, splits):
