@@ -42,6 +42,8 @@ constexpr int THREADS = 352;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float RESCALE_STEP = 8.0f;   // in powers of two
 constexpr float REDO_STEP = 64.0f;
+constexpr int MIN_TILES_A_PART = 4;    // a block that takes a part of a tile's keys takes at least so many key tiles
+constexpr int MAX_PARTS = 8;
 constexpr uint32_t HALF_BYTES = 128 * 128;   // a box of 128 rows x 64 bfloat16
 
 __device__ int lse_attn_tc_error;
@@ -79,6 +81,9 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 __device__ __forceinline__ void pair_barrier(int quarter) {   // the warps of the two groups that own the same 32 rows
   asm volatile("bar.sync %0, %1;\n" ::"r"(1 + quarter), "r"(64) : "memory");
 }
+__device__ __forceinline__ void softmax_barrier() {   // the eight softmax warps
+  asm volatile("bar.sync 5, 256;\n" ::: "memory");
+}
 template <int D>
 constexpr size_t attn_tc_smem() {
   // alignment slack, Q, a key and a value stage and a probability tile per group, barriers
@@ -91,7 +96,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
                        const int* __restrict__ block_tables, int bt_stride, const int* __restrict__ segment_start,
                        const int* __restrict__ segment_first_pos, int num_segments, int n_q, int n_kv, int page_size,
-                       float scale_log2e, int num_pages, int skip_single) {
+                       float scale_log2e, int num_pages, int skip_single, int parts, float* __restrict__ scratch,
+                       int* __restrict__ counters) {
   constexpr int HALVES = D / 64;
   constexpr uint32_t Q_BYTES = HALVES * HALF_BYTES, KV_BYTES = HALVES * HALF_BYTES, P_BYTES = 2 * HALF_BYTES;
   constexpr uint32_t GROUP_BYTES = HALVES * 1024;   // 8 keys (or values) in a stage: 8 rows x 128 bytes for every 64 columns
@@ -110,7 +116,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // blocks are numbered tile by tile, all heads of a tile side by side: the blocks that walk the most
   // keys (the last tiles) start first, whatever their head
+  // With parts > 1 (a launch of few blocks) every tile of rows has `parts` blocks side by side, which share its keys
+  // when they are many (below).
   const int head = blockIdx.x % n_q;
+  const int part = (int)(blockIdx.x / n_q) % parts;
+  const int rank = (int)(blockIdx.x / n_q) / parts;
   const int kvh = head / (n_q / n_kv);
   pdl_launch_dependents();
 
@@ -118,7 +128,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   // blocks beyond the last tile leave.  Late tiles walk the most keys and are launched first.
   int seg, r0, cnt;
   __shared__ int tile_slot[3];
-  lse_find_tile(segment_start, num_segments, BM, skip_single, (int)(blockIdx.x / n_q), tile_slot, seg, r0, cnt);
+  lse_find_tile(segment_start, num_segments, BM, skip_single, rank, tile_slot, seg, r0, cnt);
 #ifdef LSE_TRACE
   const int block_linear = blockIdx.x;
   if (tid == 0 && block_linear < 4096) { lse_attn_tc_blocks[block_linear * 4] = global_ns(); lse_attn_tc_blocks[block_linear * 4 + 2] = sm_id(); lse_attn_tc_blocks[block_linear * 4 + 3] = 0; }
@@ -131,6 +141,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const int n_tiles = last_pos / BN + 1;
   const int n_pages = last_pos / page_size + 1;
   const int* bt = block_tables + (size_t)seg * bt_stride;
+  // The keys of a tile of rows are shared by as many of its blocks as get MIN_TILES_A_PART key tiles each; the others
+  // leave.  Every sharing block leaves its part in global memory, and the one that arrives last adds the parts up.
+  const int sharing = max(1, min(parts, n_tiles / MIN_TILES_A_PART));
+  if (part >= sharing) return;
+  const int j_lo = (int)((long long)part * n_tiles / sharing);
+  const int n_local = (int)((long long)(part + 1) * n_tiles / sharing) - j_lo;
+  const int slot = rank * n_q + head;
 #ifdef LSE_TRACE
   const bool traced = seg == 0 && head == 0 && r0 + BM >= cnt && (tid == 0 || tid == GROUP_THREADS || tid == MMA_WARP * 32 || tid == PV_WARP * 32);
 #endif
@@ -139,6 +156,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     for (int i = 0; i < B_COUNT; ++i)
       mbar_init(bar(i), (i >= B_PF && i < B_PF + 2) ? GROUP_THREADS : 1);
     *abort_flag = 0;
+    *reinterpret_cast<volatile int*>(tail + 8 * B_COUNT + 12) = 1;
     mbar_init_fence();
   }
   if (warp == MMA_WARP) tmem_alloc(tmem_slot, 512);   // S and O (at most 128 columns each) of both groups
@@ -158,11 +176,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       mbar_expect_tx(bar(B_Q), Q_BYTES);
       for (int h = 0; h < HALVES; ++h) tma_load_3d(q_s + h * HALF_BYTES, &map_q, bar(B_Q), h * 64, head, row_base);
     }
-    auto page_of = [&](int j) { return (j < n_tiles && lane < min(ppt, n_pages - j * ppt)) ? LSE_CHECKED(bt[j * ppt + lane], 0, num_pages, 0, LSE_CHECK_TABLE_ENTRY) : 0; };
-    auto load = [&](int j, int page, uint32_t dst, const CUtensorMap* map, int full, int empty) -> bool {
-      const int g = j & 1;
-      const uint32_t parity = (uint32_t)(j >> 1) & 1u;
-      const int np = min(ppt, n_pages - j * ppt);
+    // tiles are counted from this block's first one (jj); the keys of tile jj are those of tile j_lo + jj
+    auto page_of = [&](int jj) {
+      const int j = j_lo + jj;
+      return (jj < n_local && lane < min(ppt, n_pages - j * ppt)) ? LSE_CHECKED(bt[j * ppt + lane], 0, num_pages, 0, LSE_CHECK_TABLE_ENTRY) : 0;
+    };
+    auto load = [&](int jj, int page, uint32_t dst, const CUtensorMap* map, int full, int empty) -> bool {
+      const int g = jj & 1;
+      const uint32_t parity = (uint32_t)(jj >> 1) & 1u;
+      const int np = min(ppt, n_pages - (j_lo + jj) * ppt);
       int ok = 1;
       if (lane == 0) ok = mbar_wait(bar(empty + g), parity ^ 1u, abort_flag, err) ? 1 : 0;
       if (!__shfl_sync(0xffffffffu, ok, 0)) return false;
@@ -175,10 +197,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     };
     int page_k = page_of(0), page_v = page_k;
     bool ok = load(0, page_k, k_s, &map_k, B_KF, B_KE);
-    for (int j = 0; j < n_tiles && ok; ++j) {
-      page_k = page_of(j + 1);
-      if (j + 1 < n_tiles) ok = load(j + 1, page_k, k_s, &map_k, B_KF, B_KE);
-      if (ok) ok = load(j, page_v, v_s, &map_v, B_VF, B_VE);
+    for (int jj = 0; jj < n_local && ok; ++jj) {
+      page_k = page_of(jj + 1);
+      if (jj + 1 < n_local) ok = load(jj + 1, page_k, k_s, &map_k, B_KF, B_KE);
+      if (ok) ok = load(jj, page_v, v_s, &map_v, B_VF, B_VE);
       page_v = page_k;
     }
   } else if (warp == MMA_WARP) {
@@ -188,7 +210,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       // wait that matters then comes last.
       const uint32_t idesc_s = instr_desc_bf16(BM, BN, false, false);
       bool ok = mbar_poll(bar(B_Q), 0, abort_flag, err);
-      for (int j = 0; j < n_tiles && ok; ++j) {
+      for (int j = 0; j < n_local && ok; ++j) {
         const int g = j & 1;
         const uint32_t parity = (uint32_t)(j >> 1) & 1u;
         TC_STAMP2(j, 1)
@@ -217,13 +239,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       // O_g += P_i V_i as soon as the probabilities of tile i are written
       const uint32_t idesc_o = instr_desc_bf16(BM, D, false, true);
       bool ok = true;
-      for (int i = 0; i < n_tiles && ok; ++i) {
+      for (int i = 0; i < n_local && ok; ++i) {
         const int g = i & 1;
         const uint32_t parity = (uint32_t)(i >> 1) & 1u;
         TC_STAMP2(i, 0)
         ok = mbar_poll(bar(B_VF + g), parity, abort_flag, err) && mbar_poll(bar(B_PF + g), parity, abort_flag, err);
         // the scores of the group's next tile go first (the group waits for them; this product is wanted later)
-        if (ok && i + GROUPS < n_tiles) ok = mbar_poll(bar(B_KE + g), parity ^ 1u, abort_flag, err);
+        if (ok && i + GROUPS < n_local) ok = mbar_poll(bar(B_KE + g), parity ^ 1u, abort_flag, err);
         if (!ok) break;
         fence_after_sync();
         TC_STAMP2(i, 3)
@@ -259,14 +281,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const bool done = mbar_test(bar(which), parity) || mbar_wait(bar(which), parity, abort_flag, err);
       return __all_sync(0xffffffffu, done ? 1 : 0) != 0;
     };
-    for (int j = g; j < n_tiles && ok; j += GROUPS) {
+    for (int j = g; j < n_local && ok; j += GROUPS) {   // j counts this block's tiles
       const uint32_t parity = (uint32_t)(j >> 1) & 1u;
       TC_STAMP(j, 0)
       ok = wait_all(B_SF + g, parity);
       if (!ok) break;
       TC_STAMP(j, 1)
       fence_after_sync();
-      const int kv0 = j * BN;
+      const int kv0 = (j_lo + j) * BN;
       const bool diagonal = kv0 + BN - 1 > my_pos;   // some keys of this tile lie beyond this row's position
       const bool first = j < GROUPS;                 // this group's first tile
       bool rescale = false;
@@ -287,7 +309,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
           for (int i = 0; i < 32; i += 2) mx = fmaxf(mx, fmaxf(__uint_as_float(s[i]), __uint_as_float(s[i + 1])));
         }
-        // a row of tile 0 always sees key 0; tile 1 may be hidden entirely (-inf: nothing is added then)
+        // a row of tile 0 always sees key 0; a row's last tile may be hidden entirely (-inf: nothing is added then)
         m_used = m_seen = mx * scale_log2e;
       } else if (pending) {   // the tile before raised the maximum by more than the step: O and the sum follow now
         rescale = true;
@@ -377,12 +399,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         l *= alpha;
       }
       TC_STAMP(j, 4)
-      if (j == n_tiles - 1 && last_pos + 1 - j * BN < BN) {
+      if (j_lo + j == n_tiles - 1 && last_pos + 1 - kv0 < BN) {
         // rows of V beyond the last key: whatever lies there (stale keys, unwritten shared memory)
         // must not meet the zero probabilities as NaN or infinity
         ok = wait_all(B_VF + g, parity);
         if (!ok) break;
-        const int valid = last_pos + 1 - j * BN, chunks = (BN - valid) * 8;
+        const int valid = last_pos + 1 - kv0, chunks = (BN - valid) * 8;
         for (int idx = tid - g * GROUP_THREADS; idx < chunks * HALVES; idx += GROUP_THREADS) {
           const int h = idx / chunks, rem = idx % chunks;
           const int r = valid + rem / 8;
@@ -404,38 +426,118 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     mine[128 + row] = l;
     pair_barrier(quarter);
     const float m_other = other[row], l_other = other[128 + row];
-    const float m_all = fmaxf(m_used, m_other);                      // finite: group 0 saw key 0
+    const float m_all = fmaxf(m_used, m_other);                      // finite when the block holds key 0
     const float w_mine = m_used == -INFINITY ? 0.f : exp2_fast(m_used - m_all);
     const float w_other = m_other == -INFINITY ? 0.f : exp2_fast(m_other - m_all);
-    const float inv = 1.0f / (l * w_mine + l_other * w_other);
+    // group 0's term first in both groups' threads: the two threads of a row hold the same bits
+    const float l_all = g == 0 ? fmaf(l_other, w_other, l * w_mine) : fmaf(l, w_mine, l_other * w_other);
+    // a block that holds all keys of its rows divides by the sum here; one that holds a part of them leaves its
+    // output relative to its own maximum, undivided
+    const bool shared = sharing > 1;
+    const float inv = shared ? 1.0f : 1.0f / l_all;
     const float w0 = (g == 0 ? w_mine : w_other) * inv, w1 = (g == 0 ? w_other : w_mine) * inv;
     // both groups' last products must have landed (group 1 has none when there is a single tile)
-    const int n0 = (n_tiles + 1) / 2, n1 = n_tiles / 2;
+    const int n0 = (n_local + 1) / 2, n1 = n_local / 2;
     if (ok) ok = wait_all(B_OD + 0, (uint32_t)(n0 - 1) & 1u);
     if (ok && n1 > 0) ok = wait_all(B_OD + 1, (uint32_t)(n1 - 1) & 1u);
-    if (ok) {
-      fence_after_sync();
-      // this thread writes columns g * D/2 .. of its row: the same columns of both groups' outputs
-      __nv_bfloat16* dst = out + ((size_t)(row_base + row) * n_q + head) * D + g * OD;
+    // this thread owns columns g * D/2 .. of its row: the same columns of both groups' outputs
+    __nv_bfloat16* dst = out + ((size_t)(row_base + row) * n_q + head) * D + g * OD;
+    if (!shared) {
+      if (ok) {
+        fence_after_sync();
 #pragma unroll
-      for (int c = 0; c < OD; c += 32) {
-        uint32_t a[32], b[32];
-        tmem_ld32(lane_addr + O_COL + g * OD + c, a);
-        if (n1 > 0) tmem_ld32(lane_addr + O_COL + D + g * OD + c, b);
-        tmem_ld_wait();
-        if (row < nrows) {
+        for (int c = 0; c < OD; c += 32) {
+          uint32_t a[32], b[32];
+          tmem_ld32(lane_addr + O_COL + g * OD + c, a);
+          if (n1 > 0) tmem_ld32(lane_addr + O_COL + D + g * OD + c, b);
+          tmem_ld_wait();
+          if (row < nrows) {
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            float v[8];
+            for (int i = 0; i < 4; ++i) {
+              float v[8];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              v[e] = __uint_as_float(a[8 * i + e]) * w0;
-              if (n1 > 0) v[e] = fmaf(__uint_as_float(b[8 * i + e]), w1, v[e]);
+              for (int e = 0; e < 8; ++e) {
+                v[e] = __uint_as_float(a[8 * i + e]) * w0;
+                if (n1 > 0) v[e] = fmaf(__uint_as_float(b[8 * i + e]), w1, v[e]);
+              }
+              *reinterpret_cast<uint4*>(dst + c + 8 * i) =
+                  make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
             }
-            *reinterpret_cast<uint4*>(dst + c + 8 * i) =
-                make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
           }
         }
+      }
+    } else {
+      // ------------------------------------------------------------ several blocks, one tile of rows
+      // Each block leaves its part in global memory: output as [D / 4][BM] groups of four columns (a warp's rows side
+      // by side), maxima [BM], sums [BM], float32.  The block that finds all other parts there adds them up, the
+      // parts in their order whoever adds, and writes the rows.  No block waits for another.  A block whose wait
+      // gave up leaves nothing and does not count itself: the rows are then never written, and the status word says so.
+      constexpr int PART_FLOATS = BM * D + 2 * BM;
+      float* const parts_base = scratch + (size_t)slot * MAX_PARTS * PART_FLOATS;
+      float* const my_part = parts_base + (size_t)part * PART_FLOATS;
+      volatile int* const arrived = reinterpret_cast<volatile int*>(tail + 8 * B_COUNT + 8);
+      volatile int* const whole = reinterpret_cast<volatile int*>(tail + 8 * B_COUNT + 12);   // 1 until a warp's wait gave up
+      if (ok) {
+        fence_after_sync();
+#pragma unroll
+        for (int c = 0; c < OD; c += 32) {
+          uint32_t a[32], b[32];
+          tmem_ld32(lane_addr + O_COL + g * OD + c, a);
+          if (n1 > 0) tmem_ld32(lane_addr + O_COL + D + g * OD + c, b);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            float v[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              v[e] = __uint_as_float(a[4 * i + e]) * w0;
+              if (n1 > 0) v[e] = fmaf(__uint_as_float(b[4 * i + e]), w1, v[e]);
+            }
+            reinterpret_cast<float4*>(my_part)[((g * OD + c) / 4 + i) * BM + row] = make_float4(v[0], v[1], v[2], v[3]);
+          }
+        }
+        if (g == 0) { my_part[BM * D + row] = m_all; my_part[BM * D + BM + row] = l_all; }
+        __threadfence();
+      }
+      if (!ok) *whole = 0;
+      softmax_barrier();
+      if (tid == 0) *arrived = *whole ? atomicAdd(counters + slot, 1) : -1;
+      softmax_barrier();
+      if (*arrived == sharing - 1) {   // all other parts are there
+        __threadfence();
+        float m_parts[MAX_PARTS], m_tile = -INFINITY;
+#pragma unroll
+        for (int p = 0; p < MAX_PARTS; ++p) {
+          m_parts[p] = p < sharing ? __ldcg(parts_base + (size_t)p * PART_FLOATS + BM * D + row) : -INFINITY;
+          m_tile = fmaxf(m_tile, m_parts[p]);
+        }
+        float sum = 0.f, weight[MAX_PARTS];
+#pragma unroll
+        for (int p = 0; p < MAX_PARTS; ++p) {
+          weight[p] = (p < sharing && m_parts[p] != -INFINITY) ? exp2_fast(m_parts[p] - m_tile) : 0.f;
+          if (p < sharing) sum = fmaf(__ldcg(parts_base + (size_t)p * PART_FLOATS + BM * D + BM + row), weight[p], sum);
+        }
+        const float inv_sum = 1.0f / sum;
+        if (row < nrows) {
+#pragma unroll 2
+          for (int c = 0; c < OD; c += 8) {
+            float4 x0 = make_float4(0.f, 0.f, 0.f, 0.f), x1 = x0;
+#pragma unroll
+            for (int p = 0; p < MAX_PARTS; ++p) {
+              if (p < sharing) {
+                const float4* src = reinterpret_cast<const float4*>(parts_base + (size_t)p * PART_FLOATS) + ((g * OD + c) / 4) * BM + row;
+                const float4 y0 = __ldcg(src), y1 = __ldcg(src + BM);
+                const float w = weight[p];
+                x0.x = fmaf(y0.x, w, x0.x); x0.y = fmaf(y0.y, w, x0.y); x0.z = fmaf(y0.z, w, x0.z); x0.w = fmaf(y0.w, w, x0.w);
+                x1.x = fmaf(y1.x, w, x1.x); x1.y = fmaf(y1.y, w, x1.y); x1.z = fmaf(y1.z, w, x1.z); x1.w = fmaf(y1.w, w, x1.w);
+              }
+            }
+            *reinterpret_cast<uint4*>(dst + c) = make_uint4(
+                pack_bf16(x0.x * inv_sum, x0.y * inv_sum), pack_bf16(x0.z * inv_sum, x0.w * inv_sum),
+                pack_bf16(x1.x * inv_sum, x1.y * inv_sum), pack_bf16(x1.z * inv_sum, x1.w * inv_sum));
+          }
+        }
+        if (tid == 0) counters[slot] = 0;   // as the next launch expects it
       }
     }
   }
@@ -447,7 +549,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   __syncthreads();
   if (warp == MMA_WARP) tmem_dealloc(tmem_base, 512);
 #ifdef LSE_TRACE
-  if (tid == 0 && block_linear < 4096) { lse_attn_tc_blocks[block_linear * 4 + 1] = global_ns(); lse_attn_tc_blocks[block_linear * 4 + 3] = n_tiles; }
+  if (tid == 0 && block_linear < 4096) { lse_attn_tc_blocks[block_linear * 4 + 1] = global_ns(); lse_attn_tc_blocks[block_linear * 4 + 3] = n_local; }
 #endif
 }
 
@@ -455,7 +557,7 @@ template <int D>
 int launch_prefill_tc(const void* q, const void* kc, const void* vc, void* out, const int* block_tables, int bt_stride,
                       const int* segment_start, const int* segment_first_pos, int num_segments, int tokens,
                       long long num_pages, int n_q, int n_kv, int page_size, float scale, int skip_single,
-                      int max_portions, cudaStream_t stream) {
+                      int max_portions, float* scratch, int* counters, long long scratch_slots, cudaStream_t stream) {
   const size_t smem = attn_tc_smem<D>();
   static bool configured = false;
   if (!configured) {
@@ -472,14 +574,34 @@ int launch_prefill_tc(const void* q, const void* kc, const void* vc, void* out, 
   // at most so many requests have tiles, the others bringing single tokens that are skipped)
   const int with_tiles = (max_portions > 0 && max_portions < num_segments) ? max_portions : num_segments;
   const int tiles = (tokens + BM - 1) / BM + with_tiles;
-  dim3 grid(tiles * n_q);
+  // With fewer blocks than SMs, several blocks share the keys of a tile of rows (the kernel decides tile by tile how
+  // many: a part is at least MIN_TILES_A_PART key tiles).  The parts meet in `scratch`.
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int device = 0;
+    cudaGetDevice(&device);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
+  }
+  const long long blocks = (long long)tiles * n_q;
+  int parts = 1;
+  if (scratch != nullptr && counters != nullptr && blocks <= scratch_slots) {
+    parts = (int)((5LL * sm_count) / (4 * blocks));
+    parts = parts < 1 ? 1 : (parts > MAX_PARTS ? MAX_PARTS : parts);
+  }
+  dim3 grid((unsigned)(blocks * parts));
   cudaError_t err = lse_launch(attn_prefill_tc_kernel<D>, grid, THREADS, smem, stream, map_q, map_k, map_v,
                                (__nv_bfloat16*)out, block_tables, bt_stride, segment_start, segment_first_pos,
-                               num_segments, n_q, n_kv, page_size, scale * LOG2E, (int)num_pages, skip_single);
+                               num_segments, n_q, n_kv, page_size, scale * LOG2E, (int)num_pages, skip_single, parts,
+                               scratch, counters);
   if (err != cudaSuccess) return (int)err;
   return (int)cudaGetLastError();
 }
 }  // namespace
+
+// Values of float32 scratch per slot (a tile of rows of one head: up to MAX_PARTS parts).  scratch (scratch_slots
+// times that) and counters (int32, scratch_slots, zero; the kernel leaves them zero) may be null: they let several
+// blocks share the keys of a tile of rows when a launch has fewer blocks than the GPU has SMs.
+extern "C" int lse_attention_tc_scratch_floats(void) { return MAX_PARTS * (BM * 128 + 2 * BM); }
 
 // Whether the kernel takes this shape (else the caller uses another kernel).
 extern "C" int lse_attention_tc_supported(int head_dim, int n_q, int n_kv, int page_size) {
@@ -521,14 +643,17 @@ extern "C" int lse_paged_attention_prefill_tc(const void* q, const void* k_cache
                                               const int* block_tables, int bt_stride, const int* segment_start,
                                               const int* segment_first_pos, int num_segments, int tokens,
                                               long long num_pages, int n_q, int n_kv, int head_dim, int page_size,
-                                              float scale, int skip_single, int max_portions, cudaStream_t stream) {
+                                              float scale, int skip_single, int max_portions, float* scratch,
+                                              int* counters, long long scratch_slots, cudaStream_t stream) {
   if (tokens <= 0 || num_segments <= 0) return 0;
   if (!lse_attention_tc_supported(head_dim, n_q, n_kv, page_size) || num_pages <= 0 || !(scale > 0.f) ||
       (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15))
     return LSE_ERR_BAD_ARGUMENT;
   if (head_dim == 128)
     return launch_prefill_tc<128>(q, k_cache, v_cache, out, block_tables, bt_stride, segment_start, segment_first_pos,
-                                  num_segments, tokens, num_pages, n_q, n_kv, page_size, scale, skip_single, max_portions, stream);
+                                  num_segments, tokens, num_pages, n_q, n_kv, page_size, scale, skip_single, max_portions, scratch,
+                                  counters, scratch_slots, stream);
   return launch_prefill_tc<64>(q, k_cache, v_cache, out, block_tables, bt_stride, segment_start, segment_first_pos,
-                               num_segments, tokens, num_pages, n_q, n_kv, page_size, scale, skip_single, max_portions, stream);
+                               num_segments, tokens, num_pages, n_q, n_kv, page_size, scale, skip_single, max_portions, scratch,
+                                  counters, scratch_slots, stream);
 }

@@ -43,7 +43,9 @@ _SIGNATURES = {
                                     c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p],
     "lse_attention_mma_supported": [c_int, c_int, c_int],
     "lse_paged_attention_prefill_tc": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
-                                       c_int, c_int, c_longlong, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p],
+                                       c_int, c_int, c_longlong, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p,
+                                       c_void_p, c_longlong, c_void_p],
+    "lse_attention_tc_scratch_floats": [],
     "lse_attention_tc_supported": [c_int, c_int, c_int, c_int],
     "lse_attention_tc_status": [],
     "lse_set_pdl": [c_int],

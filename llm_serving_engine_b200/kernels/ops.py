@@ -337,10 +337,12 @@ def attention_tc_supported(head_dim: int, n_q: int, n_kv: int, page_size: int, d
 def paged_attention_prefill_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
                                block_tables: torch.Tensor, segment_start: torch.Tensor,
                                segment_first_position: torch.Tensor, scale: float, skip_single: bool = False,
-                               max_portions: int = 0) -> torch.Tensor:
+                               max_portions: int = 0, share_keys: bool = True) -> torch.Tensor:
     """Attention of prompt portions on the 5th-generation tensor cores: the arguments and the
     result of :func:`paged_attention_prefill`; blocks of 128 rows of one head, keys in tiles of 128
-    brought in by TMA page by page, scores and outputs accumulated in tensor memory."""
+    brought in by TMA page by page, scores and outputs accumulated in tensor memory.  In a launch with fewer
+    blocks than the GPU has SMs several blocks share the keys of a tile of rows; ``share_keys=False`` keeps every
+    tile in one block (for comparisons)."""
     _need_cuda(q, k_cache, v_cache, out, block_tables, segment_start, segment_first_position)
     tokens, n_q, head_dim = q.shape
     pages, n_kv, page_size = k_cache.shape[0], k_cache.shape[1], k_cache.shape[2]
@@ -350,13 +352,34 @@ def paged_attention_prefill_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: 
     assert v_cache.shape == k_cache.shape and k_cache.shape[3] == head_dim
     assert block_tables.dtype == torch.int32 and block_tables.stride(1) == 1 and segment_start.shape[0] == segments + 1
     lib = library.load()
+    scratch, counters = _attention_tc_scratch(q.device) if share_keys else (None, None)
     check(lib.lse_paged_attention_prefill_tc(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
                                              block_tables.data_ptr(), block_tables.stride(0), segment_start.data_ptr(),
                                              segment_first_position.data_ptr(), segments, tokens, pages, n_q, n_kv,
                                              head_dim, page_size, float(scale), int(skip_single),
-                                             int(max_portions) if skip_single else 0, _stream()),
+                                             int(max_portions) if skip_single else 0, _ptr(scratch), _ptr(counters),
+                                             counters.shape[0] if counters is not None else 0, _stream()),
           "paged_attention_prefill_tc")
     return out
+
+
+_ATTENTION_TC_SCRATCH: dict = {}
+
+
+def _attention_tc_scratch(device) -> tuple[torch.Tensor, torch.Tensor]:
+    """Where the blocks of the tcgen05 prompt attention that share the keys of one tile of rows leave their parts
+    (a launch with fewer blocks than SMs), and the arrival counters, which the kernel leaves at zero.  One pair per
+    device, made at the first call (never inside a graph capture: a size class runs once before it is captured)."""
+    index = torch.device(device).index
+    index = torch.cuda.current_device() if index is None else index
+    pair = _ATTENTION_TC_SCRATCH.get(index)
+    if pair is None:
+        slots = sm_count(index)
+        floats = int(library.load().lse_attention_tc_scratch_floats())
+        where = torch.device("cuda", index)
+        pair = _ATTENTION_TC_SCRATCH[index] = (torch.empty(slots * floats, dtype=torch.float32, device=where),
+                                               torch.zeros(slots, dtype=torch.int32, device=where))
+    return pair
 
 
 def attention_tc_status() -> int:
@@ -447,6 +470,8 @@ def kernel_status_reset() -> None:
     lib = library.load()
     lib.lse_gemm_bf16_skinny_status_reset()
     lib.lse_attention_tc_status_reset()
+    for _, counters in _ATTENTION_TC_SCRATCH.values():   # a block that gave up may have left its arrival uncounted
+        counters.zero_()
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> torch.Tensor:

@@ -766,6 +766,58 @@ def test_single_tokens_beside_portions_go_to_the_decode_kernel(prompt_kernel, he
         assert err < 2.0 ** -7 * max(1.0, float(want.abs().max())), (s, before, rows, err)
 
 
+@pytest.mark.parametrize("head_dim, n_q, n_kv, page, portions", [
+    (128, 12, 2, 16, [(7800, 300)]),                     # a portion of a long prompt: 36 blocks, 60 key tiles each
+    (64, 4, 4, 32, [(1500, 700), (0, 130)]),             # earlier keys, a ragged last block of rows, a short request beside
+    (128, 7, 1, 8, [(0, 1), (3000, 128), (900, 300)]),
+])
+def test_tcgen05_prefill_attention_with_the_keys_of_a_tile_shared_by_several_blocks(head_dim, n_q, n_kv, page, portions):
+    """Fewer blocks than SMs: several blocks take a part of the keys of a tile of rows each and the last one to arrive
+    adds the parts.  Rows whose weight lies on one far key of the first part, or on one key of the last part, must
+    find it; the result equals the one with every tile in one block up to rounding, and a second launch (arrival
+    counters left at zero by the first) gives the same bits."""
+    rng = random.Random(head_dim + page)
+    torch.manual_seed(page)
+    contexts = [before + rows for before, rows in portions]
+    k_cache, v_cache, tables, dense = paged_setup(rng, contexts, n_kv, head_dim, page, torch.bfloat16)
+    total = sum(rows for _, rows in portions)
+    q = torch.randn(total, n_q, head_dim, device=DEV).bfloat16()
+    starts = [0]
+    for _, rows in portions:
+        starts.append(starts[-1] + rows)
+    needles = []
+    for s, (before, rows) in enumerate(portions):
+        if before + rows < 1200:
+            continue
+        k, v = dense[s]
+        last = rows - 1
+        for local, key, head in ((last, 3, 0), (last - 1, before + rows - 40, n_q - 1)):   # far in the first part; in the last part
+            k[key, head // (n_q // n_kv)] = (q[starts[s] + local, head].float() * 8).bfloat16()
+            k_cache[int(tables[s, key // page]), :, key % page] = k[key]
+            needles.append((s, local, key, head))
+    poison_unowned(k_cache, v_cache, tables, contexts, page)
+    scale = 1.0 / math.sqrt(head_dim)
+    start_t = torch.tensor(starts, dtype=torch.int32, device=DEV)
+    first_t = torch.tensor([b for b, _ in portions], dtype=torch.int32, device=DEV)
+    outs = []
+    for share in (True, True, False):
+        out = torch.full_like(q, 9.0)
+        ops().paged_attention_prefill_tc(q, k_cache, v_cache, out, tables, start_t, first_t, scale, share_keys=share)
+        assert ops().attention_tc_status() == 0
+        outs.append(out)
+    assert torch.equal(outs[0], outs[1])
+    assert not torch.equal(outs[0], outs[2]), "no tile's keys were shared: the case does not test what it is meant to"
+    assert float((outs[0].float() - outs[2].float()).abs().max()) <= 2.0 ** -7 * max(1.0, float(outs[2].float().abs().max()))
+    for s, (before, rows) in enumerate(portions):
+        want = dense_causal(q[starts[s]:starts[s + 1]], dense[s][0], dense[s][1], before, scale)
+        err = (outs[0][starts[s]:starts[s + 1]].double() - want).abs()
+        assert float(err.max()) < 2.0 ** -7 * max(1.0, float(want.abs().max())), (s, before, rows, float(err.max()))
+    assert needles
+    for s, local, key, head in needles:
+        value = dense[s][1][key, head // (n_q // n_kv)].double()
+        assert float((outs[0][starts[s] + local, head].double() - value).abs().max()) < 0.05, (s, local, key, head)
+
+
 @pytest.mark.parametrize("slope", [40.0, 8.0])
 def test_tcgen05_prefill_attention_when_the_maximum_grows(slope):
     """Scores that grow by far more than 2^8 from tile to tile (keys scaled up along the sequence):
