@@ -403,7 +403,7 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, int n_partials,
   LSE_TL_MARK(3)
 }
 
-// Many tokens (portions of prompts), one set of sums: a thread owns eight pairs (frequency indices
+// Many tokens (256 and more: portions of prompts), one set of sums: a thread owns eight pairs (frequency indices
 // 8c .. 8c+7) of ROPE_WIDE_HEADS heads of one token, so that the sines and cosines are worked out
 // once for those heads and sixteen-byte loads of all of them are in flight together.  The values
 // are those of the kernel above: the same angle, the same products.
@@ -534,7 +534,7 @@ extern "C" int lse_rope_kv_write(const void* qkv, int in_dtype, int n_partials, 
     return LSE_ERR_BAD_ARGUMENT;
   const int heads = n_q + 2 * n_kv;
   const int in_vec = in_dtype == LSE_DTYPE_BF16 ? 8 : 4;   // elements of a sixteen-byte load
-  if (tokens >= 64 && n_partials == 1 && head_dim % 16 == 0 && head_dim <= 1024 && qkv_stride % in_vec == 0) {
+  if (tokens >= 256 && n_partials == 1 && head_dim % 16 == 0 && head_dim <= 1024 && qkv_stride % in_vec == 0) {
     const int per_head = head_dim / 16;
     const int head_groups = (heads + ROPE_WIDE_HEADS - 1) / ROPE_WIDE_HEADS;
     const int per_token = per_head * head_groups;

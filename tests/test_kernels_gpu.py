@@ -180,8 +180,8 @@ def test_rope_bias_and_cache_write(dtype, head_dim, n_q, n_kv, page, pairing):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("tokens, head_dim, n_q, n_kv, page, pairing", [
-    (64, 16, 4, 2, 16, "interleaved"), (131, 48, 10, 2, 8, "half"), (300, 128, 12, 2, 16, "interleaved"),
-    (77, 256, 3, 1, 4, "half"), (200, 32, 7, 7, 16, "half"), (97, 64, 33, 3, 16, "interleaved")])
+    (256, 16, 4, 2, 16, "interleaved"), (331, 48, 10, 2, 8, "half"), (300, 128, 12, 2, 16, "interleaved"),
+    (277, 256, 3, 1, 4, "half"), (400, 32, 7, 7, 16, "half"), (297, 64, 33, 3, 16, "interleaved"), (64, 128, 12, 2, 16, "half")])
 def test_rope_of_many_tokens(dtype, tokens, head_dim, n_q, n_kv, page, pairing):
     """Portions of prompts take the kernel that shares sines and cosines among heads: it has to
     give what the few-token kernel gives (same angles, same products) and leave padding rows alone."""
