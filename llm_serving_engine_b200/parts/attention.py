@@ -16,18 +16,20 @@ from .linear import linear_partials
 # the portions, a prompt's last token) go to the decode kernel, which splits their keys over blocks; the portions
 # go to one of the two prompt kernels.  The tcgen05 kernel's block is 128 rows of one request and one head; the
 # mma.sync kernel's about ten rows of all heads of a group.  The portions go to the former when the longest has at
-# least TCGEN05_MIN_ROWS rows and either their blocks fit the GPU at once or they are long on average (at least 64
+# least TCGEN05_MIN_ROWS (64) rows and either their blocks fit the GPU at once or they are long on average (at least 64
 # rows each); many short portions stay on the mma.sync kernel.  LSE_PREFILL_ATTENTION=mma turns the tcgen05
 # kernel off, LSE_MIXED_DECODE_KERNEL=0 sends single tokens through the prompt kernels as well.
-TCGEN05_MIN_ROWS = int(os.environ.get("LSE_TCGEN05_MIN_ROWS", "128"))
+TCGEN05_MIN_ROWS = int(os.environ.get("LSE_TCGEN05_MIN_ROWS", "64"))
 TCGEN05_MIN_ROWS_PER_REQUEST = 64
 TCGEN05_BLOCKS_AT_ONCE = 148
 TCGEN05_PREFILL = os.environ.get("LSE_PREFILL_ATTENTION", "tcgen05") != "mma"
 MIXED_DECODE_KERNEL = os.environ.get("LSE_MIXED_DECODE_KERNEL", "1") != "0"
 # A step of fewer rows than this (portions and single tokens together) goes to the decode kernel row by row: a prompt
-# kernel would have a handful of blocks, each walking all keys of its request (64 rows on 8,000 earlier keys: 51 against
-# 151 us; 16 rows: 21 against 150 us; on 200 keys no difference).  LSE_ROWS_KERNEL_BELOW=0 turns it off.
-ROWS_KERNEL_BELOW = int(os.environ.get("LSE_ROWS_KERNEL_BELOW", "128"))
+# kernel would have a handful of blocks, each walking all keys of its request (16 rows on 8,000 earlier keys: 21 against
+# 150 us on the mma.sync kernel; on 200 keys no difference).  From 64 rows on the tcgen05 kernel, whose blocks share the
+# keys of a tile, is as fast or faster (portions of 32 / 64 / 96 tokens of an 8,192-token prompt: 1.58 / 2.13 / 2.68 ms a
+# step row by row, 1.85 / 2.15 / 2.07 on the tcgen05 kernel).  LSE_ROWS_KERNEL_BELOW=0 turns it off.
+ROWS_KERNEL_BELOW = int(os.environ.get("LSE_ROWS_KERNEL_BELOW", "64"))
 ROWS_KERNEL_BLOCKS = 256
 
 
