@@ -21,7 +21,6 @@ from .linear import linear_partials
 # kernel off, LSE_MIXED_DECODE_KERNEL=0 sends single tokens through the prompt kernels as well.
 TCGEN05_MIN_ROWS = int(os.environ.get("LSE_TCGEN05_MIN_ROWS", "64"))
 TCGEN05_MIN_ROWS_PER_REQUEST = 64
-TCGEN05_BLOCKS_AT_ONCE = 148
 TCGEN05_PREFILL = os.environ.get("LSE_PREFILL_ATTENTION", "tcgen05") != "mma"
 MIXED_DECODE_KERNEL = os.environ.get("LSE_MIXED_DECODE_KERNEL", "1") != "0"
 # A step of fewer rows than this (portions and single tokens together) goes to the decode kernel row by row: a prompt
