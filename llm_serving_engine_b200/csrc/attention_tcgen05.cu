@@ -243,9 +243,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const int g = i & 1;
         const uint32_t parity = (uint32_t)(i >> 1) & 1u;
         TC_STAMP2(i, 0)
+        // (Letting the scores of the group's next tile go first, which the group waits for sooner than for this
+        // product, was slower on long prompts: 214 against 208 ms for 30,720 tokens.)
         ok = mbar_poll(bar(B_VF + g), parity, abort_flag, err) && mbar_poll(bar(B_PF + g), parity, abort_flag, err);
-        // the scores of the group's next tile go first (the group waits for them; this product is wanted later)
-        if (ok && i + GROUPS < n_local) ok = mbar_poll(bar(B_KE + g), parity ^ 1u, abort_flag, err);
         if (!ok) break;
         fence_after_sync();
         TC_STAMP2(i, 3)
